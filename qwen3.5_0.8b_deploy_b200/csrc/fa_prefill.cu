@@ -1,0 +1,402 @@
+// F1: causal flash-attention prefill for head_dim 256 on tcgen05 tensor cores.
+//
+// One CTA per (128-query tile of one sequence, q head).  Warp roles: warps 0-3 = softmax (thread r owns
+// query row r = TMEM lane r), warp 4 = TMA producer, warp 5 = MMA issuer and TMEM owner.
+//   S[128x64]  = Q[128x256] K_j^T      tcgen05.mma kind::f16 (fp16 operands), A and B K-major, TMEM cols [0,128) double-buffered
+//   O[128x256] += P_j[128x64] V_j      A = P (written by the softmax warps, K-major), B = V tile MN-major, TMEM cols [128,384)
+// Q / K / V tiles arrive through tiled TMA with 128-byte swizzle; K and V are double-buffered.  The softmax
+// keeps logits in log2 units and rescales O only when a row maximum grows by more than 2^8.
+// Every mbarrier wait is bounded: on give-up the CTA raises an error word and leaves through the common exit.
+//
+// Replaces flash_attn_v2_prefill_kernel (src/backend/cuda/kernels/fused_kernels.cu:126-264 in the reference;
+// that kernel applies no causal mask, this one does, as the CPU reference's token loop implies) and
+// gate_sigmoid_kernel (full_attention_cuda.cu:602-614) in the epilogue.
+#include "kernels.cuh"
+#include "tc05.cuh"
+
+#include <algorithm>
+#include <vector>
+
+namespace b200 {
+
+constexpr int kBM = 128, kBN = 64;
+constexpr uint32_t kQBytes = 4 * kBM * 128;     // 65536
+constexpr uint32_t kKVBytes = 4 * kBN * 128;    // 32768
+constexpr uint32_t kPBytes = kBM * 128;         // 16384
+constexpr uint32_t kOffQ = 0, kOffK = kQBytes, kOffV = kOffK + 2 * kKVBytes, kOffP = kOffV + 2 * kKVBytes;
+constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;
+constexpr uint32_t kF1Smem = kOffBar + 256 + 1024;   // + barriers + alignment slack
+constexpr float kLog2eF = 1.4426950408889634f;
+
+enum { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 15,
+       BAR_OF = 17, BAR_COUNT = 18 };
+
+template <typename OutT>
+__global__ void __launch_bounds__(192, 1)
+fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const PrefillTile* __restrict__ tiles,
+                     const __half* __restrict__ gate, OutT* __restrict__ out, int* __restrict__ error_word) {
+    extern __shared__ unsigned char smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    unsigned char* sm = smem_raw + (base - raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kOffBar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t bar0 = base + kOffBar;
+    auto bar = [&](int i) { return bar0 + 8u * i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const PrefillTile tile = tiles[blockIdx.x];
+    const int head = blockIdx.y, kvh = head >> 2;
+    const int n_kt = (tile.q_pos0 + tile.n_rows + kBN - 1) / kBN;   // key tiles 0..n_kt-1 cover positions <= last query
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < BAR_COUNT; ++i) {
+            const bool many = (i == BAR_SE || i == BAR_SE + 1 || i == BAR_PF || i == BAR_PF + 1);
+            mbar_init(bar(i), many ? 128 : 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    if (warp == 4 && lane == 0) {
+        tma_prefetch_desc(&map_q);
+        tma_prefetch_desc(&map_k);
+        tma_prefetch_desc(&map_v);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_o = tmem + 128;
+
+    if (warp == 4) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
+            for (int blk = 0; blk < 4; ++blk)
+                tma_load_3d(base + kOffQ + blk * (kBM * 128), &map_q, bar(BAR_Q), blk * 64, head, tile.q_row0);
+            for (int j = 0; j < n_kt; ++j) {
+                const int b = j & 1;
+                const uint32_t par = ((j >> 1) - 1) & 1;
+                const int row = tile.ctx_row0 + j * kBN;
+                if (j >= 2 && !mbar_wait(bar(BAR_KE + b), par, abort_flag)) break;
+                mbar_arrive_expect_tx(bar(BAR_KF + b), kKVBytes);
+                for (int blk = 0; blk < 4; ++blk)
+                    tma_load_3d(base + kOffK + b * kKVBytes + blk * (kBN * 128), &map_k, bar(BAR_KF + b), blk * 64, kvh, row);
+                if (j >= 2 && !mbar_wait(bar(BAR_VE + b), par, abort_flag)) break;
+                mbar_arrive_expect_tx(bar(BAR_VF + b), kKVBytes);
+                for (int blk = 0; blk < 4; ++blk)
+                    tma_load_3d(base + kOffV + b * kKVBytes + blk * (kBN * 128), &map_v, bar(BAR_VF + b), blk * 64, kvh, row);
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------ MMA issuer ------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = umma_idesc(kFmtF16, kBM, kBN, 0, 0);
+            constexpr uint32_t idesc_pv = umma_idesc(kFmtF16, kBM, kHeadDim, 0, 1);
+            auto issue_pv = [&](int i) -> bool {
+                const int b = i & 1;
+                const uint32_t par = (i >> 1) & 1;
+                if (!mbar_wait(bar(BAR_VF + b), par, abort_flag)) return false;
+                if (!mbar_wait(bar(BAR_PF + b), par, abort_flag)) return false;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint64_t a = umma_smem_desc(base + kOffP + b * kPBytes + ks * 32, 16, 1024);
+                    const uint64_t bd = umma_smem_desc(base + kOffV + b * kKVBytes + ks * 2048, kBN * 128, 1024);
+                    umma_f16(tmem_o, a, bd, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(bar(BAR_PV + b));
+                umma_commit(bar(BAR_VE + b));
+                return true;
+            };
+            bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag);
+            for (int j = 0; ok && j < n_kt; ++j) {
+                const int b = j & 1;
+                if (!mbar_wait(bar(BAR_KF + b), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (j >= 2 && !mbar_wait(bar(BAR_SE + b), ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * 0 + (ks & 3) * 32;
+                    const uint64_t a = umma_smem_desc(base + kOffQ + (ks >> 2) * (kBM * 128) + off, 16, 1024);
+                    const uint64_t bd = umma_smem_desc(base + kOffK + b * kKVBytes + (ks >> 2) * (kBN * 128) + off, 16, 1024);
+                    umma_f16(tmem + b * kBN, a, bd, idesc_s, ks > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(BAR_SF + b));
+                umma_commit(bar(BAR_KE + b));
+                if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
+            }
+            if (ok) ok = issue_pv(n_kt - 1);
+            if (ok) umma_commit(bar(BAR_OF));
+        }
+    } else {
+        // ------------------------------ softmax / correction / epilogue ------------------------------
+        const int r = threadIdx.x;                       // query row == TMEM lane
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int q_pos = tile.q_pos0 + r;
+        const float sc = kLog2eF / 16.0f;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_kt; ++j) {
+            const int b = j & 1;
+            if (!mbar_wait_warp(bar(BAR_SF + b), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t sr[2][32];
+            tmem_ld32(tmem + lane_base + b * kBN, sr[0]);
+            tmem_ld32(tmem + lane_base + b * kBN + 32, sr[1]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(BAR_SE + b));
+            float s[64];
+            const bool diag = (j * kBN + kBN - 1 > tile.q_pos0);   // warp-uniform: tile may cross a diagonal
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) {
+                float v = __uint_as_float(sr[c >> 5][c & 31]) * sc;
+                if (diag && (j * kBN + c > q_pos)) v = -INFINITY;
+                s[c] = v;
+                mx = fmaxf(mx, v);
+            }
+            const float m_new = fmaxf(m_ref, mx);            // finite: key 0 is visible to every row
+            const bool need = (m_new - m_ref > 8.0f);        // also true on the first tile (m_ref = -inf)
+            if (__any_sync(0xffffffffu, need)) {
+                if (j > 0) {
+                    if (!mbar_wait_warp(bar(BAR_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const float alpha = exp2f(m_ref - m_new);
+                    l *= alpha;
+#pragma unroll 1
+                    for (int ch = 0; ch < 8; ++ch) {
+                        uint32_t orr[32];
+                        tmem_ld32(tmem_o + lane_base + ch * 32, orr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) orr[c] = __float_as_uint(__uint_as_float(orr[c]) * alpha);
+                        tmem_st32(tmem_o + lane_base + ch * 32, orr);
+                    }
+                    tmem_wait_st();
+                }
+                m_ref = m_new;
+            }
+            // P = 2^(s - m_ref) as fp16 into the swizzled K-major A tile
+            if (j >= 2 && !mbar_wait_warp(bar(BAR_PV + b), ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+            unsigned char* prow = sm + kOffP + b * kPBytes + r * 128;
+            float lsum = 0.f;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = exp2f(s[c8 * 8 + 2 * e] - m_ref);
+                    const float p1 = exp2f(s[c8 * 8 + 2 * e + 1] - m_ref);
+                    lsum += p0 + p1;
+                    pk[e] = pack_half2(p0, p1);
+                }
+                *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+            l += lsum;
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar(BAR_PF + b));
+        }
+        if (ok && mbar_wait_warp(bar(BAR_OF), 0, abort_flag)) {
+            tc_fence_after();
+            const float inv_l = 1.0f / l;
+            const bool valid = r < tile.n_rows;
+            const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
+#pragma unroll 1
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t orr[32];
+                tmem_ld32(tmem_o + lane_base + ch * 32, orr);
+                tmem_wait_ld();
+                if (valid) {
+                    float vals[32];
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) vals[c] = __uint_as_float(orr[c]) * inv_l;
+                    if (gate) {
+                        const uint4* gp = reinterpret_cast<const uint4*>(gate + orow + ch * 32);
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const uint4 gv = gp[q4];
+                            const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 gf = __half22float2(gh[e]);
+                                vals[q4 * 8 + 2 * e] *= gf.x;
+                                vals[q4 * 8 + 2 * e + 1] *= gf.y;
+                            }
+                        }
+                    }
+                    OutT* dst = out + orow + ch * 32;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) dst[c] = (OutT)vals[c];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(error_word, 4);
+}
+
+// ---- plain SIMT causal attention (cross-check at sizes the CPU checker cannot reach) ---------------------------
+// One warp per (row, head); lane owns dims 8*lane..8*lane+7.  Same inputs / outputs as the tensor-core kernel.
+template <typename OutT>
+__global__ void __launch_bounds__(128)
+fa_prefill_simt_kernel(const __half* __restrict__ q, const __half* __restrict__ ks, const __half* __restrict__ vs,
+                       const int* __restrict__ row_pos, const int* __restrict__ row_ctx0, int rows,
+                       const __half* __restrict__ gate, OutT* __restrict__ out) {
+    const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (gw >= rows * kFaHeads) return;
+    const int row = gw / kFaHeads, head = gw % kFaHeads, kvh = head >> 2;
+    const int pos = row_pos[row], ctx0 = row_ctx0[row];
+    float qv[8];
+    {
+        const uint4 raw = *reinterpret_cast<const uint4*>(q + ((size_t)row * kFaHeads + head) * kHeadDim + 8 * lane);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(h[e]); qv[2 * e] = f.x; qv[2 * e + 1] = f.y; }
+    }
+    float m = -INFINITY, l = 0.f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int t = 0; t <= pos; ++t) {
+        const size_t o = ((size_t)(ctx0 + t) * kFaKvHeads + kvh) * kHeadDim + 8 * lane;
+        const uint4 kr = *reinterpret_cast<const uint4*>(ks + o);
+        const __half2* kh = reinterpret_cast<const __half2*>(&kr);
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __half22float2(kh[e]); d += qv[2 * e] * f.x + qv[2 * e + 1] * f.y; }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+        d *= 1.0f / 16.0f;
+        const float mn = fmaxf(m, d);
+        const float a = expf(m - mn), p = expf(d - mn);
+        const uint4 vr = *reinterpret_cast<const uint4*>(vs + o);
+        const __half2* vh = reinterpret_cast<const __half2*>(&vr);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(vh[e]);
+            acc[2 * e] = acc[2 * e] * a + p * f.x;
+            acc[2 * e + 1] = acc[2 * e + 1] * a + p * f.y;
+        }
+        l = l * a + p;
+        m = mn;
+    }
+    const size_t oo = ((size_t)row * kFaHeads + head) * kHeadDim + 8 * lane;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float r = acc[e] / l;
+        if (gate) r *= __half2float(gate[oo + e]);
+        out[oo + e] = (OutT)r;
+    }
+}
+
+__global__ void f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __float2half_rn(in[i]);
+}
+int f32_to_f16(cudaStream_t s, const float* in, __half* out, size_t n) {
+    if (n == 0) return 0;
+    f32_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(in, out, n);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---- host: tensor maps + launch -------------------------------------------------------------------------------
+int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !p)
+            B2_FAIL(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
+        fn = reinterpret_cast<EncodeFn>(p);
+    }
+    cuuint64_t gdims[5], gstr[5];
+    cuuint32_t gbox[5], estr[5];
+    for (int i = 0; i < rank; ++i) { gdims[i] = dims[i]; gbox[i] = box[i]; estr[i] = 1; }
+    for (int i = 0; i + 1 < rank; ++i) gstr[i] = strides_bytes[i];
+    CUresult r = fn(out, dtype, (cuuint32_t)rank, const_cast<void*>(base), gdims, gstr, gbox, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) B2_FAIL(B200ATTN_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return 0;
+}
+
+// q [rows][8][256], kstage/vstage [ctx_rows][2][256] fp16.  d_tiles: device copy of the tile list.
+int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const __half* vstage, int ctx_rows,
+                         const PrefillTile* d_tiles, int n_tiles, const __half* gate, void* out, bool out_bf16,
+                         int* d_error, cudaStream_t s) {
+    if (n_tiles <= 0) return 0;
+    CUtensorMap mq, mk, mv;
+    {
+        const uint64_t dims[3] = {(uint64_t)kHeadDim, (uint64_t)kFaHeads, (uint64_t)rows};
+        const uint64_t str[2] = {(uint64_t)kHeadDim * 2, (uint64_t)kFaHeads * kHeadDim * 2};
+        const uint32_t box[3] = {64, 1, (uint32_t)kBM};
+        B2_TRY(make_tensor_map(&mq, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, q, dims, str, box));
+    }
+    {
+        const uint64_t dims[3] = {(uint64_t)kHeadDim, (uint64_t)kFaKvHeads, (uint64_t)ctx_rows};
+        const uint64_t str[2] = {(uint64_t)kHeadDim * 2, (uint64_t)kFaKvHeads * kHeadDim * 2};
+        const uint32_t box[3] = {64, 1, (uint32_t)kBN};
+        B2_TRY(make_tensor_map(&mk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, kstage, dims, str, box));
+        B2_TRY(make_tensor_map(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, vstage, dims, str, box));
+    }
+    static bool attr_done = false;
+    if (!attr_done) {
+        B2_CUDA(cudaFuncSetAttribute(fa_prefill_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF1Smem));
+        B2_CUDA(cudaFuncSetAttribute(fa_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF1Smem));
+        attr_done = true;
+    }
+    dim3 grid(n_tiles, kFaHeads);
+    if (out_bf16)
+        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, 192, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (__nv_bfloat16*)out, d_error);
+    else
+        fa_prefill_tc_kernel<float><<<grid, 192, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (float*)out, d_error);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_fa_prefill_simt(const __half* q, const __half* kstage, const __half* vstage, const int* d_row_pos,
+                           const int* d_row_ctx0, int rows, const __half* gate, void* out, bool out_bf16,
+                           cudaStream_t s) {
+    const int blocks = ceil_div(rows * kFaHeads, 4);
+    if (out_bf16)
+        fa_prefill_simt_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(q, kstage, vstage, d_row_pos, d_row_ctx0, rows, gate,
+                                                                    (__nv_bfloat16*)out);
+    else
+        fa_prefill_simt_kernel<float><<<blocks, 128, 0, s>>>(q, kstage, vstage, d_row_pos, d_row_ctx0, rows, gate, (float*)out);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+// Tile list for a batch: sequence i has base[i] cached tokens and counts[i] new rows; its context
+// occupies staging rows [ctx0[i], ctx0[i] + base[i] + counts[i]).  Longest contexts first.
+void build_prefill_tiles(const std::vector<int>& base, const int* counts, const std::vector<int>& ctx0, int n_seqs,
+                         std::vector<PrefillTile>& tiles) {
+    tiles.clear();
+    int row = 0;
+    for (int i = 0; i < n_seqs; ++i) {
+        for (int r0 = 0; r0 < counts[i]; r0 += kBM)
+            tiles.push_back(PrefillTile{row + r0, base[i] + r0, std::min(kBM, counts[i] - r0), ctx0[i]});
+        row += counts[i];
+    }
+    std::stable_sort(tiles.begin(), tiles.end(),
+                     [](const PrefillTile& a, const PrefillTile& b) { return a.q_pos0 + a.n_rows > b.q_pos0 + b.n_rows; });
+}
+
+}  // namespace b200

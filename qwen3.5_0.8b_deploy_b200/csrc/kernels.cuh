@@ -1,0 +1,89 @@
+// Internal declarations shared between the kernel files and the operator files.
+#pragma once
+
+#include "common.cuh"
+
+#include <vector>
+
+namespace b200 {
+
+// ---- paged KV cache (kv_cache.cu) ----------------------------------------------------------------------
+struct AppendTile {  // the tokens of one sequence that land in one cache page
+    int seq;         // index into slots[]
+    int first_row;   // first input row of the tile
+    int first_pos;   // cache position of that row
+    int ntok;        // 1..64, never crosses a page boundary
+};
+int launch_kv_append(const KvView& kv, int layer, const AppendTile* d_tiles, int n_tiles, const int* d_slots,
+                     const float* kin, int k_stride, const float* vin, int v_stride, bool do_norm_rope,
+                     const float* k_norm_w, const float* inv_freq, __half* kstage, __half* vstage,
+                     const int* d_stage_row0, bool decode_mode, cudaStream_t s);
+int launch_kv_advance(const KvView& kv, int layer, const int* d_slots, const int* d_counts, int n_seqs, cudaStream_t s);
+int launch_fa_q_epilogue(const float* qkv_raw, int rows, const float* q_norm_w, const float* inv_freq,
+                         const int* d_row_pos, const int* d_slots, const int* d_lens_layer, int max_seqs, __half* q_out,
+                         __half* gate_out, cudaStream_t s);
+int launch_kv_stage_gather(const KvView& kv, int layer, int slot, int base, int stage_row0, __half* kstage,
+                           __half* vstage, cudaStream_t s);
+void build_append_tiles(const std::vector<int>& base, const int* h_counts, int n_seqs, std::vector<AppendTile>& tiles);
+int pool_prepare_append(b200attn_kv_pool p, int layer, const int* h_slots, const int* h_counts, int n_seqs,
+                        std::vector<int>& base, int* total_rows);
+int ensure_meta(int** d_meta, int* cap, int need);
+
+// ---- decode attention (fa_decode.cu) -----------------------------------------------------------------------
+int fa_decode_max_splits(bool fp16, int max_pages_per_seq, int pages_per_warp);
+int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, int len_add, const __half* q,
+                     const __half* gate, int pages_per_warp, int max_splits, float* part_o, float* part_ml, void* out,
+                     bool out_bf16, cudaStream_t s);
+
+// ---- prefill attention (fa_prefill.cu) -----------------------------------------------------------------------
+struct PrefillTile {
+    int q_row0;    // first global row of the tile (rows of Q / out)
+    int q_pos0;    // position of that row inside its sequence's context
+    int n_rows;    // valid rows (<= 128)
+    int ctx_row0;  // staging row of the sequence's context position 0
+};
+int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const __half* vstage, int ctx_rows,
+                         const PrefillTile* d_tiles, int n_tiles, const __half* gate, void* out, bool out_bf16,
+                         int* d_error, cudaStream_t s);
+int launch_fa_prefill_simt(const __half* q, const __half* kstage, const __half* vstage, const int* d_row_pos,
+                           const int* d_row_ctx0, int rows, const __half* gate, void* out, bool out_bf16, cudaStream_t s);
+void build_prefill_tiles(const std::vector<int>& base, const int* counts, const std::vector<int>& ctx0, int n_seqs,
+                         std::vector<PrefillTile>& tiles);
+int f32_to_f16(cudaStream_t s, const float* in, __half* out, size_t n);
+
+// ---- Gated DeltaNet (la_kernels.cu, la_chunk.cu) -----------------------------------------------------------------
+struct LaSeqMeta {  // per sequence, device array
+    int slot;
+    int row0;
+    int count;
+};
+int launch_la_conv_seq(const float* mixed, const int* d_row_seq, const LaSeqMeta* d_seqs, const float* conv_layer,
+                       size_t conv_stride, const float* conv_w, const float* a_log, const float* dt_bias, int rows,
+                       bool tf32_round, float* q, float* k, float* v, float* g, float* beta, cudaStream_t s);
+int launch_la_conv_state_update(const float* mixed, const LaSeqMeta* d_seqs, int n_seqs, float* conv_layer,
+                                size_t conv_stride, cudaStream_t s);
+int launch_la_recurrent_serial(const float* q, const float* k, const float* v, const float* g, const float* beta,
+                               const LaSeqMeta* d_seqs, int n_seqs, float* rec_layer, size_t rec_stride, float* out,
+                               cudaStream_t s);
+int launch_la_gated_norm(const float* core, const float* mixed, const float* norm_w, int rows, void* out, bool out_bf16,
+                         cudaStream_t s);
+int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max_seqs, float* rec_layer,
+                     size_t rec_stride, float* conv_layer, size_t conv_stride, const float* conv_w, const float* a_log,
+                     const float* dt_bias, const float* norm_w, void* out, bool out_bf16, cudaStream_t s);
+int launch_la_conv_import(const float* ref_conv, float* mine, cudaStream_t s);
+int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
+
+// ---- operator internals shared with the stack ------------------------------------------------------------------------
+size_t fa_scratch_bytes(const b200attn_fa_config& c);
+int fa_create_internal(const b200attn_fa_config* cfg, const Scratch* shared, b200attn_fa* out);
+size_t la_scratch_bytes(const b200attn_la_config& c);
+int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b200attn_la* out);
+// Operator bodies that take activations in the stack's own formats (see stack.cu).
+int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
+                    int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
+                    float y_beta, cudaStream_t s);
+int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots, const int* h_counts,
+                    int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
+                    float y_beta, cudaStream_t s);
+
+}  // namespace b200

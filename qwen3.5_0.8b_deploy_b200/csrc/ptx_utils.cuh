@@ -1,0 +1,112 @@
+// Thin inline-PTX helpers shared by the kernels: mbarrier with bounded waits, bulk (TMA) copies,
+// warp-level mma.sync for the decode path.  tcgen05 helpers live in tc05.cuh.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace b200 {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// ---- mbarrier ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit_ns` or as soon as another thread of the CTA raised *abort_flag.
+// Returns false on give-up (and raises the flag), so every role can fall through to the common exit.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = 2000000000ull) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t it = 0;
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++it & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_timer_ns() - t0 > limit_ns) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// Warp-uniform form for roles whose next instruction is warp-collective (.sync.aligned): either every
+// lane proceeds or every lane gives up.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    const bool r = mbar_wait(bar, parity, abort_flag);
+    return __all_sync(0xffffffffu, r);
+}
+
+// ---- bulk async copy global -> shared, completion on an mbarrier (1-D TMA) -----------------------------------
+// dst, src 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- mma.sync m16n8k16 f16 x f16 -> f32 ------------------------------------------------------------------------
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Transposes an 8x8 matrix of 16-bit elements held one row-pair per lane (lane l: row l/4, columns
+// 2(l%4), 2(l%4)+1); afterwards lane l holds elements (2(l%4), l/4) and (2(l%4)+1, l/4).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+// Four signed bytes -> two half2 (b0,b1) and (b2,b3), exact.
+__device__ __forceinline__ void cvt_s8x4_half2x2(uint32_t x, uint32_t& lo, uint32_t& hi) {
+    x ^= 0x80808080u;                                          // signed -> biased unsigned
+    uint32_t l = __byte_perm(x, 0x64646464u, 0x4140);          // halves 1024 + u0, 1024 + u1
+    uint32_t h = __byte_perm(x, 0x64646464u, 0x4342);
+    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);  // 1024 + 128
+    __half2 lh = __hsub2(*reinterpret_cast<__half2*>(&l), bias);
+    __half2 hh = __hsub2(*reinterpret_cast<__half2*>(&h), bias);
+    lo = *reinterpret_cast<uint32_t*>(&lh);
+    hi = *reinterpret_cast<uint32_t*>(&hh);
+}
+
+}  // namespace b200
