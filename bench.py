@@ -1,0 +1,365 @@
+"""Benchmark of the attention hot path inside the Qwen3.5-0.8B-shaped hybrid stack.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --steps K --warmup W    # the reference's CPU path on the host cores
+
+One "step" = one whole job on one batch: prefill 1024 tokens then greedy-decode 512 tokens for 128
+sequences per GPU (24 layers = 6 x [3 Gated DeltaNet + 1 gated full attention], INT8-quantised
+weights, FP16 paged KV cache), synthetic token ids, random-init weights.  Sequences are partitioned
+across ranks (one process per GPU, model replicated, no collective on the data path), so N GPUs run
+N x 128 sequences: weak scaling.  Rank 0 prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "E2E tok/s, bs128 pp1024/tg512, 1-8 B200; attn % of HBM/TC roofline"
+UNIT = "tok/s"
+NUM_LAYERS, INTER, VOCAB = 24, 3584, 248320
+
+# Algorithmic bytes / flops per launch of the kernels the roofline object can describe.
+def algo_la_decode_bytes(n_seqs: int) -> float:
+    # per (sequence, layer, step): 2 MiB of fp32 state (read + write), conv cache 3*6144*4 B read + written,
+    # projection row 8224*4 B read, 2048 outputs (bf16) written
+    return n_seqs * (2 * 16 * 128 * 128 * 4 + 2 * 3 * 6144 * 4 + 8224 * 4 + 2048 * 2)
+
+
+def algo_fa_decode_bytes(n_seqs: int, ctx_len: float, fp16: bool) -> float:
+    # per (sequence, layer, step) at cache length L: K and V rows (+ scales for INT8) read once for all 8 q heads,
+    # q (fp16) + gate (fp16) read, output (bf16) written
+    per_tok = 2 * 2 * 256 * (2 if fp16 else 1) + (0 if fp16 else 2 * 2 * 4)
+    return n_seqs * (per_tok * ctx_len + 8 * 256 * (2 + 2 + 2))
+
+
+def algo_fa_prefill_flops(n_seqs: int, length: int) -> float:
+    return n_seqs * 2.0 * (2 * 8 * 256) * length * (length + 1) / 2      # causal QK^T + PV
+
+
+def algo_la_prefill_flops(n_seqs: int, length: int) -> float:
+    return n_seqs * 16 * length * 3.0 * 2 * 128 * 128                     # serial recurrence: 3 passes of 128x128 MACs per token-head
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return dict(hbm_gbs=d["hbm_gbs"], tflops_burst=d["bf16_tflops"], tflops_sustained=d["bf16_tflops_sustained"], source="measured")
+    return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), samples=len(sm))
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ------------------------------------------------------------------------------------------------------
+# CPU arm: the reference's CPU classes (oracle/_ref) or the C restatement, on the host cores
+# ------------------------------------------------------------------------------------------------------
+class CpuArm:
+    """The reference's CPU path for the same job on the host cores: each thread drives ONE sequence through the
+    24-layer CPU stack (reference FullAttention / LinearAttention / MLP classes from oracle/_ref when present,
+    else the C restatement) for a bounded number of tokens, greedy."""
+
+    def __init__(self, prompt_tokens: int, gen_tokens: int, threads: int, seed: int = 1234):
+        import psutil
+        from oracle import cpu_oracle as O, cpu_stack
+        synth = entry.load_package().synth
+        O.build()
+        self.use_ref = O.have_ref()
+        self.P, self.G = prompt_tokens, gen_tokens
+        weights = cpu_stack.make_stack_weights(synth, seed, NUM_LAYERS, INTER, VOCAB, int8=False)   # the CPU classes take fp32 weights
+        qw = dict(layers=weights["layers"], embed=weights["embed"], final_norm=weights["final_norm"])
+        per_seq_gb = 2.1 if self.use_ref else 0.1            # the reference classes copy their weights per object
+        free_gb = psutil.virtual_memory().available / 2**30
+        self.threads = max(1, min(threads, int((free_gb - 8) / per_seq_gb)))
+        self.make = lambda: [cpu_stack.OracleStackSequence(qw, self.P + self.G + 1, kv_mode=0, use_ref=self.use_ref)
+                             for _ in range(self.threads)]
+        self.toks = synth.rng(seed, "cpu.tokens").integers(0, VOCAB, (self.threads, self.P))
+        self.sample = (f"{self.threads} sequences (one per host thread) x ({self.P} prompt + {self.G} generated tokens) through the "
+                       f"24-layer stack, context <= {self.P + self.G} tokens; fp32 weights, fp32 KV")
+        self.kind = "reference" if self.use_ref else "port"
+
+    def step(self) -> float:
+        """One bounded sample; returns tokens/s over all threads (fresh caches every call)."""
+        seqs = self.make()
+
+        def work(i):
+            logits = None
+            for t in range(self.P):
+                _, logits = seqs[i].forward_token(int(self.toks[i, t]), want_logits=(t == self.P - 1))
+            tok = int(np.argmax(logits))
+            for _ in range(self.G):
+                _, logits = seqs[i].forward_token(tok)
+                tok = int(np.argmax(logits))
+
+        t0 = time.time()
+        ths = [threading.Thread(target=work, args=(i,)) for i in range(self.threads)]
+        [t.start() for t in ths]
+        [t.join() for t in ths]
+        self.seconds = time.time() - t0
+        return self.threads * (self.P + self.G) / self.seconds
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    arm = CpuArm(args.cpu_prompt, args.cpu_gen, os.cpu_count() or 1)
+    vals, secs = [], []
+    for i in range(args.warmup + args.steps):
+        v = arm.step()
+        if i >= args.warmup:
+            vals.append(v); secs.append(arm.seconds)
+    v = statistics.mean(vals)
+    line = dict(metric=METRIC, value=v, unit=UNIT, n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=statistics.mean(secs) * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32",
+                data="synthetic", impl="reference", config=workload_config(args),
+                cpu_baseline=dict(value=v, unit=UNIT, cores=arm.threads, kind=arm.kind, sample=arm.sample),
+                e2e=dict(value=v, unit=UNIT, h2d_bytes_per_step=0, d2h_bytes_per_step=0), gpu_launches=0)
+    print(json.dumps(line))
+
+
+def workload_config(args) -> dict:
+    return dict(workload="24-layer hybrid stack (18 Gated DeltaNet + 6 gated full attention, FFN 3584, vocab 248320, tied "
+                         "embeddings), INT8 per-output-channel weights, FP16 paged KV, greedy decode",
+                batch_per_gpu=args.batch, prompt_len=args.prompt, gen_len=args.gen,
+                parallelism=f"replica per GPU, sequences partitioned ({args.batch} per GPU)",
+                l2="inputs larger than L2: each decode step streams 4.8 GB of DeltaNet state and the KV cache")
+
+
+# ------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------
+def build_stack(ops, synth, args, seed=1234):
+    from oracle import cpu_stack  # weight generator only (numpy); nothing from the checker is executed on the timed path
+    st = ops.HybridStack(num_layers=NUM_LAYERS, intermediate_size=INTER, vocab_size=VOCAB, max_seqs=args.batch,
+                         max_seq_len=args.prompt + args.gen, prefill_chunk_seqs=max(1, 16384 // (args.prompt + args.gen)),
+                         kv_dtype=ops.KV_FP16, int8_weights=True)
+    for i in range(NUM_LAYERS):
+        lw = dict(input_norm=np.zeros(1024, np.float32), post_norm=np.zeros(1024, np.float32))
+        ffn = synth.ffn_weights(seed, f"L{i}")
+        fa = synth.fa_weights(seed, f"L{i}.fa") if synth.is_full_attention_layer(i) else None
+        la = None if fa is not None else synth.la_weights(seed, f"L{i}.la")
+        st.set_layer_weights(i, lw, ffn, fa=fa, la=la)
+    st.init_embedding_random(seed, 0.02, np.zeros(1024, np.float32))
+    return st
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--gen", type=int, default=512)
+    ap.add_argument("--cpu-prompt", type=int, default=24)
+    ap.add_argument("--cpu-gen", type=int, default=8)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import importlib
+    import torch
+    import torch.distributed as dist
+    entry.load_package()
+    replica = importlib.import_module(entry.PKG_NAME + ".replica")
+    rank, world, local = replica.env_rank()
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    torch.cuda.set_device(local)
+    if world > 1:
+        replica.init("nccl", local)
+    ops = entry.load_ops()
+    synth = entry.load_package().synth
+    peaks = read_peaks()
+
+    st = build_stack(ops, synth, args)
+    B, P, G = args.batch, args.prompt, args.gen
+    stream = torch.cuda.Stream()
+    h_tokens = torch.from_numpy(synth.rng(77 + rank, "bench.tokens").integers(0, VOCAB, (B, P)).astype(np.int32)).pin_memory()
+    d_tokens = h_tokens.cuda()
+    h_out = torch.empty(B, dtype=torch.int32).pin_memory()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def job_device():
+        """Whole job with inputs resident in HBM: reset, prefill, G captured decode steps."""
+        st.reset_cache()
+        first = st.forward_batch_prefill(d_tokens)
+        st.set_tokens(first)
+        st.launch_decode(G)          # G captured decode steps; the cache ends at P + G tokens
+
+    def job_e2e():
+        """Same job through the public API with host buffers: prompt ids H2D, generated ids D2H every step."""
+        st.reset_cache()
+        dev = h_tokens.to("cuda", non_blocking=True)
+        first = st.forward_batch_prefill(dev)
+        st.set_tokens(first)
+        h_out.copy_(first, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        for _ in range(G):
+            st.launch_decode(1)
+            h_out.copy_(st.get_tokens(B), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    with torch.cuda.stream(stream):
+        # one eager pass warms cuBLAS heuristics and kernel attributes, then the decode step is captured once
+        st.reset_cache()
+        first = st.forward_batch_prefill(d_tokens)
+        st.forward_batch_decode(first)
+        stream.synchronize()
+        st.set_tokens(first)
+        st.capture_decode(B)
+        for _ in range(args.warmup):
+            job_device()
+        stream.synchronize()
+        barrier()
+        clocks = ClockSampler(local)
+        if rank == 0:
+            clocks.start()
+        ops.launch_count(reset=True)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(args.steps):
+            job_device()
+        ev1.record(stream)
+        stream.synchronize()
+        barrier()
+        launches = ops.launch_count(reset=True)
+        clk = clocks.stop() if rank == 0 else {}
+        ms_total = ev0.elapsed_time(ev1)
+
+        # end-to-end arm (host buffers, copies inside the timed region)
+        job_e2e()
+        barrier()
+        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev2.record(stream)
+        for _ in range(args.steps):
+            job_e2e()
+        ev3.record(stream)
+        stream.synchronize()
+        barrier()
+        ms_e2e = ev2.elapsed_time(ev3)
+
+        # per-kernel device times inside real (eager) steps: one prefill + 8 decode steps with event pairs around the kernels
+        prof = {}
+        if rank == 0:
+            st.reset_cache()
+            ops.profile_reset(); ops.profile_enable(True)
+            first = st.forward_batch_prefill(d_tokens)
+            cur = first
+            for _ in range(8):
+                cur = st.forward_batch_decode(cur)
+            stream.synchronize()
+            ops.profile_enable(False)
+            for name in ("fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append"):
+                prof[name] = ops.profile_read(name)
+            ops.profile_reset()
+
+    # NCCL: the only collective of the run, and only on the counters (max of the times, sum of the tokens)
+    tokens_per_job = B * (P + G)
+    (ms_total, ms_e2e), (tokens_all,) = replica.reduce_counters([ms_total, ms_e2e], [float(tokens_per_job * args.steps)], "cuda")
+    value = replica.job_throughput(tokens_all, ms_total)
+    e2e_value = replica.job_throughput(tokens_all, ms_e2e)
+
+    if rank == 0:
+        chunks = -(-B // max(1, (max(1, 16384 // (P + G)) * (P + G)) // P))
+        per = {k: (v[0] / max(v[1], 1)) for k, v in prof.items()}       # ms per launch
+        # share of one whole job spent in each kernel class (launch counts of a full job x measured ms per launch)
+        job_ms = dict(la_decode=per["la_decode"] * 18 * G, fa_decode=per["fa_decode"] * 6 * G,
+                      fa_prefill=prof["fa_prefill"][0], la_prefill=prof["la_prefill"][0])
+        ctx_avg = P + 4.5                                                  # cache length seen by the 8 profiled decode steps
+        seqs_per_chunk = B / max(chunks, 1)
+        roof = dict(
+            la_decode=dict(bound="hbm", achieved=algo_la_decode_bytes(B) / (per["la_decode"] * 1e-3) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s"),
+            fa_decode=dict(bound="hbm", achieved=algo_fa_decode_bytes(B, ctx_avg, True) / (per["fa_decode"] * 1e-3) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s"),
+            fa_prefill=dict(bound="tensor", achieved=algo_fa_prefill_flops(seqs_per_chunk, P) / (per["fa_prefill"] * 1e-3) / 1e12, peak=peaks["tflops_sustained"], unit="TFLOP/s"),
+            la_prefill=dict(bound="tensor", achieved=algo_la_prefill_flops(seqs_per_chunk, P) / (per["la_prefill"] * 1e-3) / 1e12, peak=peaks["tflops_sustained"], unit="TFLOP/s"),
+        )
+        for k, r in roof.items():
+            r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], job_ms=job_ms[k], traffic=None, peak_source=peaks["source"])
+        dominant = max(job_ms, key=job_ms.get)
+        cpu = None
+        if not args.no_cpu_baseline:
+            arm = CpuArm(args.cpu_prompt, args.cpu_gen, os.cpu_count() or 1)
+            cpu = dict(value=arm.step(), unit=UNIT, cores=arm.threads, kind=arm.kind, sample=arm.sample)
+        line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                    data="synthetic", config=workload_config(args), clocks=clk,
+                    e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=B * P * 4, d2h_bytes_per_step=B * G * 4),
+                    gpu_launches=launches, roofline=roof[dominant], roofline_other=[roof[k] for k in roof if k != dominant],
+                    cpu_baseline=cpu)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

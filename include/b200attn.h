@@ -60,7 +60,11 @@ typedef struct b200attn_la_s* b200attn_la;             /* Gated DeltaNet operato
 typedef struct b200attn_la_state_s* b200attn_la_state; /* recurrent + conv state for all DeltaNet layers    */
 typedef struct b200attn_stack_s* b200attn_stack;       /* 24-layer hybrid stack with the captured decode step */
 
+/* Text of the calling thread's last failure.  Replaces the reference's error channels: printf-and-continue
+ * (src/backend/cuda/kernels/full_attention_cuda.cu:11-17) and std::runtime_error
+ * (src/backend/cuda/include/cuda_error_handling.cuh:19-27). */
 const char* b200attn_last_error(void);
+/* B200ATTN_ABI_VERSION of the loaded library.  No reference counterpart. */
 int b200attn_abi_version(void);
 
 /* ------------------------------------------------------------------------------------------------
@@ -89,21 +93,23 @@ typedef struct {
     int kv_dtype;          /* b200attn_kv_dtype                                               */
 } b200attn_kv_config;
 
-/* CudaKVCache::reset (full_attention_cuda.cu:252-272) / PagedKVCache::initialize (paged_kv.cpp:27-57). */
+/* CudaKVCache::reset (full_attention_cuda.cu:252-272) / PagedKVCache::initialize (paged_kv.cpp:17-47). */
 int b200attn_kv_pool_create(const b200attn_kv_config* cfg, b200attn_kv_pool* out);
+/* PagedKVCache::~PagedKVCache (paged_kv.cpp:13-15); CudaKVCache itself has no destructor
+ * (full_attention_cuda.hpp:11-33) and leaks unless the caller frees its members. */
 int b200attn_kv_pool_destroy(b200attn_kv_pool pool);
-/* PagedKVCache::allocate_sequence (paged_kv.cpp:90-107): new slot with pages for reserve_tokens. */
+/* PagedKVCache::allocate_sequence (paged_kv.cpp:90-112): new slot with pages for reserve_tokens. */
 int b200attn_kv_seq_alloc(b200attn_kv_pool pool, int reserve_tokens, int* slot_out);
-/* PagedKVCache::append_tokens page growth (paged_kv.cpp:109-131) / CudaKVCache::ensure_capacity
+/* PagedKVCache::append_tokens page growth (paged_kv.cpp:114-136) / CudaKVCache::ensure_capacity
  * (full_attention_cuda.cu:274-335): make sure the slot owns pages for total_tokens. */
 int b200attn_kv_seq_reserve(b200attn_kv_pool pool, int slot, int total_tokens);
-/* PagedKVCache::release_sequence (paged_kv.cpp:133-147). */
+/* PagedKVCache::release_sequence (paged_kv.cpp:138-148). */
 int b200attn_kv_seq_free(b200attn_kv_pool pool, int slot);
 /* CudaKVCache::clear (full_attention_cuda.cu:337-356): all lengths to zero, pages kept. */
 int b200attn_kv_clear(b200attn_kv_pool pool, b200attn_stream stream);
 /* CudaKVCache::length (full_attention_cuda.hpp:26-28); host mirror of the device length. */
 int b200attn_kv_seq_len(b200attn_kv_pool pool, int layer, int slot, int* len_out);
-/* PagedKVCache::get_allocated_pages / get_used_pages (paged_kv.hpp:34-35). */
+/* PagedKVCache::get_allocated_pages / get_used_pages (paged_kv.cpp:181-192). */
 int b200attn_kv_pages(b200attn_kv_pool pool, int* total_out, int* used_out);
 /* Reads (and clears) the pool's device-side status word: 0 = clean, 1 = slot out of range seen by a
  * kernel, 2 = append beyond the reserved pages (the write was skipped), 3/4 = a bounded wait inside
@@ -112,11 +118,11 @@ int b200attn_kv_pages(b200attn_kv_pool pool, int* total_out, int* used_out);
 int b200attn_kv_device_status(b200attn_kv_pool pool, int* code_out);
 /* Quantise-on-append of already normalised/rotated K and raw V rows, the arithmetic of
  * fused_kv_cache_int8_kernel (full_attention_cuda.cu:128-147) and kv_append_int8
- * (kv_int8_cuda.cu:160-190): d_k, d_v fp32 [sum(h_counts), kv_heads*head_dim]; sequence i receives
+ * (kv_int8_cuda.cu:193-207): d_k, d_v fp32 [sum(h_counts), kv_heads*head_dim]; sequence i receives
  * h_counts[i] tokens at its current length on `layer`, and that length advances. */
 int b200attn_kv_append(b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
                        int n_seqs, const float* d_k, const float* d_v, b200attn_stream stream);
-/* kv_get_int8 (kv_int8_cuda.cu:192-222) without dequantisation: gather one sequence's cache on one
+/* kv_get_int8 (kv_int8_cuda.cu:209-222) without dequantisation: gather one sequence's cache on one
  * layer into contiguous token-major arrays [len][kv_heads][head_dim] (int8 or half as stored) and,
  * for INT8, scales [len][kv_heads].  Scale pointers may be NULL for FP16 pools. */
 int b200attn_kv_export(b200attn_kv_pool pool, int layer, int slot, void* d_k_codes, void* d_v_codes,
@@ -147,9 +153,9 @@ typedef struct {
     const float* o_proj; /* [hidden, num_heads*head_dim] */
 } b200attn_fa_weights;
 
-/* CudaFullAttention::CudaFullAttention (full_attention_cuda.cu:188-213). */
+/* CudaFullAttention::CudaFullAttention (full_attention_cuda.cu:174-201). */
 int b200attn_fa_create(const b200attn_fa_config* cfg, b200attn_fa* out);
-/* CudaFullAttention::~CudaFullAttention (full_attention_cuda.cu:215-228). */
+/* CudaFullAttention::~CudaFullAttention (full_attention_cuda.cu:203-228). */
 int b200attn_fa_destroy(b200attn_fa fa);
 /* CudaFullAttention::set_weights (full_attention_cuda.cu:230-250); host pointers. */
 int b200attn_fa_set_weights(b200attn_fa fa, const b200attn_fa_weights* h_w);
@@ -219,13 +225,16 @@ typedef struct {
     int num_heads, key_dim, value_dim, conv_kernel;
 } b200attn_la_state_config;
 
-/* CudaLinearAttention::CudaLinearAttention (linear_attention_cuda.cu:292-330). */
+/* CudaLinearAttention::CudaLinearAttention (linear_attention_cuda.cu:292-326). */
 int b200attn_la_create(const b200attn_la_config* cfg, b200attn_la* out);
+/* CudaLinearAttention::~CudaLinearAttention (linear_attention_cuda.cu:328-379). */
 int b200attn_la_destroy(b200attn_la la);
-/* CudaLinearAttention::set_weights (linear_attention_cuda.cu:372-466); host pointers. */
+/* CudaLinearAttention::set_weights (linear_attention_cuda.cu:412-466); host pointers. */
 int b200attn_la_set_weights(b200attn_la la, const b200attn_la_weights* h_w);
 /* CudaLinearAttnState::reset (linear_attention_cuda.cu:266-282): allocate and zero. */
 int b200attn_la_state_create(const b200attn_la_state_config* cfg, b200attn_la_state* out);
+/* CudaLinearAttnState has no destructor (linear_attention_cuda.hpp:11-22); the reference's tests free
+ * d_recurrent_state / d_conv_state by hand (tests/integration/v2_kernel_accuracy_validate.cu:181-190). */
 int b200attn_la_state_destroy(b200attn_la_state st);
 /* CudaLinearAttnState::clear (linear_attention_cuda.cu:284-290) for one slot (slot < 0: all). */
 int b200attn_la_state_clear(b200attn_la_state st, int slot, b200attn_stream stream);
@@ -234,6 +243,7 @@ int b200attn_la_state_clear(b200attn_la_state st, int slot, b200attn_stream stre
  * (src/backend/cpu/core/attention/language_linear_attn.hpp:7-35).  Either pointer may be NULL. */
 int b200attn_la_state_import(b200attn_la_state st, int layer, int slot, const float* d_recurrent,
                              const float* d_conv, b200attn_stream stream);
+/* The reverse copy, same layouts (language_linear_attn.hpp:7-35). */
 int b200attn_la_state_export(b200attn_la_state st, int layer, int slot, float* d_recurrent,
                              float* d_conv, b200attn_stream stream);
 /* CudaLinearAttention::forward_batch / CudaLinearAttentionV2::forward_batch
@@ -247,6 +257,12 @@ int b200attn_la_prefill(b200attn_la la, b200attn_la_state st, int layer, const i
  * sequences: one token each, d_slots device int32.  Safe inside stream capture. */
 int b200attn_la_decode(b200attn_la la, b200attn_la_state st, int layer, const int* d_slots,
                        int n_seqs, const float* d_x, float* d_y, b200attn_stream stream);
+/* The fused recurrent step alone (gated_delta_kernel + conv1d_update + l2norm + norm_gate of
+ * linear_attention_cuda.cu:47-172 in one launch): d_mixed fp32 [n_seqs, 8224] is the fused input
+ * projection of the step (columns: 6144 q|k|v pre-conv, 2048 z, 16 a, 16 b); d_out fp32 [n_seqs, 2048]
+ * receives the gated, normalised head outputs (the input of out_proj).  Updates state and conv cache. */
+int b200attn_la_decode_core(b200attn_la la, b200attn_la_state st, int layer, const int* d_slots,
+                            int n_seqs, const float* d_mixed, float* d_out, b200attn_stream stream);
 /* Recurrence core alone (gated_delta_batch_fused_v2_kernel, linear_attention_v2.cu:492-595):
  * d_q, d_k fp32 [rows, heads, key_dim] (already L2-normalised, q scaled), d_v fp32
  * [rows, heads, value_dim], d_g (log decay) and d_beta fp32 [rows, heads]; d_out fp32
@@ -290,14 +306,18 @@ typedef struct {
     const b200attn_la_weights* la; /* non-NULL for DeltaNet layers */
 } b200attn_layer_weights;
 
+/* CudaEngine::CudaEngine (cuda_engine.cu:158-181, buffers :196-225): layers, caches and activation buffers. */
 int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_stack* out);
+/* CudaEngine::~CudaEngine (cuda_engine.cu:183-194). */
 int b200attn_stack_destroy(b200attn_stack st);
-/* CudaEngine::set_layer_weights (cuda_engine.cu:269-293). */
+/* CudaEngine::set_layer_weights (cuda_engine.cu:244-298). */
 int b200attn_stack_set_layer_weights(b200attn_stack st, int layer, const b200attn_layer_weights* h_w);
-/* Token embedding (tied with the LM head) [vocab, hidden] and final norm [hidden]; host pointers. */
+/* Token embedding (tied with the LM head) [vocab, hidden] and final norm [hidden]; host pointers.
+ * CudaTokenEmbedding::set_weight / CudaLMHead::set_weight as the benchmark driver calls them
+ * (src/backend/cuda/performance_test.cu:196-202; CudaEngine::set_final_norm_weight / set_lm_head_weight, cuda_engine.cu:300-306). */
 int b200attn_stack_set_embedding(b200attn_stack st, const float* h_embed, const float* h_final_norm);
 /* Same, but the embedding is generated on the device as N(0, std) from `seed` (the 1 GB host copy
- * is not needed for throughput runs with random-init weights). */
+ * is not needed for throughput runs with random-init weights).  No reference counterpart. */
 int b200attn_stack_init_embedding_random(b200attn_stack st, uint64_t seed, float std_dev,
                                          const float* h_final_norm);
 /* CudaEngine::reset_cache (cuda_engine.cu:514-519). */
@@ -319,11 +339,25 @@ int b200attn_stack_decode(b200attn_stack st, int n_seqs, const int* d_tokens_in,
 int b200attn_decode_graph_capture(b200attn_stack st, int n_seqs, b200attn_stream stream);
 /* cudaGraphLaunch (cuda_engine.cu:472-476): run `steps` captured steps back to back. */
 int b200attn_decode_graph_launch(b200attn_stack st, int steps, b200attn_stream stream);
+/* Seed / read the token buffer of the captured step (d_tokens int32 [n_seqs]).  The reference copies
+ * token ids host -> device every step instead (performance_test.cu:297-312). */
 int b200attn_stack_set_tokens(b200attn_stack st, const int* d_tokens, int n_seqs, b200attn_stream stream);
+/* See b200attn_stack_set_tokens (performance_test.cu:313-319 reads the sampled ids back each step). */
 int b200attn_stack_get_tokens(b200attn_stack st, int* d_tokens, int n_seqs, b200attn_stream stream);
 /* Number of kernels this library launched on behalf of the calling thread since the last call
- * with reset != 0 (graph replays count the nodes of the captured step). */
+ * with reset != 0 (graph replays count the nodes of the captured step).  No reference counterpart. */
 long long b200attn_launch_count(int reset);
+
+/* ------------------------------------------------------------------------------------------------
+ * Per-kernel device timing (the reference's LatencyStats over cudaEvent pairs,
+ * src/backend/cuda/performance_test.cu:60-97, applied per kernel class).  While enabled, every launch
+ * of the named kernel classes is bracketed by an event pair on its own stream (do not enable during
+ * stream capture).  Names: "fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append".
+ * b200attn_profile_read synchronises the device and returns the summed device time and launch count.
+ * ---------------------------------------------------------------------------------------------- */
+int b200attn_profile_enable(int on);
+int b200attn_profile_reset(void);
+int b200attn_profile_read(const char* name, double* total_ms_out, long long* launches_out);
 
 /* ------------------------------------------------------------------------------------------------
  * Self-test of the tcgen05 / TMA building blocks: D[M,N] = A[M,K] * B^T on one CTA with the

@@ -67,6 +67,17 @@ inline void count_launch(int n = 1) { g_launches += n; }
         if (_s != 0) return _s;  \
     } while (0)
 
+// ---- per-kernel event timing (gemm.cu) ------------------------------------------------------------------
+enum ProfKind { PROF_FA_PREFILL = 0, PROF_FA_DECODE, PROF_LA_PREFILL, PROF_LA_DECODE, PROF_KV_APPEND, PROF_COUNT };
+extern bool g_prof_on;
+void prof_begin(ProfKind k, cudaStream_t s);
+void prof_end(ProfKind k, cudaStream_t s);
+struct ProfScope {   // brackets the launches issued during its lifetime when profiling is enabled
+    ProfKind k; cudaStream_t s;
+    ProfScope(ProfKind kind, cudaStream_t st) : k(kind), s(st) { if (g_prof_on) prof_begin(k, s); }
+    ~ProfScope() { if (g_prof_on) prof_end(k, s); }
+};
+
 inline cudaStream_t as_stream(b200attn_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 

@@ -1,6 +1,6 @@
 // Gated full-attention operator: weights, scratch, and the prefill / decode sequencing of
 // projection GEMM -> Q/K epilogues + quantise-on-append -> attention core -> output projection.
-// Mirrors qwen::cuda::CudaFullAttention (src/backend/cuda/kernels/full_attention_cuda.cu:188-250,
+// Mirrors qwen::cuda::CudaFullAttention (src/backend/cuda/kernels/full_attention_cuda.cu:174-250,
 // 369-449, 644-715 in the reference).
 #include "kernels.cuh"
 
@@ -192,8 +192,11 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
                                     pool->d_lens + (size_t)layer * pool->cfg.max_seqs, kv.max_seqs, fa->d_q, fa->d_gate, s));
         B2_TRY(launch_kv_append(kv, layer, nullptr, n_seqs, d_slots_in, k_in, kFaQkvCols, v_in, kFaQkvCols, true, fa->d_knorm,
                                 fa->d_inv_freq, nullptr, nullptr, nullptr, true, s));
-        B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, 1, fa->d_q, fa->d_gate, ppw, splits, fa->d_part_o,
-                                fa->d_part_ml, fa->d_attn, bf16, s));
+        {
+            ProfScope prof(PROF_FA_DECODE, s);
+            B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, 1, fa->d_q, fa->d_gate, ppw, splits, fa->d_part_o,
+                                    fa->d_part_ml, fa->d_attn, bf16, s));
+        }
         B2_TRY(launch_kv_advance(kv, layer, d_slots_in, nullptr, n_seqs, s));
         B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, s));
         pool->lens_dirty = true;
@@ -237,10 +240,16 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
                                 fa->d_q, fa->d_gate, s));
     for (int i = 0; i < n_seqs; ++i)
         B2_TRY(launch_kv_stage_gather(kv, layer, h_slots[i], base[i], ctx0[i], fa->d_kstage, fa->d_vstage, s));
-    B2_TRY(launch_kv_append(kv, layer, d_atiles, (int)atiles.size(), d_slots, k_in, kFaQkvCols, v_in, kFaQkvCols, true,
-                            fa->d_knorm, fa->d_inv_freq, fa->d_kstage, fa->d_vstage, d_ctx0, false, s));
-    B2_TRY(launch_fa_prefill_tc(fa->d_q, rows, fa->d_kstage, fa->d_vstage, ctx_rows, d_ptiles, (int)ptiles.size(),
-                                fa->d_gate, fa->d_attn, bf16, pool->d_error, s));
+    {
+        ProfScope prof(PROF_KV_APPEND, s);
+        B2_TRY(launch_kv_append(kv, layer, d_atiles, (int)atiles.size(), d_slots, k_in, kFaQkvCols, v_in, kFaQkvCols, true,
+                                fa->d_knorm, fa->d_inv_freq, fa->d_kstage, fa->d_vstage, d_ctx0, false, s));
+    }
+    {
+        ProfScope prof(PROF_FA_PREFILL, s);
+        B2_TRY(launch_fa_prefill_tc(fa->d_q, rows, fa->d_kstage, fa->d_vstage, ctx_rows, d_ptiles, (int)ptiles.size(),
+                                    fa->d_gate, fa->d_attn, bf16, pool->d_error, s));
+    }
     B2_TRY(launch_kv_advance(kv, layer, d_slots, d_counts, n_seqs, s));
     B2_TRY(fa_project_out(fa, d_y, y_beta, rows, s));
     for (int i = 0; i < n_seqs; ++i) pool->h_lens[(size_t)layer * pool->cfg.max_seqs + h_slots[i]] += h_counts[i];
@@ -269,6 +278,7 @@ extern "C" int b200attn_fa_decode_core(b200attn_fa fa, b200attn_kv_pool pool, in
     const int ppw = decode_pages_per_warp(pool);
     const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
     B2_TRY(f32_to_f16(s, d_q, fa->d_q, (size_t)n_seqs * kFaHeads * kHeadDim));
+    ProfScope prof(PROF_FA_DECODE, s);
     return launch_fa_decode(kv, layer, d_slots, n_seqs, 0, fa->d_q, nullptr, ppw, splits, fa->d_part_o, fa->d_part_ml, d_out,
                             false, s);
 }

@@ -3,6 +3,8 @@
 #include "common.cuh"
 
 #include <mutex>
+#include <utility>
+#include <vector>
 
 namespace b200 {
 
@@ -14,6 +16,28 @@ void set_error(const char* fmt, ...) {
     va_start(ap, fmt);
     vsnprintf(g_error, sizeof(g_error), fmt, ap);
     va_end(ap);
+}
+
+// ---- per-kernel event timing ------------------------------------------------------------------------------
+bool g_prof_on = false;
+namespace {
+struct ProfRec { std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev; cudaEvent_t open = nullptr; };
+ProfRec g_prof[PROF_COUNT];
+const char* kProfNames[PROF_COUNT] = {"fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append"};
+}  // namespace
+void prof_begin(ProfKind k, cudaStream_t s) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    cudaEventRecord(e, s);
+    g_prof[k].open = e;
+}
+void prof_end(ProfKind k, cudaStream_t s) {
+    if (!g_prof[k].open) return;
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    cudaEventRecord(e, s);
+    g_prof[k].ev.emplace_back(g_prof[k].open, e);
+    g_prof[k].open = nullptr;
 }
 
 static cublasHandle_t g_handle = nullptr;
@@ -104,4 +128,32 @@ extern "C" long long b200attn_launch_count(int reset) {
     const long long v = b200::g_launches;
     if (reset) b200::g_launches = 0;
     return v;
+}
+
+extern "C" int b200attn_profile_enable(int on) { b200::g_prof_on = on != 0; return 0; }
+extern "C" int b200attn_profile_reset(void) {
+    using namespace b200;
+    cudaDeviceSynchronize();
+    for (auto& r : g_prof) {
+        for (auto& p : r.ev) { cudaEventDestroy(p.first); cudaEventDestroy(p.second); }
+        r.ev.clear();
+        if (r.open) { cudaEventDestroy(r.open); r.open = nullptr; }
+    }
+    return 0;
+}
+extern "C" int b200attn_profile_read(const char* name, double* total_ms_out, long long* launches_out) {
+    using namespace b200;
+    B2_CHECK_ARG(name && total_ms_out && launches_out, "profile_read: null argument");
+    int k = -1;
+    for (int i = 0; i < PROF_COUNT; ++i) if (std::strcmp(name, kProfNames[i]) == 0) k = i;
+    B2_CHECK_ARG(k >= 0, "profile_read: unknown kernel class '%s'", name);
+    B2_CUDA(cudaDeviceSynchronize());
+    double total = 0.0;
+    for (auto& p : g_prof[k].ev) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, p.first, p.second) == cudaSuccess) total += ms;
+    }
+    *total_ms_out = total;
+    *launches_out = (long long)g_prof[k].ev.size();
+    return 0;
 }

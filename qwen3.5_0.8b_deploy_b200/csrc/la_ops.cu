@@ -1,7 +1,7 @@
 // Gated DeltaNet operator and state pool: weights, scratch, and the prefill / decode sequencing of
 // fused input projection -> conv/norm/gates -> delta-rule recurrence -> gated RMSNorm -> output projection.
 // Mirrors qwen::cuda::CudaLinearAttention / CudaLinearAttentionV2 / CudaLinearAttnState
-// (src/backend/cuda/kernels/linear_attention_cuda.cu:266-330,372-684, linear_attention_v2.cu:734-883 in
+// (src/backend/cuda/kernels/linear_attention_cuda.cu:266-326,412-684, linear_attention_v2.cu:734-883 in
 // the reference).
 #include "kernels.cuh"
 
@@ -255,6 +255,7 @@ static int la_recurrence(b200attn_la la, b200attn_la_state st, int layer, const 
                          int rows, float* out, bool tensor_cores, cudaStream_t s) {
     float* rec_layer = st->d_recurrent + (size_t)layer * st->cfg.max_seqs * st->rec_stride_slot();
     const int n_seqs = (int)h_seqs.size();
+    ProfScope prof(PROF_LA_PREFILL, s);
     if (tensor_cores)
         return launch_la_chunk_tc(q, k, v, g, beta, d_seqs, h_seqs.data(), n_seqs, rows, rec_layer, st->rec_stride_slot(), out,
                                   la->d_meta + la->meta_cap - 1, s);
@@ -287,9 +288,12 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
         B2_CHECK_ARG(d_slots, "la_decode: null slots");
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= la->cfg.max_batch, "la_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, la->cfg.max_batch);
         B2_TRY(project_in(n_seqs));
-        B2_TRY(launch_la_decode(la->d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
-                                st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, la->d_gated,
-                                bf16, s));
+        {
+            ProfScope prof(PROF_LA_DECODE, s);
+            B2_TRY(launch_la_decode(la->d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
+                                    st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, la->d_gated,
+                                    bf16, s));
+        }
         return project_out(n_seqs);
     }
     int rows = 0;
@@ -335,4 +339,18 @@ extern "C" int b200attn_la_prefill_core(b200attn_la la, b200attn_la_state st, in
     B2_TRY(la_build_meta(la, st, h_slots, h_counts, n_seqs, &rows, seqs, &d_seqs, &d_row_seq, false, s));
     if (rows == 0) return 0;
     return la_recurrence(la, st, layer, d_q, d_k, d_v, d_g, d_beta, d_seqs, seqs, rows, d_out, use_tensor_cores != 0, s);
+}
+
+extern "C" int b200attn_la_decode_core(b200attn_la la, b200attn_la_state st, int layer, const int* d_slots, int n_seqs,
+                                       const float* d_mixed, float* d_out, b200attn_stream stream) {
+    B2_CHECK_ARG(la && st && d_slots && d_mixed && d_out, "la_decode_core: null argument");
+    if (!la->ready) B2_FAIL(B200ATTN_ERR_NOT_READY, "LinearAttention weights not set");
+    B2_CHECK_ARG(layer >= 0 && layer < st->cfg.num_layers, "la_decode_core: layer %d out of range", layer);
+    B2_CHECK_ARG(n_seqs > 0, "la_decode_core: n_seqs must be > 0");
+    cudaStream_t s = as_stream(stream);
+    float* rec_layer = st->d_recurrent + (size_t)layer * st->cfg.max_seqs * st->rec_stride_slot();
+    float* conv_layer = st->d_conv + (size_t)layer * st->cfg.max_seqs * st->conv_stride_slot();
+    ProfScope prof(PROF_LA_DECODE, s);
+    return launch_la_decode(d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
+                            st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, d_out, false, s);
 }

@@ -3,7 +3,7 @@
 // Layer wiring follows qwen::LanguageLayer::forward (src/backend/cpu/core/common/language_backbone.cpp:55-91
 // in the reference): h1 = RMSNorm(x); a = attention(h1); h = x + a; h2 = RMSNorm(h); y = h + MLP(h2), with the
 // (1 + w) RMSNorm of language_common.cpp:21-38 and the SwiGLU MLP of core/mlp/language_mlp.cpp:54-91.
-// Engine-level behaviour mirrors qwen::cuda::CudaEngine (src/backend/cuda/kernels/cuda_engine.cu:250-519):
+// Engine-level behaviour mirrors qwen::cuda::CudaEngine (src/backend/cuda/kernels/cuda_engine.cu:158-519):
 // per-layer weights, prefill over token batches, a decode step for the whole batch, reset_cache, and a
 // graph-captured step (there: prefill, :391-479; here: decode with device-resident lengths and tokens).
 // The residual stream is fp32; GEMM operands are bf16 with fp32 accumulation (cuBLAS).

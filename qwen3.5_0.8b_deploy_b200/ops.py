@@ -31,7 +31,8 @@ ABI_SYMBOLS = [
     "b200attn_fa_decode_core", "b200attn_fa_prefill_core",
     "b200attn_la_create", "b200attn_la_destroy", "b200attn_la_set_weights", "b200attn_la_state_create",
     "b200attn_la_state_destroy", "b200attn_la_state_clear", "b200attn_la_state_import", "b200attn_la_state_export",
-    "b200attn_la_prefill", "b200attn_la_decode", "b200attn_la_prefill_core",
+    "b200attn_la_prefill", "b200attn_la_decode", "b200attn_la_decode_core", "b200attn_la_prefill_core",
+    "b200attn_profile_enable", "b200attn_profile_reset", "b200attn_profile_read",
     "b200attn_stack_create", "b200attn_stack_destroy", "b200attn_stack_set_layer_weights",
     "b200attn_stack_set_embedding", "b200attn_stack_init_embedding_random", "b200attn_stack_reset",
     "b200attn_stack_prefill", "b200attn_stack_decode", "b200attn_decode_graph_capture",
@@ -334,6 +335,12 @@ class LinearAttention:
                                        _dev(y), _stream()))
         return y
 
+    def decode_core(self, mixed: torch.Tensor, state: LinearAttnState, layer: int, d_slots: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((mixed.shape[0], 2048), dtype=torch.float32, device="cuda")
+        _check(_lib.b200attn_la_decode_core(self.h, state.h, C.c_int(layer), _dev(d_slots), C.c_int(d_slots.numel()),
+                                            _dev(mixed), _dev(out), _stream()))
+        return out
+
     def prefill_core(self, q, k, v, g, beta, state: LinearAttnState, layer: int, slots, counts,
                      use_tensor_cores: bool = True) -> torch.Tensor:
         s, c = _host_i32(slots), _host_i32(counts)
@@ -420,6 +427,21 @@ class HybridStack:
                 _lib.b200attn_stack_destroy(self.h)
         except Exception:
             pass
+
+
+def profile_enable(on: bool) -> None:
+    _check(_lib.b200attn_profile_enable(C.c_int(1 if on else 0)))
+
+
+def profile_reset() -> None:
+    _check(_lib.b200attn_profile_reset())
+
+
+def profile_read(name: str) -> tuple[float, int]:
+    """(summed device milliseconds, launches) of one kernel class since the last reset."""
+    ms, n = C.c_double(0.0), C.c_longlong(0)
+    _check(_lib.b200attn_profile_read(name.encode(), C.byref(ms), C.byref(n)))
+    return ms.value, n.value
 
 
 def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, n: int, k: int) -> torch.Tensor:

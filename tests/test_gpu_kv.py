@@ -1,0 +1,116 @@
+"""GPU: paged KV cache — quantise-on-append is bit-exact against the oracle's quantiser on the same
+fp32 K/V rows (ragged batches, page-boundary crossings, repeated appends), FP16 storage is the IEEE
+round-to-nearest conversion, and the page bookkeeping behaves like the reference's allocator."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _kv_rows(oracle, synth, seed, tokens):
+    """fp32 K (normalised + rotated) and raw V rows as the reference computes them."""
+    w = synth.fa_weights(seed)
+    x = synth.hidden_states(seed, "kv.rows", tokens)
+    o = oracle.OracleFullAttention(w, tokens, kv_mode=0)
+    o.forward_sequence(x)
+    return o.k_cache[:tokens].copy(), o.v_cache[:tokens].copy()
+
+
+def test_int8_append_bit_exact_ragged(ops, cuda, oracle, synth):
+    torch = cuda
+    counts = [1, 63, 64, 65, 130, 7]
+    k, v = _kv_rows(oracle, synth, 21, max(counts) + 70)
+    kv = ops.KVCache(2, 8, 512, ops.KV_INT8)
+    slots = [kv.allocate_sequence(0) for _ in counts]
+    # first append: ragged batch, each sequence takes rows [0, c)
+    rows_k = np.concatenate([k[:c] for c in counts])
+    rows_v = np.concatenate([v[:c] for c in counts])
+    kv.append(1, slots, counts, torch.from_numpy(rows_k).cuda(), torch.from_numpy(rows_v).cuda())
+    # second append continues each sequence mid-page: rows [c, c + 70)
+    rows_k2 = np.concatenate([k[c:c + 70] for c in counts])
+    rows_v2 = np.concatenate([v[c:c + 70] for c in counts])
+    kv.append(1, slots, [70] * len(counts), torch.from_numpy(rows_k2).cuda(), torch.from_numpy(rows_v2).cuda())
+    assert kv.device_status() == 0
+    for s, c in zip(slots, counts):
+        n = c + 70
+        assert kv.length(1, s) == n and kv.length(0, s) == 0
+        kc, vc, ks, vs = [t.cpu().numpy() for t in kv.export(1, s)]
+        want_kc, want_ks = oracle.quantize_rows(k[:n].reshape(n, 2, 256))
+        want_vc, want_vs = oracle.quantize_rows(v[:n].reshape(n, 2, 256))
+        np.testing.assert_array_equal(kc, want_kc)
+        np.testing.assert_array_equal(vc, want_vc)
+        np.testing.assert_array_equal(ks.view(np.uint32), want_ks.view(np.uint32))   # scales bit for bit
+        np.testing.assert_array_equal(vs.view(np.uint32), want_vs.view(np.uint32))
+
+
+def test_int8_append_edge_rows(ops, cuda, oracle):
+    torch = cuda
+    rows = np.zeros((5, 512), np.float32)
+    rows[1, :] = 1e-7                       # absmax/127 below 1e-8 -> scale 1.0, codes 0
+    rows[2, 0], rows[2, 1], rows[2, 2] = 127.0, 0.5, -2.5     # ties: roundf goes away from zero
+    rows[3, :256] = np.linspace(-3, 3, 256)
+    rows[4, 256:] = -np.linspace(0, 9, 256)
+    kv = ops.KVCache(1, 2, 64, ops.KV_INT8)
+    s = kv.allocate_sequence(5)
+    kv.append(0, [s], [5], torch.from_numpy(rows).cuda(), torch.from_numpy(rows[::-1].copy()).cuda())
+    kc, vc, ks, vs = [t.cpu().numpy() for t in kv.export(0, s)]
+    wk, wks = oracle.quantize_rows(rows.reshape(5, 2, 256))
+    wv, wvs = oracle.quantize_rows(rows[::-1].reshape(5, 2, 256))
+    np.testing.assert_array_equal(kc, wk)
+    np.testing.assert_array_equal(ks, wks)
+    np.testing.assert_array_equal(vc, wv)
+    np.testing.assert_array_equal(vs, wvs)
+    assert kc[2, 0, 0] == 127 and kc[2, 0, 1] == 1 and kc[2, 0, 2] == -3
+
+
+def test_fp16_append_is_ieee_rounding(ops, cuda, oracle, synth):
+    torch = cuda
+    k, v = _kv_rows(oracle, synth, 22, 100)
+    kv = ops.KVCache(1, 2, 128, ops.KV_FP16)
+    s = kv.allocate_sequence(100)
+    kv.append(0, [s], [100], torch.from_numpy(k).cuda(), torch.from_numpy(v).cuda())
+    kc, vc, ks, vs = kv.export(0, s)
+    assert ks is None and vs is None
+    np.testing.assert_array_equal(kc.cpu().numpy().reshape(100, 512), k.astype(np.float16))
+    np.testing.assert_array_equal(vc.cpu().numpy().reshape(100, 512), v.astype(np.float16))
+
+
+def test_page_bookkeeping(ops, cuda):
+    kv = ops.KVCache(1, 4, 256, ops.KV_INT8, num_pages=6)
+    assert kv.pages() == (6, 0)
+    a = kv.allocate_sequence(65)           # 2 pages
+    b = kv.allocate_sequence(0)
+    assert kv.pages() == (6, 2)
+    kv.reserve(b, 256)                     # 4 pages -> pool full
+    assert kv.pages() == (6, 6)
+    c = kv.allocate_sequence(0)
+    with pytest.raises(ops.B200AttnError) as e:
+        kv.reserve(c, 1)                   # exhausted pool
+    assert e.value.status == ops.ERR_NOMEM
+    with pytest.raises(ops.B200AttnError):
+        kv.reserve(a, 257)                 # beyond the block-table width
+    kv.release_sequence(b)
+    assert kv.pages() == (6, 2)
+    kv.reserve(c, 64)
+    assert kv.pages() == (6, 3)
+    with pytest.raises(ops.InvalidArgument):
+        kv.release_sequence(b)             # already released
+    with pytest.raises(ops.InvalidArgument):
+        kv.length(0, 99)
+
+
+def test_append_rejects_bad_batches(ops, cuda):
+    torch = cuda
+    kv = ops.KVCache(1, 2, 64, ops.KV_INT8)
+    s = kv.allocate_sequence(8)
+    z = torch.zeros((4, 512), device="cuda")
+    with pytest.raises(ops.InvalidArgument):
+        kv.append(0, [s, s], [2, 2], z, z)            # same slot twice
+    with pytest.raises(ops.InvalidArgument):
+        kv.append(3, [s], [4], z, z)                  # layer out of range
+    with pytest.raises(ops.InvalidArgument):
+        kv.append(0, [1], [4], z, z)                  # slot never allocated
+    kv.append(0, [s], [0], z, z)                      # empty append is a no-op
+    assert kv.length(0, s) == 0
+    kv.clear()
+    assert kv.length(0, s) == 0

@@ -1,0 +1,162 @@
+"""GPU: Gated DeltaNet — whole-layer parity with the CPU reference semantics (sequence pass and
+recurrent decode, outputs and final state), the recurrence cores against each other, state
+import/export in the reference's layouts."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import allclose_report
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+ATOL, RTOL, STATE_REL = 2e-3, 1e-2, 1e-3
+
+
+def _rel(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / max(np.linalg.norm(b.astype(np.float64)), 1e-30))
+
+
+def test_layer_prefill1024_outputs_and_final_state(ops, cuda, oracle, synth):
+    """Workload: batch 1, 1024 tokens, zero initial state, fp32 projections; compare outputs and final state."""
+    torch = cuda
+    w = synth.la_weights(51)
+    x = synth.hidden_states(51, "cfg1.x", 1024)
+    ref = oracle.OracleLinearAttention(w)
+    want = ref.forward_sequence(x)
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=1024)
+    la.set_weights(w)
+    st = ops.LinearAttnState(1, 2)
+    got = la.forward_batch(torch.from_numpy(x).cuda(), st, 0, [1], [1024]).cpu().numpy()
+    ok, msg = allclose_report(got, want, ATOL, RTOL)
+    assert ok, msg
+    rec, conv = st.export_state(0, 1)
+    assert _rel(rec.cpu().numpy(), ref.recurrent) <= STATE_REL
+    np.testing.assert_allclose(conv.cpu().numpy(), ref.conv_state, rtol=1e-4, atol=1e-5)
+
+
+def test_layer_against_reference_fixture(ops, cuda, synth):
+    torch = cuda
+    g = np.load(os.path.join(GOLD, "la_ref_seed202_t24.npz"))
+    seed, T = int(g["seed"]), int(g["tokens"])
+    w = synth.la_weights(seed)
+    x = synth.hidden_states(seed, "golden.la.x", T)
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=64)
+    la.set_weights(w)
+    st = ops.LinearAttnState(1, 1)
+    xt = torch.from_numpy(x).cuda()
+    d_slots = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = [la.forward_batch(xt[:20].contiguous(), st, 0, [0], [20])]
+    for t in range(20, T):
+        got.append(la.forward(xt[t:t + 1].contiguous(), st, 0, d_slots))
+    got = torch.cat(got).cpu().numpy()
+    ok, msg = allclose_report(got, g["y"], ATOL, RTOL)
+    assert ok, msg
+    rec, conv = st.export_state(0, 0)
+    assert _rel(rec.cpu().numpy()[g["recurrent_heads"]], g["recurrent"]) <= STATE_REL
+    np.testing.assert_allclose(conv.cpu().numpy(), g["conv"], rtol=1e-4, atol=1e-5)
+
+
+def test_decode_from_seeded_state(ops, cuda, oracle, synth):
+    """Recurrent decode: 4 sequences, state ~ N(0, 0.05) and a warm conv cache imported in the
+    reference's layouts, 24 single-token steps; outputs every step, state at the end."""
+    torch = cuda
+    w = synth.la_weights(52)
+    n, steps = 4, 24
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=n, max_prefill_rows=64)
+    la.set_weights(w)
+    st = ops.LinearAttnState(2, n)
+    refs = []
+    for i in range(n):
+        r = oracle.OracleLinearAttention(w)
+        r.recurrent[:] = synth.normal(52, f"state.{i}", (16, 128, 128), 0.05)
+        r.conv_state[:] = synth.normal(52, f"conv.{i}", (6144, 3), 0.5)
+        st.import_state(1, i, torch.from_numpy(r.recurrent).cuda(), torch.from_numpy(r.conv_state).cuda())
+        refs.append(r)
+    # import/export round trip is exact
+    rec, conv = st.export_state(1, 2)
+    np.testing.assert_array_equal(rec.cpu().numpy(), refs[2].recurrent)
+    np.testing.assert_array_equal(conv.cpu().numpy(), refs[2].conv_state)
+    d_slots = torch.arange(n, dtype=torch.int32, device="cuda")
+    for t in range(steps):
+        x = synth.hidden_states(52, f"step.{t}", n)
+        got = la.forward(torch.from_numpy(x).cuda(), st, 1, d_slots).cpu().numpy()
+        want = np.stack([refs[i].forward(x[i]) for i in range(n)])
+        ok, msg = allclose_report(got, want, ATOL, RTOL)
+        assert ok, f"step {t}: {msg}"
+    for i in range(n):
+        rec, conv = st.export_state(1, i)
+        assert _rel(rec.cpu().numpy(), refs[i].recurrent) <= STATE_REL
+        np.testing.assert_allclose(conv.cpu().numpy(), refs[i].conv_state, rtol=1e-4, atol=1e-5)
+    rec0, _ = st.export_state(0, 0)          # the other layer was never touched
+    assert not rec0.any()
+
+
+def test_ragged_batch_and_continuation(ops, cuda, oracle, synth):
+    torch = cuda
+    w = synth.la_weights(53)
+    lens1, lens2 = [2, 70, 64], [1, 0, 67]
+    xs = [synth.hidden_states(53, f"rag.{i}", lens1[i] + lens2[i]) for i in range(3)]
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=4, max_prefill_rows=256)
+    la.set_weights(w)
+    st = ops.LinearAttnState(1, 4)
+    slots = [3, 0, 2]
+    y1 = la.forward_batch(torch.from_numpy(np.concatenate([xs[i][:lens1[i]] for i in range(3)])).cuda(), st, 0, slots, lens1).cpu().numpy()
+    y2 = la.forward_batch(torch.from_numpy(np.concatenate([xs[i][lens1[i]:] for i in range(3)])).cuda(), st, 0, slots, lens2).cpu().numpy()
+    o1 = o2 = 0
+    for i in range(3):
+        ref = oracle.OracleLinearAttention(w)
+        want = ref.forward_sequence(xs[i])
+        got = np.concatenate([y1[o1:o1 + lens1[i]], y2[o2:o2 + lens2[i]]])
+        o1 += lens1[i]; o2 += lens2[i]
+        ok, msg = allclose_report(got, want, ATOL, RTOL)
+        assert ok, f"sequence {i}: {msg}"
+        rec, conv = st.export_state(0, slots[i])
+        assert _rel(rec.cpu().numpy(), ref.recurrent) <= STATE_REL
+        np.testing.assert_allclose(conv.cpu().numpy(), ref.conv_state, rtol=1e-4, atol=1e-5)
+
+
+def test_recurrence_cores_agree_and_match_oracle(ops, cuda, oracle, synth):
+    """Core kernels on oracle-produced q, k, v, g, beta: the chunked tensor-core path and the
+    token-serial path against the reference recurrence (outputs before the gated norm, final state)."""
+    torch = cuda
+    w = synth.la_weights(54)
+    T = 200
+    x = synth.hidden_states(54, "core.x", T)
+    ref = oracle.OracleLinearAttention(w)
+    taps = []
+    for t in range(T):
+        d = {}
+        ref.forward(x[t], d)
+        taps.append(d)
+    q = np.stack([d["q"] for d in taps]).reshape(T, 16, 128)
+    k = np.stack([d["k"] for d in taps]).reshape(T, 16, 128)
+    v = np.stack([d["v"] for d in taps]).reshape(T, 16, 128)
+    g = np.stack([d["g"] for d in taps]); beta = np.stack([d["beta"] for d in taps])
+    core = np.stack([d["core"] for d in taps]).reshape(T, 16, 128)
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=256)
+    args = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in (q, k, v, g, beta)]
+    for use_tc in (False, True):
+        st = ops.LinearAttnState(1, 1)
+        out = la.prefill_core(*args, st, 0, [0], [T], use_tensor_cores=use_tc).cpu().numpy()
+        err = np.abs(out - core)
+        assert np.all(err <= 1e-4 + 2e-3 * np.abs(core)), f"tensor_cores={use_tc}: max abs err {err.max():.3e}"
+        rec, _ = st.export_state(0, 0)
+        assert _rel(rec.cpu().numpy(), ref.recurrent) <= STATE_REL, f"tensor_cores={use_tc}"
+
+
+def test_errors(ops, cuda, synth):
+    torch = cuda
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=64)
+    st = ops.LinearAttnState(1, 2)
+    x = torch.zeros((4, 1024), device="cuda")
+    with pytest.raises(ops.B200AttnError) as e:
+        la.forward_batch(x, st, 0, [0], [4])
+    assert e.value.status == ops.ERR_NOT_READY and "weights not set" in str(e.value)
+    la.set_weights(synth.la_weights(1))
+    with pytest.raises(ops.InvalidArgument):
+        la.forward_batch(x, st, 0, [5], [4])         # slot out of range
+    with pytest.raises(ops.InvalidArgument):
+        la.forward_batch(x, st, 2, [0], [4])         # layer out of range
+    with pytest.raises(ops.InvalidArgument):
+        st.export_state(0, 9)

@@ -1,0 +1,94 @@
+"""GPU: the hybrid stack (4 layers = 3 DeltaNet + 1 full attention, small FFN and vocabulary so the CPU
+checker finishes in seconds) — prefill hidden states and greedy tokens against the CPU composition,
+eager decode against the graph-captured decode step."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+L, INTER, VOCAB = 4, 256, 512
+
+
+def _build(ops, synth, weights, max_seqs=4, max_seq_len=128, kv_dtype=1):
+    st = ops.HybridStack(num_layers=L, intermediate_size=INTER, vocab_size=VOCAB, max_seqs=max_seqs,
+                         max_seq_len=max_seq_len, prefill_chunk_seqs=2, kv_dtype=kv_dtype, int8_weights=True)
+    for i, lw in enumerate(weights["layers"]):
+        st.set_layer_weights(i, lw, lw["ffn"], fa=lw.get("fa"), la=lw.get("la"))
+    st.set_embedding(weights["embed"], weights["final_norm"])
+    return st
+
+
+def test_prefill_and_decode_against_cpu_composition(ops, cuda, oracle, synth):
+    torch = cuda
+    from oracle import cpu_stack
+    weights = cpu_stack.make_stack_weights(synth, 61, L, INTER, VOCAB, int8=True)
+    qw = cpu_stack.quantized_view(weights)
+    n, T, D = 3, 40, 4
+    tokens = synth.rng(61, "tokens").integers(0, VOCAB, (n, T)).astype(np.int32)
+    st = _build(ops, synth, weights)
+    nxt, hid = st.forward_batch_prefill(torch.from_numpy(tokens).cuda(), want_hidden=True)
+    nxt, hid = nxt.cpu().numpy(), hid.cpu().numpy()
+    seqs = [cpu_stack.OracleStackSequence(qw, T + D + 1, kv_mode=2) for _ in range(n)]
+    for i in range(n):
+        for t in range(T):
+            hn, logits = seqs[i].forward_token(int(tokens[i, t]), want_logits=(t == T - 1))
+        cos = float(hn @ hid[i] / (np.linalg.norm(hn) * np.linalg.norm(hid[i])))
+        assert cos > 0.999, f"sequence {i}: cosine {cos:.5f}"
+        assert np.abs(hid[i] - hn).max() < 0.08, f"sequence {i}: max abs err {np.abs(hid[i] - hn).max():.3e}"
+        # greedy token: the GPU's pick must be (near-)maximal under the CPU logits
+        assert logits[nxt[i]] >= logits.max() - 0.05 * (logits.max() - logits.mean())
+    # decode steps fed with the GPU's own tokens on both sides
+    cur = torch.from_numpy(nxt).cuda()
+    for d in range(D):
+        fed = cur.cpu().numpy()
+        cur = st.forward_batch_decode(cur)
+        got = cur.cpu().numpy()
+        for i in range(n):
+            _, logits = seqs[i].forward_token(int(fed[i]))
+            assert logits[got[i]] >= logits.max() - 0.05 * (logits.max() - logits.mean()), f"step {d} seq {i}"
+
+
+def test_graph_replay_equals_eager_decode(ops, cuda, synth):
+    torch = cuda
+    from oracle import cpu_stack
+    weights = cpu_stack.make_stack_weights(synth, 62, L, INTER, VOCAB, int8=True)
+    n, T, D = 4, 70, 6
+    tokens = torch.from_numpy(synth.rng(62, "tokens").integers(0, VOCAB, (n, T)).astype(np.int32)).cuda()
+    st = _build(ops, synth, weights)
+    first = st.forward_batch_prefill(tokens)
+    cur, eager = first.clone(), []
+    for _ in range(D):
+        cur = st.forward_batch_decode(cur)
+        eager.append(cur.clone())
+    st.reset_cache()
+    again = st.forward_batch_prefill(tokens)
+    assert torch.equal(again, first)                  # reset + prefill is reproducible
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        st.set_tokens(again)
+        ops.launch_count(reset=True)
+        st.capture_decode(n)
+        assert ops.launch_count() == 0                # capture runs nothing
+        replayed = []
+        for _ in range(D):
+            st.launch_decode(1)
+            replayed.append(st.get_tokens(n))
+        side.synchronize()
+        assert ops.launch_count() > D * 20
+    for a, b in zip(eager, replayed):
+        assert torch.equal(a, b)
+
+
+def test_stack_errors(ops, cuda, synth):
+    torch = cuda
+    st = ops.HybridStack(num_layers=L, intermediate_size=INTER, vocab_size=VOCAB, max_seqs=2, max_seq_len=64,
+                         prefill_chunk_seqs=1)
+    toks = torch.zeros((1, 8), dtype=torch.int32, device="cuda")
+    with pytest.raises(ops.B200AttnError) as e:
+        st.forward_batch_prefill(toks)
+    assert e.value.status == ops.ERR_NOT_READY
+    with pytest.raises(ops.B200AttnError):
+        st.launch_decode(1)                            # nothing captured
+    with pytest.raises(ops.InvalidArgument):
+        st.set_layer_weights(99, dict(input_norm=np.zeros(1024), post_norm=np.zeros(1024)),
+                             dict(gate=np.zeros((INTER, 1024)), up=np.zeros((INTER, 1024)), down=np.zeros((1024, INTER))))
