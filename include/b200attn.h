@@ -362,9 +362,9 @@ int b200attn_profile_read(const char* name, double* total_ms_out, long long* lau
 /* ------------------------------------------------------------------------------------------------
  * Self-test of the tcgen05 / TMA building blocks: D[M,N] = A[M,K] * B^T on one CTA with the
  * operand formats the prefill kernels use.  variant: 0 = fp16 K-major A and B, 1 = fp16 K-major A,
- * MN-major B, 2 = tf32 K-major A and B, 3 = tf32 K-major A, MN-major B.  d_a fp32 [128, K],
- * d_b fp32 [N, K] (variants 0, 2) or [K, N] (variants 1, 3), d_d fp32 [128, N]; K a multiple of
- * 64 (fp16) or 32 (tf32), N in {64, 128, 256}.  No reference counterpart.
+ * MN-major B, 2 = tf32 K-major A and B (3, tf32 with an MN-major B, returns B200ATTN_ERR_UNSUPPORTED).
+ * d_a fp32 [128, K], d_b fp32 [N, K] (variants 0, 2) or [K, N] (variant 1), d_d fp32 [128, N]; K a
+ * multiple of 64 (fp16) or 32 (tf32), N in {64, 128, 256}.  No reference counterpart.
  * ---------------------------------------------------------------------------------------------- */
 int b200attn_selftest_umma(int variant, int n, int k, const float* d_a, const float* d_b, float* d_d,
                            b200attn_stream stream);

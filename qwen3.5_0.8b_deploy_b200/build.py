@@ -56,7 +56,29 @@ def build(force: bool = False, verbose: bool = False) -> str:
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise RuntimeError(f"link failed:\n{p.stderr[-4000:]}")
+    build_compat(force)
     return OUT
+
+
+def build_compat(force: bool = False) -> None:
+    """libb200attn_compat.so (the reference's operator classes on top of the C ABI) and the compat_check program."""
+    comp = os.path.join(HERE, "compat")
+    lib = os.path.join(HERE, "libb200attn_compat.so")
+    exe = os.path.join(comp, "compat_check")
+    srcs = [os.path.join(comp, f) for f in ("qwen_cuda_compat.cpp", "qwen_cuda_compat.hpp", "compat_check.cpp")]
+    newest = max(os.path.getmtime(f) for f in srcs + [OUT])
+    if not force and os.path.exists(lib) and os.path.exists(exe) and min(os.path.getmtime(lib), os.path.getmtime(exe)) > newest:
+        return
+    cxx = os.environ.get("CXX", "g++")
+    common = ["-std=c++17", "-O2", "-I/usr/local/cuda/include", "-L/usr/local/cuda/lib64", f"-L{HERE}"]
+    for cmd in (
+        [cxx, *common, "-fPIC", "-shared", "-o", lib, srcs[0], "-lb200attn", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"],
+        [cxx, *common, "-o", exe, srcs[2], "-lb200attn_compat", "-lb200attn", "-lcudart", "-Wl,-rpath,$ORIGIN/..",
+         "-Wl,-rpath,/usr/local/cuda/lib64"],
+    ):
+        p = subprocess.run(cmd, capture_output=True, text=True)
+        if p.returncode != 0:
+            raise RuntimeError(f"compat build failed: {' '.join(cmd)}\n{p.stderr[-4000:]}")
 
 
 if __name__ == "__main__":

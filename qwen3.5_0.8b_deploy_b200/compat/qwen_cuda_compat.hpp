@@ -1,0 +1,142 @@
+// Source-compatible stand-ins for the reference's attention operator classes, implemented on the b200attn C ABI.
+//
+// The class and member names, constructor defaults and method signatures are those of
+//   src/backend/cuda/include/full_attention_cuda.hpp:11-58   (CudaKVCache, CudaFullAttention)
+//   src/backend/cuda/include/linear_attention_cuda.hpp:11-51 (CudaLinearAttnState, CudaLinearAttention)
+//   src/backend/cuda/include/linear_attention_v2.cuh:10-33   (CudaLinearAttentionV2)
+//   src/backend/cuda/include/flash_attention.cuh:25-27       (flash_attention_decode)
+// so the reference's layer code (src/backend/cuda/kernels/cuda_engine.cu:109-156) and its stand-alone checks
+// (src/backend/cuda/verify_linear_attn_batch.cu, tests/integration/v2_kernel_accuracy_validate.cu) compile against
+// this header instead.  Differences a maintainer has to know are listed next to each member.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <stdexcept>
+#include <vector>
+
+#include "../../include/b200attn.h"
+
+namespace qwen {
+namespace cuda {
+
+// One sequence, `num_layers` layers, stored in the paged pool of the library.
+struct CudaKVCache {
+    // Kept for source compatibility. They point at the library's page arrays (K [page][head][64][256],
+    // V [page][head][256][64], scales [page][head][64]), not at the reference's contiguous [layer][seq][head][dim].
+    int8_t* d_k_cache = nullptr;
+    int8_t* d_v_cache = nullptr;
+    float* d_k_scale = nullptr;
+    float* d_v_scale = nullptr;
+    std::vector<int> layer_lengths;
+    int num_layers = 0;
+    int num_kv_heads = 0;
+    int head_dim = 0;
+    int max_seq_len = 0;
+    int capacity_seq_len = 0;
+
+    // init_capacity is rounded up to 8192 tokens (the reference's decode kernel attends to at most 8192 keys,
+    // full_attention_cuda.cu:181,380-382); pages are reserved on demand inside that bound.
+    void reset(int nl, int nkh, int hd, int init_capacity = 1024);
+    void clear();
+    int length(int layer_idx) const { return layer_lengths[layer_idx]; }
+    void ensure_capacity(int required_seq_len);   // throws std::runtime_error beyond max_seq_len
+
+    b200attn_kv_pool pool = nullptr;   // library handle (not in the reference)
+    int slot = -1;
+    int* d_slot = nullptr;             // device copy of `slot` for the decode entry point
+};
+
+class CudaFullAttention {
+  public:
+    CudaFullAttention(int hidden_size = 1024, int num_heads = 8, int num_kv_heads = 2, int q_head_dim = 256,
+                      int kv_head_dim = 256);
+    ~CudaFullAttention();
+    void set_weights(const std::vector<float>& q_proj_weight, const std::vector<float>& k_proj_weight,
+                     const std::vector<float>& v_proj_weight, const std::vector<float>& q_norm_weight,
+                     const std::vector<float>& k_norm_weight, const std::vector<float>& o_proj_weight);
+    // One token.  `position` must equal the layer's cache length (the reference's callers always pass that).
+    void forward(const float* input, float* output, CudaKVCache& kv_cache, int layer_idx, int position) const;
+    // batch_size consecutive tokens of the cache's sequence, causal.  `positions` (device) is not read: row i sits
+    // at cache length + i.  (The reference kernel applies no causal mask, fused_kernels.cu:126-264; this follows
+    // the CPU class, language_full_attn.cpp:227-252.)
+    void forward_batch_prefill(const float* input, float* output, CudaKVCache& kv_cache, int layer_idx,
+                               const int* positions, int batch_size, int max_seq = 0) const;
+    int hidden_size() const { return hidden_size_; }
+    int num_heads() const { return num_heads_; }
+
+  private:
+    int hidden_size_, num_heads_, num_kv_heads_, q_head_dim_, kv_head_dim_;
+    b200attn_fa op_ = nullptr;
+};
+
+struct CudaLinearAttnState {
+    // Reference-layout mirrors of the library's state ([heads][key_dim*value_dim] and [conv_dim][conv_kernel-1] with
+    // index 0 = newest).  They are imported before and exported after every forward call, so code that reads or
+    // writes them between calls (as tests/integration/v2_kernel_accuracy_validate.cu does) keeps working, and the
+    // caller may cudaFree them by hand as the reference's tests do.
+    float* d_recurrent_state = nullptr;
+    float* d_conv_state = nullptr;
+    int num_heads = 0;
+    int key_dim = 0;
+    int value_dim = 0;
+    int conv_dim = 0;
+    int conv_kernel = 0;
+    void reset(int nh, int kd, int vd, int conv_k = 4);
+    void clear();
+
+    b200attn_la_state state = nullptr;    // library handle (not in the reference)
+    int* d_slot = nullptr;
+};
+
+class CudaLinearAttention {
+  public:
+    CudaLinearAttention(int hidden_size = 1024, int num_heads = 16, int key_dim = 128, int value_dim = 128,
+                        int conv_kernel = 4);
+    ~CudaLinearAttention();
+    // Note the order: out_proj comes before a_log (linear_attention_cuda.hpp:31-39).  Empty a_log / dt_bias mean
+    // zeros, empty norm_weight means ones (linear_attention_cuda.cu:449-465).
+    void set_weights(const std::vector<float>& in_proj_qkv_weight, const std::vector<float>& in_proj_a_weight,
+                     const std::vector<float>& in_proj_b_weight, const std::vector<float>& in_proj_z_weight,
+                     const std::vector<float>& conv1d_weight, const std::vector<float>& out_proj_weight,
+                     const std::vector<float>& a_log = {}, const std::vector<float>& dt_bias = {},
+                     const std::vector<float>& norm_weight = {});
+    void forward(const float* input, float* output, CudaLinearAttnState& state) const;
+    // batch_size consecutive tokens of the state's sequence (a true causal pass: every token sees the conv
+    // history of the tokens before it, unlike linear_attention_cuda.cu:552-559).
+    void forward_batch(const float* input, float* output, CudaLinearAttnState& state, int batch_size) const;
+    void forward_fused(const float* input, float* output, CudaLinearAttnState& state) const;
+    int hidden_size() const { return hidden_size_; }
+    int num_heads() const { return num_heads_; }
+
+  protected:
+    int hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_;
+    b200attn_la op_ = nullptr;
+    int proj_precision_ = B200ATTN_PROJ_BF16;   // the reference rounds these weights to bf16 at load
+};
+
+// Same operator with fp32 weights and an explicit stream on forward_batch (linear_attention_v2.cuh:10-33).
+class CudaLinearAttentionV2 {
+  public:
+    CudaLinearAttentionV2(int hidden_size = 1024, int num_heads = 16, int key_dim = 128, int value_dim = 128,
+                          int conv_kernel = 4);
+    ~CudaLinearAttentionV2();
+    void set_weights(const std::vector<float>& in_proj_qkv_weight, const std::vector<float>& in_proj_a_weight,
+                     const std::vector<float>& in_proj_b_weight, const std::vector<float>& in_proj_z_weight,
+                     const std::vector<float>& conv1d_weight, const std::vector<float>& out_proj_weight,
+                     const std::vector<float>& a_log = {}, const std::vector<float>& dt_bias = {},
+                     const std::vector<float>& norm_weight = {});
+    void forward(const float* input, float* output, CudaLinearAttnState& state) const;
+    void forward_batch(const float* input, float* output, CudaLinearAttnState& state, int batch_size,
+                       cudaStream_t stream = 0) const;
+    int hidden_size() const { return hidden_size_; }
+    int num_heads() const { return num_heads_; }
+
+  private:
+    int hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_;
+    b200attn_la op_ = nullptr;
+};
+
+}  // namespace cuda
+}  // namespace qwen

@@ -199,7 +199,10 @@ struct b200attn_la_s {
     float* d_mixed = nullptr;              // [max_rows, 8224]
     float* d_q = nullptr;                  // [max_rows, 16, 128]
     float* d_k = nullptr;
+    __half* d_qh = nullptr;                // fp16 copies for the tensor-core recurrence
+    __half* d_kh = nullptr;
     float* d_v = nullptr;
+    int* d_error = nullptr;                // device status word of the tensor-core recurrence
     float* d_g = nullptr;                  // [max_rows, 16]
     float* d_beta = nullptr;
     float* d_core = nullptr;               // [max_rows, 16, 128]

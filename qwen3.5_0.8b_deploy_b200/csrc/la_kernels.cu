@@ -20,25 +20,18 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : logf(1.0f + expf(x)); }
-// Round an fp32 value to the nearest tf32 (10-bit mantissa), ties away: operands stored this way are
-// exact under the tensor core's truncating tf32 read.
-__device__ __forceinline__ float round_tf32(float x) {
-    uint32_t u;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-    return __uint_as_float(u);
-}
 
 // ---- C1, sequence form -------------------------------------------------------------------------------
 // One warp per (row, head): conv + SiLU over the head's q, k and v channels, L2 norm of q and k
-// (eps inside the sqrt), q * 1/sqrt(128), beta and log-decay g.  tf32_round != 0 stores q, k, v
-// rounded to tf32 for the tensor-core recurrence.
+// (eps inside the sqrt), q * 1/sqrt(128), beta and log-decay g.  q and k are written as fp32 (q_out, k_out)
+// and / or fp16 (qh_out, kh_out, the operand format of the tensor-core recurrence); null pointers are skipped.
 __global__ void __launch_bounds__(128)
 la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_seq,
                    const LaSeqMeta* __restrict__ seqs, const float* __restrict__ conv_state_layer,
                    size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
-                   const float* __restrict__ dt_bias, int rows, int tf32_round, float* __restrict__ q_out,
-                   float* __restrict__ k_out, float* __restrict__ v_out, float* __restrict__ g_out,
-                   float* __restrict__ beta_out) {
+                   const float* __restrict__ dt_bias, int rows, float* __restrict__ q_out,
+                   float* __restrict__ k_out, __half* __restrict__ qh_out, __half* __restrict__ kh_out,
+                   float* __restrict__ v_out, float* __restrict__ g_out, float* __restrict__ beta_out) {
     const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (gw >= rows * kLaHeads) return;
@@ -83,11 +76,16 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
         qp[i] = __fdiv_rn(res[0][i], qs) * q_scale;
         kp[i] = __fdiv_rn(res[1][i], ksq);
         vp[i] = res[2][i];
-        if (tf32_round) { qp[i] = round_tf32(qp[i]); kp[i] = round_tf32(kp[i]); vp[i] = round_tf32(vp[i]); }
     }
     const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
-    *reinterpret_cast<float4*>(q_out + o) = q4;
-    *reinterpret_cast<float4*>(k_out + o) = k4;
+    if (q_out) *reinterpret_cast<float4*>(q_out + o) = q4;
+    if (k_out) *reinterpret_cast<float4*>(k_out + o) = k4;
+    if (qh_out) {
+        __half2 a = __floats2half2_rn(q4.x, q4.y), b = __floats2half2_rn(q4.z, q4.w);
+        __half2 c = __floats2half2_rn(k4.x, k4.y), d = __floats2half2_rn(k4.z, k4.w);
+        *reinterpret_cast<uint2*>(qh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+        *reinterpret_cast<uint2*>(kh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+    }
     *reinterpret_cast<float4*>(v_out + o) = v4;
     if (lane == 0) {
         const float a = mixed[(size_t)row * kLaProjCols + kLaAOff + h];
@@ -326,10 +324,9 @@ __global__ void la_conv_export_kernel(const float* __restrict__ mine, float* __r
 // ---- launchers ------------------------------------------------------------------------------------------
 int launch_la_conv_seq(const float* mixed, const int* d_row_seq, const LaSeqMeta* d_seqs, const float* conv_layer,
                        size_t conv_stride, const float* conv_w, const float* a_log, const float* dt_bias, int rows,
-                       bool tf32_round, float* q, float* k, float* v, float* g, float* beta, cudaStream_t s) {
+                       float* q, float* k, __half* qh, __half* kh, float* v, float* g, float* beta, cudaStream_t s) {
     la_conv_seq_kernel<<<ceil_div(rows * kLaHeads, 4), 128, 0, s>>>(mixed, d_row_seq, d_seqs, conv_layer, conv_stride,
-                                                                  conv_w, a_log, dt_bias, rows, tf32_round ? 1 : 0,
-                                                                  q, k, v, g, beta);
+                                                                  conv_w, a_log, dt_bias, rows, q, k, qh, kh, v, g, beta);
     B2_LAUNCH_CHECK();
     return 0;
 }

@@ -13,10 +13,6 @@
 
 namespace b200 {
 
-int launch_la_chunk_tc(const float* q, const float* k, const float* v, const float* g, const float* beta,
-                       const LaSeqMeta* d_seqs, const LaSeqMeta* h_seqs, int n_seqs, int rows, float* rec_layer,
-                       size_t rec_stride, float* out, int* d_error, cudaStream_t s);
-
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 size_t la_scratch_bytes(const b200attn_la_config& c) {
@@ -24,11 +20,13 @@ size_t la_scratch_bytes(const b200attn_la_config& c) {
     size_t n = 0;
     n += align_up(R * kLaProjCols * 4, 256);            // mixed
     n += 3 * align_up(R * kLaHeads * kLaKd * 4, 256);   // q, k, v
+    n += 2 * align_up(R * kLaHeads * kLaKd * 2, 256);   // q, k as fp16
     n += 2 * align_up(R * kLaHeads * 4, 256);           // g, beta
     n += align_up(R * kLaHeads * kLaVd * 4, 256);       // core
     n += align_up(R * kHidden * 2, 256);                // xb
     n += align_up(R * kLaHeads * kLaVd * 4, 256);       // gated
     n += align_up((2 * R + 65536) * 4, 256);            // meta
+    n += 256;                                            // device status word
     return n;
 }
 
@@ -42,6 +40,8 @@ static void la_carve_scratch(b200attn_la la) {
     la->d_q = (float*)take(R * kLaHeads * kLaKd * 4);
     la->d_k = (float*)take(R * kLaHeads * kLaKd * 4);
     la->d_v = (float*)take(R * kLaHeads * kLaKd * 4);
+    la->d_qh = (__half*)take(R * kLaHeads * kLaKd * 2);
+    la->d_kh = (__half*)take(R * kLaHeads * kLaKd * 2);
     la->d_g = (float*)take(R * kLaHeads * 4);
     la->d_beta = (float*)take(R * kLaHeads * 4);
     la->d_core = (float*)take(R * kLaHeads * kLaVd * 4);
@@ -49,6 +49,7 @@ static void la_carve_scratch(b200attn_la la) {
     la->d_gated = take(R * kLaHeads * kLaVd * 4);
     la->meta_cap = (int)(2 * R + 65536);
     la->d_meta = (int*)take((size_t)la->meta_cap * 4);
+    la->d_error = (int*)take(256);
 }
 
 int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b200attn_la* out) {
@@ -250,15 +251,15 @@ static int la_build_meta(b200attn_la la, b200attn_la_state st, const int* h_slot
     return 0;
 }
 
+// Runs the delta-rule recurrence over the batch.  tensor_cores: q and k must already be in la->d_qh / d_kh.
 static int la_recurrence(b200attn_la la, b200attn_la_state st, int layer, const float* q, const float* k, const float* v,
-                         const float* g, const float* beta, const LaSeqMeta* d_seqs, const std::vector<LaSeqMeta>& h_seqs,
-                         int rows, float* out, bool tensor_cores, cudaStream_t s) {
+                         const float* g, const float* beta, const LaSeqMeta* d_seqs, int n_seqs, int rows, float* out,
+                         bool tensor_cores, cudaStream_t s) {
     float* rec_layer = st->d_recurrent + (size_t)layer * st->cfg.max_seqs * st->rec_stride_slot();
-    const int n_seqs = (int)h_seqs.size();
     ProfScope prof(PROF_LA_PREFILL, s);
     if (tensor_cores)
-        return launch_la_chunk_tc(q, k, v, g, beta, d_seqs, h_seqs.data(), n_seqs, rows, rec_layer, st->rec_stride_slot(), out,
-                                  la->d_meta + la->meta_cap - 1, s);
+        return launch_la_chunk_tc(la->d_qh, la->d_kh, v, g, beta, d_seqs, n_seqs, rows, rec_layer, st->rec_stride_slot(), out,
+                                  la->d_error, s);
     return launch_la_recurrent_serial(q, k, v, g, beta, d_seqs, n_seqs, rec_layer, st->rec_stride_slot(), out, s);
 }
 
@@ -306,8 +307,9 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
     const bool tc = la_use_tensor_cores();
     B2_TRY(project_in(rows));
     B2_TRY(launch_la_conv_seq(la->d_mixed, d_row_seq, d_seqs, conv_layer, st->conv_stride_slot(), la->d_conv_w, la->d_a_log,
-                              la->d_dt_bias, rows, tc, la->d_q, la->d_k, la->d_v, la->d_g, la->d_beta, s));
-    B2_TRY(la_recurrence(la, st, layer, la->d_q, la->d_k, la->d_v, la->d_g, la->d_beta, d_seqs, seqs, rows, la->d_core, tc, s));
+                              la->d_dt_bias, rows, tc ? nullptr : la->d_q, tc ? nullptr : la->d_k, tc ? la->d_qh : nullptr,
+                              tc ? la->d_kh : nullptr, la->d_v, la->d_g, la->d_beta, s));
+    B2_TRY(la_recurrence(la, st, layer, la->d_q, la->d_k, la->d_v, la->d_g, la->d_beta, d_seqs, n_seqs, rows, la->d_core, tc, s));
     B2_TRY(launch_la_conv_state_update(la->d_mixed, d_seqs, n_seqs, conv_layer, st->conv_stride_slot(), s));
     B2_TRY(launch_la_gated_norm(la->d_core, la->d_mixed, la->d_norm, rows, la->d_gated, bf16, s));
     return project_out(rows);
@@ -338,7 +340,19 @@ extern "C" int b200attn_la_prefill_core(b200attn_la la, b200attn_la_state st, in
     int* d_row_seq = nullptr;
     B2_TRY(la_build_meta(la, st, h_slots, h_counts, n_seqs, &rows, seqs, &d_seqs, &d_row_seq, false, s));
     if (rows == 0) return 0;
-    return la_recurrence(la, st, layer, d_q, d_k, d_v, d_g, d_beta, d_seqs, seqs, rows, d_out, use_tensor_cores != 0, s);
+    if (use_tensor_cores) {
+        B2_TRY(f32_to_f16(s, d_q, la->d_qh, (size_t)rows * kLaHeads * kLaKd));
+        B2_TRY(f32_to_f16(s, d_k, la->d_kh, (size_t)rows * kLaHeads * kLaKd));
+        B2_CUDA(cudaMemsetAsync(la->d_error, 0, 4, s));
+    }
+    B2_TRY(la_recurrence(la, st, layer, d_q, d_k, d_v, d_g, d_beta, d_seqs, n_seqs, rows, d_out, use_tensor_cores != 0, s));
+    if (use_tensor_cores) {
+        int err = 0;
+        B2_CUDA(cudaMemcpyAsync(&err, la->d_error, 4, cudaMemcpyDeviceToHost, s));
+        B2_CUDA(cudaStreamSynchronize(s));
+        if (err != 0) B2_FAIL(B200ATTN_ERR_DEVICE, "la_prefill_core: kernel reported device status %d (bounded wait ran out)", err);
+    }
+    return 0;
 }
 
 extern "C" int b200attn_la_decode_core(b200attn_la la, b200attn_la_state st, int layer, const int* d_slots, int n_seqs,

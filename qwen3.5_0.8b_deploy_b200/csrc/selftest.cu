@@ -96,6 +96,9 @@ using namespace b200;
 extern "C" int b200attn_selftest_umma(int variant, int n, int k, const float* d_a, const float* d_b, float* d_d,
                                       b200attn_stream stream) {
     B2_CHECK_ARG(variant >= 0 && variant < 4, "selftest_umma: variant must be 0..3");
+    // An MN-major tf32 operand needs the 32-byte-atom form of the 128-byte swizzle, which none of the kernels
+    // here use (their MN-major operands are fp16).
+    if (variant == 3) B2_FAIL(B200ATTN_ERR_UNSUPPORTED, "selftest_umma: tf32 with an MN-major operand is not built");
     B2_CHECK_ARG(d_a && d_b && d_d, "selftest_umma: null argument");
     const bool tf32 = (variant & 2) != 0, bmn = (variant & 1) != 0;
     const int kb = tf32 ? 32 : 64;

@@ -179,7 +179,7 @@ def test_prefill_core_full_length_tensor_core_vs_simt(ops, cuda, synth):
 def test_errors(ops, cuda, synth):
     torch = cuda
     fa = ops.FullAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=64)
-    kv = ops.KVCache(1, 2, 64, ops.KV_INT8)
+    kv = ops.KVCache(1, 2, 256, ops.KV_INT8)
     s = kv.allocate_sequence(8)
     x = torch.zeros((4, 1024), device="cuda")
     with pytest.raises(ops.B200AttnError) as e:       # weights not set -> the reference throws runtime_error

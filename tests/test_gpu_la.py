@@ -145,6 +145,36 @@ def test_recurrence_cores_agree_and_match_oracle(ops, cuda, oracle, synth):
         assert _rel(rec.cpu().numpy(), ref.recurrent) <= STATE_REL, f"tensor_cores={use_tc}"
 
 
+@pytest.mark.parametrize("counts", [[1], [63], [64], [65], [129, 1, 300]])
+def test_chunked_kernel_equals_serial_kernel_from_a_nonzero_state(ops, cuda, synth, counts):
+    """Tensor-core chunked recurrence against the token-serial fp32 kernel on random inputs (decays spanning
+    e^-10 .. 1 per step), starting from a random state, in two consecutive calls."""
+    torch = cuda
+    n = len(counts)
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=4, max_prefill_rows=1024)
+    outs, states = [], []
+    for use_tc in (False, True):
+        st = ops.LinearAttnState(1, 4)
+        for i in range(n):
+            st.import_state(0, i, torch.from_numpy(synth.normal(55, f"s0.{i}", (16, 128, 128), 0.05)).cuda(), None)
+        res = []
+        for call in range(2):
+            rows = sum(counts)
+            q = synth.normal(55, f"q.{call}.{rows}", (rows, 16, 128)); q /= np.linalg.norm(q, axis=-1, keepdims=True) * np.sqrt(128)
+            k = synth.normal(55, f"k.{call}.{rows}", (rows, 16, 128)); k /= np.linalg.norm(k, axis=-1, keepdims=True)
+            v = synth.normal(55, f"v.{call}.{rows}", (rows, 16, 128), 0.5)
+            g = -np.exp(synth.rng(55, f"g.{call}.{rows}").uniform(-6.0, 2.3, (rows, 16))).astype(np.float32)
+            beta = synth.rng(55, f"b.{call}.{rows}").uniform(0.0, 1.0, (rows, 16)).astype(np.float32)
+            args = [torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda() for a in (q, k, v, g, beta)]
+            res.append(la.prefill_core(*args, st, 0, list(range(n)), counts, use_tensor_cores=use_tc).cpu().numpy())
+        outs.append(np.concatenate(res))
+        states.append([st.export_state(0, i)[0].cpu().numpy() for i in range(n)])
+    err = np.abs(outs[0] - outs[1])
+    assert np.all(err <= 1e-4 + 2e-3 * np.abs(outs[0])), f"outputs: max abs err {err.max():.3e}"
+    for i in range(n):
+        assert _rel(states[1][i], states[0][i]) <= STATE_REL, f"state of sequence {i}: rel {_rel(states[1][i], states[0][i]):.3e}"
+
+
 def test_errors(ops, cuda, synth):
     torch = cuda
     la = ops.LinearAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=64)
