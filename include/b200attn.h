@@ -231,6 +231,10 @@ int b200attn_la_create(const b200attn_la_config* cfg, b200attn_la* out);
 int b200attn_la_destroy(b200attn_la la);
 /* CudaLinearAttention::set_weights (linear_attention_cuda.cu:412-466); host pointers. */
 int b200attn_la_set_weights(b200attn_la la, const b200attn_la_weights* h_w);
+/* Reads (and clears) the operator's device-side status word: 0 = clean, 6 = a bounded wait inside the
+ * chunked prefill kernel ran out (the affected sequences' outputs and states are then undefined).
+ * Synchronises the device.  No reference counterpart. */
+int b200attn_la_device_status(b200attn_la la, int* code_out);
 /* CudaLinearAttnState::reset (linear_attention_cuda.cu:266-282): allocate and zero. */
 int b200attn_la_state_create(const b200attn_la_state_config* cfg, b200attn_la_state* out);
 /* CudaLinearAttnState has no destructor (linear_attention_cuda.hpp:11-22); the reference's tests free

@@ -50,6 +50,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
 
     const int slot = slots[seq];
     if (slot < 0 || slot >= kv.max_seqs) return;
+    if (*reinterpret_cast<volatile int*>(kv.error) == 3) return;     // an earlier CTA gave up: do not queue more bounded waits
     const int L = kv.lens[layer * kv.max_seqs + slot] + len_add;
     const int n_pages = (L + kPageTokens - 1) / kPageTokens;
     const int pages_per_cta = pages_per_warp * Cfg::kWarps;

@@ -46,6 +46,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t bar0 = base + kOffBar;
     auto bar = [&](int i) { return bar0 + 8u * i; };
 
+    if (*reinterpret_cast<volatile int*>(error_word) != 0) return;   // an earlier CTA gave up: do not queue more bounded waits
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const PrefillTile tile = tiles[blockIdx.x];
     const int head = blockIdx.y, kvh = head >> 2;

@@ -70,6 +70,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
     const int n_chunks = (sq.count + kC - 1) / kC;
     if (n_chunks == 0) return;
+    if (*reinterpret_cast<volatile int*>(error_word) != 0) return;   // an earlier CTA gave up: do not queue more bounded waits
     float* Sg = rec_layer + (size_t)sq.slot * rec_stride_slot + (size_t)h * kLaKd * kLaVd;
 
     if (tid == 0) {

@@ -76,6 +76,10 @@ int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b20
         la->scratch.owned = true;
     }
     la_carve_scratch(la);
+    if (cudaMemset(la->d_error, 0, sizeof(int)) != cudaSuccess) {
+        b200attn_la_destroy(la);
+        B2_FAIL(B200ATTN_ERR_CUDA, "la_create: clearing the status word failed");
+    }
     int st = cublas_init();
     if (st != 0) { b200attn_la_destroy(la); return st; }
     *out = la;
@@ -127,6 +131,14 @@ extern "C" int b200attn_la_set_weights(b200attn_la la, const b200attn_la_weights
     B2_TRY(upload_f32(w->dt_bias, &la->d_dt_bias, kLaHeads));
     B2_TRY(upload_f32(w->norm, &la->d_norm, kLaVd));
     la->ready = true;
+    return 0;
+}
+
+extern "C" int b200attn_la_device_status(b200attn_la la, int* code_out) {
+    B2_CHECK_ARG(la && code_out, "la_device_status: null argument");
+    B2_CUDA(cudaDeviceSynchronize());
+    B2_CUDA(cudaMemcpy(code_out, la->d_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*code_out != 0) B2_CUDA(cudaMemset(la->d_error, 0, sizeof(int)));
     return 0;
 }
 

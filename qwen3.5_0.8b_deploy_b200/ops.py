@@ -29,7 +29,7 @@ ABI_SYMBOLS = [
     "b200attn_kv_export", "b200attn_kv_device_status",
     "b200attn_fa_create", "b200attn_fa_destroy", "b200attn_fa_set_weights", "b200attn_fa_prefill", "b200attn_fa_decode",
     "b200attn_fa_decode_core", "b200attn_fa_prefill_core",
-    "b200attn_la_create", "b200attn_la_destroy", "b200attn_la_set_weights", "b200attn_la_state_create",
+    "b200attn_la_create", "b200attn_la_destroy", "b200attn_la_set_weights", "b200attn_la_device_status", "b200attn_la_state_create",
     "b200attn_la_state_destroy", "b200attn_la_state_clear", "b200attn_la_state_import", "b200attn_la_state_export",
     "b200attn_la_prefill", "b200attn_la_decode", "b200attn_la_decode_core", "b200attn_la_prefill_core",
     "b200attn_profile_enable", "b200attn_profile_reset", "b200attn_profile_read",
@@ -334,6 +334,11 @@ class LinearAttention:
         _check(_lib.b200attn_la_decode(self.h, state.h, C.c_int(layer), _dev(d_slots), C.c_int(d_slots.numel()), _dev(x),
                                        _dev(y), _stream()))
         return y
+
+    def device_status(self) -> int:
+        code = C.c_int(0)
+        _check(_lib.b200attn_la_device_status(self.h, C.byref(code)))
+        return code.value
 
     def decode_core(self, mixed: torch.Tensor, state: LinearAttnState, layer: int, d_slots: torch.Tensor) -> torch.Tensor:
         out = torch.empty((mixed.shape[0], 2048), dtype=torch.float32, device="cuda")
