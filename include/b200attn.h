@@ -178,6 +178,16 @@ int b200attn_fa_decode(b200attn_fa fa, b200attn_kv_pool pool, int layer, const i
  * [n_seqs, heads, head_dim] = softmax(q K^T / sqrt(head_dim)) V, no gate. */
 int b200attn_fa_decode_core(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* d_slots,
                             int n_seqs, const float* d_q, float* d_out, b200attn_stream stream);
+/* The same decode attention core for callers that cannot allocate device memory: hosts that must stay off
+ * cudaMalloc / cudaFree once warm (both synchronise the device) or that run under a fixed device-memory
+ * budget.  It takes no operator handle; its scratch (fp16 q, split partials) is a fixed array built into
+ * the library (about 4.3 MB per GPU, held until exit), so it creates and frees nothing.  Limits: at most 32
+ * sequences per call and pools with at most 512 pages per sequence (B200ATTN_ERR_INVALID beyond).  All calls
+ * share that array: calls that overlap on the GPU race, serialise them.  The first call on each device looks
+ * up the array's address; make it outside stream capture.  This entry point has no counterpart in the
+ * reference. */
+int b200attn_fa_decode_core_static(b200attn_kv_pool pool, int layer, const int* d_slots, int n_seqs,
+                                   const float* d_q, float* d_out, b200attn_stream stream);
 /* launch_flash_attn_v2_prefill* (include/fused_kernels.cuh:37-82) with a causal mask: d_q fp32
  * [rows, heads, head_dim], d_k / d_v fp32 [rows, kv_heads, head_dim]; rows are h_counts[i]
  * consecutive tokens of n_seqs sequences, each starting at position 0; d_out fp32

@@ -28,7 +28,7 @@ ABI_SYMBOLS = [
     "b200attn_kv_seq_free", "b200attn_kv_clear", "b200attn_kv_seq_len", "b200attn_kv_pages", "b200attn_kv_append",
     "b200attn_kv_export", "b200attn_kv_device_status",
     "b200attn_fa_create", "b200attn_fa_destroy", "b200attn_fa_set_weights", "b200attn_fa_prefill", "b200attn_fa_decode",
-    "b200attn_fa_decode_core", "b200attn_fa_prefill_core",
+    "b200attn_fa_decode_core", "b200attn_fa_decode_core_static", "b200attn_fa_prefill_core",
     "b200attn_la_create", "b200attn_la_destroy", "b200attn_la_set_weights", "b200attn_la_device_status", "b200attn_la_state_create",
     "b200attn_la_state_destroy", "b200attn_la_state_clear", "b200attn_la_state_import", "b200attn_la_state_export",
     "b200attn_la_prefill", "b200attn_la_decode", "b200attn_la_decode_core", "b200attn_la_prefill_core",
@@ -432,6 +432,12 @@ class HybridStack:
                 _lib.b200attn_stack_destroy(self.h)
         except Exception:
             pass
+
+
+def fa_decode_core_static(q: torch.Tensor, kv: KVCache, layer: int, d_slots: torch.Tensor, out: torch.Tensor) -> None:
+    """Decode attention core through the allocation-free entry point; `out` is supplied by the caller."""
+    _check(_lib.b200attn_fa_decode_core_static(kv.h, C.c_int(layer), _dev(d_slots), C.c_int(d_slots.numel()), _dev(q),
+                                               _dev(out), _stream()))
 
 
 def profile_enable(on: bool) -> None:
