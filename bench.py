@@ -189,10 +189,15 @@ def workload_config(args) -> dict:
 # ------------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------------
+def prefill_chunk_seqs(args) -> int:
+    """Activation scratch sized so the whole batch's prompt goes through each layer in one pass."""
+    return -(-args.batch * args.prompt // (args.prompt + args.gen))
+
+
 def build_stack(ops, synth, args, seed=1234):
     from oracle import cpu_stack  # weight generator only (numpy); nothing from the checker is executed on the timed path
     st = ops.HybridStack(num_layers=NUM_LAYERS, intermediate_size=INTER, vocab_size=VOCAB, max_seqs=args.batch,
-                         max_seq_len=args.prompt + args.gen, prefill_chunk_seqs=max(1, 16384 // (args.prompt + args.gen)),
+                         max_seq_len=args.prompt + args.gen, prefill_chunk_seqs=prefill_chunk_seqs(args),
                          kv_dtype=ops.KV_FP16, int8_weights=True)
     for i in range(NUM_LAYERS):
         lw = dict(input_norm=np.zeros(1024, np.float32), post_norm=np.zeros(1024, np.float32))
@@ -330,7 +335,7 @@ def main():
     e2e_value = replica.job_throughput(tokens_all, ms_e2e)
 
     if rank == 0:
-        chunks = -(-B // max(1, (max(1, 16384 // (P + G)) * (P + G)) // P))
+        chunks = -(-B // max(1, (prefill_chunk_seqs(args) * (P + G)) // P))
         per = {k: (v[0] / max(v[1], 1)) for k, v in prof.items()}       # ms per launch
         # share of one whole job spent in each kernel class (launch counts of a full job x measured ms per launch)
         job_ms = dict(la_decode=per["la_decode"] * 18 * G, fa_decode=per["fa_decode"] * 6 * G,

@@ -32,9 +32,10 @@ constexpr uint32_t kOffVN = 98304;             // B of (d): V_new, [2 blocks (64
 constexpr uint32_t kOffVT = 114688;            // A of (u): (e^{b_C-b} V_new)^T, [128 vd rows][128 B = 64 tokens]
 constexpr uint32_t kOffMQ = 131072;            // A of (d): [128 rows][128 B]; rows 0-63 zero, rows 64-127 Mq
 constexpr uint32_t kOffAM = 147456;            // fp32 A matrix [64][64]
-constexpr uint32_t kOffUS = 163840;            // fp32 U [64][128]
-constexpr uint32_t kOffSC = 196608;            // scalars: b[64], beta[64], eb[64], ebc[64]
-constexpr uint32_t kOffBarG = 197632;
+constexpr uint32_t kOffUS = 163840;            // fp32 U [64][kUSStride] (row stride 129 floats: conflict-free column and row access)
+constexpr int kUSStride = 129;
+constexpr uint32_t kOffSC = 197632;            // scalars: b[64], beta[64], eb[64], ebc[64]   (US ends at 163840 + 64*129*4 = 196864)
+constexpr uint32_t kOffBarG = 198656;
 constexpr uint32_t kG1Smem = kOffBarG + 128 + 1024;
 enum { G_KQ_FULL = 0, G_A_DONE, G_B_READY, G_B_DONE, G_V_READY, G_D_DONE, G_KQ_FREE, G_BAR_COUNT };
 
@@ -261,21 +262,23 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
             named_sync_128();
-            // ---- forward substitution (I + A) x = rhs, two columns per thread, fp32 ----
+            // ---- forward substitution (I + A) x = rhs, two columns per thread, fp32; four partial sums per
+            //      column keep the FMA chains short ----
             {
                 const float4* AM4 = reinterpret_cast<const float4*>(AM);
 #pragma unroll
                 for (int i = 1; i < 64; ++i) {
-                    float au = xu[i], aw = xw[i];
+                    float u0 = 0.f, u1 = 0.f, u2 = 0.f, u3 = 0.f, w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
 #pragma unroll
                     for (int j4 = 0; j4 * 4 < i; ++j4) {
                         const float4 a = AM4[i * 16 + j4];     // entries with j >= i are exact zeros
-                        au -= a.x * xu[j4 * 4];     aw -= a.x * xw[j4 * 4];
-                        au -= a.y * xu[j4 * 4 + 1]; aw -= a.y * xw[j4 * 4 + 1];
-                        au -= a.z * xu[j4 * 4 + 2]; aw -= a.z * xw[j4 * 4 + 2];
-                        au -= a.w * xu[j4 * 4 + 3]; aw -= a.w * xw[j4 * 4 + 3];
+                        u0 += a.x * xu[j4 * 4];     w0 += a.x * xw[j4 * 4];
+                        u1 += a.y * xu[j4 * 4 + 1]; w1 += a.y * xw[j4 * 4 + 1];
+                        u2 += a.z * xu[j4 * 4 + 2]; w2 += a.z * xw[j4 * 4 + 2];
+                        u3 += a.w * xu[j4 * 4 + 3]; w3 += a.w * xw[j4 * 4 + 3];
                     }
-                    xu[i] = au; xw[i] = aw;
+                    xu[i] -= (u0 + u1) + (u2 + u3);
+                    xw[i] -= (w0 + w1) + (w2 + w3);
                 }
             }
             // ---- publish U (fp32, row-major), W and Q e^{b} (fp16, swizzled K-major A tile of (b)) ----
@@ -283,7 +286,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 unsigned char* wq_blk = sm + kOffWQ + (tid >> 6) * 16384;
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
-                    US[i * 128 + tid] = xu[i];
+                    US[i * kUSStride + tid] = xu[i];
                     const uint32_t sw = (((tcol >> 3) ^ (i & 7)) << 4) + (tcol & 7) * 2;      // (64 + i) & 7 == i & 7
                     *reinterpret_cast<uint16_t*>(wq_blk + i * 128 + sw) = f2h_bits(xw[i]);
                     const __half qh = *reinterpret_cast<const __half*>(kq_blk + (64 + i) * 128 + sw);
@@ -305,7 +308,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tmem_wait_ld();
                     float vn[32];
 #pragma unroll
-                    for (int c2 = 0; c2 < 32; ++c2) vn[c2] = US[r * 128 + ch * 32 + c2] - __uint_as_float(d2[c2]);
+                    for (int c2 = 0; c2 < 32; ++c2) vn[c2] = US[r * kUSStride + ch * 32 + c2] - __uint_as_float(d2[c2]);
                     unsigned char* vn_row = sm + kOffVN + (ch >> 1) * 8192 + r * 128;
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4) {
