@@ -280,6 +280,8 @@ def main():
         first = st.forward_batch_prefill(d_tokens)
         st.forward_batch_decode(first)
         stream.synchronize()
+        status = st.device_status()
+        assert status == 0, f"device status {status} after the first eager step: a kernel gave up on a bounded wait"
         st.set_tokens(first)
         st.capture_decode(B)
         for _ in range(args.warmup):
@@ -300,6 +302,8 @@ def main():
         launches = ops.launch_count(reset=True)
         clk = clocks.stop() if rank == 0 else {}
         ms_total = ev0.elapsed_time(ev1)
+        status = st.device_status()
+        assert status == 0, f"device status {status} after the timed region"
 
         # end-to-end arm (host buffers, copies inside the timed region)
         job_e2e()

@@ -334,6 +334,11 @@ int b200attn_stack_set_embedding(b200attn_stack st, const float* h_embed, const 
  * is not needed for throughput runs with random-init weights).  No reference counterpart. */
 int b200attn_stack_init_embedding_random(b200attn_stack st, uint64_t seed, float std_dev,
                                          const float* h_final_norm);
+/* Reads (and clears) the device-side status words of the stack (its KV pool, its DeltaNet operators and its own
+ * GEMM kernels): 0 = clean, otherwise the first non-zero code found (codes as in b200attn_kv_device_status /
+ * b200attn_la_device_status; 7 = a bounded wait inside a decode-step GEMM ran out).  Synchronises the device.
+ * No reference counterpart. */
+int b200attn_stack_device_status(b200attn_stack st, int* code_out);
 /* CudaEngine::reset_cache (cuda_engine.cu:514-519). */
 int b200attn_stack_reset(b200attn_stack st, b200attn_stream stream);
 /* CudaEngine::forward_batch_prefill (cuda_engine.cu:354-389) for n_seqs sequences of prompt_len

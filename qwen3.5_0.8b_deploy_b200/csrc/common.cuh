@@ -168,6 +168,7 @@ struct b200attn_fa_s {
     void* d_attn = nullptr;                // [max_rows, 2048] fp32 or bf16
     float* d_part_o = nullptr;             // split-KV partials
     float* d_part_ml = nullptr;
+    int* d_counters = nullptr;             // split arrival counters [max_batch][kv_heads], zero between launches
     int* d_meta = nullptr;                 // slots / cu_rows / row->seq for prefill
     int meta_cap = 0;
     int max_splits = 0;

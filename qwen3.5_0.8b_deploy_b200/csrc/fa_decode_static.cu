@@ -11,9 +11,10 @@
 //   * at most kStaticMaxSeqs sequences per call and a block table of at most kStaticMaxPages pages per sequence;
 //     larger requests are refused with B200ATTN_ERR_INVALID;
 //   * the array (about 4.3 MB) exists once per GPU that loads the library and stays until the process exits;
-//   * every call uses the same array and leaves its intermediate data there.  Nothing in it has to start at zero
-//     (each split's slot is written before the combine step reads it), but two calls that overlap on the GPU
-//     (different streams, or different host threads) overwrite each other's partials: serialise them;
+//   * every call uses the same array and leaves its intermediate data there.  Only the split arrival counters
+//     have to start at zero; the entry point clears them (cudaMemsetAsync on the caller's stream) before each
+//     launch.  Two calls that overlap on the GPU (different streams, or different host threads) overwrite each
+//     other's partials and counters: serialise them;
 //   * the device address of the array is looked up with cudaGetSymbolAddress on the first call made on each
 //     device.  Make that first call outside any stream capture.
 #include "kernels.cuh"
@@ -29,7 +30,8 @@ constexpr int kStaticMaxPages = 512;     // block-table width the split heuristi
 constexpr size_t kStaticQBytes = (size_t)kStaticMaxSeqs * kFaHeads * kHeadDim * sizeof(__half);                         // 128 KB
 constexpr size_t kStaticPartOBytes = (size_t)kStaticMaxSeqs * kFaKvHeads * kStaticMaxSplits * 4 * kHeadDim * sizeof(float);  // 4 MB
 constexpr size_t kStaticPartMlBytes = (size_t)kStaticMaxSeqs * kFaKvHeads * kStaticMaxSplits * 4 * 2 * sizeof(float);        // 32 KB
-constexpr size_t kStaticBytes = kStaticQBytes + kStaticPartOBytes + kStaticPartMlBytes;
+constexpr size_t kStaticCounterBytes = (size_t)kStaticMaxSeqs * kFaKvHeads * sizeof(int);                                     // 256 B
+constexpr size_t kStaticBytes = kStaticQBytes + kStaticPartOBytes + kStaticPartMlBytes + kStaticCounterBytes;
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to hand to a kernel.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
@@ -77,7 +79,9 @@ extern "C" int b200attn_fa_decode_core_static(b200attn_kv_pool pool, int layer, 
     __half* q16 = reinterpret_cast<__half*>(base);
     float* part_o = reinterpret_cast<float*>(base + kStaticQBytes);
     float* part_ml = reinterpret_cast<float*>(base + kStaticQBytes + kStaticPartOBytes);
+    int* counters = reinterpret_cast<int*>(base + kStaticQBytes + kStaticPartOBytes + kStaticPartMlBytes);
     cudaStream_t s = as_stream(stream);
+    B2_CUDA(cudaMemsetAsync(counters, 0, kStaticCounterBytes, s));
     B2_TRY(f32_to_f16(s, d_q, q16, (size_t)n_seqs * kFaHeads * kHeadDim));
-    return launch_fa_decode(kv, layer, d_slots, n_seqs, 0, q16, nullptr, ppw, splits, part_o, part_ml, d_out, false, s);
+    return launch_fa_decode(kv, layer, d_slots, n_seqs, 0, q16, nullptr, ppw, splits, part_o, part_ml, counters, d_out, false, s);
 }

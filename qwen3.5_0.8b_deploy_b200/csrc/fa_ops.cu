@@ -28,6 +28,7 @@ size_t fa_scratch_bytes(const b200attn_fa_config& c) {
     n += align_up(B * kFaKvHeads * kMaxSplitsCap * 4 * kHeadDim * 4, 256);   // part_o
     n += align_up(B * kFaKvHeads * kMaxSplitsCap * 4 * 2 * 4, 256);          // part_ml
     n += align_up((4 * R + 65536) * 4, 256);                // meta
+    n += align_up(B * kFaKvHeads * 4, 256);                 // split arrival counters
     return n;
 }
 
@@ -49,6 +50,7 @@ void fa_carve_scratch(b200attn_fa fa) {
     fa->d_part_ml = (float*)take(B * kFaKvHeads * kMaxSplitsCap * 4 * 2 * 4);
     fa->meta_cap = (int)(4 * R + 65536);
     fa->d_meta = (int*)take((size_t)fa->meta_cap * 4);
+    fa->d_counters = (int*)take(B * kFaKvHeads * 4);
     fa->max_splits = kMaxSplitsCap;
 }
 
@@ -77,6 +79,10 @@ int fa_create_internal(const b200attn_fa_config* cfg, const Scratch* shared, b20
         fa->scratch.owned = true;
     }
     fa_carve_scratch(fa);
+    if (cudaMemset(fa->d_counters, 0, (size_t)cfg->max_batch * kFaKvHeads * 4) != cudaSuccess) {
+        b200attn_fa_destroy(fa);
+        B2_FAIL(B200ATTN_ERR_CUDA, "fa_create: clearing the split counters failed");
+    }
     // inv_freq[i] = 1 / theta^(2i / rotary_dim), evaluated in fp32 exactly as the reference does
     // (language_full_attn.cpp:93-95).
     std::vector<float> inv(kRotaryDim / 2);
@@ -143,20 +149,31 @@ static int fa_check(b200attn_fa fa, b200attn_kv_pool pool, int layer) {
     return 0;
 }
 
-static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_bf16, int rows, cudaStream_t s) {
+static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_bf16, int rows, bool decode, int* d_error, cudaStream_t s) {
     if (fa->cfg.proj_precision == B200ATTN_PROJ_BF16) {
         const void* xb = d_x;
         if (!x_is_bf16) {
             B2_TRY(f32_to_bf16(s, (const float*)d_x, fa->d_xb, (size_t)rows * kHidden));
             xb = fa->d_xb;
         }
+        if (decode && rows <= 128 && gemm_tc_enabled())   // weight-streaming tcgen05 GEMM
+            return gemm_tc_store(s, (const __nv_bfloat16*)xb, fa->d_wqkv_bf16, fa->d_qkv_raw, rows, kFaQkvCols, kHidden, kFaQkvCols, 1, 0, d_error);
         return gemm_xwT(s, xb, true, fa->d_wqkv_bf16, true, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden);
     }
     if (x_is_bf16) B2_FAIL(B200ATTN_ERR_INVALID, "full attention: bf16 activations need the bf16 projection mode");
     return gemm_xwT(s, d_x, false, fa->d_wqkv_f32, false, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden);
 }
 
-static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, cudaStream_t s) {
+static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, bool decode, DecodeOut* dout, int* d_error, cudaStream_t s) {
+    if (fa->cfg.proj_precision == B200ATTN_PROJ_BF16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || beta == 0.f)) {
+        const int K = kFaHeads * kHeadDim;
+        if (dout) {
+            dout->n_splits = gemm_tc_splits(kHidden, K, 64);
+            return gemm_tc_store(s, (const __nv_bfloat16*)fa->d_attn, fa->d_wo_bf16, dout->partials, rows, kHidden, K, kHidden,
+                                 dout->n_splits, dout->stride, d_error);
+        }
+        return gemm_tc_store(s, (const __nv_bfloat16*)fa->d_attn, fa->d_wo_bf16, d_y, rows, kHidden, K, kHidden, 1, 0, d_error);
+    }
     if (fa->cfg.proj_precision == B200ATTN_PROJ_BF16)
         return gemm_xwT(s, fa->d_attn, true, fa->d_wo_bf16, true, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
     return gemm_xwT(s, fa->d_attn, false, fa->d_wo_f32, false, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
@@ -175,7 +192,7 @@ static int decode_pages_per_warp(const b200attn_kv_pool pool) {
 // on the device, no host synchronisation or allocation (capture-safe).  d_y = beta * d_y + attn W_o^T.
 int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
                     int n_seqs, const int* d_slots_in, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
-                    float y_beta, cudaStream_t s) {
+                    float y_beta, DecodeOut* dout, cudaStream_t s) {
     B2_CHECK_ARG(pool && d_x && d_y, "full attention: null argument");
     B2_TRY(fa_check(fa, pool, layer));
     const KvView kv = pool->view();
@@ -187,7 +204,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= fa->cfg.max_batch, "fa_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, fa->cfg.max_batch);
         const int ppw = decode_pages_per_warp(pool);
         const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
-        B2_TRY(fa_project_in(fa, d_x, x_is_bf16, n_seqs, s));
+        B2_TRY(fa_project_in(fa, d_x, x_is_bf16, n_seqs, true, pool->d_error, s));
         B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, n_seqs, fa->d_qnorm, fa->d_inv_freq, nullptr, d_slots_in,
                                     pool->d_lens + (size_t)layer * pool->cfg.max_seqs, kv.max_seqs, fa->d_q, fa->d_gate, s));
         B2_TRY(launch_kv_append(kv, layer, nullptr, n_seqs, d_slots_in, k_in, kFaQkvCols, v_in, kFaQkvCols, true, fa->d_knorm,
@@ -195,10 +212,10 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
         {
             ProfScope prof(PROF_FA_DECODE, s);
             B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, 1, fa->d_q, fa->d_gate, ppw, splits, fa->d_part_o,
-                                    fa->d_part_ml, fa->d_attn, bf16, s));
+                                    fa->d_part_ml, fa->d_counters, fa->d_attn, bf16, s));
         }
         B2_TRY(launch_kv_advance(kv, layer, d_slots_in, nullptr, n_seqs, s));
-        B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, s));
+        B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
         pool->lens_dirty = true;
         return 0;
     }
@@ -235,7 +252,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
     B2_CUDA(cudaMemcpyAsync(d_atiles, atiles.data(), atiles.size() * sizeof(AppendTile), cudaMemcpyHostToDevice, s));
     B2_CUDA(cudaMemcpyAsync(d_ptiles, ptiles.data(), ptiles.size() * sizeof(PrefillTile), cudaMemcpyHostToDevice, s));
 
-    B2_TRY(fa_project_in(fa, d_x, x_is_bf16, rows, s));
+    B2_TRY(fa_project_in(fa, d_x, x_is_bf16, rows, false, pool->d_error, s));
     B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, rows, fa->d_qnorm, fa->d_inv_freq, d_row_pos, nullptr, nullptr, kv.max_seqs,
                                 fa->d_q, fa->d_gate, s));
     for (int i = 0; i < n_seqs; ++i)
@@ -251,7 +268,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
                                     fa->d_gate, fa->d_attn, bf16, pool->d_error, s));
     }
     B2_TRY(launch_kv_advance(kv, layer, d_slots, d_counts, n_seqs, s));
-    B2_TRY(fa_project_out(fa, d_y, y_beta, rows, s));
+    B2_TRY(fa_project_out(fa, d_y, y_beta, rows, false, nullptr, pool->d_error, s));
     for (int i = 0; i < n_seqs; ++i) pool->h_lens[(size_t)layer * pool->cfg.max_seqs + h_slots[i]] += h_counts[i];
     return 0;
 }
@@ -260,12 +277,12 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
 
 extern "C" int b200attn_fa_prefill(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots,
                                    const int* h_counts, int n_seqs, const float* d_x, float* d_y, b200attn_stream stream) {
-    return fa_forward_rows(fa, pool, layer, h_slots, h_counts, n_seqs, nullptr, false, d_x, false, d_y, 0.f, as_stream(stream));
+    return fa_forward_rows(fa, pool, layer, h_slots, h_counts, n_seqs, nullptr, false, d_x, false, d_y, 0.f, nullptr, as_stream(stream));
 }
 
 extern "C" int b200attn_fa_decode(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* d_slots, int n_seqs,
                                   const float* d_x, float* d_y, b200attn_stream stream) {
-    return fa_forward_rows(fa, pool, layer, nullptr, nullptr, n_seqs, d_slots, true, d_x, false, d_y, 0.f, as_stream(stream));
+    return fa_forward_rows(fa, pool, layer, nullptr, nullptr, n_seqs, d_slots, true, d_x, false, d_y, 0.f, nullptr, as_stream(stream));
 }
 
 extern "C" int b200attn_fa_decode_core(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* d_slots, int n_seqs,
@@ -279,8 +296,8 @@ extern "C" int b200attn_fa_decode_core(b200attn_fa fa, b200attn_kv_pool pool, in
     const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
     B2_TRY(f32_to_f16(s, d_q, fa->d_q, (size_t)n_seqs * kFaHeads * kHeadDim));
     ProfScope prof(PROF_FA_DECODE, s);
-    return launch_fa_decode(kv, layer, d_slots, n_seqs, 0, fa->d_q, nullptr, ppw, splits, fa->d_part_o, fa->d_part_ml, d_out,
-                            false, s);
+    return launch_fa_decode(kv, layer, d_slots, n_seqs, 0, fa->d_q, nullptr, ppw, splits, fa->d_part_o, fa->d_part_ml, fa->d_counters,
+                            d_out, false, s);
 }
 
 extern "C" int b200attn_fa_prefill_core(b200attn_fa fa, const int* h_counts, int n_seqs, const float* d_q,

@@ -234,9 +234,21 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                             }
                         }
                     }
-                    OutT* dst = out + orow + ch * 32;
+                    OutT* dst = out + orow + ch * 32;          // 32 consecutive outputs of this row: 16-byte stores
+                    if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) dst[c] = (OutT)vals[c];
+                        for (int q4 = 0; q4 < 8; ++q4)
+                            *reinterpret_cast<float4*>(dst + 4 * q4) =
+                                make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
+                    } else {
+#pragma unroll
+                        for (int q8 = 0; q8 < 4; ++q8) {
+                            __nv_bfloat162 h[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
+                            *reinterpret_cast<uint4*>(dst + 8 * q8) = *reinterpret_cast<uint4*>(h);
+                        }
+                    }
                 }
             }
         }

@@ -32,8 +32,8 @@ int ensure_meta(int** d_meta, int* cap, int need);
 // ---- decode attention (fa_decode.cu) -----------------------------------------------------------------------
 int fa_decode_max_splits(bool fp16, int max_pages_per_seq, int pages_per_warp);
 int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, int len_add, const __half* q,
-                     const __half* gate, int pages_per_warp, int max_splits, float* part_o, float* part_ml, void* out,
-                     bool out_bf16, cudaStream_t s);
+                     const __half* gate, int pages_per_warp, int max_splits, float* part_o, float* part_ml, int* counters,
+                     void* out, bool out_bf16, cudaStream_t s);
 
 // ---- prefill attention (fa_prefill.cu) -----------------------------------------------------------------------
 struct PrefillTile {
@@ -76,6 +76,24 @@ int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max
 int launch_la_conv_import(const float* ref_conv, float* mine, cudaStream_t s);
 int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
 
+// ---- tcgen05 skinny GEMMs for the decode step (gemm_tc.cu) ---------------------------------------------------------
+int gemm_tc_splits(int N, int K, int bn);
+bool gemm_tc_enabled();
+int gemm_tc_store(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, float* Y, int M, int N, int K, int ld_out,
+                  int splits, size_t split_stride, int* d_error);
+int gemm_tc_swiglu(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, __nv_bfloat16* act, int M, int N, int K,
+                   int* d_error);
+int gemm_tc_argmax(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, unsigned long long* d_packed, int* tokens,
+                   int M, int N, int K, int* d_error);
+void gemm_tc_forget(const void* ptr);
+// Where a decode-step output projection leaves its result when the caller sums split-K partials itself (the stack's
+// next RMSNorm does): `n_splits` matrices [rows, hidden], `stride` floats apart.  n_splits is set by the operator.
+struct DecodeOut {
+    float* partials;
+    size_t stride;
+    int n_splits;
+};
+
 // ---- operator internals shared with the stack ------------------------------------------------------------------------
 size_t fa_scratch_bytes(const b200attn_fa_config& c);
 int fa_create_internal(const b200attn_fa_config* cfg, const Scratch* shared, b200attn_fa* out);
@@ -84,9 +102,9 @@ int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b20
 // Operator bodies that take activations in the stack's own formats (see stack.cu).
 int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
                     int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
-                    float y_beta, cudaStream_t s);
+                    float y_beta, DecodeOut* dout, cudaStream_t s);
 int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots, const int* h_counts,
                     int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
-                    float y_beta, cudaStream_t s);
+                    float y_beta, DecodeOut* dout, cudaStream_t s);
 
 }  // namespace b200

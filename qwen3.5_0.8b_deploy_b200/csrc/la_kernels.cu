@@ -10,6 +10,8 @@
 // + w[d][2] * x_{t-3} (language_linear_attn.cpp:145-152).
 #include "kernels.cuh"
 
+#include <cstdlib>
+
 namespace b200 {
 
 __device__ __forceinline__ float warp_sum_f(float v) {
@@ -197,8 +199,8 @@ la_gated_norm_kernel(const float* __restrict__ core, const float* __restrict__ m
 // L2 norms, gates, then ONE pass over the 128x128 fp32 state: thread (warp r, lane c) keeps rows
 // 16r..16r+15 of columns 4c..4c+3 in registers between the read (kv = S^T k) and the write
 // (S' = g S + k (x) delta, o = S'^T q), followed by the gated RMSNorm.
-template <typename OutT>
-__global__ void __launch_bounds__(256)
+template <typename OutT, int kMinBlocks>
+__global__ void __launch_bounds__(256, kMinBlocks)
 la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots, int max_seqs,
                  float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
                  size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
@@ -359,13 +361,16 @@ int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max
                      size_t rec_stride, float* conv_layer, size_t conv_stride, const float* conv_w, const float* a_log,
                      const float* dt_bias, const float* norm_w, void* out, bool out_bf16, cudaStream_t s) {
     dim3 grid(kLaHeads, n_seqs);
-    if (out_bf16)
-        la_decode_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(mixed, d_slots, max_seqs, rec_layer, rec_stride, conv_layer,
-                                                            conv_stride, conv_w, a_log, dt_bias, norm_w,
-                                                            (__nv_bfloat16*)out);
-    else
-        la_decode_kernel<float><<<grid, 256, 0, s>>>(mixed, d_slots, max_seqs, rec_layer, rec_stride, conv_layer,
-                                                    conv_stride, conv_w, a_log, dt_bias, norm_w, (float*)out);
+    static int occ = 0;      // resident CTAs per SM the kernel is compiled for: 2 (123 registers) or 3 (80 registers)
+    if (occ == 0) {
+        const char* e = std::getenv("B200ATTN_LA_DECODE_OCC");
+        occ = (e && e[0] == '2') ? 2 : 3;
+    }
+#define LA_DEC(T, O) la_decode_kernel<T, O><<<grid, 256, 0, s>>>(mixed, d_slots, max_seqs, rec_layer, rec_stride, conv_layer, \
+                                                               conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out)
+    if (out_bf16) { if (occ == 2) LA_DEC(__nv_bfloat16, 2); else LA_DEC(__nv_bfloat16, 3); }
+    else          { if (occ == 2) LA_DEC(float, 2); else LA_DEC(float, 3); }
+#undef LA_DEC
     B2_LAUNCH_CHECK();
     return 0;
 }

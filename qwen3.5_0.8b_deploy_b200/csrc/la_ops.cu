@@ -277,7 +277,7 @@ static int la_recurrence(b200attn_la la, b200attn_la_state st, int layer, const 
 
 int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots, const int* h_counts, int n_seqs,
                     const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y, float y_beta,
-                    cudaStream_t s) {
+                    DecodeOut* dout, cudaStream_t s) {
     B2_CHECK_ARG(la && st && d_x && d_y, "linear attention: null argument");
     if (!la->ready) B2_FAIL(B200ATTN_ERR_NOT_READY, "LinearAttention weights not set");
     B2_CHECK_ARG(layer >= 0 && layer < st->cfg.num_layers, "linear attention: layer %d out of range", layer);
@@ -289,11 +289,22 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
         if (bf16) {
             const void* xb = d_x;
             if (!x_is_bf16) { B2_TRY(f32_to_bf16(s, (const float*)d_x, la->d_xb, (size_t)rows * kHidden)); xb = la->d_xb; }
+            if (decode && rows <= 128 && gemm_tc_enabled())   // weight-streaming tcgen05 GEMM
+                return gemm_tc_store(s, (const __nv_bfloat16*)xb, la->d_win_bf16, la->d_mixed, rows, kLaProjCols, kHidden, kLaProjCols, 1, 0, la->d_error);
             return gemm_xwT(s, xb, true, la->d_win_bf16, true, la->d_mixed, false, rows, kLaProjCols, kHidden);
         }
         return gemm_xwT(s, d_x, false, la->d_win_f32, false, la->d_mixed, false, rows, kLaProjCols, kHidden);
     };
     auto project_out = [&](int rows) -> int {
+        if (bf16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || y_beta == 0.f)) {
+            const int K = kLaHeads * kLaVd;
+            if (dout) {
+                dout->n_splits = gemm_tc_splits(kHidden, K, 64);
+                return gemm_tc_store(s, (const __nv_bfloat16*)la->d_gated, la->d_wout_bf16, dout->partials, rows, kHidden, K, kHidden,
+                                     dout->n_splits, dout->stride, la->d_error);
+            }
+            return gemm_tc_store(s, (const __nv_bfloat16*)la->d_gated, la->d_wout_bf16, d_y, rows, kHidden, K, kHidden, 1, 0, la->d_error);
+        }
         if (bf16) return gemm_xwT(s, la->d_gated, true, la->d_wout_bf16, true, d_y, false, rows, kHidden, kLaHeads * kLaVd, y_beta);
         return gemm_xwT(s, la->d_gated, false, la->d_wout_f32, false, d_y, false, rows, kHidden, kLaHeads * kLaVd, y_beta);
     };
@@ -331,12 +342,12 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
 
 extern "C" int b200attn_la_prefill(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots, const int* h_counts,
                                    int n_seqs, const float* d_x, float* d_y, b200attn_stream stream) {
-    return la_forward_rows(la, st, layer, h_slots, h_counts, n_seqs, nullptr, false, d_x, false, d_y, 0.f, as_stream(stream));
+    return la_forward_rows(la, st, layer, h_slots, h_counts, n_seqs, nullptr, false, d_x, false, d_y, 0.f, nullptr, as_stream(stream));
 }
 
 extern "C" int b200attn_la_decode(b200attn_la la, b200attn_la_state st, int layer, const int* d_slots, int n_seqs,
                                   const float* d_x, float* d_y, b200attn_stream stream) {
-    return la_forward_rows(la, st, layer, nullptr, nullptr, n_seqs, d_slots, true, d_x, false, d_y, 0.f, as_stream(stream));
+    return la_forward_rows(la, st, layer, nullptr, nullptr, n_seqs, d_slots, true, d_x, false, d_y, 0.f, nullptr, as_stream(stream));
 }
 
 extern "C" int b200attn_la_prefill_core(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots,

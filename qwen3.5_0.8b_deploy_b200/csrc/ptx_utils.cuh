@@ -41,10 +41,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// Non-blocking probe (try_wait may park the thread for a while when the phase is not complete; a producer that
+// polls several barriers must not).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after `limit_ns` or as soon as another thread of the CTA raised *abort_flag.
 // Returns false on give-up (and raises the flag), so every role can fall through to the common exit.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint64_t limit_ns = 2000000000ull) {
+                                          uint64_t limit_ns = 500000000ull) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     uint32_t it = 0;

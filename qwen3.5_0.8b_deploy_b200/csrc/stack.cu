@@ -38,6 +38,9 @@ struct b200attn_stack_s {
     float* d_logits = nullptr;         // [max_seqs, vocab]
     int* d_tokens = nullptr;           // [max_seqs] decode token buffer (in place)
     int* d_slots = nullptr;            // [max_seqs] identity slots
+    float* d_partials = nullptr;       // [kMaxSplits][128][hidden] split-K partials of the decode-step output projections
+    unsigned long long* d_packed = nullptr;   // [128] running argmax words of the LM head
+    int* d_error = nullptr;            // device status word of the stack's own tcgen05 GEMMs
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
     int graph_nseqs = 0;
@@ -65,17 +68,28 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const __nv_b
 }
 
 // RMSNorm with (1 + w), fp32 in, bf16 out (and optional fp32 copy).  One warp per row; optional row gather.
+// n_splits > 0: first x[row] += sum of the split-K partial rows (written back), i.e. the residual add of the
+// preceding output projection happens here.
 __global__ void __launch_bounds__(128)
-rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w, float eps,
-               int rows, __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32) {
+rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w, float eps,
+               int rows, __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32,
+               const float* __restrict__ partials, int n_splits, size_t split_stride) {
     const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (gw >= rows) return;
-    const float* src = x + (size_t)(row_index ? row_index[gw] : gw) * kHidden;
+    const size_t srow = (size_t)(row_index ? row_index[gw] : gw);
+    float* src = x + srow * kHidden;
     float v[32];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const float4 t = *reinterpret_cast<const float4*>(src + 128 * i + 4 * lane);
+        float4 t = *reinterpret_cast<const float4*>(src + 128 * i + 4 * lane);
+        if (n_splits > 0) {
+            for (int sp = 0; sp < n_splits; ++sp) {
+                const float4 p = *reinterpret_cast<const float4*>(partials + (size_t)sp * split_stride + srow * kHidden + 128 * i + 4 * lane);
+                t.x += p.x; t.y += p.y; t.z += p.z; t.w += p.w;
+            }
+            *reinterpret_cast<float4*>(src + 128 * i + 4 * lane) = t;
+        }
         v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
         ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
     }
@@ -97,14 +111,16 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index, c
     }
 }
 
-// act = silu(gate) * up; gu rows are [gate (inter) | up (inter)], bf16.
+// act = silu(gate) * up.  gu rows hold tiles of 64 columns: 32 gate columns followed by the 32 matching up columns
+// (the layout the decode-step GEMM epilogue consumes as well).  bf16.
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int inter, size_t n_pairs, __nv_bfloat16* __restrict__ act) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // index over (row, inter/2)
     if (i >= n_pairs) return;
     const size_t half_inter = inter / 2;
-    const size_t row = i / half_inter, c = (i % half_inter) * 2;
-    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gu + row * 2 * inter + c);
-    const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(gu + row * 2 * inter + inter + c);
+    const size_t row = i / half_inter, c = (i % half_inter) * 2;      // output channel pair c, c+1
+    const size_t gcol = (c / 32) * 64 + (c % 32);
+    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gu + row * 2 * inter + gcol);
+    const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(gu + row * 2 * inter + gcol + 32);
     const float2 g = __bfloat1622float2(g2), u = __bfloat1622float2(u2);
     const float a0 = g.x / (1.0f + expf(-g.x)) * u.x, a1 = g.y / (1.0f + expf(-g.y)) * u.y;
     *reinterpret_cast<__nv_bfloat162*>(act + row * inter + c) = __floats2bfloat162_rn(a0, a1);
@@ -180,6 +196,7 @@ __global__ void quantize_rows_kernel(float* __restrict__ w, int rows, int cols) 
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+constexpr int kMaxSplits = 16;
 
 // Uploads a host fp32 matrix as bf16, optionally through the INT8 fake quantiser.
 static int upload_matrix(const float* h, int rows, int cols, bool int8, __nv_bfloat16** out) {
@@ -219,13 +236,14 @@ extern "C" int b200attn_stack_destroy(b200attn_stack st) {
     cudaFree(st->op_scratch.base);
     cudaFree(st->d_h); cudaFree(st->d_xb); cudaFree(st->d_gu); cudaFree(st->d_act); cudaFree(st->d_last);
     cudaFree(st->d_logits); cudaFree(st->d_tokens); cudaFree(st->d_slots);
+    cudaFree(st->d_partials); cudaFree(st->d_packed); cudaFree(st->d_error);
     delete st;
     return 0;
 }
 
 extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_stack* out) {
     B2_CHECK_ARG(cfg && out, "stack_create: null argument");
-    B2_CHECK_ARG(cfg->num_layers > 0 && cfg->intermediate_size > 0 && cfg->intermediate_size % 2 == 0 && cfg->vocab_size > 0 &&
+    B2_CHECK_ARG(cfg->num_layers > 0 && cfg->intermediate_size > 0 && cfg->intermediate_size % 64 == 0 && cfg->vocab_size > 0 &&
                      cfg->max_seqs > 0 && cfg->max_seq_len > 0 && cfg->prefill_chunk_seqs > 0,
                  "stack_create: all sizes must be > 0");
     if (cfg->hidden_size != kHidden) B2_FAIL(B200ATTN_ERR_UNSUPPORTED, "stack_create: kernels are built for hidden=1024");
@@ -285,6 +303,11 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
     ST_CUDA(cudaMalloc(&st->d_tokens, (size_t)cfg->max_seqs * 4));
     ST_CUDA(cudaMalloc(&st->d_slots, (size_t)cfg->max_seqs * 4));
     ST_CUDA(cudaMemset(st->d_tokens, 0, (size_t)cfg->max_seqs * 4));
+    ST_CUDA(cudaMalloc(&st->d_partials, (size_t)kMaxSplits * 128 * kHidden * 4));
+    ST_CUDA(cudaMalloc(&st->d_packed, 128 * sizeof(unsigned long long)));
+    ST_CUDA(cudaMemset(st->d_packed, 0, 128 * sizeof(unsigned long long)));
+    ST_CUDA(cudaMalloc(&st->d_error, sizeof(int)));
+    ST_CUDA(cudaMemset(st->d_error, 0, sizeof(int)));
     iota_kernel<<<ceil_div(cfg->max_seqs, 128), 128>>>(st->d_slots, cfg->max_seqs);
     ST_CUDA(cudaDeviceSynchronize());
 #undef ST_CUDA
@@ -303,9 +326,13 @@ extern "C" int b200attn_stack_set_layer_weights(b200attn_stack st, int layer, co
     st->d_in_norm[layer] = st->d_post_norm[layer] = nullptr; st->d_wgu[layer] = st->d_wdown[layer] = nullptr;
     B2_TRY(upload_f32(w->input_norm, &st->d_in_norm[layer], kHidden));
     B2_TRY(upload_f32(w->post_norm, &st->d_post_norm[layer], kHidden));
+    // rows in tiles of 64: 32 gate rows then the 32 matching up rows (see swiglu_kernel)
     std::vector<float> gu((size_t)2 * inter * kHidden);
-    std::memcpy(gu.data(), w->ffn_gate, (size_t)inter * kHidden * 4);
-    std::memcpy(gu.data() + (size_t)inter * kHidden, w->ffn_up, (size_t)inter * kHidden * 4);
+    for (int c = 0; c < inter; ++c) {
+        const size_t tile = c / 32, j = c % 32;
+        std::memcpy(gu.data() + (tile * 64 + j) * kHidden, w->ffn_gate + (size_t)c * kHidden, (size_t)kHidden * 4);
+        std::memcpy(gu.data() + (tile * 64 + 32 + j) * kHidden, w->ffn_up + (size_t)c * kHidden, (size_t)kHidden * 4);
+    }
     B2_TRY(upload_matrix(gu.data(), 2 * inter, kHidden, q8, &st->d_wgu[layer]));
     B2_TRY(upload_matrix(w->ffn_down, kHidden, inter, q8, &st->d_wdown[layer]));
     // Attention matrices go through the same per-output-channel quantiser when int8_weights is set.
@@ -370,6 +397,18 @@ extern "C" int b200attn_stack_init_embedding_random(b200attn_stack st, uint64_t 
     return 0;
 }
 
+extern "C" int b200attn_stack_device_status(b200attn_stack st, int* code_out) {
+    B2_CHECK_ARG(st && code_out, "stack_device_status: null argument");
+    *code_out = 0;
+    int c = 0;
+    if (st->pool) { B2_TRY(b200attn_kv_device_status(st->pool, &c)); if (c && !*code_out) *code_out = c; }
+    for (auto l : st->la) { B2_TRY(b200attn_la_device_status(l, &c)); if (c && !*code_out) *code_out = c; }
+    B2_CUDA(cudaDeviceSynchronize());
+    B2_CUDA(cudaMemcpy(&c, st->d_error, sizeof(int), cudaMemcpyDeviceToHost));
+    if (c) { B2_CUDA(cudaMemset(st->d_error, 0, sizeof(int))); if (!*code_out) *code_out = c; }
+    return 0;
+}
+
 extern "C" int b200attn_stack_reset(b200attn_stack st, b200attn_stream stream) {
     B2_CHECK_ARG(st, "stack_reset: null stack");
     if (st->pool) B2_TRY(b200attn_kv_clear(st->pool, stream));
@@ -387,35 +426,54 @@ static int stack_ready(b200attn_stack st) {
     return 0;
 }
 
-// All layers over `rows` rows already embedded in d_h.
+// All layers over `rows` rows already embedded in d_h.  Returns through *pending the number of split-K partial
+// matrices of the last output projection that still have to be added to d_h (decode path only).
 static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const int* h_counts, int n_seqs, const int* d_slots,
-                        bool decode, cudaStream_t s) {
+                        bool decode, int* pending_out, cudaStream_t s) {
     const int inter = st->cfg.intermediate_size;
+    const bool tc = decode && rows <= 128 && gemm_tc_enabled();          // weight-streaming tcgen05 GEMMs with fused epilogues
+    const size_t pstride = (size_t)128 * kHidden;
+    int pending = 0;
     for (int i = 0; i < st->cfg.num_layers; ++i) {
-        rmsnorm_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr);
+        rmsnorm_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
+                                                        st->d_partials, pending, pstride);
         B2_LAUNCH_CHECK();
+        DecodeOut dout{st->d_partials, pstride, 0};
         if (st->layer_kind[i])
             B2_TRY(fa_forward_rows(st->fa[st->layer_sub[i]], st->pool, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots,
-                                   decode, st->d_xb, true, st->d_h, 1.0f, s));
+                                   decode, st->d_xb, true, st->d_h, 1.0f, tc ? &dout : nullptr, s));
         else
             B2_TRY(la_forward_rows(st->la[st->layer_sub[i]], st->state, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots,
-                                   decode, st->d_xb, true, st->d_h, 1.0f, s));
-        rmsnorm_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr);
+                                   decode, st->d_xb, true, st->d_h, 1.0f, tc ? &dout : nullptr, s));
+        rmsnorm_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
+                                                        st->d_partials, dout.n_splits, pstride);
         B2_LAUNCH_CHECK();
-        B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_wgu[i], true, st->d_gu, true, rows, 2 * inter, kHidden));
-        const size_t pairs = (size_t)rows * inter / 2;
-        swiglu_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(st->d_gu, inter, pairs, st->d_act);
-        B2_LAUNCH_CHECK();
-        B2_TRY(gemm_xwT(s, st->d_act, true, st->d_wdown[i], true, st->d_h, false, rows, kHidden, inter, 1.0f));
+        if (tc) {
+            B2_TRY(gemm_tc_swiglu(s, st->d_xb, st->d_wgu[i], st->d_act, rows, 2 * inter, kHidden, st->d_error));
+            pending = std::min(kMaxSplits, gemm_tc_splits(kHidden, inter, 64));
+            B2_TRY(gemm_tc_store(s, st->d_act, st->d_wdown[i], st->d_partials, rows, kHidden, inter, kHidden, pending, pstride, st->d_error));
+        } else {
+            B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_wgu[i], true, st->d_gu, true, rows, 2 * inter, kHidden));
+            const size_t pairs = (size_t)rows * inter / 2;
+            swiglu_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(st->d_gu, inter, pairs, st->d_act);
+            B2_LAUNCH_CHECK();
+            B2_TRY(gemm_xwT(s, st->d_act, true, st->d_wdown[i], true, st->d_h, false, rows, kHidden, inter, 1.0f));
+            pending = 0;
+        }
     }
+    *pending_out = pending;
     return 0;
 }
 
-// Final norm of the selected rows, tied LM head, greedy argmax.
-static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int* d_next, float* d_hidden_out, cudaStream_t s) {
+// Final norm of the selected rows (after adding `pending` partial matrices), tied LM head, greedy argmax.
+static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int pending, int* d_next, float* d_hidden_out,
+                      cudaStream_t s) {
     rmsnorm_kernel<<<ceil_div(n_seqs, 4), 128, 0, s>>>(st->d_h, d_row_index, st->d_final_norm, st->cfg.rms_eps, n_seqs, st->d_xb,
-                                                      d_hidden_out ? d_hidden_out : nullptr);
+                                                      d_hidden_out ? d_hidden_out : nullptr, st->d_partials, pending,
+                                                      (size_t)128 * kHidden);
     B2_LAUNCH_CHECK();
+    if (n_seqs <= 128 && gemm_tc_enabled())    // LM head with the argmax in the GEMM epilogue: the logits never reach memory
+        return gemm_tc_argmax(s, st->d_xb, st->d_embed, st->d_packed, d_next, n_seqs, st->cfg.vocab_size, kHidden, st->d_error);
     B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_embed, true, st->d_logits, false, n_seqs, st->cfg.vocab_size, kHidden));
     argmax_kernel<<<n_seqs, 1024, 0, s>>>(st->d_logits, st->cfg.vocab_size, d_next);
     B2_LAUNCH_CHECK();
@@ -425,8 +483,9 @@ static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int
 static int stack_decode_step(b200attn_stack st, int n_seqs, const int* d_tokens_in, int* d_tokens_out, cudaStream_t s) {
     embed_gather_kernel<<<n_seqs, 256, 0, s>>>(d_tokens_in, st->d_embed, st->cfg.vocab_size, st->d_h);
     B2_LAUNCH_CHECK();
-    B2_TRY(stack_layers(st, n_seqs, nullptr, nullptr, n_seqs, st->d_slots, true, s));
-    return stack_head(st, n_seqs, nullptr, d_tokens_out, nullptr, s);
+    int pending = 0;
+    B2_TRY(stack_layers(st, n_seqs, nullptr, nullptr, n_seqs, st->d_slots, true, &pending, s));
+    return stack_head(st, n_seqs, nullptr, pending, d_tokens_out, nullptr, s);
 }
 
 }  // namespace b200
@@ -449,11 +508,12 @@ extern "C" int b200attn_stack_prefill(b200attn_stack st, int n_seqs, int prompt_
         for (int i = 0; i < n; ++i) slots[i] = s0 + i;
         embed_gather_kernel<<<rows, 256, 0, s>>>(d_tokens + (size_t)s0 * prompt_len, st->d_embed, st->cfg.vocab_size, st->d_h);
         count_launch();
-        rc = stack_layers(st, rows, slots.data(), counts.data(), n, nullptr, false, s);
+        int pending = 0;
+        rc = stack_layers(st, rows, slots.data(), counts.data(), n, nullptr, false, &pending, s);
         if (rc != 0) break;
         last_row_index_kernel<<<ceil_div(n, 128), 128, 0, s>>>(d_idx, n, prompt_len);
         count_launch();
-        rc = stack_head(st, n, d_idx, d_next + s0, d_hidden_out ? d_hidden_out + (size_t)s0 * kHidden : nullptr, s);
+        rc = stack_head(st, n, d_idx, pending, d_next + s0, d_hidden_out ? d_hidden_out + (size_t)s0 * kHidden : nullptr, s);
     }
     cudaError_t e = cudaStreamSynchronize(s);
     cudaFree(d_idx);

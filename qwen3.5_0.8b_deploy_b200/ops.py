@@ -35,6 +35,7 @@ ABI_SYMBOLS = [
     "b200attn_profile_enable", "b200attn_profile_reset", "b200attn_profile_read",
     "b200attn_stack_create", "b200attn_stack_destroy", "b200attn_stack_set_layer_weights",
     "b200attn_stack_set_embedding", "b200attn_stack_init_embedding_random", "b200attn_stack_reset",
+    "b200attn_stack_device_status",
     "b200attn_stack_prefill", "b200attn_stack_decode", "b200attn_decode_graph_capture",
     "b200attn_decode_graph_launch", "b200attn_stack_set_tokens", "b200attn_stack_get_tokens",
     "b200attn_selftest_umma",
@@ -396,6 +397,11 @@ class HybridStack:
     def init_embedding_random(self, seed: int, std: float, final_norm: np.ndarray) -> None:
         f = _host_f32(final_norm)
         _check(_lib.b200attn_stack_init_embedding_random(self.h, C.c_uint64(seed), C.c_float(std), f.ctypes.data_as(_f32p)))
+
+    def device_status(self) -> int:
+        code = C.c_int(0)
+        _check(_lib.b200attn_stack_device_status(self.h, C.byref(code)))
+        return code.value
 
     def reset_cache(self) -> None:
         _check(_lib.b200attn_stack_reset(self.h, _stream()))

@@ -4,7 +4,7 @@ oracle/_ref/libqwen_ref.so by oracle/Makefile) on seeded synthetic inputs.
 
     python tests/golden/make_golden.py
 
-Needs the reference checkout (default /root/reference); the fixtures it writes are committed so the
+Needs the reference checkout (location: environment variable QWEN_REFERENCE_ROOT); the fixtures it writes are committed so the
 tests that use them run anywhere.  Shapes are the real model dims; token counts are kept small so
 the files stay a few hundred KB.
 """

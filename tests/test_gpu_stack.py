@@ -77,6 +77,7 @@ def test_graph_replay_equals_eager_decode(ops, cuda, synth):
         assert ops.launch_count() > D * 20
     for a, b in zip(eager, replayed):
         assert torch.equal(a, b)
+    assert st.device_status() == 0
 
 
 def test_stack_errors(ops, cuda, synth):
