@@ -78,6 +78,25 @@ struct ProfScope {   // brackets the launches issued during its lifetime when pr
     ~ProfScope() { if (g_prof_on) prof_end(k, s); }
 };
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may become resident while the previous
+// kernel of the stream drains; it must call pdl_wait() before touching anything that kernel produced or still reads.
+// B200ATTN_PDL=0 turns the attribute off (ordinary stream order).
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline cudaStream_t as_stream(b200attn_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 

@@ -53,6 +53,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    pdl_enter();
 
     const int slot = slots[seq];
     if (slot < 0 || slot >= kv.max_seqs) return;
@@ -364,8 +365,8 @@ int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs
         attr_done = true;
     }
 #define FA_DEC_LAUNCH(F16, T)                                                                                          \
-    fa_decode_split_kernel<F16, T><<<grid, DecodeCfg<F16>::kThreads, DecodeCfg<F16>::kSmemBytes, s>>>(                 \
-        kv, layer, d_slots, len_add, q, gate, pages_per_warp, max_splits, part_o, part_ml, counters, (T*)out)
+    launch_pdl(fa_decode_split_kernel<F16, T>, grid, dim3(DecodeCfg<F16>::kThreads), DecodeCfg<F16>::kSmemBytes, s,    \
+               kv, layer, d_slots, len_add, q, gate, pages_per_warp, max_splits, part_o, part_ml, counters, (T*)out)
     if (kv.is_fp16) { if (out_bf16) FA_DEC_LAUNCH(true, __nv_bfloat16); else FA_DEC_LAUNCH(true, float); }
     else            { if (out_bf16) FA_DEC_LAUNCH(false, __nv_bfloat16); else FA_DEC_LAUNCH(false, float); }
 #undef FA_DEC_LAUNCH

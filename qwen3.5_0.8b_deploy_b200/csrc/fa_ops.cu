@@ -181,7 +181,7 @@ static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, bool
 
 static int decode_pages_per_warp(const b200attn_kv_pool pool) {
     const bool fp16 = pool->cfg.kv_dtype == B200ATTN_KV_FP16;
-    int ppw = fp16 ? 2 : 1;
+    int ppw = fp16 ? 8 : 4;
     if (const char* e = std::getenv("B200ATTN_DECODE_PPW")) { const int v = std::atoi(e); if (v > 0) ppw = v; }
     while (fa_decode_max_splits(fp16, pool->cfg.max_pages_per_seq, ppw) > kMaxSplitsCap) ++ppw;
     return ppw;

@@ -1,6 +1,7 @@
 // Library GEMMs (cuBLAS) for the projections around the attention cores, error text, launch counter and
 // small conversion helpers.
 #include "common.cuh"
+#include <cstdlib>
 
 #include <mutex>
 #include <utility>
@@ -10,6 +11,14 @@ namespace b200 {
 
 thread_local char g_error[512] = "";
 thread_local long long g_launches = 0;
+bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("B200ATTN_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
 
 void set_error(const char* fmt, ...) {
     va_list ap;

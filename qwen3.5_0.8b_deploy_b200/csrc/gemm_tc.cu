@@ -20,7 +20,6 @@
 
 namespace b200 {
 
-constexpr int kGemmStages = 8;      // 8 x (16 KB activations + BN x 128 B weights) in flight per CTA
 enum { kEpiStore = 0, kEpiSwiglu = 1, kEpiArgmax = 2 };
 
 template <int BN>
@@ -28,7 +27,8 @@ struct GemmCfg {
     static constexpr uint32_t kABytes = 128 * 128;          // 128 rows x 64 bf16
     static constexpr uint32_t kBBytes = BN * 128;
     static constexpr uint32_t kStage = kABytes + kBBytes;
-    static constexpr uint32_t kSmem = kGemmStages * kStage + 128 + 1024;
+    static constexpr int kStages = (8 * kStage <= 200 * 1024) ? 8 : (int)(200 * 1024 / kStage);   // ring depth
+    static constexpr uint32_t kSmem = kStages * kStage + 256 + 1024;
 };
 
 __device__ __forceinline__ unsigned long long pack_argmax(float v, int idx) {
@@ -38,6 +38,10 @@ __device__ __forceinline__ unsigned long long pack_argmax(float v, int idx) {
 }
 
 // grid (ceil(N / BN), splits), block 192: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2-5 = epilogue.
+// Launched as a programmatic dependent: barriers, TMEM and the first ring of WEIGHT tiles (which no kernel of the
+// step writes) are set up before the wait on the preceding kernel; activations are loaded and results written after.
+// Every CTA walks its k tiles from a different starting tile so that the CTAs of a wave do not all pull the same
+// activation tile from the same L2 slice at once.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, int M, int N,
@@ -45,27 +49,27 @@ gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     __nv_bfloat16* __restrict__ out_bf16, unsigned long long* __restrict__ argmax_out,
                     int* __restrict__ error_word) {
     using Cfg = GemmCfg<BN>;
+    constexpr int kStages = Cfg::kStages;
     extern __shared__ unsigned char smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     unsigned char* sm = smem_raw + (base - raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kGemmStages * Cfg::kStage);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kGemmStages + 1);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kStages * Cfg::kStage);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    const uint32_t bar0 = base + kGemmStages * Cfg::kStage;
+    const uint32_t bar0 = base + kStages * Cfg::kStage;
     auto full = [&](int s) { return bar0 + 8u * s; };
-    auto empty = [&](int s) { return bar0 + 8u * (kGemmStages + s); };
-    const uint32_t acc_done = bar0 + 8u * (2 * kGemmStages);
+    auto empty = [&](int s) { return bar0 + 8u * (kStages + s); };
+    const uint32_t acc_done = bar0 + 8u * (2 * kStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * BN, split = blockIdx.y;
     const int ks0 = split * k_steps_per_split;
     const int nk = min(k_steps_per_split, k_steps_total - ks0);
-    if (nk <= 0) return;
-    if (*reinterpret_cast<volatile int*>(error_word) != 0) return;
+    if (nk <= 0 || *reinterpret_cast<volatile int*>(error_word) != 0) { pdl_enter(); return; }
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < 2 * kGemmStages + 1; ++i) mbar_init(bar0 + 8u * i, 1);
+        for (int i = 0; i < 2 * kStages + 1; ++i) mbar_init(bar0 + 8u * i, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -79,24 +83,34 @@ gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
-        if (lane == 0) {
-            for (int ks = 0; ks < nk; ++ks) {
-                const int st = ks % kGemmStages;
-                if (ks >= kGemmStages && !mbar_wait(empty(st), ((ks / kGemmStages) - 1) & 1, abort_flag)) break;
-                const uint32_t dst = base + st * Cfg::kStage;
-                mbar_arrive_expect_tx(full(st), Cfg::kStage);
-                tma_load_2d(dst, &map_x, full(st), (ks0 + ks) * 64, 0);
-                tma_load_2d(dst + Cfg::kABytes, &map_w, full(st), (ks0 + ks) * 64, n0);
-            }
+    if (warp == 0 && lane == 0) {
+        const int rot = (int)((blockIdx.x * 3u + blockIdx.y * 7u) % (unsigned)nk);
+        auto ktile = [&](int ks) { int k = ks + rot; if (k >= nk) k -= nk; return (ks0 + k) * 64; };
+        const int pre = min(nk, kStages);
+        for (int ks = 0; ks < pre; ++ks) {
+            mbar_arrive_expect_tx(full(ks), Cfg::kStage);
+            tma_load_2d(base + ks * Cfg::kStage + Cfg::kABytes, &map_w, full(ks), ktile(ks), n0);
         }
-    } else if (warp == 1) {
+        pdl_enter();
+        for (int ks = 0; ks < pre; ++ks) tma_load_2d(base + ks * Cfg::kStage, &map_x, full(ks), ktile(ks), 0);
+        for (int ks = pre; ks < nk; ++ks) {
+            const int st = ks % kStages;
+            if (!mbar_wait(empty(st), ((ks / kStages) - 1) & 1, abort_flag)) break;
+            const uint32_t dst = base + st * Cfg::kStage;
+            mbar_arrive_expect_tx(full(st), Cfg::kStage);
+            tma_load_2d(dst, &map_x, full(st), ktile(ks), 0);
+            tma_load_2d(dst + Cfg::kABytes, &map_w, full(st), ktile(ks), n0);
+        }
+    } else {
+        pdl_enter();
+    }
+    if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(kFmtBF16, 128, BN, 0, 0);
             bool ok = true;
             for (int ks = 0; ks < nk; ++ks) {
-                const int st = ks % kGemmStages;
-                if (!mbar_wait(full(st), (ks / kGemmStages) & 1, abort_flag)) { ok = false; break; }
+                const int st = ks % kStages;
+                if (!mbar_wait(full(st), (ks / kStages) & 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t a = base + st * Cfg::kStage, b = a + Cfg::kABytes;
 #pragma unroll
@@ -107,54 +121,66 @@ gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             }
             if (ok) umma_commit(acc_done);
         }
-    } else {
+    } else if (warp >= 2) {
         const int q = warp & 3;                       // TMEM lane quadrant this warp may read
         const int m = 32 * q + lane;                  // output row
         if (mbar_wait_warp(acc_done, 0, abort_flag)) {
             tc_fence_after();
             const uint32_t lane_base = (uint32_t)(32 * q) << 16;
-            float acc[BN];
-#pragma unroll
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                uint32_t v[32];
-                tmem_ld32(tmem + lane_base + ch * 32, v);
-                tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) acc[ch * 32 + c] = __uint_as_float(v[c]);
-            }
             const int n_valid = min(BN, N - n0);
-            if (m < M) {
-                if constexpr (EPI == kEpiStore) {
-                    float* dst = out_f32 + (size_t)split * split_stride + (size_t)m * ld_out + n0;
-                    if (n_valid == BN) {
+            if constexpr (EPI == kEpiStore) {
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + lane_base + ch * 32, v);
+                    tmem_wait_ld();
+                    if (m < M) {
+                        float* dst = out_f32 + (size_t)split * split_stride + (size_t)m * ld_out + n0 + ch * 32;
+                        if (n_valid == BN) {
 #pragma unroll
-                        for (int c4 = 0; c4 < BN / 4; ++c4)
-                            *reinterpret_cast<float4*>(dst + 4 * c4) = make_float4(acc[4 * c4], acc[4 * c4 + 1], acc[4 * c4 + 2], acc[4 * c4 + 3]);
-                    } else {
+                            for (int c4 = 0; c4 < 8; ++c4)
+                                *reinterpret_cast<uint4*>(dst + 4 * c4) = make_uint4(v[4 * c4], v[4 * c4 + 1], v[4 * c4 + 2], v[4 * c4 + 3]);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < BN; ++c) if (c < n_valid) dst[c] = acc[c];
+                            for (int c = 0; c < 32; ++c) if (ch * 32 + c < n_valid) dst[c] = __uint_as_float(v[c]);
+                        }
                     }
-                } else if constexpr (EPI == kEpiSwiglu) {
-                    __nv_bfloat16* dst = out_bf16 + (size_t)m * ld_out + blockIdx.x * (BN / 2);
+                }
+            } else if constexpr (EPI == kEpiSwiglu) {
+                static_assert(EPI != kEpiSwiglu || BN == 64, "SwiGLU tiles are 32 gate + 32 up columns");
+                uint32_t gt[32], up[32];
+                tmem_ld32(tmem + lane_base, gt);
+                tmem_ld32(tmem + lane_base + 32, up);
+                tmem_wait_ld();
+                if (m < M) {
+                    __nv_bfloat16* dst = out_bf16 + (size_t)m * ld_out + blockIdx.x * 32;
 #pragma unroll
-                    for (int c8 = 0; c8 < BN / 16; ++c8) {
+                    for (int c8 = 0; c8 < 4; ++c8) {
                         __nv_bfloat162 h[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float g0 = acc[8 * c8 + 2 * e], g1 = acc[8 * c8 + 2 * e + 1];
-                            const float u0 = acc[BN / 2 + 8 * c8 + 2 * e], u1 = acc[BN / 2 + 8 * c8 + 2 * e + 1];
+                            const float g0 = __uint_as_float(gt[8 * c8 + 2 * e]), g1 = __uint_as_float(gt[8 * c8 + 2 * e + 1]);
+                            const float u0 = __uint_as_float(up[8 * c8 + 2 * e]), u1 = __uint_as_float(up[8 * c8 + 2 * e + 1]);
                             h[e] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
                         }
                         *reinterpret_cast<uint4*>(dst + 8 * c8) = *reinterpret_cast<uint4*>(h);
                     }
-                } else {
-                    float best = -INFINITY;
-                    int bi = 0;
-#pragma unroll
-                    for (int c = 0; c < BN; ++c)
-                        if (c < n_valid && acc[c] > best) { best = acc[c]; bi = c; }
-                    atomicMax(argmax_out + m, pack_argmax(best, n0 + bi));
                 }
+            } else {
+                float best = -INFINITY;
+                int bi = 0;
+#pragma unroll 1
+                for (int ch = 0; ch < BN / 32; ++ch) {
+                    uint32_t v[32];
+                    tmem_ld32(tmem + lane_base + ch * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const float x = __uint_as_float(v[c]);
+                        if (ch * 32 + c < n_valid && x > best) { best = x; bi = ch * 32 + c; }
+                    }
+                }
+                if (m < M) atomicMax(argmax_out + m, pack_argmax(best, n0 + bi));
             }
         }
     }
@@ -169,6 +195,7 @@ gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
 // packed running argmax -> token ids; leaves the packed words at zero for the next step.
 __global__ void argmax_unpack_kernel(unsigned long long* __restrict__ packed, int n, int* __restrict__ tokens) {
+    pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const unsigned long long p = packed[i];
@@ -207,8 +234,8 @@ int launch_one(const CUtensorMap& mx, const CUtensorMap& mw, int M, int N, int K
     const int k_steps = K / 64;
     const int per = ceil_div(k_steps, splits);
     dim3 grid(ceil_div(N, BN), ceil_div(k_steps, per));
-    gemm_small_m_kernel<BN, EPI><<<grid, 192, GemmCfg<BN>::kSmem, s>>>(mx, mw, M, N, per, k_steps, out_f32, ld_out, split_stride,
-                                                                      out_bf16, argmax_out, d_error);
+    launch_pdl(gemm_small_m_kernel<BN, EPI>, grid, dim3(192), GemmCfg<BN>::kSmem, s, mx, mw, M, N, per, k_steps, out_f32, ld_out,
+               split_stride, out_bf16, argmax_out, d_error);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -220,17 +247,15 @@ void gemm_tc_forget(const void* ptr) {     // drop cached maps of a buffer that 
         it = (std::get<0>(it->first) == ptr) ? g_maps.erase(it) : std::next(it);
 }
 
-// Number of split-K slices a [M<=128, N] x K product is cut into when the caller can sum partial tiles.
-// B200ATTN_DECODE_GEMM=cublas routes the decode-step projections back through cuBLAS (A/B measurements).
+// B200ATTN_DECODE_GEMM selects the projections of the decode step: "tc" = the kernel above with its fused epilogues,
+// "cublas" (default: measured faster end to end so far) = cuBLAS GEMMs with separate SwiGLU / argmax kernels.  Read on
+// every call so one process can exercise both.
 bool gemm_tc_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = std::getenv("B200ATTN_DECODE_GEMM");
-        v = (e && std::string(e) == "cublas") ? 0 : 1;
-    }
-    return v == 1;
+    const char* e = std::getenv("B200ATTN_DECODE_GEMM");
+    return e && std::string(e) == "tc";
 }
 
+// Number of split-K slices a [M<=128, N] x K product is cut into when the caller can sum partial tiles.
 int gemm_tc_splits(int N, int K, int bn) {
     const int tiles = ceil_div(N, bn);
     int s = std::max(1, 148 / std::max(tiles, 1));
@@ -268,9 +293,9 @@ int gemm_tc_argmax(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* 
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N > 0, "gemm_tc_argmax: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
     B2_TRY(bf16_map(X, M, K, 128, &mx));
-    B2_TRY(bf16_map(W, N, K, 64, &mw));
-    B2_TRY((launch_one<64, kEpiArgmax>(mx, mw, M, N, K, 1, nullptr, 0, 0, nullptr, d_packed, d_error, s)));
-    argmax_unpack_kernel<<<ceil_div(M, 128), 128, 0, s>>>(d_packed, M, tokens);
+    B2_TRY(bf16_map(W, N, K, 256, &mw));
+    B2_TRY((launch_one<256, kEpiArgmax>(mx, mw, M, N, K, 1, nullptr, 0, 0, nullptr, d_packed, d_error, s)));
+    launch_pdl(argmax_unpack_kernel, dim3(ceil_div(M, 128)), dim3(128), 0, s, d_packed, M, tokens);
     B2_LAUNCH_CHECK();
     return 0;
 }

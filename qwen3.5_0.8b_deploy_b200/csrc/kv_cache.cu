@@ -5,6 +5,7 @@
 // (src/backend/cuda/kernels/full_attention_cuda.cu:78-148 in the reference): per (token, kv head)
 // scale = absmax / 127 (IEEE division), 1.0 if not > 1e-8, code = clamp(roundf(x / scale), +-127).
 #include "kernels.cuh"
+#include "ptx_utils.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -86,6 +87,7 @@ kv_append_kernel(KvView kv, int layer, const AppendTile* __restrict__ tiles, con
     __shared__ __align__(16) VT sV[kHeadDim][kPageTokens + (kFp16 ? 8 : 16)];
     const int kvh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_enter();
     AppendTile tile;
     if (decode_mode) {
         tile.seq = blockIdx.x;
@@ -171,6 +173,7 @@ kv_append_kernel(KvView kv, int layer, const AppendTile* __restrict__ tiles, con
 // After all tiles of a call were written: lens[layer][slot] += count (one thread per sequence).
 __global__ void kv_advance_kernel(KvView kv, int layer, const int* __restrict__ slots,
                                   const int* __restrict__ counts, int n_seqs) {
+    pdl_enter();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_seqs) return;
     const int slot = slots[i];
@@ -189,6 +192,7 @@ fa_q_epilogue_kernel(const float* __restrict__ qkv_raw, int rows, const float* _
                      const float* __restrict__ inv_freq, const int* __restrict__ row_pos,
                      const int* __restrict__ slots, const int* __restrict__ lens_layer, int max_seqs,
                      __half* __restrict__ q_out, __half* __restrict__ gate_out) {
+    pdl_enter();
     const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (gw >= rows * kFaHeads) return;
@@ -268,20 +272,18 @@ int launch_kv_append(const KvView& kv, int layer, const AppendTile* d_tiles, int
     if (n_tiles <= 0) return 0;
     dim3 grid(n_tiles, kFaKvHeads);
     if (kv.is_fp16)
-        kv_append_kernel<true><<<grid, 256, 0, s>>>(kv, layer, d_tiles, d_slots, kin, k_stride, vin, v_stride,
-                                                    do_norm_rope, k_norm_w, inv_freq, kstage, vstage,
-                                                    d_stage_row0, decode_mode);
+        launch_pdl(kv_append_kernel<true>, grid, dim3(256), 0, s, kv, layer, d_tiles, d_slots, kin, k_stride, vin, v_stride,
+                   do_norm_rope, k_norm_w, inv_freq, kstage, vstage, d_stage_row0, decode_mode);
     else
-        kv_append_kernel<false><<<grid, 256, 0, s>>>(kv, layer, d_tiles, d_slots, kin, k_stride, vin, v_stride,
-                                                     do_norm_rope, k_norm_w, inv_freq, kstage, vstage,
-                                                     d_stage_row0, decode_mode);
+        launch_pdl(kv_append_kernel<false>, grid, dim3(256), 0, s, kv, layer, d_tiles, d_slots, kin, k_stride, vin, v_stride,
+                   do_norm_rope, k_norm_w, inv_freq, kstage, vstage, d_stage_row0, decode_mode);
     B2_LAUNCH_CHECK();
     return 0;
 }
 
 int launch_kv_advance(const KvView& kv, int layer, const int* d_slots, const int* d_counts, int n_seqs,
                       cudaStream_t s) {
-    kv_advance_kernel<<<ceil_div(n_seqs, 128), 128, 0, s>>>(kv, layer, d_slots, d_counts, n_seqs);
+    launch_pdl(kv_advance_kernel, dim3(ceil_div(n_seqs, 128)), dim3(128), 0, s, kv, layer, d_slots, d_counts, n_seqs);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -290,8 +292,8 @@ int launch_fa_q_epilogue(const float* qkv_raw, int rows, const float* q_norm_w, 
                          const int* d_row_pos, const int* d_slots, const int* d_lens_layer, int max_seqs,
                          __half* q_out, __half* gate_out, cudaStream_t s) {
     const int warps = rows * kFaHeads;
-    fa_q_epilogue_kernel<<<ceil_div(warps, 4), 128, 0, s>>>(qkv_raw, rows, q_norm_w, inv_freq, d_row_pos,
-                                                           d_slots, d_lens_layer, max_seqs, q_out, gate_out);
+    launch_pdl(fa_q_epilogue_kernel, dim3(ceil_div(warps, 4)), dim3(128), 0, s, qkv_raw, rows, q_norm_w, inv_freq, d_row_pos,
+               d_slots, d_lens_layer, max_seqs, q_out, gate_out);
     B2_LAUNCH_CHECK();
     return 0;
 }

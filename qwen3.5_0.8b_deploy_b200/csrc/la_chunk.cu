@@ -5,44 +5,66 @@
 //     S_i = e^{g_i} S_{i-1} + k_i (x) beta_i (v_i - (e^{g_i} S_{i-1})^T k_i),   o_i = S_i^T q_i
 // (src/backend/cpu/core/attention/language_linear_attn.cpp:206-240 in the reference; its CUDA form is the
 // token-serial gated_delta_batch_fused_v2_kernel, linear_attention_v2.cu:492-595) is equivalent to
-//     A_ij   = beta_i e^{b_i-b_j} (k_i.k_j)  (j < i),      (I + A) [U | W] = [beta V | beta e^{b} K]
-//     V_new  = U - W S0
-//     O      = (Q e^{b}) S0 + tril(e^{b_i-b_j} (q_i.k_j)) V_new
-//     S_C    = e^{b_C} S0 + K^T (e^{b_C-b} V_new)
+//     A_ij  = beta_i e^{b_i-b_j} (k_i.k_j)  (j < i),     T = (I + A)^-1
+//     U     = T (beta V),   W = T (beta e^{b} K),        V_new = U - W S0
+//     O     = (Q e^{b}) S0 + tril(e^{b_i-b_j} (q_i.k_j)) V_new
+//     S_C   = e^{b_C} S0 + K^T (e^{b_C-b} V_new)
 // Every decay factor is formed as exp(b_i - b_j) with i >= j, never as a quotient of products.
 //
-// Contractions on the tensor cores (tcgen05.mma kind::f16, fp16 operands = the same 10-bit mantissa as tf32,
-// fp32 accumulation in TMEM; all operand tiles use the 128-byte swizzle):
-//   (a) D1[128x64]  = [K ; Q] K^T                      rows 0-63: K K^T, rows 64-127: Q K^T
-//   (b) D2[128x128] = [W ; Q e^{b}] S0                 rows 0-63: W S0,  rows 64-127: inter-chunk output
-//   (d) D2         += [0 ; Mq] V_new                   adds the intra-chunk output to rows 64-127
-//   (u) D3[128x128] = e^{b_C} D3 + (e^{b_C-b} V_new)^T K    D3 holds S^T (lane = value dim) for the whole sequence
-// The unit-lower-triangular solve runs in fp32 on the CUDA cores (thread t owns column t of U and of W).
-// Warps 0-3 compute, warp 4 issues TMA loads and MMAs.  All waits are bounded.
+// All state-sized objects are kept TRANSPOSED in TMEM (lane = value dim or key dim, column = token), so every
+// tensor-core product has M = 128 and every tile a thread writes is one of its own rows:
+//   (a)  D1  [128 x 64] = [K ; Q] K^T                         rows 0-63: K K^T, rows 64-127: Q K^T
+//   (uw) Ut  [vd x 64]  = (beta V)^T T^T,   Wt [kd x 64] = (beta e^b K)^T T^T     (T as an fp16 hi + lo pair)
+//   (ws) Ut -= S0^T W^T                                        -> V_new^T, accumulated in place (negated A operand)
+//   (o)  Ot  [vd x 64]  = S0^T (Q e^b)^T + V_new^T Mq^T
+//   (u)  D3  [vd x kd]  = e^{b_C} D3 + (e^{b_C-b} V_new)^T K  D3 holds S^T for the whole sequence
+// tcgen05.mma kind::f16: fp16 operands (the same 10-bit mantissa as tf32), fp32 accumulation; 128-byte swizzle.
+// T itself is built in fp32 in shared memory by a blocked inverse (16 x 16 blocks) on the CUDA cores.
+// Warps 0-3 compute, warp 4 issues TMA loads (K/Q tiles double-buffered) and MMAs.  All waits are bounded.
 #include "kernels.cuh"
 #include "tc05.cuh"
 
 namespace b200 {
 
 constexpr int kC = 64;
-constexpr uint32_t kOffKQ = 0;                 // [2 blocks][128 rows][128 B]: rows 0-63 K chunk, rows 64-127 Q chunk
-constexpr uint32_t kOffWQ = 32768;             // A of (b): [2 blocks][128 rows][128 B]
-constexpr uint32_t kOffST = 65536;             // B of (b): S^T, [2 blocks (64 kd)][128 vd rows][128 B]
-constexpr uint32_t kOffVN = 98304;             // B of (d): V_new, [2 blocks (64 vd)][64 token rows][128 B]
-constexpr uint32_t kOffVT = 114688;            // A of (u): (e^{b_C-b} V_new)^T, [128 vd rows][128 B = 64 tokens]
-constexpr uint32_t kOffMQ = 131072;            // A of (d): [128 rows][128 B]; rows 0-63 zero, rows 64-127 Mq
-constexpr uint32_t kOffAM = 147456;            // fp32 A matrix [64][64]
-constexpr uint32_t kOffUS = 163840;            // fp32 U [64][kUSStride] (row stride 129 floats: conflict-free column and row access)
-constexpr int kUSStride = 129;
-constexpr uint32_t kOffSC = 197632;            // scalars: b[64], beta[64], eb[64], ebc[64]   (US ends at 163840 + 64*129*4 = 196864)
-constexpr uint32_t kOffBarG = 198656;
+// shared-memory map (bytes from a 1024-aligned base)
+constexpr uint32_t kOffKQ = 0;        // 2 buffers x [2 blocks][128 rows][128 B]: rows 0-63 K chunk, rows 64-127 Q chunk
+constexpr uint32_t kOffST = 65536;    // S0^T fp16: [2 blocks (64 kd)][128 vd rows][128 B]            A of (ws), (o)
+constexpr uint32_t kOffRV = 98304;    // (beta V)^T [128 vd rows][64 tokens];  later V_new^T           A of (uw) / (o)
+constexpr uint32_t kOffRK = 114688;   // (beta e^b K)^T [128 kd rows][64 tokens]; later decayed V_new^T A of (uw) / (u)
+constexpr uint32_t kOffTT = 131072;   // T hi [64][64] fp16, then T lo                                   B of (uw)
+constexpr uint32_t kOffWT = 147456;   // W [2 blocks][64 token rows][128 B]                              B of (ws)
+constexpr uint32_t kOffQT = 163840;   // Q e^b, same shape                                               B of (o)
+constexpr uint32_t kOffMQ = 180224;   // Mq [64][64] fp16                                                B of (o)
+constexpr uint32_t kOffAM = 188416;   // fp32 A [64][64]; its (zero) upper blocks double as scratch of the inverse
+constexpr uint32_t kOffTF = 204800;   // fp32 T [64][64]
+constexpr uint32_t kOffSC = 221184;   // scalars: b[64], beta[64], eb[64], ebc[64]
+constexpr uint32_t kOffBarG = 222208;
 constexpr uint32_t kG1Smem = kOffBarG + 128 + 1024;
-enum { G_KQ_FULL = 0, G_A_DONE, G_B_READY, G_B_DONE, G_V_READY, G_D_DONE, G_KQ_FREE, G_BAR_COUNT };
+enum { G_KQ_FULL0 = 0, G_KQ_FULL1, G_A_DONE, G_B1, G_C1, G_B2, G_C2, G_B3, G_C3, G_KQ_FREE, G_BAR_COUNT };
 
 __device__ __forceinline__ void named_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 __device__ __forceinline__ uint16_t f2h_bits(float x) {
     const __half h = __float2half_rn(x);
     return *reinterpret_cast<const uint16_t*>(&h);
+}
+
+// dst(16x16 block at dr,dc) (+)= sign * A(16x16 at ar,ac) * B(16x16 at br,bc); matrices 64x64 fp32 row-major in
+// shared memory; 128 threads, two outputs each.
+__device__ __forceinline__ void block_product(float* dst, int dr, int dc, const float* A, int ar, int ac, const float* B,
+                                              int br, int bc, float sign, bool accumulate, int tid) {
+    const int r = tid >> 3, c0 = (tid & 7) * 2;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const float a = A[(ar + r) * 64 + ac + k];
+        const float2 b = *reinterpret_cast<const float2*>(&B[(br + k) * 64 + bc + c0]);
+        s0 += a * b.x;
+        s1 += a * b.y;
+    }
+    float2* d = reinterpret_cast<float2*>(&dst[(dr + r) * 64 + dc + c0]);
+    if (accumulate) { float2 o = *d; o.x += sign * s0; o.y += sign * s1; *d = o; }
+    else *d = make_float2(sign * s0, sign * s1);
 }
 
 // grid (heads, n_seqs), block 160
@@ -64,7 +86,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     float* s_eb = s_b + 128;
     float* s_ebc = s_b + 192;
     float* AM = reinterpret_cast<float*>(sm + kOffAM);
-    float* US = reinterpret_cast<float*>(sm + kOffUS);
+    float* TF = reinterpret_cast<float*>(sm + kOffTF);
 
     const int h = blockIdx.x;
     const LaSeqMeta sq = seqs[blockIdx.y];
@@ -76,7 +98,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 
     if (tid == 0) {
         for (int i = 0; i < G_BAR_COUNT; ++i)
-            mbar_init(bar(i), (i == G_B_READY || i == G_V_READY || i == G_KQ_FREE) ? 128 : 1);
+            mbar_init(bar(i), (i == G_B1 || i == G_B2 || i == G_B3 || i == G_KQ_FREE) ? 128 : 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -89,66 +111,82 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_d1 = tmem, tm_d2 = tmem + 64, tm_d3 = tmem + 192;
+    const uint32_t tm_d1 = tmem, tm_ut = tmem + 64, tm_wt = tmem + 128, tm_ot = tmem + 192, tm_d3 = tmem + 256;
 
     if (warp == 4) {
         // ------------------------------ TMA + MMA issuer ------------------------------
         if (lane == 0) {
-            constexpr uint32_t id_a = umma_idesc(kFmtF16, 128, 64, 0, 0);
-            constexpr uint32_t id_b = umma_idesc(kFmtF16, 128, 128, 0, 0);
-            constexpr uint32_t id_mn = umma_idesc(kFmtF16, 128, 128, 0, 1);
-            for (int c = 0; c < n_chunks; ++c) {
-                const uint32_t par = c & 1, prev = (c - 1) & 1;
-                if (c > 0) {
-                    if (!mbar_wait(bar(G_D_DONE), prev, abort_flag)) break;
-                    if (!mbar_wait(bar(G_KQ_FREE), prev, abort_flag)) break;
-                }
+            constexpr uint32_t id64 = umma_idesc(kFmtF16, 128, 64, 0, 0);
+            constexpr uint32_t id64_neg = id64 | (1u << 13);                  // negated A operand
+            constexpr uint32_t id_u = umma_idesc(kFmtF16, 128, 128, 0, 1);    // B MN-major, N = 128
+            auto load_kq = [&](int c) {
+                const uint32_t dst = base + kOffKQ + (c & 1) * 32768;
+                const uint32_t fb = bar(G_KQ_FULL0 + (c & 1));
                 const int row = sq.row0 + c * kC;
-                mbar_arrive_expect_tx(bar(G_KQ_FULL), 32768);
+                mbar_arrive_expect_tx(fb, 32768);
                 for (int blk = 0; blk < 2; ++blk) {
-                    tma_load_3d(base + kOffKQ + blk * 16384, &map_k, bar(G_KQ_FULL), blk * 64, h, row);
-                    tma_load_3d(base + kOffKQ + blk * 16384 + 8192, &map_q, bar(G_KQ_FULL), blk * 64, h, row);
+                    tma_load_3d(dst + blk * 16384, &map_k, fb, blk * 64, h, row);
+                    tma_load_3d(dst + blk * 16384 + 8192, &map_q, fb, blk * 64, h, row);
                 }
-                if (!mbar_wait(bar(G_KQ_FULL), par, abort_flag)) break;
+            };
+            load_kq(0);
+            for (int c = 0; c < n_chunks; ++c) {
+                const uint32_t par = c & 1;
+                const uint32_t kq = base + kOffKQ + (c & 1) * 32768;
+                // prefetch the next chunk's K/Q into the other buffer: it was last read by chunk c-1, whose
+                // threads (KQ_FREE) and whose state-update MMA (C3) must be done with it
+                if (c + 1 < n_chunks) {
+                    if (c >= 1) {
+                        if (!mbar_wait(bar(G_C3), (c - 1) & 1, abort_flag)) break;
+                        if (!mbar_wait(bar(G_KQ_FREE), (c - 1) & 1, abort_flag)) break;
+                    }
+                    load_kq(c + 1);
+                }
+                if (!mbar_wait(bar(G_KQ_FULL0 + (c & 1)), (c >> 1) & 1, abort_flag)) break;
                 tc_fence_after();
-                // (a) D1 = [K;Q] K^T
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
+                for (int ks = 0; ks < 8; ++ks) {   // (a) D1 = [K;Q] K^T
                     const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                    umma_f16(tm_d1, umma_smem_desc(base + kOffKQ + off, 16, 1024), umma_smem_desc(base + kOffKQ + off, 16, 1024),
-                             id_a, ks > 0 ? 1u : 0u);
+                    umma_f16(tm_d1, umma_smem_desc(kq + off, 16, 1024), umma_smem_desc(kq + off, 16, 1024), id64, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(G_A_DONE));
-                // (b) D2 = [W;Qe^b] S0
-                if (!mbar_wait(bar(G_B_READY), par, abort_flag)) break;
+                if (!mbar_wait(bar(G_B1), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                    umma_f16(tm_d2, umma_smem_desc(base + kOffWQ + off, 16, 1024), umma_smem_desc(base + kOffST + off, 16, 1024),
-                             id_b, ks > 0 ? 1u : 0u);
+                for (int hl = 0; hl < 2; ++hl)    // (uw) with T = hi + lo
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t bt = umma_smem_desc(base + kOffTT + hl * 8192 + ks * 32, 16, 1024);
+                        umma_f16(tm_ut, umma_smem_desc(base + kOffRV + ks * 32, 16, 1024), bt, id64, (hl > 0 || ks > 0) ? 1u : 0u);
+                        umma_f16(tm_wt, umma_smem_desc(base + kOffRK + ks * 32, 16, 1024), bt, id64, (hl > 0 || ks > 0) ? 1u : 0u);
+                    }
+                umma_commit(bar(G_C1));
+                if (!mbar_wait(bar(G_B2), par, abort_flag)) break;
+                tc_fence_after();
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {   // (ws) Ut -= S0^T W^T ; (o) Ot = S0^T (Q e^b)^T
+                    const uint64_t a = umma_smem_desc(base + kOffST + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+                    const uint32_t boff = (ks >> 2) * 8192 + (ks & 3) * 32;
+                    umma_f16(tm_ut, a, umma_smem_desc(base + kOffWT + boff, 16, 1024), id64_neg, 1u);
+                    umma_f16(tm_ot, a, umma_smem_desc(base + kOffQT + boff, 16, 1024), id64, ks > 0 ? 1u : 0u);
                 }
-                umma_commit(bar(G_B_DONE));
-                // (d) D2 += [0;Mq] V_new     (u) D3 += (e^{b_C-b} V_new)^T K
-                if (!mbar_wait(bar(G_V_READY), par, abort_flag)) break;
+                umma_commit(bar(G_C2));
+                if (!mbar_wait(bar(G_B3), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    umma_f16(tm_d2, umma_smem_desc(base + kOffMQ + ks * 32, 16, 1024),
-                             umma_smem_desc(base + kOffVN + ks * 2048, 8192, 1024), id_mn, 1u);
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    umma_f16(tm_d3, umma_smem_desc(base + kOffVT + ks * 32, 16, 1024),
-                             umma_smem_desc(base + kOffKQ + ks * 2048, 16384, 1024), id_mn, 1u);
-                umma_commit(bar(G_D_DONE));
+                for (int ks = 0; ks < 4; ++ks) {   // (o) Ot += V_new^T Mq^T ; (u) D3 += (e^{b_C-b} V_new)^T K
+                    umma_f16(tm_ot, umma_smem_desc(base + kOffRV + ks * 32, 16, 1024), umma_smem_desc(base + kOffMQ + ks * 32, 16, 1024),
+                             id64, 1u);
+                    umma_f16(tm_d3, umma_smem_desc(base + kOffRK + ks * 32, 16, 1024), umma_smem_desc(kq + ks * 2048, 16384, 1024),
+                             id_u, 1u);
+                }
+                umma_commit(bar(G_C3));
             }
         }
     } else {
         // ------------------------------ compute warps ------------------------------
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        const int r = tid;                      // TMEM lane: D1/D2 row, D3 value dim, and the solve column
-        // MQ rows 0-63 stay zero for the whole kernel
-        for (int i = tid; i < 64 * 8; i += 128) *reinterpret_cast<uint4*>(sm + kOffMQ + i * 16) = make_uint4(0, 0, 0, 0);
+        const int r = tid;   // TMEM lane: D1 row, value dim of Ut/Ot/D3, key dim of Wt; also this thread's tile row / column
         // D3 <- S^T from the state pool: lane vd = r, column kd
 #pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
@@ -163,11 +201,11 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint32_t par = c & 1, prev = (c - 1) & 1;
             const int tok0 = c * kC;
             const int n_valid = min(kC, sq.count - tok0);
+            const unsigned char* kq = sm + kOffKQ + (c & 1) * 32768;
             // ---- per-chunk scalars: b = cumsum(g), beta; padded tokens get g = 0, beta = 0 ----
             if (warp < 2) {
-                const int i = tid;
-                const bool val = i < n_valid;
-                const size_t gi = (size_t)(sq.row0 + tok0 + i) * kLaHeads + h;
+                const bool val = tid < n_valid;
+                const size_t gi = (size_t)(sq.row0 + tok0 + tid) * kLaHeads + h;
                 float gv = val ? g[gi] : 0.f;
                 const float bv = val ? beta[gi] : 0.f;
 #pragma unroll
@@ -175,8 +213,8 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     const float t2 = __shfl_up_sync(0xffffffffu, gv, o);
                     if (lane >= o) gv += t2;
                 }
-                s_b[i] = gv;
-                s_beta[i] = bv;
+                s_b[tid] = gv;
+                s_beta[tid] = bv;
             }
             named_sync_128();
             if (warp == 1) s_b[tid] += s_b[31];
@@ -187,8 +225,13 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             named_sync_128();
             const float e_bc = expf(s_b[63]);
-            // ---- S prep: D3 (S^T of the chunk start) -> fp16 tile for (b), and back to TMEM scaled by e^{b_C} ----
-            if (c > 0 && !mbar_wait_warp(bar(G_D_DONE), prev, abort_flag)) { ok = false; break; }
+            // ---- this thread's column of beta V (global loads overlap the previous chunk's MMAs) ----
+            float vcol[64];
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+                vcol[i] = (i < n_valid) ? s_beta[i] * v[((size_t)(sq.row0 + tok0 + i) * kLaHeads + h) * kLaVd + tid] : 0.f;
+            // ---- S prep: D3 (S^T of the chunk start) -> fp16 tile, and back to TMEM scaled by e^{b_C} ----
+            if (c > 0 && !mbar_wait_warp(bar(G_C3), prev, abort_flag)) { ok = false; break; }
             tc_fence_after();
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
@@ -197,7 +240,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_wait_ld();
                 unsigned char* row_ptr = sm + kOffST + (ch >> 1) * 16384 + r * 128;
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {     // 8 halves = 16 bytes per store
+                for (int q4 = 0; q4 < 4; ++q4) {
                     uint32_t pk[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e)
@@ -210,19 +253,36 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_st32(tm_d3 + lane_base + ch * 32, sv);
             }
             tmem_wait_st();
-            // ---- right-hand sides: xu = beta V[:, t], xw = beta e^{b} K[:, t]  (t = tid) ----
-            float xu[64], xw[64];
+            // ---- rows / columns this thread owns: (beta V)^T row r, (beta e^b K)^T row r, column r of Q e^b ----
+            if (!mbar_wait_warp(bar(G_KQ_FULL0 + (c & 1)), (c >> 1) & 1, abort_flag)) { ok = false; break; }
+            {
+                const unsigned char* kq_blk = kq + (tid >> 6) * 16384;
+                unsigned char* qt_blk = sm + kOffQT + (tid >> 6) * 8192;
+                const int tcol = tid & 63;
+                unsigned char* rv_row = sm + kOffRV + r * 128;
+                unsigned char* rk_row = sm + kOffRK + r * 128;
 #pragma unroll
-            for (int i = 0; i < 64; ++i)
-                xu[i] = (i < n_valid) ? s_beta[i] * v[((size_t)(sq.row0 + tok0 + i) * kLaHeads + h) * kLaVd + tid] : 0.f;
-            if (!mbar_wait_warp(bar(G_KQ_FULL), par, abort_flag)) { ok = false; break; }
-            const unsigned char* kq_blk = sm + kOffKQ + (tid >> 6) * 16384;
-            const int tcol = tid & 63;
+                for (int c8 = 0; c8 < 8; ++c8) {
+                    uint32_t pv[4], pk[4];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const __half kh = *reinterpret_cast<const __half*>(kq_blk + i * 128 + (((tcol >> 3) ^ (i & 7)) << 4) + (tcol & 7) * 2);
-                xw[i] = s_beta[i] * s_eb[i] * __half2float(kh);
+                    for (int e = 0; e < 4; ++e) {
+                        const int i0 = c8 * 8 + 2 * e, i1 = i0 + 1;
+                        const uint32_t sw0 = (((tcol >> 3) ^ (i0 & 7)) << 4) + (tcol & 7) * 2;
+                        const uint32_t sw1 = (((tcol >> 3) ^ (i1 & 7)) << 4) + (tcol & 7) * 2;
+                        const float k0 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i0 * 128 + sw0));
+                        const float k1 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i1 * 128 + sw1));
+                        pv[e] = pack_half2(vcol[i0], vcol[i1]);
+                        pk[e] = pack_half2(s_beta[i0] * s_eb[i0] * k0, s_beta[i1] * s_eb[i1] * k1);
+                        const float q0 = __half2float(*reinterpret_cast<const __half*>(kq_blk + (64 + i0) * 128 + sw0));
+                        const float q1 = __half2float(*reinterpret_cast<const __half*>(kq_blk + (64 + i1) * 128 + sw1));
+                        *reinterpret_cast<uint16_t*>(qt_blk + i0 * 128 + sw0) = f2h_bits(s_eb[i0] * q0);
+                        *reinterpret_cast<uint16_t*>(qt_blk + i1 * 128 + sw1) = f2h_bits(s_eb[i1] * q1);
+                    }
+                    *reinterpret_cast<uint4*>(rv_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pv[0], pv[1], pv[2], pv[3]);
+                    *reinterpret_cast<uint4*>(rk_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
             }
+            mbar_arrive(bar(G_KQ_FREE));       // no thread reads this K/Q buffer after this point
             // ---- D1 -> A matrix (rows 0-63) and masked, decayed Q K^T (rows 64-127) ----
             if (!mbar_wait_warp(bar(G_A_DONE), par, abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -246,7 +306,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 } else {
                     const int i = r - 64;
                     const float bi = s_b[i];
-                    unsigned char* row_ptr = sm + kOffMQ + r * 128;
+                    unsigned char* row_ptr = sm + kOffMQ + i * 128;
 #pragma unroll
                     for (int c8 = 0; c8 < 8; ++c8) {
                         uint32_t pk[4];
@@ -257,103 +317,143 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                             const float m1 = (j1 <= i) ? expf(bi - s_b[j1]) * __uint_as_float(d1[j1 >> 5][j1 & 31]) : 0.f;
                             pk[e] = pack_half2(m0, m1);
                         }
-                        *reinterpret_cast<uint4*>(row_ptr + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        *reinterpret_cast<uint4*>(row_ptr + ((c8 ^ (i & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                     }
                 }
             }
             named_sync_128();
-            // ---- forward substitution (I + A) x = rhs, two columns per thread, fp32; four partial sums per
-            //      column keep the FMA chains short ----
-            {
-                const float4* AM4 = reinterpret_cast<const float4*>(AM);
+            // ---- T = (I + A)^-1, blocked 16 x 16: diagonal blocks by forward substitution, the rest by block products
+            //      T_ij = -T_ii sum_{k=j}^{i-1} A_ik T_kj.  The inner sums are staged in A's upper blocks, which are zero
+            //      and not otherwise used. ----
+            if (tid < 64) {
+                const int b0 = (tid >> 4) * 16, col = tid & 15;      // column `col` of diagonal block b0 / 16
+                float t[16];
 #pragma unroll
-                for (int i = 1; i < 64; ++i) {
-                    float u0 = 0.f, u1 = 0.f, u2 = 0.f, u3 = 0.f, w0 = 0.f, w1 = 0.f, w2 = 0.f, w3 = 0.f;
+                for (int i = 0; i < 16; ++i) t[i] = (i == col) ? 1.f : 0.f;
 #pragma unroll
-                    for (int j4 = 0; j4 * 4 < i; ++j4) {
-                        const float4 a = AM4[i * 16 + j4];     // entries with j >= i are exact zeros
-                        u0 += a.x * xu[j4 * 4];     w0 += a.x * xw[j4 * 4];
-                        u1 += a.y * xu[j4 * 4 + 1]; w1 += a.y * xw[j4 * 4 + 1];
-                        u2 += a.z * xu[j4 * 4 + 2]; w2 += a.z * xw[j4 * 4 + 2];
-                        u3 += a.w * xu[j4 * 4 + 3]; w3 += a.w * xw[j4 * 4 + 3];
-                    }
-                    xu[i] -= (u0 + u1) + (u2 + u3);
-                    xw[i] -= (w0 + w1) + (w2 + w3);
+                for (int i = 1; i < 16; ++i) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int j = 0; j < i; ++j) acc += AM[(b0 + i) * 64 + b0 + j] * t[j];
+                    t[i] -= acc;      // rows <= col keep their start value: A is strictly lower and t[j < col] = 0
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) TF[(b0 + i) * 64 + b0 + col] = t[i];
+            } else {
+                const int u = tid - 64;       // the other 64 threads clear T's six upper blocks
+                for (int idx = u; idx < 6 * 256; idx += 64) {
+                    const int blk = idx >> 8, e = idx & 255;
+                    const int bi = (blk < 3) ? 0 : (blk < 5 ? 1 : 2);
+                    const int bj = (blk < 3) ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+                    TF[(bi * 16 + (e >> 4)) * 64 + bj * 16 + (e & 15)] = 0.f;
                 }
             }
-            // ---- publish U (fp32, row-major), W and Q e^{b} (fp16, swizzled K-major A tile of (b)) ----
+            named_sync_128();
+            for (int i = 1; i < 4; ++i)   // first sub-diagonal
+                block_product(AM, (i - 1) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 1) * 16, 1.f, false, tid);
+            named_sync_128();
+            for (int i = 1; i < 4; ++i)
+                block_product(TF, i * 16, (i - 1) * 16, TF, i * 16, i * 16, AM, (i - 1) * 16, i * 16, -1.f, false, tid);
+            named_sync_128();
+            for (int i = 2; i < 4; ++i) {   // second sub-diagonal
+                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 2) * 16, TF, (i - 2) * 16, (i - 2) * 16, 1.f, false, tid);
+                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 2) * 16, 1.f, true, tid);
+            }
+            named_sync_128();
+            for (int i = 2; i < 4; ++i)
+                block_product(TF, i * 16, (i - 2) * 16, TF, i * 16, i * 16, AM, (i - 2) * 16, i * 16, -1.f, false, tid);
+            named_sync_128();
+            block_product(AM, 0, 48, AM, 48, 0, TF, 0, 0, 1.f, false, tid);      // corner block
+            block_product(AM, 0, 48, AM, 48, 16, TF, 16, 0, 1.f, true, tid);
+            block_product(AM, 0, 48, AM, 48, 32, TF, 32, 0, 1.f, true, tid);
+            named_sync_128();
+            block_product(TF, 48, 0, TF, 48, 48, AM, 0, 48, -1.f, false, tid);
+            named_sync_128();
+            {   // T -> fp16 hi + lo tiles (row = i, K = j)
+                const int i = tid >> 1, half = tid & 1;
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    uint32_t ph[4], pl[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = half * 32 + c8 * 8 + 2 * e;
+                        const float t0 = TF[i * 64 + j], t1 = TF[i * 64 + j + 1];
+                        const float h0 = __half2float(__float2half_rn(t0)), h1 = __half2float(__float2half_rn(t1));
+                        ph[e] = pack_half2(h0, h1);
+                        pl[e] = pack_half2(t0 - h0, t1 - h1);
+                    }
+                    const int chunk16 = half * 4 + c8;
+                    *reinterpret_cast<uint4*>(sm + kOffTT + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                    *reinterpret_cast<uint4*>(sm + kOffTT + 8192 + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar(G_B1));
+            // ---- W^T (lane = key dim) -> column r of the W tile ----
+            if (!mbar_wait_warp(bar(G_C1), par, abort_flag)) { ok = false; break; }
+            tc_fence_after();
             {
-                unsigned char* wq_blk = sm + kOffWQ + (tid >> 6) * 16384;
+                uint32_t w0[32], w1[32];
+                tmem_ld32(tm_wt + lane_base, w0);
+                tmem_ld32(tm_wt + lane_base + 32, w1);
+                tmem_wait_ld();
+                unsigned char* wt_blk = sm + kOffWT + (tid >> 6) * 8192;
+                const int tcol = tid & 63;
 #pragma unroll
                 for (int i = 0; i < 64; ++i) {
-                    US[i * kUSStride + tid] = xu[i];
-                    const uint32_t sw = (((tcol >> 3) ^ (i & 7)) << 4) + (tcol & 7) * 2;      // (64 + i) & 7 == i & 7
-                    *reinterpret_cast<uint16_t*>(wq_blk + i * 128 + sw) = f2h_bits(xw[i]);
-                    const __half qh = *reinterpret_cast<const __half*>(kq_blk + (64 + i) * 128 + sw);
-                    *reinterpret_cast<uint16_t*>(wq_blk + (64 + i) * 128 + sw) = f2h_bits(s_eb[i] * __half2float(qh));
+                    const float wv = __uint_as_float(i < 32 ? w0[i & 31] : w1[i & 31]);
+                    *reinterpret_cast<uint16_t*>(wt_blk + i * 128 + (((tcol >> 3) ^ (i & 7)) << 4) + (tcol & 7) * 2) = f2h_bits(wv);
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before();
-            mbar_arrive(bar(G_B_READY));
-            // ---- V_new = U - W S0 (threads 0-63, one token each) ----
-            if (!mbar_wait_warp(bar(G_B_DONE), par, abort_flag)) { ok = false; break; }
+            mbar_arrive(bar(G_B2));
+            // ---- V_new^T (lane = value dim): plain and decayed fp16 rows ----
+            if (!mbar_wait_warp(bar(G_C2), par, abort_flag)) { ok = false; break; }
             tc_fence_after();
-            if (r < 64) {
-                const float ebc = s_ebc[r];
-#pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t d2[32];
-                    tmem_ld32(tm_d2 + lane_base + ch * 32, d2);
-                    tmem_wait_ld();
-                    float vn[32];
+            {
+                uint32_t u0[32], u1[32];
+                tmem_ld32(tm_ut + lane_base, u0);
+                tmem_ld32(tm_ut + lane_base + 32, u1);
+                tmem_wait_ld();
+                unsigned char* rv_row = sm + kOffRV + r * 128;
+                unsigned char* rk_row = sm + kOffRK + r * 128;
 #pragma unroll
-                    for (int c2 = 0; c2 < 32; ++c2) vn[c2] = US[r * kUSStride + ch * 32 + c2] - __uint_as_float(d2[c2]);
-                    unsigned char* vn_row = sm + kOffVN + (ch >> 1) * 8192 + r * 128;
+                for (int c8 = 0; c8 < 8; ++c8) {
+                    uint32_t pa[4], pb[4];
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        uint32_t pk[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) pk[e] = pack_half2(vn[q4 * 8 + 2 * e], vn[q4 * 8 + 2 * e + 1]);
-                        const int chunk16 = (ch & 1) * 4 + q4;
-                        *reinterpret_cast<uint4*>(vn_row + ((chunk16 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    for (int e = 0; e < 4; ++e) {
+                        const int j0 = c8 * 8 + 2 * e, j1 = j0 + 1;
+                        const float x0 = __uint_as_float(j0 < 32 ? u0[j0 & 31] : u1[j0 & 31]);
+                        const float x1 = __uint_as_float(j1 < 32 ? u0[j1 & 31] : u1[j1 & 31]);
+                        pa[e] = pack_half2(x0, x1);
+                        pb[e] = pack_half2(x0 * s_ebc[j0], x1 * s_ebc[j1]);
                     }
-#pragma unroll
-                    for (int c2 = 0; c2 < 32; ++c2) {
-                        const int vd = ch * 32 + c2;
-                        *reinterpret_cast<uint16_t*>(sm + kOffVT + vd * 128 + (((r >> 3) ^ (vd & 7)) << 4) + (r & 7) * 2) =
-                            f2h_bits(ebc * vn[c2]);
-                    }
+                    *reinterpret_cast<uint4*>(rv_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                    *reinterpret_cast<uint4*>(rk_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before();
-            mbar_arrive(bar(G_V_READY));
-            mbar_arrive(bar(G_KQ_FREE));       // no thread reads the K/Q tile after this point
-            // ---- outputs: D2 rows 64-127 once (d) has been added ----
-            if (r >= 64) {
-                if (!mbar_wait_warp(bar(G_D_DONE), par, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-                const int i = r - 64;
-                float* orow = out + ((size_t)(sq.row0 + tok0 + i) * kLaHeads + h) * kLaVd;
-#pragma unroll 1
-                for (int ch = 0; ch < 4; ++ch) {
-                    uint32_t d2[32];
-                    tmem_ld32(tm_d2 + lane_base + ch * 32, d2);
-                    tmem_wait_ld();
-                    if (i < n_valid) {
+            mbar_arrive(bar(G_B3));
+            // ---- outputs: O^T (lane = value dim) -> out[token][head][vd] ----
+            if (!mbar_wait_warp(bar(G_C3), par, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            {
+                uint32_t o0[32], o1[32];
+                tmem_ld32(tm_ot + lane_base, o0);
+                tmem_ld32(tm_ot + lane_base + 32, o1);
+                tmem_wait_ld();
+                float* obase = out + ((size_t)(sq.row0 + tok0) * kLaHeads + h) * kLaVd + r;
 #pragma unroll
-                        for (int q4 = 0; q4 < 8; ++q4)
-                            *reinterpret_cast<float4*>(orow + ch * 32 + q4 * 4) =
-                                make_float4(__uint_as_float(d2[q4 * 4]), __uint_as_float(d2[q4 * 4 + 1]),
-                                            __uint_as_float(d2[q4 * 4 + 2]), __uint_as_float(d2[q4 * 4 + 3]));
-                    }
-                }
-                tc_fence_before();
+                for (int j = 0; j < 64; ++j)
+                    if (j < n_valid) obase[(size_t)j * kLaHeads * kLaVd] = __uint_as_float(j < 32 ? o0[j & 31] : o1[j & 31]);
             }
+            tc_fence_before();
         }
-        // ---- final state: D3 (S^T) -> state pool ----
-        if (ok && mbar_wait_warp(bar(G_D_DONE), (n_chunks - 1) & 1, abort_flag)) {
+        // ---- final state: D3 (S^T) -> state pool (every thread has seen the last chunk's C3) ----
+        if (ok) {
             tc_fence_after();
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {

@@ -9,6 +9,7 @@
 // [6144][3] with index 0 = newest.  Conv taps: w[d][3] * x_t + w[d][0] * x_{t-1} + w[d][1] * x_{t-2}
 // + w[d][2] * x_{t-3} (language_linear_attn.cpp:145-152).
 #include "kernels.cuh"
+#include "ptx_utils.cuh"
 
 #include <cstdlib>
 
@@ -222,6 +223,8 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
     const float* Sp = Sg + (size_t)(warp * 16) * kLaVd + 4 * lane;
 #pragma unroll
     for (int i = 0; i < 16; ++i) S[i] = __ldcs(reinterpret_cast<const float4*>(Sp + (size_t)i * kLaVd));
+    // The state was last written by this layer's previous step; everything read below comes from the preceding kernel.
+    pdl_enter();
 
     // conv + SiLU + state shift for the head's q, k, v channels (384 values, 256 threads)
     for (int i = tid; i < 3 * kLaKd; i += 256) {
@@ -366,8 +369,8 @@ int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max
         const char* e = std::getenv("B200ATTN_LA_DECODE_OCC");
         occ = (e && e[0] == '2') ? 2 : 3;
     }
-#define LA_DEC(T, O) la_decode_kernel<T, O><<<grid, 256, 0, s>>>(mixed, d_slots, max_seqs, rec_layer, rec_stride, conv_layer, \
-                                                               conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out)
+#define LA_DEC(T, O) launch_pdl(la_decode_kernel<T, O>, grid, dim3(256), 0, s, mixed, d_slots, max_seqs, rec_layer, rec_stride, \
+                                conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out)
     if (out_bf16) { if (occ == 2) LA_DEC(__nv_bfloat16, 2); else LA_DEC(__nv_bfloat16, 3); }
     else          { if (occ == 2) LA_DEC(float, 2); else LA_DEC(float, 3); }
 #undef LA_DEC

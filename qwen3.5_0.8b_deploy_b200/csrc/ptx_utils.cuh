@@ -80,6 +80,15 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
     return __all_sync(0xffffffffu, r);
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the
+// stream is still running.  pdl_wait() blocks until the predecessor has completed and its writes are visible: it
+// must precede every global read of produced data and every global write.  pdl_launch_dependents() lets the next
+// kernel of the stream begin its own prologue.  Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_enter() { pdl_wait(); pdl_launch_dependents(); }
+
 // ---- bulk async copy global -> shared, completion on an mbarrier (1-D TMA) -----------------------------------
 // dst, src 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {

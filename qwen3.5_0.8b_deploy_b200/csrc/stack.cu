@@ -8,6 +8,7 @@
 // graph-captured step (there: prefill, :391-479; here: decode with device-resident lengths and tokens).
 // The residual stream is fp32; GEMM operands are bf16 with fp32 accumulation (cuBLAS).
 #include "kernels.cuh"
+#include "ptx_utils.cuh"
 
 #include <algorithm>
 #include <new>
@@ -58,6 +59,7 @@ __device__ __forceinline__ float wsum(float v) {
 // h[row] = embed[token[row]] (bf16 -> fp32). grid rows, block 256 (4 elements per thread).
 __global__ void embed_gather_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed, int vocab,
                                     float* __restrict__ h) {
+    pdl_enter();
     const int row = blockIdx.x;
     int tok = tokens[row];
     tok = min(max(tok, 0), vocab - 1);
@@ -67,48 +69,50 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const __nv_b
     *reinterpret_cast<float4*>(h + (size_t)row * kHidden + 4 * threadIdx.x) = make_float4(a.x, a.y, b.x, b.y);
 }
 
-// RMSNorm with (1 + w), fp32 in, bf16 out (and optional fp32 copy).  One warp per row; optional row gather.
-// n_splits > 0: first x[row] += sum of the split-K partial rows (written back), i.e. the residual add of the
-// preceding output projection happens here.
-__global__ void __launch_bounds__(128)
+// RMSNorm with (1 + w), fp32 in, bf16 out (and optional fp32 copy).  One 256-thread block per row, one float4 per
+// thread; optional row gather.  n_splits > 0: first x[row] += sum of the split-K partial rows (written back), i.e.
+// the residual add of the preceding output projection happens here; the partial loads are issued four at a time.
+__global__ void __launch_bounds__(256)
 rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w, float eps,
                int rows, __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32,
                const float* __restrict__ partials, int n_splits, size_t split_stride) {
-    const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (gw >= rows) return;
-    const size_t srow = (size_t)(row_index ? row_index[gw] : gw);
-    float* src = x + srow * kHidden;
-    float v[32];
-    float ss = 0.f;
+    __shared__ float s_part[8];
+    const int row = blockIdx.x, t = threadIdx.x;
+    const float4 ww = *reinterpret_cast<const float4*>(w + 4 * t);
+    pdl_enter();
+    const size_t srow = (size_t)(row_index ? row_index[row] : row);
+    float4* src = reinterpret_cast<float4*>(x + srow * kHidden) + t;
+    float4 v = *src;
+    if (n_splits > 0) {
+        const float4* p = reinterpret_cast<const float4*>(partials + srow * kHidden) + t;
+        const size_t step = split_stride / 4;
+        for (int sp = 0; sp < n_splits; sp += 4) {
+            float4 q[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float4 t = *reinterpret_cast<const float4*>(src + 128 * i + 4 * lane);
-        if (n_splits > 0) {
-            for (int sp = 0; sp < n_splits; ++sp) {
-                const float4 p = *reinterpret_cast<const float4*>(partials + (size_t)sp * split_stride + srow * kHidden + 128 * i + 4 * lane);
-                t.x += p.x; t.y += p.y; t.z += p.z; t.w += p.w;
-            }
-            *reinterpret_cast<float4*>(src + 128 * i + 4 * lane) = t;
+            for (int e = 0; e < 4; ++e)
+                q[e] = (sp + e < n_splits) ? __ldcg(p + (size_t)(sp + e) * step) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { v.x += q[e].x; v.y += q[e].y; v.z += q[e].z; v.w += q[e].w; }
         }
-        v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
-        ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
+        *src = v;
     }
-    ss = wsum(ss);
+    float ss = wsum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    if ((t & 31) == 0) s_part[t >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += s_part[i];
     const float rms = sqrtf(ss / (float)kHidden + eps);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float4 ww = *reinterpret_cast<const float4*>(w + 128 * i + 4 * lane);
-        const float r0 = v[4 * i] / rms * (1.0f + ww.x), r1 = v[4 * i + 1] / rms * (1.0f + ww.y);
-        const float r2 = v[4 * i + 2] / rms * (1.0f + ww.z), r3 = v[4 * i + 3] / rms * (1.0f + ww.w);
-        if (out_bf16) {
-            __nv_bfloat162 a = __floats2bfloat162_rn(r0, r1), b = __floats2bfloat162_rn(r2, r3);
-            uint2 pk;
-            pk.x = *reinterpret_cast<uint32_t*>(&a);
-            pk.y = *reinterpret_cast<uint32_t*>(&b);
-            *reinterpret_cast<uint2*>(out_bf16 + (size_t)gw * kHidden + 128 * i + 4 * lane) = pk;
-        }
-        if (out_f32) *reinterpret_cast<float4*>(out_f32 + (size_t)gw * kHidden + 128 * i + 4 * lane) = make_float4(r0, r1, r2, r3);
+    const float r0 = v.x / rms * (1.0f + ww.x), r1 = v.y / rms * (1.0f + ww.y);
+    const float r2 = v.z / rms * (1.0f + ww.z), r3 = v.w / rms * (1.0f + ww.w);
+    if (out_bf16) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(r0, r1), b = __floats2bfloat162_rn(r2, r3);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&a);
+        pk.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(out_bf16 + (size_t)row * kHidden + 4 * t) = pk;
     }
+    if (out_f32) *reinterpret_cast<float4*>(out_f32 + (size_t)row * kHidden + 4 * t) = make_float4(r0, r1, r2, r3);
 }
 
 // act = silu(gate) * up.  gu rows hold tiles of 64 columns: 32 gate columns followed by the 32 matching up columns
@@ -435,7 +439,7 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
     const size_t pstride = (size_t)128 * kHidden;
     int pending = 0;
     for (int i = 0; i < st->cfg.num_layers; ++i) {
-        rmsnorm_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
+        launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
                                                         st->d_partials, pending, pstride);
         B2_LAUNCH_CHECK();
         DecodeOut dout{st->d_partials, pstride, 0};
@@ -445,7 +449,7 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
         else
             B2_TRY(la_forward_rows(st->la[st->layer_sub[i]], st->state, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots,
                                    decode, st->d_xb, true, st->d_h, 1.0f, tc ? &dout : nullptr, s));
-        rmsnorm_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
+        launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
                                                         st->d_partials, dout.n_splits, pstride);
         B2_LAUNCH_CHECK();
         if (tc) {
@@ -468,7 +472,7 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
 // Final norm of the selected rows (after adding `pending` partial matrices), tied LM head, greedy argmax.
 static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int pending, int* d_next, float* d_hidden_out,
                       cudaStream_t s) {
-    rmsnorm_kernel<<<ceil_div(n_seqs, 4), 128, 0, s>>>(st->d_h, d_row_index, st->d_final_norm, st->cfg.rms_eps, n_seqs, st->d_xb,
+    launch_pdl(rmsnorm_kernel, dim3(n_seqs), dim3(256), 0, s, st->d_h, d_row_index, st->d_final_norm, st->cfg.rms_eps, n_seqs, st->d_xb,
                                                       d_hidden_out ? d_hidden_out : nullptr, st->d_partials, pending,
                                                       (size_t)128 * kHidden);
     B2_LAUNCH_CHECK();
@@ -481,7 +485,7 @@ static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int
 }
 
 static int stack_decode_step(b200attn_stack st, int n_seqs, const int* d_tokens_in, int* d_tokens_out, cudaStream_t s) {
-    embed_gather_kernel<<<n_seqs, 256, 0, s>>>(d_tokens_in, st->d_embed, st->cfg.vocab_size, st->d_h);
+    launch_pdl(embed_gather_kernel, dim3(n_seqs), dim3(256), 0, s, d_tokens_in, st->d_embed, st->cfg.vocab_size, st->d_h);
     B2_LAUNCH_CHECK();
     int pending = 0;
     B2_TRY(stack_layers(st, n_seqs, nullptr, nullptr, n_seqs, st->d_slots, true, &pending, s));
@@ -506,7 +510,7 @@ extern "C" int b200attn_stack_prefill(b200attn_stack st, int n_seqs, int prompt_
         const int n = std::min(chunk, n_seqs - s0);
         const int rows = n * prompt_len;
         for (int i = 0; i < n; ++i) slots[i] = s0 + i;
-        embed_gather_kernel<<<rows, 256, 0, s>>>(d_tokens + (size_t)s0 * prompt_len, st->d_embed, st->cfg.vocab_size, st->d_h);
+        launch_pdl(embed_gather_kernel, dim3(rows), dim3(256), 0, s, d_tokens + (size_t)s0 * prompt_len, st->d_embed, st->cfg.vocab_size, st->d_h);
         count_launch();
         int pending = 0;
         rc = stack_layers(st, rows, slots.data(), counts.data(), n, nullptr, false, &pending, s);

@@ -18,7 +18,15 @@ def _build(ops, synth, weights, max_seqs=4, max_seq_len=128, kv_dtype=1):
     return st
 
 
-def test_prefill_and_decode_against_cpu_composition(ops, cuda, oracle, synth):
+@pytest.fixture(params=["cublas", "tc"])
+def decode_gemm(request, monkeypatch):
+    """Both implementations of the decode-step projections: cuBLAS + separate SwiGLU / argmax kernels, and the
+    tcgen05 skinny GEMM with fused epilogues.  The library reads the variable on every call."""
+    monkeypatch.setenv("B200ATTN_DECODE_GEMM", request.param)
+    return request.param
+
+
+def test_prefill_and_decode_against_cpu_composition(ops, cuda, oracle, synth, decode_gemm):
     torch = cuda
     from oracle import cpu_stack
     weights = cpu_stack.make_stack_weights(synth, 61, L, INTER, VOCAB, int8=True)
@@ -48,7 +56,7 @@ def test_prefill_and_decode_against_cpu_composition(ops, cuda, oracle, synth):
             assert logits[got[i]] >= logits.max() - 0.05 * (logits.max() - logits.mean()), f"step {d} seq {i}"
 
 
-def test_graph_replay_equals_eager_decode(ops, cuda, synth):
+def test_graph_replay_equals_eager_decode(ops, cuda, synth, decode_gemm):
     torch = cuda
     from oracle import cpu_stack
     weights = cpu_stack.make_stack_weights(synth, 62, L, INTER, VOCAB, int8=True)
