@@ -317,20 +317,51 @@ def main():
         barrier()
         ms_e2e = ev2.elapsed_time(ev3)
 
-        # per-kernel device times inside real (eager) steps: one prefill + 8 decode steps with event pairs around the kernels
-        prof = {}
+        # per-kernel device times (rank 0): the prefill kernels in an eager pass (milliseconds each, launch gaps do not
+        # matter), the decode kernels inside a captured decode step with event nodes around them and programmatic
+        # dependent launch off, so that an event pair sees exactly one kernel and no CPU launch gap.
+        prof, phases, timing = {}, {}, ""
         if rank == 0:
+            os.environ["B200ATTN_PDL"] = "0"
             st.reset_cache()
             ops.profile_reset(); ops.profile_enable(True)
             first = st.forward_batch_prefill(d_tokens)
-            cur = first
-            for _ in range(8):
-                cur = st.forward_batch_decode(cur)
+            st.set_tokens(first)
+            st.capture_decode(B)
+            st.launch_decode(8)
             stream.synchronize()
             ops.profile_enable(False)
             for name in ("fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append"):
                 prof[name] = ops.profile_read(name)
             ops.profile_reset()
+            timing = "event nodes inside the captured decode step"
+            if prof["la_decode"][1] == 0 or prof["fa_decode"][1] == 0:
+                # events recorded by graph nodes gave no time on this driver: eager decode steps instead (the event
+                # pairs then also see the CPU launch gap in front of each kernel)
+                timing = "eager launches"
+                ops.profile_enable(True)
+                cur = first
+                for _ in range(8):
+                    cur = st.forward_batch_decode(cur)
+                stream.synchronize()
+                ops.profile_enable(False)
+                for name in ("fa_decode", "la_decode", "kv_append"):
+                    prof[name] = ops.profile_read(name)
+                ops.profile_reset()
+            del os.environ["B200ATTN_PDL"]
+            st.capture_decode(B)
+            # where the job time goes: prefill pass vs captured decode steps
+            job_device()
+            ea, eb, ec = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            st.reset_cache()
+            ea.record(stream)
+            first = st.forward_batch_prefill(d_tokens)
+            st.set_tokens(first)
+            eb.record(stream)
+            st.launch_decode(G)
+            ec.record(stream)
+            stream.synchronize()
+            phases = dict(prefill_ms=ea.elapsed_time(eb), decode_step_ms=eb.elapsed_time(ec) / G)
 
     # NCCL: the only collective of the run, and only on the counters (max of the times, sum of the tokens)
     tokens_per_job = B * (P + G)
@@ -344,7 +375,7 @@ def main():
         # share of one whole job spent in each kernel class (launch counts of a full job x measured ms per launch)
         job_ms = dict(la_decode=per["la_decode"] * 18 * G, fa_decode=per["fa_decode"] * 6 * G,
                       fa_prefill=prof["fa_prefill"][0], la_prefill=prof["la_prefill"][0])
-        ctx_avg = P + 4.5                                                  # cache length seen by the 8 profiled decode steps
+        ctx_avg = P + (8 if timing.startswith("event") else 4.5)           # cache length the timed decode launches saw
         seqs_per_chunk = B / max(chunks, 1)
         roof = dict(
             la_decode=dict(bound="hbm", achieved=algo_la_decode_bytes(B) / (per["la_decode"] * 1e-3) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s"),
@@ -353,7 +384,7 @@ def main():
             la_prefill=dict(bound="tensor", achieved=algo_la_prefill_flops(seqs_per_chunk, P) / (per["la_prefill"] * 1e-3) / 1e12, peak=peaks["tflops_sustained"], unit="TFLOP/s"),
         )
         for k, r in roof.items():
-            r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], job_ms=job_ms[k], traffic=None, peak_source=peaks["source"])
+            r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], timing=(timing if k.endswith("decode") else "eager launches"), job_ms=job_ms[k], traffic=None, peak_source=peaks["source"])
         dominant = max(job_ms, key=job_ms.get)
         cpu = None
         if not args.no_cpu_baseline:
@@ -363,7 +394,7 @@ def main():
                     ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
                     data="synthetic", config=workload_config(args), clocks=clk,
                     e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=B * P * 4, d2h_bytes_per_step=B * G * 4),
-                    gpu_launches=launches, roofline=roof[dominant], roofline_other=[roof[k] for k in roof if k != dominant],
+                    gpu_launches=launches, phases=phases, roofline=roof[dominant], roofline_other=[roof[k] for k in roof if k != dominant],
                     cpu_baseline=cpu)
         print(json.dumps(line))
     if world > 1:

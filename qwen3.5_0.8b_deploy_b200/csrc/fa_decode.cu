@@ -1,11 +1,15 @@
 // D1: split-KV decode attention over the paged INT8 / FP16 cache.
 //
-// One CTA per (sequence, kv head, split).  A producer warp streams whole cache pages (K block,
-// token-minor V block and the two scale rows of one page and kv head are each contiguous) into a
-// shared-memory ring with 1-D bulk (TMA) copies; each consumer warp owns one ring stage and runs
-// the four query heads of the GQA group against its page on mma.sync m16n8k16 (fp16 operands, fp32
-// accumulation), so every K/V byte leaves HBM once for all four heads.  INT8 codes are widened to
-// fp16 in registers (exact); K scales multiply the logits, V scales are folded into P.
+// Persistent kernel, one CTA per SM.  The pages of all (sequence, kv head) pairs of the batch form one linear
+// list; it is cut into equal contiguous ranges, one per consumer WARP of the grid, so every SM streams the same
+// number of bytes whatever the sequence lengths are.  A producer warp streams whole cache pages (K block,
+// token-minor V block and the two scale rows of one page and kv head are each contiguous) into shared memory with
+// 1-D bulk (TMA) copies; each consumer warp owns a K buffer and a V buffer and runs the four query heads of the
+// GQA group against its pages on mma.sync m16n8k16 (fp16 operands, fp32 accumulation), so every K/V byte leaves
+// HBM once for all four heads.  INT8 codes are widened to fp16 in registers (exact); K scales multiply the
+// logits, V scales are folded into P.  A range that ends inside a (sequence, kv head) pair leaves a partial
+// (m, l, O) in global memory; the warp that delivers the last partial of a pair combines them, applies the gate
+// and writes the output (arrival counter in `counters`, left at zero again).
 //
 // Orientation: S^T[key, head] = K[key, dim] Q^T[dim, head] and O^T[dim, head] = V^T[dim, key] P^T[key, head],
 // so the big operands (K rows, token-minor V rows) are the row-major A fragments and load straight
@@ -31,70 +35,114 @@ struct DecodeCfg {
     static constexpr int kHalfBytes = kBlockBytes + kScaleBytes;              // one K (or V) buffer with its scale row
     static constexpr int kStageBytes = 2 * kHalfBytes;
     static constexpr int kWarps = kFp16 ? 3 : 6;                              // consumer warps, each with a K and a V buffer
-    static constexpr int kMergeBytes = 4 * kHeadDim * 4 + 32;                 // per warp: O^T [4][256] + m[4] + l[4]
-    static constexpr int kSmemBytes = kWarps * (kStageBytes + kMergeBytes) + 4 * kWarps * 8 + 16;
+    static constexpr int kSmemBytes = kWarps * kStageBytes + 4 * kWarps * 8 + 16;
     static constexpr int kThreads = (kWarps + 1) * 32;
     static constexpr float kVBoost = kFp16 ? 1.0f : 256.0f;                   // keeps P * v_scale out of fp16 subnormals
 };
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-// grid (max_splits, kv_heads, n_seqs).  The CTA that finishes last for a (sequence, kv head) combines the splits,
-// applies the gate and writes the output (arrival counter in `counters`, left at zero again).
+constexpr int kDecodeMaxSeqs = 2048;      // sequences per launch (prefix table in shared memory)
+
+// Position of linear page x: sequence (searched from `seq`, which must not be past it), kv head, page in sequence.
+__device__ __forceinline__ void locate_page(const int* s_pref, int n_seqs, int x, int& seq, int& kvh, int& page) {
+    while (seq + 1 < n_seqs && x >= 2 * s_pref[seq + 1]) ++seq;
+    const int pages = s_pref[seq + 1] - s_pref[seq];
+    const int rem = x - 2 * s_pref[seq];
+    kvh = rem >= pages ? 1 : 0;
+    page = rem - kvh * pages;
+}
+__device__ __forceinline__ int find_seq(const int* s_pref, int n_seqs, int x) {   // largest seq with 2 * pref[seq] <= x
+    int lo = 0, hi = n_seqs - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (2 * s_pref[mid] <= x) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+// grid (number of SMs).  max_parts = partial slots per (sequence, kv head) in part_o / part_ml (>= 3).
 template <bool kFp16, typename OutT>
 __global__ void __launch_bounds__(DecodeCfg<kFp16>::kThreads, 1)
-fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int len_add,
-                       const __half* __restrict__ q, const __half* __restrict__ gate, int pages_per_warp,
-                       int max_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-                       int* __restrict__ counters, OutT* __restrict__ out) {
+fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int n_seqs, int len_add,
+                       const __half* __restrict__ q, const __half* __restrict__ gate, int max_parts,
+                       float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
+                       OutT* __restrict__ out) {
     using Cfg = DecodeCfg<kFp16>;
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ int s_last;
-    const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    __shared__ int s_pref[kDecodeMaxSeqs + 1];      // s_pref[i] = pages of the sequences before i
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    pdl_enter();
-
-    const int slot = slots[seq];
-    if (slot < 0 || slot >= kv.max_seqs) return;
-    if (*reinterpret_cast<volatile int*>(kv.error) == 3) return;     // an earlier CTA gave up: do not queue more bounded waits
-    const int L = kv.lens[layer * kv.max_seqs + slot] + len_add;
-    const int n_pages = (L + kPageTokens - 1) / kPageTokens;
-    const int pages_per_cta = pages_per_warp * Cfg::kWarps;
-    const int p_begin = split * pages_per_cta;
-    if (p_begin >= n_pages) {
-        // A sequence without cached tokens has no split at all: split 0 writes zeros so the output is defined.
-        if (n_pages == 0 && split == 0)
-            for (int idx = threadIdx.x; idx < 4 * kHeadDim; idx += Cfg::kThreads)
-                out[((size_t)seq * kFaHeads + kvh * 4) * kHeadDim + idx] = (OutT)0.f;
-        return;
-    }
-    const int p_end = min(n_pages, p_begin + pages_per_cta);
-    const int n_my = p_end - p_begin;
-    const int n_splits = (n_pages + pages_per_cta - 1) / pages_per_cta;
 
     unsigned char* stage_base = smem;
-    float* merge_base = reinterpret_cast<float*>(smem + Cfg::kWarps * Cfg::kStageBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kWarps * (Cfg::kStageBytes + Cfg::kMergeBytes));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kWarps * Cfg::kStageBytes);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 4 * Cfg::kWarps);
     const uint32_t full_k0 = smem_u32(bars), full_v0 = full_k0 + 8 * Cfg::kWarps;
     const uint32_t empty_k0 = full_v0 + 8 * Cfg::kWarps, empty_v0 = empty_k0 + 8 * Cfg::kWarps;
-
     if (threadIdx.x == 0) {
         for (int i = 0; i < 4 * Cfg::kWarps; ++i) mbar_init(full_k0 + 8 * i, 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
+    pdl_enter();
+    __shared__ int s_stop;
+    if (threadIdx.x == 0) s_stop = (*reinterpret_cast<volatile int*>(kv.error) == 3);   // an earlier launch gave up: queue no more bounded waits
+
+    // ---- pages per sequence and their prefix sums ----
+    for (int i = threadIdx.x; i < n_seqs; i += Cfg::kThreads) {
+        const int slot = slots[i];
+        int pages = 0;
+        if (slot >= 0 && slot < kv.max_seqs) pages = (kv.lens[layer * kv.max_seqs + slot] + len_add + kPageTokens - 1) / kPageTokens;
+        s_pref[i + 1] = pages;
+        if (pages == 0 && blockIdx.x == 0 && slot >= 0 && slot < kv.max_seqs)    // no cached token: the output is defined as zero
+            for (int idx = 0; idx < kFaHeads * kHeadDim; ++idx) out[(size_t)i * kFaHeads * kHeadDim + idx] = (OutT)0.f;
+    }
+    if (threadIdx.x == 0) s_pref[0] = 0;
     __syncthreads();
+    if (s_stop) return;
+    if (warp == 0) {
+        const int per = (n_seqs + 31) / 32;
+        const int b0 = min(n_seqs, lane * per), b1 = min(n_seqs, b0 + per);
+        int sum = 0;
+        for (int i = b0; i < b1; ++i) sum += s_pref[i + 1];
+        int incl = sum;
+#pragma unroll
+        for (int o2 = 1; o2 < 32; o2 <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o2);
+            if (lane >= o2) incl += v;
+        }
+        int off = incl - sum;
+        for (int i = b0; i < b1; ++i) { off += s_pref[i + 1]; s_pref[i + 1] = off; }
+    }
+    __syncthreads();
+    const int P = 2 * s_pref[n_seqs];                 // linear page list: sequence-major, then kv head, then page
+    if (P == 0) return;
+    // Equal contiguous ranges, one per consumer warp of the grid; a floor on the range length bounds the number of
+    // ranges that can touch one (sequence, kv head) pair to max_parts.
+    const int W = gridDim.x * Cfg::kWarps;
+    const int r_min = max(1, (kv.max_pages_per_seq + max_parts - 3) / (max_parts - 2));
+    const int W_eff = min(W, max(1, P / r_min));
+    auto range_start = [&](int w) { return (int)(((long long)w * P) / W_eff); };
+    auto owner_of = [&](int x) { return (int)((((long long)(x + 1)) * W_eff - 1) / P); };   // worker whose range holds page x
 
     if (warp == Cfg::kWarps) {
         // ---------------- producer: one lane keeps every warp's K and V buffer refilled ----------------
         if (lane == 0) {
-            const int* bt = kv.block_table + (size_t)slot * kv.max_pages_per_seq;
+            int xk[Cfg::kWarps], xv[Cfg::kWarps], xe[Cfg::kWarps], sk[Cfg::kWarps], sv[Cfg::kWarps];
             int rk[Cfg::kWarps], rv[Cfg::kWarps];      // rounds issued per warp
+            int remaining = 0;
 #pragma unroll
-            for (int w = 0; w < Cfg::kWarps; ++w) { rk[w] = 0; rv[w] = 0; }
-            int remaining = 2 * n_my;
+            for (int w = 0; w < Cfg::kWarps; ++w) {
+                const int wid = blockIdx.x + gridDim.x * w;
+                rk[w] = 0; rv[w] = 0;
+                xk[w] = xv[w] = xe[w] = 0; sk[w] = sv[w] = 0;
+                if (wid < W_eff) {
+                    xk[w] = xv[w] = range_start(wid);
+                    xe[w] = range_start(wid + 1);
+                    if (xe[w] > xk[w]) sk[w] = sv[w] = find_seq(s_pref, n_seqs, xk[w]);
+                    remaining += 2 * (xe[w] - xk[w]);
+                }
+            }
             const uint64_t t0 = global_timer_ns();
             uint32_t idle = 0;
             while (remaining > 0) {
@@ -103,12 +151,15 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                 for (int w = 0; w < Cfg::kWarps; ++w) {
 #pragma unroll
                     for (int is_v = 0; is_v < 2; ++is_v) {
+                        const int x = is_v ? xv[w] : xk[w];
+                        if (x >= xe[w]) continue;
                         const int r = is_v ? rv[w] : rk[w];
-                        const int i = w + r * Cfg::kWarps;
-                        if (i >= n_my) continue;
                         const uint32_t eb = (is_v ? empty_v0 : empty_k0) + 8 * w;
                         if (r > 0 && !mbar_test_wait(eb, (r - 1) & 1)) continue;
-                        const int page = bt[p_begin + i];
+                        int seq = is_v ? sv[w] : sk[w], kvh, pg;
+                        locate_page(s_pref, n_seqs, x, seq, kvh, pg);
+                        if (is_v) sv[w] = seq; else sk[w] = seq;
+                        const int page = kv.block_table[(size_t)slots[seq] * kv.max_pages_per_seq + pg];
                         const size_t head_base = (size_t)(layer * kv.num_pages + page) * kFaKvHeads + kvh;
                         const unsigned char* src = reinterpret_cast<const unsigned char*>(is_v ? kv.v : kv.k) + head_base * Cfg::kBlockBytes;
                         const uint32_t dst = smem_u32(stage_base + w * Cfg::kStageBytes + is_v * Cfg::kHalfBytes);
@@ -117,7 +168,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                         bulk_g2s(dst, src, Cfg::kBlockBytes, fb);
                         if constexpr (!kFp16)
                             bulk_g2s(dst + Cfg::kBlockBytes, (is_v ? kv.vs : kv.ks) + head_base * kPageTokens, Cfg::kScaleBytes, fb);
-                        if (is_v) ++rv[w]; else ++rk[w];
+                        if (is_v) { ++rv[w]; ++xv[w]; } else { ++rk[w]; ++xk[w]; }
                         --remaining;
                         progressed = true;
                     }
@@ -130,6 +181,27 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
         }
     } else {
         // ---------------- consumers ----------------
+        const int wid = blockIdx.x + gridDim.x * warp;
+        int x = 0, x_end = 0;
+        if (wid < W_eff) { x = range_start(wid); x_end = range_start(wid + 1); }
+        const float sm_scale = kLog2e / 16.0f;   // 1/sqrt(256), logits kept in log2 units
+        const unsigned char* sK = stage_base + warp * Cfg::kStageBytes;
+        const float* sKs = reinterpret_cast<const float*>(sK + Cfg::kBlockBytes);
+        const unsigned char* sV = sK + Cfg::kHalfBytes;
+        const float* sVs = reinterpret_cast<const float*>(sV + Cfg::kBlockBytes);
+        const uint32_t my_full_k = full_k0 + 8 * warp, my_full_v = full_v0 + 8 * warp;
+        const uint32_t my_empty_k = empty_k0 + 8 * warp, my_empty_v = empty_v0 + 8 * warp;
+        int round = 0;
+        int seq = (x < x_end) ? find_seq(s_pref, n_seqs, x) : 0;
+        bool alive = true;
+        while (x < x_end && alive) {
+        // ---- one (sequence, kv head) pair, pages [pg0, pg0 + n_my) of it ----
+        int kvh, pg0;
+        locate_page(s_pref, n_seqs, x, seq, kvh, pg0);
+        const int seg_pages = s_pref[seq + 1] - s_pref[seq];
+        const int seg_begin = 2 * s_pref[seq] + kvh * seg_pages;
+        const int n_my = min(x_end, seg_begin + seg_pages) - x;
+        const int L = kv.lens[layer * kv.max_seqs + slots[seq]] + len_add;
         // Q^T B-fragments: k-step ks = 4*blk + s covers dims 64*blk + 16*t + 4*s + {0,1 | 2,3}; head = g (< 4).
         uint32_t qf[16][2];
         {
@@ -146,18 +218,10 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
 #pragma unroll
         for (int j = 0; j < 16; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-        const float sm_scale = kLog2e / 16.0f;   // 1/sqrt(256), logits kept in log2 units
 
-        const unsigned char* sK = stage_base + warp * Cfg::kStageBytes;
-        const float* sKs = reinterpret_cast<const float*>(sK + Cfg::kBlockBytes);
-        const unsigned char* sV = sK + Cfg::kHalfBytes;
-        const float* sVs = reinterpret_cast<const float*>(sV + Cfg::kBlockBytes);
-        const uint32_t my_full_k = full_k0 + 8 * warp, my_full_v = full_v0 + 8 * warp;
-        const uint32_t my_empty_k = empty_k0 + 8 * warp, my_empty_v = empty_v0 + 8 * warp;
-
-        for (int i = warp, round = 0; i < n_my; i += Cfg::kWarps, ++round) {
-            if (!mbar_wait_warp(my_full_k, round & 1, abort_flag)) break;
-            const int page_pos0 = (p_begin + i) * kPageTokens;
+        for (int i = 0; i < n_my; ++i, ++round) {
+            if (!mbar_wait_warp(my_full_k, round & 1, abort_flag)) { alive = false; break; }
+            const int page_pos0 = (pg0 + i) * kPageTokens;
 
             // ---- S^T = K Q^T for the four 16-token tiles of the page ----
             float s[4][4];
@@ -232,7 +296,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                 l0 += p[w][0] + p[w][2]; l1 += p[w][1] + p[w][3];
             }
             // ---- O^T += V^T P^T ----
-            if (!mbar_wait_warp(my_full_v, round & 1, abort_flag)) break;
+            if (!mbar_wait_warp(my_full_v, round & 1, abort_flag)) { alive = false; break; }
             uint32_t pb[4][2];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -275,98 +339,117 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
             __syncwarp();
             if (lane == 0) mbar_arrive(my_empty_v);
         }
-        // ---- publish this warp's (m, l, O^T) for the CTA merge ----
+        if (!alive) break;
+        // ---- this range's share of the pair is done: write the output, or a partial for the combine ----
 #pragma unroll
         for (int off = 4; off < 32; off <<= 1) {
             l0 += __shfl_xor_sync(0xffffffffu, l0, off);
             l1 += __shfl_xor_sync(0xffffffffu, l1, off);
         }
-        float* mO = merge_base + warp * (Cfg::kMergeBytes / 4);
-        float* mM = mO + 4 * kHeadDim;
-        float* mL = mM + 4;
-        if (t < 2) {
+        constexpr float inv_boost = 1.0f / Cfg::kVBoost;
+        const int pair = seq * kFaKvHeads + kvh;
+        const int w_first = owner_of(seg_begin), w_last = owner_of(seg_begin + seg_pages - 1);
+        const int n_parts = w_last - w_first + 1;
+        const size_t obase = ((size_t)seq * kFaHeads + kvh * 4) * kHeadDim;
+        if (n_parts == 1) {
+            if (t < 2) {
+                const float i0 = inv_boost / l0, i1 = inv_boost / l1;
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                mO[(2 * t) * kHeadDim + 16 * j + g] = o[j][0];
-                mO[(2 * t + 1) * kHeadDim + 16 * j + g] = o[j][1];
-                mO[(2 * t) * kHeadDim + 16 * j + 8 + g] = o[j][2];
-                mO[(2 * t + 1) * kHeadDim + 16 * j + 8 + g] = o[j][3];
+                for (int j = 0; j < 16; ++j) {
+                    const size_t a0 = obase + (size_t)(2 * t) * kHeadDim + 16 * j + g, a1 = a0 + kHeadDim;
+                    float r0 = o[j][0] * i0, r1 = o[j][1] * i1, r2 = o[j][2] * i0, r3 = o[j][3] * i1;
+                    if (gate) {
+                        r0 *= __half2float(gate[a0]); r1 *= __half2float(gate[a1]);
+                        r2 *= __half2float(gate[a0 + 8]); r3 *= __half2float(gate[a1 + 8]);
+                    }
+                    out[a0] = (OutT)r0; out[a1] = (OutT)r1; out[a0 + 8] = (OutT)r2; out[a1 + 8] = (OutT)r3;
+                }
             }
-            if (g == 0) { mM[2 * t] = m0; mM[2 * t + 1] = m1; mL[2 * t] = l0; mL[2 * t + 1] = l1; }
-        }
-    }
-    __syncthreads();
-    if (*abort_flag) {
-        if (threadIdx.x == 0) atomicExch(kv.error, 3);
-        return;
-    }
-    // ---- merge the consumer warps and write this split's partial ----
-    const size_t pbase = ((size_t)(seq * kFaKvHeads + kvh) * max_splits) * 4;
-    for (int idx = threadIdx.x; idx < 4 * kHeadDim; idx += Cfg::kThreads) {
-        const int head = idx / kHeadDim, dim = idx % kHeadDim;
-        float mmax = -INFINITY;
+        } else {
+            const size_t pbase = ((size_t)pair * max_parts) * 4;
+            const int part = wid - w_first;
+            if (t < 2) {
+                float* po0 = part_o + (pbase + part * 4 + 2 * t) * kHeadDim;
+                float* po1 = po0 + kHeadDim;
 #pragma unroll
-        for (int w = 0; w < Cfg::kWarps; ++w) mmax = fmaxf(mmax, merge_base[w * (Cfg::kMergeBytes / 4) + 4 * kHeadDim + head]);
-        float acc = 0.f, lsum = 0.f;
+                for (int j = 0; j < 16; ++j) {
+                    po0[16 * j + g] = o[j][0]; po1[16 * j + g] = o[j][1];
+                    po0[16 * j + 8 + g] = o[j][2]; po1[16 * j + 8 + g] = o[j][3];
+                }
+                if (g == 0) {
+                    float* ml = part_ml + (pbase + part * 4 + 2 * t) * 2;
+                    ml[0] = m0; ml[1] = l0; ml[2] = m1; ml[3] = l1;
+                }
+            }
+            __threadfence();
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                const int old = atomicAdd(&counters[pair], 1);
+                last = (old == n_parts - 1);
+                if (last) counters[pair] = 0;          // ready for the next launch
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {                                // the last partial of the pair to arrive: combine them all
+                __threadfence();
+#pragma unroll 1
+                for (int head = 0; head < 4; ++head) {
+                    float mmax = -INFINITY;
+                    for (int sp = 0; sp < n_parts; ++sp) mmax = fmaxf(mmax, __ldcg(&part_ml[(pbase + sp * 4 + head) * 2]));
+                    float acc[8], lsum = 0.f;
 #pragma unroll
-        for (int w = 0; w < Cfg::kWarps; ++w) {
-            const float* mw = merge_base + w * (Cfg::kMergeBytes / 4);
-            const float wgt = exp2f(mw[4 * kHeadDim + head] - mmax);   // a warp without pages has m = -inf -> weight 0
-            acc += mw[head * kHeadDim + dim] * wgt;
-            lsum += mw[4 * kHeadDim + 4 + head] * wgt;
+                    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+                    for (int sp = 0; sp < n_parts; ++sp) {
+                        const float wgt = exp2f(__ldcg(&part_ml[(pbase + sp * 4 + head) * 2]) - mmax);
+                        lsum += __ldcg(&part_ml[(pbase + sp * 4 + head) * 2 + 1]) * wgt;
+                        const float* po = part_o + (pbase + sp * 4 + head) * kHeadDim + lane;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) acc[k] += __ldcg(po + 32 * k) * wgt;
+                    }
+                    const float inv = inv_boost / lsum;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const size_t oo = obase + (size_t)head * kHeadDim + lane + 32 * k;
+                        float r = acc[k] * inv;
+                        if (gate) r *= __half2float(gate[oo]);
+                        out[oo] = (OutT)r;
+                    }
+                }
+            }
         }
-        part_o[(pbase + split * 4 + head) * kHeadDim + dim] = acc;
-        if (dim == 0) { part_ml[(pbase + split * 4 + head) * 2] = mmax; part_ml[(pbase + split * 4 + head) * 2 + 1] = lsum; }
-    }
-    // ---- the last split to arrive combines all of them ----
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const int old = atomicAdd(&counters[seq * kFaKvHeads + kvh], 1);
-        s_last = (old == n_splits - 1);
-        if (s_last) counters[seq * kFaKvHeads + kvh] = 0;   // ready for the next launch
+        x += n_my;
+        }   // pairs of this range
     }
     __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    constexpr float inv_boost = 1.0f / Cfg::kVBoost;
-    for (int idx = threadIdx.x; idx < 4 * kHeadDim; idx += Cfg::kThreads) {
-        const int head = idx / kHeadDim, dim = idx % kHeadDim;
-        float mmax = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) mmax = fmaxf(mmax, __ldcg(&part_ml[(pbase + sp * 4 + head) * 2]));
-        float acc = 0.f, lsum = 0.f;
-        for (int sp = 0; sp < n_splits; ++sp) {
-            const float wgt = exp2f(__ldcg(&part_ml[(pbase + sp * 4 + head) * 2]) - mmax);
-            acc += __ldcg(&part_o[(pbase + sp * 4 + head) * kHeadDim + dim]) * wgt;
-            lsum += __ldcg(&part_ml[(pbase + sp * 4 + head) * 2 + 1]) * wgt;
-        }
-        float r = acc / lsum * inv_boost;
-        const size_t oo = ((size_t)seq * kFaHeads + kvh * 4 + head) * kHeadDim + dim;
-        if (gate) r *= __half2float(gate[oo]);
-        out[oo] = (OutT)r;
-    }
+    if (*abort_flag && threadIdx.x == 0) atomicExch(kv.error, 3);
 }
 
-int fa_decode_max_splits(bool fp16, int max_pages_per_seq, int pages_per_warp) {
-    const int per_cta = pages_per_warp * (fp16 ? DecodeCfg<true>::kWarps : DecodeCfg<false>::kWarps);
-    return ceil_div(max_pages_per_seq, per_cta);
-}
+// Partial slots per (sequence, kv head) the kernel may use; callers size part_o / part_ml with it.
+int fa_decode_max_splits(bool, int, int) { return 16; }
 
+// pages_per_warp is unused (ranges are balanced on the device); max_splits = partial slots per pair in the scratch.
 int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, int len_add, const __half* q,
                      const __half* gate, int pages_per_warp, int max_splits, float* part_o, float* part_ml, int* counters,
                      void* out, bool out_bf16, cudaStream_t s) {
-    dim3 grid(max_splits, kFaKvHeads, n_seqs);
+    (void)pages_per_warp;
+    B2_CHECK_ARG(n_seqs > 0 && n_seqs <= kDecodeMaxSeqs, "decode attention: %d sequences outside (0, %d]", n_seqs, kDecodeMaxSeqs);
+    B2_CHECK_ARG(max_splits >= 3, "decode attention: scratch for %d partials per head group, need >= 3", max_splits);
+    static int n_sm = 0;
     static bool attr_done = false;
     if (!attr_done) {
+        int dev = 0;
+        B2_CUDA(cudaGetDevice(&dev));
+        B2_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
         B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<true, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<true>::kSmemBytes));
         B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<true, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<true>::kSmemBytes));
         B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<false, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<false>::kSmemBytes));
         B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<false, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<false>::kSmemBytes));
         attr_done = true;
     }
+    dim3 grid(n_sm);
 #define FA_DEC_LAUNCH(F16, T)                                                                                          \
     launch_pdl(fa_decode_split_kernel<F16, T>, grid, dim3(DecodeCfg<F16>::kThreads), DecodeCfg<F16>::kSmemBytes, s,    \
-               kv, layer, d_slots, len_add, q, gate, pages_per_warp, max_splits, part_o, part_ml, counters, (T*)out)
+               kv, layer, d_slots, n_seqs, len_add, q, gate, max_splits, part_o, part_ml, counters, (T*)out)
     if (kv.is_fp16) { if (out_bf16) FA_DEC_LAUNCH(true, __nv_bfloat16); else FA_DEC_LAUNCH(true, float); }
     else            { if (out_bf16) FA_DEC_LAUNCH(false, __nv_bfloat16); else FA_DEC_LAUNCH(false, float); }
 #undef FA_DEC_LAUNCH

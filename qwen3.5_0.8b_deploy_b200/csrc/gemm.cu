@@ -11,13 +11,9 @@ namespace b200 {
 
 thread_local char g_error[512] = "";
 thread_local long long g_launches = 0;
-bool pdl_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = std::getenv("B200ATTN_PDL");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
+bool pdl_enabled() {     // read on every launch so one process can compare both modes
+    const char* e = std::getenv("B200ATTN_PDL");
+    return !(e && e[0] == '0');
 }
 
 void set_error(const char* fmt, ...) {
@@ -148,6 +144,7 @@ extern "C" int b200attn_profile_reset(void) {
         r.ev.clear();
         if (r.open) { cudaEventDestroy(r.open); r.open = nullptr; }
     }
+    (void)cudaGetLastError();
     return 0;
 }
 extern "C" int b200attn_profile_read(const char* name, double* total_ms_out, long long* launches_out) {
@@ -158,11 +155,13 @@ extern "C" int b200attn_profile_read(const char* name, double* total_ms_out, lon
     B2_CHECK_ARG(k >= 0, "profile_read: unknown kernel class '%s'", name);
     B2_CUDA(cudaDeviceSynchronize());
     double total = 0.0;
+    long long timed = 0;
     for (auto& p : g_prof[k].ev) {
         float ms = 0.f;
-        if (cudaEventElapsedTime(&ms, p.first, p.second) == cudaSuccess) total += ms;
+        if (cudaEventElapsedTime(&ms, p.first, p.second) == cudaSuccess) { total += ms; ++timed; }
     }
+    (void)cudaGetLastError();      // a pair that could not be timed must not surface as the next launch's error
     *total_ms_out = total;
-    *launches_out = (long long)g_prof[k].ev.size();
+    *launches_out = timed;         // pairs that produced a time
     return 0;
 }

@@ -16,11 +16,16 @@
 //   (a)  D1  [128 x 64] = [K ; Q] K^T                         rows 0-63: K K^T, rows 64-127: Q K^T
 //   (uw) Ut  [vd x 64]  = (beta V)^T T^T,   Wt [kd x 64] = (beta e^b K)^T T^T     (T as an fp16 hi + lo pair)
 //   (ws) Ut -= S0^T W^T                                        -> V_new^T, accumulated in place (negated A operand)
-//   (o)  Ot  [vd x 64]  = S0^T (Q e^b)^T + V_new^T Mq^T
+//   (o)  Ot  [vd x 64]  = S0^T (Q e^b)^T + V_new^T Mq^T       (Q is scaled in place in its TMA tile)
 //   (u)  D3  [vd x kd]  = e^{b_C} D3 + (e^{b_C-b} V_new)^T K  D3 holds S^T for the whole sequence
 // tcgen05.mma kind::f16: fp16 operands (the same 10-bit mantissa as tf32), fp32 accumulation; 128-byte swizzle.
 // T itself is built in fp32 in shared memory by a blocked inverse (16 x 16 blocks) on the CUDA cores.
-// Warps 0-3 compute, warp 4 issues TMA loads (K/Q tiles double-buffered) and MMAs.  All waits are bounded.
+//
+// Eight compute warps (two threads per TMEM lane, each owning half of the 64 token columns) and one warp that
+// issues TMA loads (K/Q tiles double-buffered) and MMAs.  The chunk is split in a front half that does not need
+// the state (scalars, A, T, operand tiles -> B1) and a back half (S0 tile, W, V_new -> B2, B3); the front half of
+// chunk c+1 runs while the tensor core finishes (o) and (u) of chunk c, whose outputs are stored one chunk late.
+// All waits are bounded.
 #include "kernels.cuh"
 #include "tc05.cuh"
 
@@ -29,46 +34,42 @@ namespace b200 {
 constexpr int kC = 64;
 // shared-memory map (bytes from a 1024-aligned base)
 constexpr uint32_t kOffKQ = 0;        // 2 buffers x [2 blocks][128 rows][128 B]: rows 0-63 K chunk, rows 64-127 Q chunk
-constexpr uint32_t kOffST = 65536;    // S0^T fp16: [2 blocks (64 kd)][128 vd rows][128 B]            A of (ws), (o)
-constexpr uint32_t kOffRV = 98304;    // (beta V)^T [128 vd rows][64 tokens];  later V_new^T           A of (uw) / (o)
-constexpr uint32_t kOffRK = 114688;   // (beta e^b K)^T [128 kd rows][64 tokens]; later decayed V_new^T A of (uw) / (u)
-constexpr uint32_t kOffTT = 131072;   // T hi [64][64] fp16, then T lo                                   B of (uw)
-constexpr uint32_t kOffWT = 147456;   // W [2 blocks][64 token rows][128 B]                              B of (ws)
-constexpr uint32_t kOffQT = 163840;   // Q e^b, same shape                                               B of (o)
-constexpr uint32_t kOffMQ = 180224;   // Mq [64][64] fp16                                                B of (o)
-constexpr uint32_t kOffAM = 188416;   // fp32 A [64][64]; its (zero) upper blocks double as scratch of the inverse
-constexpr uint32_t kOffTF = 204800;   // fp32 T [64][64]
-constexpr uint32_t kOffSC = 221184;   // scalars: b[64], beta[64], eb[64], ebc[64]
-constexpr uint32_t kOffBarG = 222208;
+constexpr uint32_t kOffAM = 65536;    // fp32 A [64][64]; its (zero) upper blocks double as scratch of the inverse
+constexpr uint32_t kOffTF = 81920;    // fp32 T [64][64]
+constexpr uint32_t kOffST = 65536;    // S0^T fp16 [2 blocks (64 kd)][128 vd rows][128 B], over A / T once T is converted
+constexpr uint32_t kOffRV = 98304;    // (beta V)^T [128 vd rows][64 tokens]            A of (uw)
+constexpr uint32_t kOffRK = 114688;   // (beta e^b K)^T [128 kd rows][64 tokens]        A of (uw)
+constexpr uint32_t kOffVN = 131072;   // V_new^T [128 vd rows][64 tokens]               A of (o)
+constexpr uint32_t kOffVS = 147456;   // (e^{b_C-b} V_new)^T                            A of (u)
+constexpr uint32_t kOffTT = 163840;   // T hi [64][64] fp16, then T lo                  B of (uw)
+constexpr uint32_t kOffWT = 163840;   // W [2 blocks][64 token rows][128 B], over T     B of (ws)
+constexpr uint32_t kOffMQ = 180224;   // 2 buffers x Mq [64][64] fp16                   B of (o)
+constexpr uint32_t kOffSC = 196608;   // 2 buffers x scalars: b[64], beta[64], eb[64], ebc[64]
+constexpr uint32_t kOffBarG = 198656;
 constexpr uint32_t kG1Smem = kOffBarG + 128 + 1024;
-enum { G_KQ_FULL0 = 0, G_KQ_FULL1, G_A_DONE, G_B1, G_C1, G_B2, G_C2, G_B3, G_C3, G_KQ_FREE, G_BAR_COUNT };
+constexpr int kG1Threads = 288;
+enum { G_KQ_FULL0 = 0, G_KQ_FULL1, G_A_DONE, G_B1, G_C1, G_B2, G_C2, G_B3, G_C3, G_BAR_COUNT };
 
-__device__ __forceinline__ void named_sync_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-__device__ __forceinline__ uint16_t f2h_bits(float x) {
-    const __half h = __float2half_rn(x);
-    return *reinterpret_cast<const uint16_t*>(&h);
-}
+__device__ __forceinline__ void named_sync_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // dst(16x16 block at dr,dc) (+)= sign * A(16x16 at ar,ac) * B(16x16 at br,bc); matrices 64x64 fp32 row-major in
-// shared memory; 128 threads, two outputs each.
+// shared memory; 256 threads, one output each.
 __device__ __forceinline__ void block_product(float* dst, int dr, int dc, const float* A, int ar, int ac, const float* B,
                                               int br, int bc, float sign, bool accumulate, int tid) {
-    const int r = tid >> 3, c0 = (tid & 7) * 2;
+    const int r = tid >> 4, c = tid & 15;
     float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
-        const float a = A[(ar + r) * 64 + ac + k];
-        const float2 b = *reinterpret_cast<const float2*>(&B[(br + k) * 64 + bc + c0]);
-        s0 += a * b.x;
-        s1 += a * b.y;
+    for (int k = 0; k < 16; k += 2) {
+        s0 += A[(ar + r) * 64 + ac + k] * B[(br + k) * 64 + bc + c];
+        s1 += A[(ar + r) * 64 + ac + k + 1] * B[(br + k + 1) * 64 + bc + c];
     }
-    float2* d = reinterpret_cast<float2*>(&dst[(dr + r) * 64 + dc + c0]);
-    if (accumulate) { float2 o = *d; o.x += sign * s0; o.y += sign * s1; *d = o; }
-    else *d = make_float2(sign * s0, sign * s1);
+    float* d = &dst[(dr + r) * 64 + dc + c];
+    const float v = sign * (s0 + s1);
+    *d = accumulate ? *d + v : v;
 }
 
-// grid (heads, n_seqs), block 160
-__global__ void __launch_bounds__(160, 1)
+// grid (heads, n_seqs), block 288
+__global__ void __launch_bounds__(kG1Threads, 1)
 la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const float* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
                    const LaSeqMeta* __restrict__ seqs, float* __restrict__ rec_layer, size_t rec_stride_slot,
@@ -81,10 +82,6 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + G_BAR_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     auto bar = [&](int i) { return base + kOffBarG + 8u * i; };
-    float* s_b = reinterpret_cast<float*>(sm + kOffSC);
-    float* s_beta = s_b + 64;
-    float* s_eb = s_b + 128;
-    float* s_ebc = s_b + 192;
     float* AM = reinterpret_cast<float*>(sm + kOffAM);
     float* TF = reinterpret_cast<float*>(sm + kOffTF);
 
@@ -97,12 +94,11 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     float* Sg = rec_layer + (size_t)sq.slot * rec_stride_slot + (size_t)h * kLaKd * kLaVd;
 
     if (tid == 0) {
-        for (int i = 0; i < G_BAR_COUNT; ++i)
-            mbar_init(bar(i), (i == G_B1 || i == G_B2 || i == G_B3 || i == G_KQ_FREE) ? 128 : 1);
+        for (int i = 0; i < G_BAR_COUNT; ++i) mbar_init(bar(i), (i == G_B1 || i == G_B2 || i == G_B3) ? 256 : 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 4) {
+    if (warp == 8) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
         if (lane == 0) { tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); }
@@ -113,7 +109,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_d1 = tmem, tm_ut = tmem + 64, tm_wt = tmem + 128, tm_ot = tmem + 192, tm_d3 = tmem + 256;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ TMA + MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t id64 = umma_idesc(kFmtF16, 128, 64, 0, 0);
@@ -133,15 +129,6 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             for (int c = 0; c < n_chunks; ++c) {
                 const uint32_t par = c & 1;
                 const uint32_t kq = base + kOffKQ + (c & 1) * 32768;
-                // prefetch the next chunk's K/Q into the other buffer: it was last read by chunk c-1, whose
-                // threads (KQ_FREE) and whose state-update MMA (C3) must be done with it
-                if (c + 1 < n_chunks) {
-                    if (c >= 1) {
-                        if (!mbar_wait(bar(G_C3), (c - 1) & 1, abort_flag)) break;
-                        if (!mbar_wait(bar(G_KQ_FREE), (c - 1) & 1, abort_flag)) break;
-                    }
-                    load_kq(c + 1);
-                }
                 if (!mbar_wait(bar(G_KQ_FULL0 + (c & 1)), (c >> 1) & 1, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
@@ -150,6 +137,11 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     umma_f16(tm_d1, umma_smem_desc(kq + off, 16, 1024), umma_smem_desc(kq + off, 16, 1024), id64, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(G_A_DONE));
+                // the other K/Q buffer was last read by (o) and (u) of chunk c-1 (its threads were done with it before B2)
+                if (c + 1 < n_chunks) {
+                    if (c >= 1 && !mbar_wait(bar(G_C3), (c - 1) & 1, abort_flag)) break;
+                    load_kq(c + 1);
+                }
                 if (!mbar_wait(bar(G_B1), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
@@ -166,18 +158,17 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {   // (ws) Ut -= S0^T W^T ; (o) Ot = S0^T (Q e^b)^T
                     const uint64_t a = umma_smem_desc(base + kOffST + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-                    const uint32_t boff = (ks >> 2) * 8192 + (ks & 3) * 32;
-                    umma_f16(tm_ut, a, umma_smem_desc(base + kOffWT + boff, 16, 1024), id64_neg, 1u);
-                    umma_f16(tm_ot, a, umma_smem_desc(base + kOffQT + boff, 16, 1024), id64, ks > 0 ? 1u : 0u);
+                    umma_f16(tm_ut, a, umma_smem_desc(base + kOffWT + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), id64_neg, 1u);
+                    umma_f16(tm_ot, a, umma_smem_desc(kq + 8192 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024), id64, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(G_C2));
                 if (!mbar_wait(bar(G_B3), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {   // (o) Ot += V_new^T Mq^T ; (u) D3 += (e^{b_C-b} V_new)^T K
-                    umma_f16(tm_ot, umma_smem_desc(base + kOffRV + ks * 32, 16, 1024), umma_smem_desc(base + kOffMQ + ks * 32, 16, 1024),
-                             id64, 1u);
-                    umma_f16(tm_d3, umma_smem_desc(base + kOffRK + ks * 32, 16, 1024), umma_smem_desc(kq + ks * 2048, 16384, 1024),
+                    umma_f16(tm_ot, umma_smem_desc(base + kOffVN + ks * 32, 16, 1024),
+                             umma_smem_desc(base + kOffMQ + (c & 1) * 8192 + ks * 32, 16, 1024), id64, 1u);
+                    umma_f16(tm_d3, umma_smem_desc(base + kOffVS + ks * 32, 16, 1024), umma_smem_desc(kq + ks * 2048, 16384, 1024),
                              id_u, 1u);
                 }
                 umma_commit(bar(G_C3));
@@ -185,25 +176,44 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
     } else {
         // ------------------------------ compute warps ------------------------------
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-        const int r = tid;   // TMEM lane: D1 row, value dim of Ut/Ot/D3, key dim of Wt; also this thread's tile row / column
+        const int r = tid & 127;     // TMEM lane: D1 row, value dim of Ut/Ot/D3, key dim of Wt; also this thread's tile row
+        const int hf = tid >> 7;     // which 32 of the 64 token columns (or which half of the state columns) it handles
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         // D3 <- S^T from the state pool: lane vd = r, column kd
 #pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int cc = 0; cc < 2; ++cc) {
+            const int ch = hf * 2 + cc;
             uint32_t sv[32];
 #pragma unroll
             for (int c2 = 0; c2 < 32; ++c2) sv[c2] = __float_as_uint(Sg[(size_t)(ch * 32 + c2) * kLaVd + r]);
             tmem_st32(tm_d3 + lane_base + ch * 32, sv);
         }
         tmem_wait_st();
+        // stores the outputs of chunk cp (Ot, lane = value dim) -> out[token][head][vd]
+        auto store_out = [&](int cp) {
+            const int tok0 = cp * kC;
+            const int n_valid = min(kC, sq.count - tok0);
+            uint32_t ov[32];
+            tmem_ld32(tm_ot + lane_base + hf * 32, ov);
+            tmem_wait_ld();
+            float* obase = out + ((size_t)(sq.row0 + tok0 + hf * 32) * kLaHeads + h) * kLaVd + r;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (hf * 32 + j < n_valid) obase[(size_t)j * kLaHeads * kLaVd] = __uint_as_float(ov[j]);
+        };
         bool ok = true;
-        for (int c = 0; c < n_chunks && ok; ++c) {
+        for (int c = 0; c < n_chunks; ++c) {   // after a failed wait the warp keeps the barrier protocol going, without waiting or storing
             const uint32_t par = c & 1, prev = (c - 1) & 1;
             const int tok0 = c * kC;
             const int n_valid = min(kC, sq.count - tok0);
-            const unsigned char* kq = sm + kOffKQ + (c & 1) * 32768;
+            unsigned char* kq = sm + kOffKQ + (c & 1) * 32768;
+            float* s_b = reinterpret_cast<float*>(sm + kOffSC) + (c & 1) * 256;
+            float* s_beta = s_b + 64;
+            float* s_eb = s_b + 128;
+            float* s_ebc = s_b + 192;
+            // ======================= front half: needs nothing of the state =======================
             // ---- per-chunk scalars: b = cumsum(g), beta; padded tokens get g = 0, beta = 0 ----
-            if (warp < 2) {
+            if (tid < 64) {
                 const bool val = tid < n_valid;
                 const size_t gi = (size_t)(sq.row0 + tok0 + tid) * kLaHeads + h;
                 float gv = val ? g[gi] : 0.f;
@@ -216,25 +226,185 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 s_b[tid] = gv;
                 s_beta[tid] = bv;
             }
-            named_sync_128();
+            named_sync_256();
             if (warp == 1) s_b[tid] += s_b[31];
-            named_sync_128();
+            named_sync_256();
             if (tid < 64) {
                 s_eb[tid] = expf(s_b[tid]);
                 s_ebc[tid] = expf(s_b[63] - s_b[tid]);
             }
-            named_sync_128();
+            named_sync_256();
             const float e_bc = expf(s_b[63]);
-            // ---- this thread's column of beta V (global loads overlap the previous chunk's MMAs) ----
-            float vcol[64];
+            // ---- this thread's half column of beta V ----
+            float vcol[32];
 #pragma unroll
-            for (int i = 0; i < 64; ++i)
-                vcol[i] = (i < n_valid) ? s_beta[i] * v[((size_t)(sq.row0 + tok0 + i) * kLaHeads + h) * kLaVd + tid] : 0.f;
-            // ---- S prep: D3 (S^T of the chunk start) -> fp16 tile, and back to TMEM scaled by e^{b_C} ----
-            if (c > 0 && !mbar_wait_warp(bar(G_C3), prev, abort_flag)) { ok = false; break; }
+            for (int i = 0; i < 32; ++i) {
+                const int tk = hf * 32 + i;
+                vcol[i] = (tk < n_valid) ? s_beta[tk] * v[((size_t)(sq.row0 + tok0 + tk) * kLaHeads + h) * kLaVd + r] : 0.f;
+            }
+            // ---- (beta V)^T row r and (beta e^b K)^T row r, tokens of this half ----
+            if (!mbar_wait_warp(bar(G_KQ_FULL0 + (c & 1)), (c >> 1) & 1, abort_flag)) ok = false;
+            {
+                const unsigned char* kq_blk = kq + (r >> 6) * 16384;
+                const int tcol = r & 63;
+                unsigned char* rv_row = sm + kOffRV + r * 128;
+                unsigned char* rk_row = sm + kOffRK + r * 128;
+#pragma unroll
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int c8 = hf * 4 + cc;
+                    uint32_t pv[4], pk[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int l0 = cc * 8 + 2 * e;                 // index into vcol
+                        const int i0 = c8 * 8 + 2 * e, i1 = i0 + 1;    // token
+                        const uint32_t sw0 = (((tcol >> 3) ^ (i0 & 7)) << 4) + (tcol & 7) * 2;
+                        const uint32_t sw1 = (((tcol >> 3) ^ (i1 & 7)) << 4) + (tcol & 7) * 2;
+                        const float k0 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i0 * 128 + sw0));
+                        const float k1 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i1 * 128 + sw1));
+                        pv[e] = pack_half2(vcol[l0], vcol[l0 + 1]);
+                        pk[e] = pack_half2(s_beta[i0] * s_eb[i0] * k0, s_beta[i1] * s_eb[i1] * k1);
+                    }
+                    *reinterpret_cast<uint4*>(rv_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pv[0], pv[1], pv[2], pv[3]);
+                    *reinterpret_cast<uint4*>(rk_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                }
+            }
+            // ---- D1 -> A matrix (rows 0-63) and masked, decayed Q K^T (rows 64-127); then Q *= e^b in place ----
+            if (!mbar_wait_warp(bar(G_A_DONE), par, abort_flag)) ok = false;
             tc_fence_after();
+            {
+                uint32_t d1[32];
+                tmem_ld32(tm_d1 + lane_base + hf * 32, d1);
+                tmem_wait_ld();
+                if (r < 64) {
+                    const float bi = s_b[r], be = s_beta[r];
+#pragma unroll
+                    for (int j4 = 0; j4 < 8; ++j4) {
+                        float a4[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j = hf * 32 + j4 * 4 + e;
+                            a4[e] = (j < r) ? be * expf(bi - s_b[j]) * __uint_as_float(d1[j4 * 4 + e]) : 0.f;
+                        }
+                        *reinterpret_cast<float4*>(AM + r * 64 + hf * 32 + j4 * 4) = make_float4(a4[0], a4[1], a4[2], a4[3]);
+                    }
+                } else {
+                    const int i = r - 64;
+                    const float bi = s_b[i];
+                    unsigned char* row_ptr = sm + kOffMQ + (c & 1) * 8192 + i * 128;
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        uint32_t pk[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int j0 = hf * 32 + cc * 8 + 2 * e, j1 = j0 + 1;
+                            const float m0 = (j0 <= i) ? expf(bi - s_b[j0]) * __uint_as_float(d1[cc * 8 + 2 * e]) : 0.f;
+                            const float m1 = (j1 <= i) ? expf(bi - s_b[j1]) * __uint_as_float(d1[cc * 8 + 2 * e + 1]) : 0.f;
+                            pk[e] = pack_half2(m0, m1);
+                        }
+                        *reinterpret_cast<uint4*>(row_ptr + (((hf * 4 + cc) ^ (i & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                    }
+                }
+                {   // Q tile rows (token i): every element times e^{b_i}; the swizzle only permutes 16-byte pieces inside a row
+                    const int i = tid >> 2;
+                    const float sc = s_eb[i];
+#pragma unroll
+                    for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            uint4* p4 = reinterpret_cast<uint4*>(kq + blk * 16384 + 8192 + i * 128 + (((tid & 3) * 2 + e) << 4));
+                            uint4 x = *p4;
+                            __half2* hx = reinterpret_cast<__half2*>(&x);
+#pragma unroll
+                            for (int w2 = 0; w2 < 4; ++w2) {
+                                const float2 f = __half22float2(hx[w2]);
+                                hx[w2] = __floats2half2_rn(f.x * sc, f.y * sc);
+                            }
+                            *p4 = x;
+                        }
+                }
+            }
+            named_sync_256();
+            // ---- T = (I + A)^-1, blocked 16 x 16: diagonal blocks by forward substitution, the rest by block products
+            //      T_ij = -T_ii sum_{k=j}^{i-1} A_ik T_kj.  The inner sums are staged in A's upper blocks, which are zero
+            //      and not otherwise used. ----
+            if (tid < 64) {
+                const int b0 = (tid >> 4) * 16, col = tid & 15;      // column `col` of diagonal block b0 / 16
+                float t[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) t[i] = (i == col) ? 1.f : 0.f;
+#pragma unroll
+                for (int i = 1; i < 16; ++i) {
+                    float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+                    for (int j = 0; j + 1 < i; j += 2) {
+                        acc0 += AM[(b0 + i) * 64 + b0 + j] * t[j];
+                        acc1 += AM[(b0 + i) * 64 + b0 + j + 1] * t[j + 1];
+                    }
+                    if (i & 1) acc0 += AM[(b0 + i) * 64 + b0 + i - 1] * t[i - 1];
+                    t[i] -= acc0 + acc1;   // rows <= col keep their start value: A is strictly lower and t[j < col] = 0
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) TF[(b0 + i) * 64 + b0 + col] = t[i];
+            } else {
+                for (int idx = tid - 64; idx < 6 * 256; idx += 192) {   // the other threads clear T's six upper blocks
+                    const int blk = idx >> 8, e = idx & 255;
+                    const int bi = (blk < 3) ? 0 : (blk < 5 ? 1 : 2);
+                    const int bj = (blk < 3) ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+                    TF[(bi * 16 + (e >> 4)) * 64 + bj * 16 + (e & 15)] = 0.f;
+                }
+            }
+            named_sync_256();
+            for (int i = 1; i < 4; ++i)   // first sub-diagonal
+                block_product(AM, (i - 1) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 1) * 16, 1.f, false, tid);
+            named_sync_256();
+            for (int i = 1; i < 4; ++i)
+                block_product(TF, i * 16, (i - 1) * 16, TF, i * 16, i * 16, AM, (i - 1) * 16, i * 16, -1.f, false, tid);
+            named_sync_256();
+            for (int i = 2; i < 4; ++i) {   // second sub-diagonal
+                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 2) * 16, TF, (i - 2) * 16, (i - 2) * 16, 1.f, false, tid);
+                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 2) * 16, 1.f, true, tid);
+            }
+            named_sync_256();
+            for (int i = 2; i < 4; ++i)
+                block_product(TF, i * 16, (i - 2) * 16, TF, i * 16, i * 16, AM, (i - 2) * 16, i * 16, -1.f, false, tid);
+            named_sync_256();
+            block_product(AM, 0, 48, AM, 48, 0, TF, 0, 0, 1.f, false, tid);      // corner block
+            block_product(AM, 0, 48, AM, 48, 16, TF, 16, 0, 1.f, true, tid);
+            block_product(AM, 0, 48, AM, 48, 32, TF, 32, 0, 1.f, true, tid);
+            named_sync_256();
+            block_product(TF, 48, 0, TF, 48, 48, AM, 0, 48, -1.f, false, tid);
+            named_sync_256();
+            {   // T -> fp16 hi + lo tiles (row = i, K = j)
+                const int i = tid >> 2, qd = tid & 3;
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    uint32_t ph[4], pl[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 t2 = *reinterpret_cast<const float2*>(&TF[i * 64 + qd * 16 + cc * 8 + 2 * e]);
+                        const float h0 = __half2float(__float2half_rn(t2.x)), h1 = __half2float(__float2half_rn(t2.y));
+                        ph[e] = pack_half2(h0, h1);
+                        pl[e] = pack_half2(t2.x - h0, t2.y - h1);
+                    }
+                    const int chunk16 = qd * 2 + cc;
+                    *reinterpret_cast<uint4*>(sm + kOffTT + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                    *reinterpret_cast<uint4*>(sm + kOffTT + 8192 + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(bar(G_B1));
+            named_sync_256();     // every thread is done reading A / T: their space becomes the S0 tile below
+            // ======================= back half: needs the state of the chunk start =======================
+            if (c > 0) {
+                if (!mbar_wait_warp(bar(G_C3), prev, abort_flag)) ok = false;
+                tc_fence_after();
+                if (ok) store_out(c - 1);
+            }
+            // ---- D3 (S^T of the chunk start) -> fp16 tile, and back to TMEM scaled by e^{b_C} ----
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int cc = 0; cc < 2; ++cc) {
+                const int ch = hf * 2 + cc;
                 uint32_t sv[32];
                 tmem_ld32(tm_d3 + lane_base + ch * 32, sv);
                 tmem_wait_ld();
@@ -253,210 +423,60 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_st32(tm_d3 + lane_base + ch * 32, sv);
             }
             tmem_wait_st();
-            // ---- rows / columns this thread owns: (beta V)^T row r, (beta e^b K)^T row r, column r of Q e^b ----
-            if (!mbar_wait_warp(bar(G_KQ_FULL0 + (c & 1)), (c >> 1) & 1, abort_flag)) { ok = false; break; }
-            {
-                const unsigned char* kq_blk = kq + (tid >> 6) * 16384;
-                unsigned char* qt_blk = sm + kOffQT + (tid >> 6) * 8192;
-                const int tcol = tid & 63;
-                unsigned char* rv_row = sm + kOffRV + r * 128;
-                unsigned char* rk_row = sm + kOffRK + r * 128;
-#pragma unroll
-                for (int c8 = 0; c8 < 8; ++c8) {
-                    uint32_t pv[4], pk[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int i0 = c8 * 8 + 2 * e, i1 = i0 + 1;
-                        const uint32_t sw0 = (((tcol >> 3) ^ (i0 & 7)) << 4) + (tcol & 7) * 2;
-                        const uint32_t sw1 = (((tcol >> 3) ^ (i1 & 7)) << 4) + (tcol & 7) * 2;
-                        const float k0 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i0 * 128 + sw0));
-                        const float k1 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i1 * 128 + sw1));
-                        pv[e] = pack_half2(vcol[i0], vcol[i1]);
-                        pk[e] = pack_half2(s_beta[i0] * s_eb[i0] * k0, s_beta[i1] * s_eb[i1] * k1);
-                        const float q0 = __half2float(*reinterpret_cast<const __half*>(kq_blk + (64 + i0) * 128 + sw0));
-                        const float q1 = __half2float(*reinterpret_cast<const __half*>(kq_blk + (64 + i1) * 128 + sw1));
-                        *reinterpret_cast<uint16_t*>(qt_blk + i0 * 128 + sw0) = f2h_bits(s_eb[i0] * q0);
-                        *reinterpret_cast<uint16_t*>(qt_blk + i1 * 128 + sw1) = f2h_bits(s_eb[i1] * q1);
-                    }
-                    *reinterpret_cast<uint4*>(rv_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pv[0], pv[1], pv[2], pv[3]);
-                    *reinterpret_cast<uint4*>(rk_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                }
-            }
-            mbar_arrive(bar(G_KQ_FREE));       // no thread reads this K/Q buffer after this point
-            // ---- D1 -> A matrix (rows 0-63) and masked, decayed Q K^T (rows 64-127) ----
-            if (!mbar_wait_warp(bar(G_A_DONE), par, abort_flag)) { ok = false; break; }
+            // ---- W^T (lane = key dim) -> column r of the W tile (over T, which (uw) has finished reading) ----
+            if (!mbar_wait_warp(bar(G_C1), par, abort_flag)) ok = false;
             tc_fence_after();
             {
-                uint32_t d1[2][32];
-                tmem_ld32(tm_d1 + lane_base, d1[0]);
-                tmem_ld32(tm_d1 + lane_base + 32, d1[1]);
+                uint32_t wv[32];
+                tmem_ld32(tm_wt + lane_base + hf * 32, wv);
                 tmem_wait_ld();
-                if (r < 64) {
-                    const float bi = s_b[r], be = s_beta[r];
+                unsigned char* wt_blk = sm + kOffWT + (r >> 6) * 8192;
+                const int tcol = r & 63;
 #pragma unroll
-                    for (int j4 = 0; j4 < 16; ++j4) {
-                        float a4[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int j = j4 * 4 + e;
-                            a4[e] = (j < r) ? be * expf(bi - s_b[j]) * __uint_as_float(d1[j >> 5][j & 31]) : 0.f;
-                        }
-                        *reinterpret_cast<float4*>(AM + r * 64 + j4 * 4) = make_float4(a4[0], a4[1], a4[2], a4[3]);
-                    }
-                } else {
-                    const int i = r - 64;
-                    const float bi = s_b[i];
-                    unsigned char* row_ptr = sm + kOffMQ + i * 128;
-#pragma unroll
-                    for (int c8 = 0; c8 < 8; ++c8) {
-                        uint32_t pk[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int j0 = c8 * 8 + 2 * e, j1 = j0 + 1;
-                            const float m0 = (j0 <= i) ? expf(bi - s_b[j0]) * __uint_as_float(d1[j0 >> 5][j0 & 31]) : 0.f;
-                            const float m1 = (j1 <= i) ? expf(bi - s_b[j1]) * __uint_as_float(d1[j1 >> 5][j1 & 31]) : 0.f;
-                            pk[e] = pack_half2(m0, m1);
-                        }
-                        *reinterpret_cast<uint4*>(row_ptr + ((c8 ^ (i & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                    }
-                }
-            }
-            named_sync_128();
-            // ---- T = (I + A)^-1, blocked 16 x 16: diagonal blocks by forward substitution, the rest by block products
-            //      T_ij = -T_ii sum_{k=j}^{i-1} A_ik T_kj.  The inner sums are staged in A's upper blocks, which are zero
-            //      and not otherwise used. ----
-            if (tid < 64) {
-                const int b0 = (tid >> 4) * 16, col = tid & 15;      // column `col` of diagonal block b0 / 16
-                float t[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) t[i] = (i == col) ? 1.f : 0.f;
-#pragma unroll
-                for (int i = 1; i < 16; ++i) {
-                    float acc = 0.f;
-#pragma unroll
-                    for (int j = 0; j < i; ++j) acc += AM[(b0 + i) * 64 + b0 + j] * t[j];
-                    t[i] -= acc;      // rows <= col keep their start value: A is strictly lower and t[j < col] = 0
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) TF[(b0 + i) * 64 + b0 + col] = t[i];
-            } else {
-                const int u = tid - 64;       // the other 64 threads clear T's six upper blocks
-                for (int idx = u; idx < 6 * 256; idx += 64) {
-                    const int blk = idx >> 8, e = idx & 255;
-                    const int bi = (blk < 3) ? 0 : (blk < 5 ? 1 : 2);
-                    const int bj = (blk < 3) ? blk + 1 : (blk < 5 ? blk - 1 : 3);
-                    TF[(bi * 16 + (e >> 4)) * 64 + bj * 16 + (e & 15)] = 0.f;
-                }
-            }
-            named_sync_128();
-            for (int i = 1; i < 4; ++i)   // first sub-diagonal
-                block_product(AM, (i - 1) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 1) * 16, 1.f, false, tid);
-            named_sync_128();
-            for (int i = 1; i < 4; ++i)
-                block_product(TF, i * 16, (i - 1) * 16, TF, i * 16, i * 16, AM, (i - 1) * 16, i * 16, -1.f, false, tid);
-            named_sync_128();
-            for (int i = 2; i < 4; ++i) {   // second sub-diagonal
-                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 2) * 16, TF, (i - 2) * 16, (i - 2) * 16, 1.f, false, tid);
-                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 2) * 16, 1.f, true, tid);
-            }
-            named_sync_128();
-            for (int i = 2; i < 4; ++i)
-                block_product(TF, i * 16, (i - 2) * 16, TF, i * 16, i * 16, AM, (i - 2) * 16, i * 16, -1.f, false, tid);
-            named_sync_128();
-            block_product(AM, 0, 48, AM, 48, 0, TF, 0, 0, 1.f, false, tid);      // corner block
-            block_product(AM, 0, 48, AM, 48, 16, TF, 16, 0, 1.f, true, tid);
-            block_product(AM, 0, 48, AM, 48, 32, TF, 32, 0, 1.f, true, tid);
-            named_sync_128();
-            block_product(TF, 48, 0, TF, 48, 48, AM, 0, 48, -1.f, false, tid);
-            named_sync_128();
-            {   // T -> fp16 hi + lo tiles (row = i, K = j)
-                const int i = tid >> 1, half = tid & 1;
-#pragma unroll
-                for (int c8 = 0; c8 < 4; ++c8) {
-                    uint32_t ph[4], pl[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int j = half * 32 + c8 * 8 + 2 * e;
-                        const float t0 = TF[i * 64 + j], t1 = TF[i * 64 + j + 1];
-                        const float h0 = __half2float(__float2half_rn(t0)), h1 = __half2float(__float2half_rn(t1));
-                        ph[e] = pack_half2(h0, h1);
-                        pl[e] = pack_half2(t0 - h0, t1 - h1);
-                    }
-                    const int chunk16 = half * 4 + c8;
-                    *reinterpret_cast<uint4*>(sm + kOffTT + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                    *reinterpret_cast<uint4*>(sm + kOffTT + 8192 + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-                }
-            }
-            fence_proxy_async_smem();
-            tc_fence_before();
-            mbar_arrive(bar(G_B1));
-            // ---- W^T (lane = key dim) -> column r of the W tile ----
-            if (!mbar_wait_warp(bar(G_C1), par, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            {
-                uint32_t w0[32], w1[32];
-                tmem_ld32(tm_wt + lane_base, w0);
-                tmem_ld32(tm_wt + lane_base + 32, w1);
-                tmem_wait_ld();
-                unsigned char* wt_blk = sm + kOffWT + (tid >> 6) * 8192;
-                const int tcol = tid & 63;
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const float wv = __uint_as_float(i < 32 ? w0[i & 31] : w1[i & 31]);
-                    *reinterpret_cast<uint16_t*>(wt_blk + i * 128 + (((tcol >> 3) ^ (i & 7)) << 4) + (tcol & 7) * 2) = f2h_bits(wv);
+                for (int j = 0; j < 32; ++j) {
+                    const int i = hf * 32 + j;
+                    const __half hv = __float2half_rn(__uint_as_float(wv[j]));
+                    *reinterpret_cast<__half*>(wt_blk + i * 128 + (((tcol >> 3) ^ (i & 7)) << 4) + (tcol & 7) * 2) = hv;
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(bar(G_B2));
             // ---- V_new^T (lane = value dim): plain and decayed fp16 rows ----
-            if (!mbar_wait_warp(bar(G_C2), par, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_warp(bar(G_C2), par, abort_flag)) ok = false;
             tc_fence_after();
             {
-                uint32_t u0[32], u1[32];
-                tmem_ld32(tm_ut + lane_base, u0);
-                tmem_ld32(tm_ut + lane_base + 32, u1);
+                uint32_t uv[32];
+                tmem_ld32(tm_ut + lane_base + hf * 32, uv);
                 tmem_wait_ld();
-                unsigned char* rv_row = sm + kOffRV + r * 128;
-                unsigned char* rk_row = sm + kOffRK + r * 128;
+                unsigned char* vn_row = sm + kOffVN + r * 128;
+                unsigned char* vs_row = sm + kOffVS + r * 128;
 #pragma unroll
-                for (int c8 = 0; c8 < 8; ++c8) {
+                for (int cc = 0; cc < 4; ++cc) {
                     uint32_t pa[4], pb[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const int j0 = c8 * 8 + 2 * e, j1 = j0 + 1;
-                        const float x0 = __uint_as_float(j0 < 32 ? u0[j0 & 31] : u1[j0 & 31]);
-                        const float x1 = __uint_as_float(j1 < 32 ? u0[j1 & 31] : u1[j1 & 31]);
+                        const int l0 = cc * 8 + 2 * e, j0 = hf * 32 + l0;
+                        const float x0 = __uint_as_float(uv[l0]), x1 = __uint_as_float(uv[l0 + 1]);
                         pa[e] = pack_half2(x0, x1);
-                        pb[e] = pack_half2(x0 * s_ebc[j0], x1 * s_ebc[j1]);
+                        pb[e] = pack_half2(x0 * s_ebc[j0], x1 * s_ebc[j0 + 1]);
                     }
-                    *reinterpret_cast<uint4*>(rv_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
-                    *reinterpret_cast<uint4*>(rk_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
+                    const int c8 = hf * 4 + cc;
+                    *reinterpret_cast<uint4*>(vn_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
+                    *reinterpret_cast<uint4*>(vs_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(bar(G_B3));
-            // ---- outputs: O^T (lane = value dim) -> out[token][head][vd] ----
-            if (!mbar_wait_warp(bar(G_C3), par, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            {
-                uint32_t o0[32], o1[32];
-                tmem_ld32(tm_ot + lane_base, o0);
-                tmem_ld32(tm_ot + lane_base + 32, o1);
-                tmem_wait_ld();
-                float* obase = out + ((size_t)(sq.row0 + tok0) * kLaHeads + h) * kLaVd + r;
-#pragma unroll
-                for (int j = 0; j < 64; ++j)
-                    if (j < n_valid) obase[(size_t)j * kLaHeads * kLaVd] = __uint_as_float(j < 32 ? o0[j & 31] : o1[j & 31]);
-            }
-            tc_fence_before();
         }
-        // ---- final state: D3 (S^T) -> state pool (every thread has seen the last chunk's C3) ----
-        if (ok) {
+        // ---- last chunk's outputs and the final state: D3 (S^T) -> state pool ----
+        if (ok && mbar_wait_warp(bar(G_C3), (n_chunks - 1) & 1, abort_flag)) {
             tc_fence_after();
+            store_out(n_chunks - 1);
 #pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int cc = 0; cc < 2; ++cc) {
+                const int ch = hf * 2 + cc;
                 uint32_t sv[32];
                 tmem_ld32(tm_d3 + lane_base + ch * 32, sv);
                 tmem_wait_ld();
@@ -467,7 +487,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
@@ -490,7 +510,7 @@ int launch_la_chunk_tc(const __half* q_h, const __half* k_h, const float* v, con
         attr_done = true;
     }
     dim3 grid(kLaHeads, n_seqs);
-    la_chunk_tc_kernel<<<grid, 160, kG1Smem, s>>>(mq, mk, v, g, beta, d_seqs, rec_layer, rec_stride, out, d_error);
+    la_chunk_tc_kernel<<<grid, kG1Threads, kG1Smem, s>>>(mq, mk, v, g, beta, d_seqs, rec_layer, rec_stride, out, d_error);
     B2_LAUNCH_CHECK();
     return 0;
 }

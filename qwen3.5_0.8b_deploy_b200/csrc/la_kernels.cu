@@ -25,9 +25,12 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : logf(1.0f + expf(x)); }
 
 // ---- C1, sequence form -------------------------------------------------------------------------------
-// One warp per (row, head): conv + SiLU over the head's q, k and v channels, L2 norm of q and k
-// (eps inside the sqrt), q * 1/sqrt(128), beta and log-decay g.  q and k are written as fp32 (q_out, k_out)
-// and / or fp16 (qh_out, kh_out, the operand format of the tensor-core recurrence); null pointers are skipped.
+// One warp per (run of kConvRun consecutive rows, head): conv + SiLU over the head's q, k and v channels, L2 norm
+// of q and k (eps inside the sqrt), q * 1/sqrt(128), beta and log-decay g.  The warp slides the four-tap window
+// along its rows in registers, so every input row is read once (plus three rows of history per run) and the tap
+// weights stay in registers.  q and k are written as fp32 (q_out, k_out) and / or fp16 (qh_out, kh_out, the operand
+// format of the tensor-core recurrence); null pointers are skipped.
+constexpr int kConvRun = 16;
 __global__ void __launch_bounds__(128)
 la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_seq,
                    const LaSeqMeta* __restrict__ seqs, const float* __restrict__ conv_state_layer,
@@ -37,64 +40,95 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
                    float* __restrict__ v_out, float* __restrict__ g_out, float* __restrict__ beta_out) {
     const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (gw >= rows * kLaHeads) return;
-    const int row = gw / kLaHeads, h = gw % kLaHeads;
-    const LaSeqMeta sm = seqs[row_seq[row]];
-    const int t = row - sm.row0;   // index inside this call's chunk of the sequence
-    const float* st = conv_state_layer + (size_t)sm.slot * conv_stride_slot;
-    float res[3][4];
+    const int n_runs = (rows + kConvRun - 1) / kConvRun;
+    if (gw >= n_runs * kLaHeads) return;
+    const int run = gw / kLaHeads, h = gw % kLaHeads;
+    const int row_begin = run * kConvRun, row_end = min(rows, row_begin + kConvRun);
+    float4 w[3][4];          // tap weights of this lane's four channels per part
 #pragma unroll
-    for (int part = 0; part < 3; ++part) {
-        const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + 4 * lane;   // kd == vd == 128
-        float4 x[4];   // x[0] = t-3 ... x[3] = t
+    for (int part = 0; part < 3; ++part)
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const int tt = t - 3 + b;
-            const float* src = (tt >= 0) ? mixed + (size_t)(sm.row0 + tt) * kLaProjCols + ch
-                                         : st + (size_t)(tt + 3) * kLaConvDim + ch;
-            x[b] = *reinterpret_cast<const float4*>(src);
+        for (int i = 0; i < 4; ++i)
+            w[part][i] = *reinterpret_cast<const float4*>(conv_w + (size_t)(part * (kLaHeads * kLaKd) + h * kLaKd + 4 * lane + i) * kLaConvK);
+    const float decay = -expf(a_log[h]), dtb = dt_bias[h];
+    const float q_scale = 1.0f / sqrtf((float)kLaKd);
+    float4 x[3][3];          // x[part][0..2] = inputs at t-3, t-2, t-1
+    int cur_seq = -1;
+    LaSeqMeta sm = {};
+    const float* mrow0 = mixed + h * kLaKd + 4 * lane;
+    float4 nxt[3];           // the next row's inputs, requested one iteration ahead
+#pragma unroll
+    for (int part = 0; part < 3; ++part)
+        nxt[part] = *reinterpret_cast<const float4*>(mrow0 + (size_t)row_begin * kLaProjCols + part * (kLaHeads * kLaKd));
+    for (int row = row_begin; row < row_end; ++row) {
+        float4 cur[3] = {nxt[0], nxt[1], nxt[2]};
+        if (row + 1 < row_end) {
+#pragma unroll
+            for (int part = 0; part < 3; ++part)
+                nxt[part] = *reinterpret_cast<const float4*>(mrow0 + (size_t)(row + 1) * kLaProjCols + part * (kLaHeads * kLaKd));
         }
-        const float xs[4][4] = {{x[0].x, x[0].y, x[0].z, x[0].w}, {x[1].x, x[1].y, x[1].z, x[1].w},
-                                {x[2].x, x[2].y, x[2].z, x[2].w}, {x[3].x, x[3].y, x[3].z, x[3].w}};
+        const int sidx = row_seq[row];
+        const bool fresh = sidx != cur_seq;      // first row of the run, or the run crosses into the next sequence
+        if (fresh) { cur_seq = sidx; sm = seqs[sidx]; }
+        const int t = row - sm.row0;             // index inside this call's chunk of the sequence
+        float res[3][4];
+#pragma unroll
+        for (int part = 0; part < 3; ++part) {
+            const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + 4 * lane;   // kd == vd == 128
+            if (fresh) {
+                const float* st = conv_state_layer + (size_t)sm.slot * conv_stride_slot;
+#pragma unroll
+                for (int b = 0; b < 3; ++b) {
+                    const int tt = t - 3 + b;
+                    const float* src = (tt >= 0) ? mixed + (size_t)(sm.row0 + tt) * kLaProjCols + ch
+                                                 : st + (size_t)(tt + 3) * kLaConvDim + ch;
+                    x[part][b] = *reinterpret_cast<const float4*>(src);
+                }
+            }
+            const float4 xn = cur[part];
+            const float x0[4] = {x[part][0].x, x[part][0].y, x[part][0].z, x[part][0].w};
+            const float x1[4] = {x[part][1].x, x[part][1].y, x[part][1].z, x[part][1].w};
+            const float x2[4] = {x[part][2].x, x[part][2].y, x[part][2].z, x[part][2].w};
+            const float x3[4] = {xn.x, xn.y, xn.z, xn.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float s2 = w[part][i].w * x3[i];
+                s2 += w[part][i].x * x2[i];
+                s2 += w[part][i].y * x1[i];
+                s2 += w[part][i].z * x0[i];
+                res[part][i] = silu_f(s2);
+            }
+            x[part][0] = x[part][1]; x[part][1] = x[part][2]; x[part][2] = xn;
+        }
+        float qs = 0.f, ksq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { qs += res[0][i] * res[0][i]; ksq += res[1][i] * res[1][i]; }
+        qs = sqrtf(warp_sum_f(qs) + 1e-6f);
+        ksq = sqrtf(warp_sum_f(ksq) + 1e-6f);
+        float4 q4, k4, v4;
+        float* qp = &q4.x; float* kp = &k4.x; float* vp = &v4.x;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)(ch + i) * kLaConvK);
-            float s = w.w * xs[3][i];
-            s += w.x * xs[2][i];
-            s += w.y * xs[1][i];
-            s += w.z * xs[0][i];
-            res[part][i] = silu_f(s);
+            qp[i] = __fdiv_rn(res[0][i], qs) * q_scale;
+            kp[i] = __fdiv_rn(res[1][i], ksq);
+            vp[i] = res[2][i];
         }
-    }
-    float qs = 0.f, ksq = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { qs += res[0][i] * res[0][i]; ksq += res[1][i] * res[1][i]; }
-    qs = sqrtf(warp_sum_f(qs) + 1e-6f);
-    ksq = sqrtf(warp_sum_f(ksq) + 1e-6f);
-    const float q_scale = 1.0f / sqrtf((float)kLaKd);
-    float4 q4, k4, v4;
-    float* qp = &q4.x; float* kp = &k4.x; float* vp = &v4.x;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        qp[i] = __fdiv_rn(res[0][i], qs) * q_scale;
-        kp[i] = __fdiv_rn(res[1][i], ksq);
-        vp[i] = res[2][i];
-    }
-    const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
-    if (q_out) *reinterpret_cast<float4*>(q_out + o) = q4;
-    if (k_out) *reinterpret_cast<float4*>(k_out + o) = k4;
-    if (qh_out) {
-        __half2 a = __floats2half2_rn(q4.x, q4.y), b = __floats2half2_rn(q4.z, q4.w);
-        __half2 c = __floats2half2_rn(k4.x, k4.y), d = __floats2half2_rn(k4.z, k4.w);
-        *reinterpret_cast<uint2*>(qh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-        *reinterpret_cast<uint2*>(kh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
-    }
-    *reinterpret_cast<float4*>(v_out + o) = v4;
-    if (lane == 0) {
-        const float a = mixed[(size_t)row * kLaProjCols + kLaAOff + h];
-        const float b = mixed[(size_t)row * kLaProjCols + kLaBOff + h];
-        beta_out[row * kLaHeads + h] = sigmoid_f(b);
-        g_out[row * kLaHeads + h] = -expf(a_log[h]) * softplus_f(a + dt_bias[h]);
+        const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
+        if (q_out) *reinterpret_cast<float4*>(q_out + o) = q4;
+        if (k_out) *reinterpret_cast<float4*>(k_out + o) = k4;
+        if (qh_out) {
+            __half2 a = __floats2half2_rn(q4.x, q4.y), b = __floats2half2_rn(q4.z, q4.w);
+            __half2 c = __floats2half2_rn(k4.x, k4.y), d = __floats2half2_rn(k4.z, k4.w);
+            *reinterpret_cast<uint2*>(qh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+            *reinterpret_cast<uint2*>(kh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+        }
+        *reinterpret_cast<float4*>(v_out + o) = v4;
+        if (lane == 0) {
+            const float a = mixed[(size_t)row * kLaProjCols + kLaAOff + h];
+            const float b = mixed[(size_t)row * kLaProjCols + kLaBOff + h];
+            beta_out[row * kLaHeads + h] = sigmoid_f(b);
+            g_out[row * kLaHeads + h] = decay * softplus_f(a + dtb);
+        }
     }
 }
 
@@ -330,7 +364,7 @@ __global__ void la_conv_export_kernel(const float* __restrict__ mine, float* __r
 int launch_la_conv_seq(const float* mixed, const int* d_row_seq, const LaSeqMeta* d_seqs, const float* conv_layer,
                        size_t conv_stride, const float* conv_w, const float* a_log, const float* dt_bias, int rows,
                        float* q, float* k, __half* qh, __half* kh, float* v, float* g, float* beta, cudaStream_t s) {
-    la_conv_seq_kernel<<<ceil_div(rows * kLaHeads, 4), 128, 0, s>>>(mixed, d_row_seq, d_seqs, conv_layer, conv_stride,
+    la_conv_seq_kernel<<<ceil_div(ceil_div(rows, kConvRun) * kLaHeads, 4), 128, 0, s>>>(mixed, d_row_seq, d_seqs, conv_layer, conv_stride,
                                                                   conv_w, a_log, dt_bias, rows, q, k, qh, kh, v, g, beta);
     B2_LAUNCH_CHECK();
     return 0;
