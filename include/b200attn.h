@@ -113,7 +113,8 @@ int b200attn_kv_seq_len(b200attn_kv_pool pool, int layer, int slot, int* len_out
 int b200attn_kv_pages(b200attn_kv_pool pool, int* total_out, int* used_out);
 /* Reads (and clears) the pool's device-side status word: 0 = clean, 1 = slot out of range seen by a
  * kernel, 2 = append beyond the reserved pages (the write was skipped), 3/4 = a bounded wait inside
- * the decode / prefill attention kernel ran out.  Synchronises the device.  No reference counterpart:
+ * the decode / prefill attention kernel ran out, 8 = the prefill kernel found its shared-memory window
+ * misaligned and did nothing.  Synchronises the device.  No reference counterpart:
  * the reference's kernels report nothing (full_attention_cuda.cu:11-17 prints and continues). */
 int b200attn_kv_device_status(b200attn_kv_pool pool, int* code_out);
 /* Quantise-on-append of already normalised/rotated K and raw V rows, the arithmetic of

@@ -1,7 +1,8 @@
 // F1: causal flash-attention prefill for head_dim 256 on tcgen05 tensor cores.
 //
-// One CTA per (128-query tile of one sequence, q head).  Warp roles: warps 0-3 = softmax (thread r owns
-// query row r = TMEM lane r), warp 4 = TMA producer, warp 5 = MMA issuer and TMEM owner.
+// One CTA per (128-query tile of one sequence, q head).  Warp roles: warps 0-7 = softmax (two threads per query
+// row = TMEM lane, each owning 32 of the 64 key columns of a tile and half of the output columns; the pair
+// exchanges its row maxima through shared memory), warp 8 = TMA producer, warp 9 = MMA issuer and TMEM owner.
 //   S[128x64]  = Q[128x256] K_j^T      tcgen05.mma kind::f16 (fp16 operands), A and B K-major, TMEM cols [0,128) double-buffered
 //   O[128x256] += P_j[128x64] V_j      A = P (written by the softmax warps, K-major), B = V tile MN-major, TMEM cols [128,384)
 // Q / K / V tiles arrive through tiled TMA with 128-byte swizzle; K and V are double-buffered.  The softmax
@@ -25,21 +26,26 @@ constexpr uint32_t kKVBytes = 4 * kBN * 128;    // 32768
 constexpr uint32_t kPBytes = kBM * 128;         // 16384
 constexpr uint32_t kOffQ = 0, kOffK = kQBytes, kOffV = kOffK + 2 * kKVBytes, kOffP = kOffV + 2 * kKVBytes;
 constexpr uint32_t kOffBar = kOffP + 2 * kPBytes;
-constexpr uint32_t kF1Smem = kOffBar + 256 + 1024;   // + barriers + alignment slack
+constexpr uint32_t kOffXch = kOffBar + 256;          // row-maximum exchange [2 tiles][2 halves][128]; row sums reuse the idle tile slot
+constexpr uint32_t kF1Smem = kOffXch + 2048;         // no alignment slack: the kernel checks its base instead
+constexpr int kF1Threads = 320;
 constexpr float kLog2eF = 1.4426950408889634f;
 
 enum { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 15,
        BAR_OF = 17, BAR_COUNT = 18 };
 
 template <typename OutT>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kF1Threads, 1)
 fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const PrefillTile* __restrict__ tiles,
                      const __half* __restrict__ gate, OutT* __restrict__ out, int* __restrict__ error_word) {
-    extern __shared__ unsigned char smem_raw[];
-    const uint32_t raw = smem_u32(smem_raw);
-    const uint32_t base = (raw + 1023u) & ~1023u;
-    unsigned char* sm = smem_raw + (base - raw);
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    unsigned char* sm = smem_raw;
+    if (base & 1023u) {            // the 128-byte swizzle needs 1024-byte aligned tiles
+        if (threadIdx.x == 0) atomicExch(error_word, 8);
+        return;
+    }
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + kOffBar);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + BAR_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -55,16 +61,16 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     if (threadIdx.x == 0) {
         for (int i = 0; i < BAR_COUNT; ++i) {
             const bool many = (i == BAR_SE || i == BAR_SE + 1 || i == BAR_PF || i == BAR_PF + 1);
-            mbar_init(bar(i), many ? 128 : 1);
+            mbar_init(bar(i), many ? 256 : 1);
         }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 5) {
+    if (warp == 9) {
         tmem_alloc(smem_u32(tmem_slot), 512);
         tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
@@ -75,7 +81,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_o = tmem + 128;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
@@ -95,7 +101,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     tma_load_3d(base + kOffV + b * kKVBytes + blk * (kBN * 128), &map_v, bar(BAR_VF + b), blk * 64, kvh, row);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------ MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(kFmtF16, kBM, kBN, 0, 0);
@@ -138,42 +144,49 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
     } else {
         // ------------------------------ softmax / correction / epilogue ------------------------------
-        const int r = threadIdx.x;                       // query row == TMEM lane
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int r = threadIdx.x & 127;                 // query row == TMEM lane
+        const int hf = threadIdx.x >> 7;                 // which 32 of a tile's 64 key columns / which half of the output columns
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        const int pair_bar = 1 + (warp & 3);             // named barrier shared by the two warps that cover the same rows
+        float* x_mx = reinterpret_cast<float*>(sm + kOffXch);          // [2][2][128]
+        float* x_l = x_mx + (n_kt & 1) * 256;                           // [2][128]: the slot the last tile does not use
         const int q_pos = tile.q_pos0 + r;
         const float sc = kLog2eF / 16.0f;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kt; ++j) {
             const int b = j & 1;
-            if (!mbar_wait_warp(bar(BAR_SF + b), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait_warp(bar(BAR_SF + b), (j >> 1) & 1, abort_flag)) ok = false;
             tc_fence_after();
-            uint32_t sr[2][32];
-            tmem_ld32(tmem + lane_base + b * kBN, sr[0]);
-            tmem_ld32(tmem + lane_base + b * kBN + 32, sr[1]);
+            uint32_t sr[32];
+            tmem_ld32(tmem + lane_base + b * kBN + hf * 32, sr);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(bar(BAR_SE + b));
-            float s[64];
-            const bool diag = (j * kBN + kBN - 1 > tile.q_pos0);   // warp-uniform: tile may cross a diagonal
+            const int col0 = j * kBN + hf * 32;
+            const bool diag = (col0 + 31 > tile.q_pos0);   // warp-uniform: this half tile may cross a diagonal
             float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                float v = __uint_as_float(sr[c >> 5][c & 31]) * sc;
-                if (diag && (j * kBN + c > q_pos)) v = -INFINITY;
-                s[c] = v;
+            for (int c = 0; c < 32; ++c) {
+                float v = __uint_as_float(sr[c]);
+                if (diag && (col0 + c > q_pos)) v = -INFINITY;
+                sr[c] = __float_as_uint(v);
                 mx = fmaxf(mx, v);
             }
+            x_mx[(b * 2 + hf) * 128 + r] = mx;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            mx = fmaxf(mx, x_mx[(b * 2 + (hf ^ 1)) * 128 + r]) * sc;
             const float m_new = fmaxf(m_ref, mx);            // finite: key 0 is visible to every row
             const bool need = (m_new - m_ref > 8.0f);        // also true on the first tile (m_ref = -inf)
-            if (__any_sync(0xffffffffu, need)) {
+            if (__any_sync(0xffffffffu, need)) {             // same decision in both warps of the pair: same rows, same values
                 if (j > 0) {
-                    if (!mbar_wait_warp(bar(BAR_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait_warp(bar(BAR_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag)) ok = false;
                     tc_fence_after();
                     const float alpha = exp2f(m_ref - m_new);
                     l *= alpha;
 #pragma unroll 1
-                    for (int ch = 0; ch < 8; ++ch) {
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const int ch = hf * 4 + cc;
                         uint32_t orr[32];
                         tmem_ld32(tmem_o + lane_base + ch * 32, orr);
                         tmem_wait_ld();
@@ -185,34 +198,38 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 m_ref = m_new;
             }
-            // P = 2^(s - m_ref) as fp16 into the swizzled K-major A tile
-            if (j >= 2 && !mbar_wait_warp(bar(BAR_PV + b), ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+            // P = 2^(s * scale - m_ref) as fp16 into the swizzled K-major A tile
+            if (j >= 2 && !mbar_wait_warp(bar(BAR_PV + b), ((j >> 1) - 1) & 1, abort_flag)) ok = false;
             unsigned char* prow = sm + kOffP + b * kPBytes + r * 128;
             float lsum = 0.f;
 #pragma unroll
-            for (int c8 = 0; c8 < 8; ++c8) {
+            for (int c8 = 0; c8 < 4; ++c8) {
                 uint32_t pk[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p0 = exp2f(s[c8 * 8 + 2 * e] - m_ref);
-                    const float p1 = exp2f(s[c8 * 8 + 2 * e + 1] - m_ref);
+                    const float p0 = exp2f(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e]), sc, -m_ref));
+                    const float p1 = exp2f(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e + 1]), sc, -m_ref));
                     lsum += p0 + p1;
                     pk[e] = pack_half2(p0, p1);
                 }
-                *reinterpret_cast<uint4*>(prow + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(prow + (((hf * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
             l += lsum;
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(bar(BAR_PF + b));
         }
-        if (ok && mbar_wait_warp(bar(BAR_OF), 0, abort_flag)) {
+        x_l[hf * 128 + r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+        l += x_l[(hf ^ 1) * 128 + r];
+        if (mbar_wait_warp(bar(BAR_OF), 0, abort_flag) && ok) {
             tc_fence_after();
             const float inv_l = 1.0f / l;
             const bool valid = r < tile.n_rows;
             const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
 #pragma unroll 1
-            for (int ch = 0; ch < 8; ++ch) {
+            for (int cc = 0; cc < 4; ++cc) {
+                const int ch = hf * 4 + cc;
                 uint32_t orr[32];
                 tmem_ld32(tmem_o + lane_base + ch * 32, orr);
                 tmem_wait_ld();
@@ -255,7 +272,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
@@ -377,9 +394,9 @@ int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const 
     }
     dim3 grid(n_tiles, kFaHeads);
     if (out_bf16)
-        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, 192, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (__nv_bfloat16*)out, d_error);
+        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (__nv_bfloat16*)out, d_error);
     else
-        fa_prefill_tc_kernel<float><<<grid, 192, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (float*)out, d_error);
+        fa_prefill_tc_kernel<float><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (float*)out, d_error);
     B2_LAUNCH_CHECK();
     return 0;
 }

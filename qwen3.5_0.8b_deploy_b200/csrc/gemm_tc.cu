@@ -269,12 +269,14 @@ int gemm_tc_store(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N > 0, "gemm_tc: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
     B2_TRY(bf16_map(X, M, K, 128, &mx));
-    if (ceil_div(N, 64) >= 100 || splits > 1) {
-        B2_TRY(bf16_map(W, N, K, 64, &mw));
-        return launch_one<64, kEpiStore>(mx, mw, M, N, K, splits, Y, ld_out, split_stride, nullptr, nullptr, d_error, s);
+    // Without split-K every CTA reads all of X from L2, so wide N (the input projections) takes 128-column tiles:
+    // half as many CTAs pull the activations, and 40-65 SMs still stream the weights faster than HBM delivers them.
+    if (splits <= 1 && N >= 2048) {
+        B2_TRY(bf16_map(W, N, K, 128, &mw));
+        return launch_one<128, kEpiStore>(mx, mw, M, N, K, 1, Y, ld_out, split_stride, nullptr, nullptr, d_error, s);
     }
-    B2_TRY(bf16_map(W, N, K, 32, &mw));
-    return launch_one<32, kEpiStore>(mx, mw, M, N, K, splits, Y, ld_out, split_stride, nullptr, nullptr, d_error, s);
+    B2_TRY(bf16_map(W, N, K, 64, &mw));
+    return launch_one<64, kEpiStore>(mx, mw, M, N, K, splits, Y, ld_out, split_stride, nullptr, nullptr, d_error, s);
 }
 
 // act[M, N/2] = silu(gate) * up with W rows arranged in tiles of 32 gate rows followed by the 32 matching up rows.

@@ -25,11 +25,12 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : logf(1.0f + expf(x)); }
 
 // ---- C1, sequence form -------------------------------------------------------------------------------
-// One warp per (run of kConvRun consecutive rows, head): conv + SiLU over the head's q, k and v channels, L2 norm
-// of q and k (eps inside the sqrt), q * 1/sqrt(128), beta and log-decay g.  The warp slides the four-tap window
-// along its rows in registers, so every input row is read once (plus three rows of history per run) and the tap
-// weights stay in registers.  q and k are written as fp32 (q_out, k_out) and / or fp16 (qh_out, kh_out, the operand
-// format of the tensor-core recurrence); null pointers are skipped.
+// One warp per (run of kConvRun consecutive rows, head, part) with part = q, k or v channels of the head: conv +
+// SiLU, L2 norm of q and k (eps inside the sqrt), q * 1/sqrt(128); the v warps also produce beta and the log-decay g.
+// A warp requests its whole input window (the run's rows plus three rows of history, 16 bytes per lane and row) before
+// it computes anything, so every input row leaves HBM once and enough loads are in flight to cover the latency.
+// q and k are written as fp32 (q_out, k_out) and / or fp16 (qh_out, kh_out, the operand format of the tensor-core
+// recurrence); null pointers are skipped.
 constexpr int kConvRun = 16;
 __global__ void __launch_bounds__(128)
 la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_seq,
@@ -41,94 +42,92 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
     const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int n_runs = (rows + kConvRun - 1) / kConvRun;
-    if (gw >= n_runs * kLaHeads) return;
-    const int run = gw / kLaHeads, h = gw % kLaHeads;
-    const int row_begin = run * kConvRun, row_end = min(rows, row_begin + kConvRun);
-    float4 w[3][4];          // tap weights of this lane's four channels per part
+    if (gw >= n_runs * kLaHeads * 3) return;
+    const int part = gw % 3, h = (gw / 3) % kLaHeads, run = gw / (3 * kLaHeads);
+    const int row_begin = run * kConvRun, n = min(rows - row_begin, kConvRun);
+    const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + 4 * lane;   // kd == vd == 128
+    float4 w[4];             // tap weights of this lane's four channels
 #pragma unroll
-    for (int part = 0; part < 3; ++part)
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-            w[part][i] = *reinterpret_cast<const float4*>(conv_w + (size_t)(part * (kLaHeads * kLaKd) + h * kLaKd + 4 * lane + i) * kLaConvK);
-    const float decay = -expf(a_log[h]), dtb = dt_bias[h];
+    for (int i = 0; i < 4; ++i) w[i] = *reinterpret_cast<const float4*>(conv_w + (size_t)(ch + i) * kLaConvK);
     const float q_scale = 1.0f / sqrtf((float)kLaKd);
-    float4 x[3][3];          // x[part][0..2] = inputs at t-3, t-2, t-1
-    int cur_seq = -1;
-    LaSeqMeta sm = {};
-    const float* mrow0 = mixed + h * kLaKd + 4 * lane;
-    float4 nxt[3];           // the next row's inputs, requested one iteration ahead
+    const int s_first = row_seq[row_begin], s_last = row_seq[row_begin + n - 1];
+    float4 x[kConvRun + 3];  // the window: x[i] = input at (first row of the run) - 3 + i
+    LaSeqMeta sm = seqs[s_first];
+    if (s_first == s_last) {
+        const int t0 = row_begin - sm.row0;             // index of the run's first row inside this call's chunk of the sequence
+        const float* st = conv_state_layer + (size_t)sm.slot * conv_stride_slot;
 #pragma unroll
-    for (int part = 0; part < 3; ++part)
-        nxt[part] = *reinterpret_cast<const float4*>(mrow0 + (size_t)row_begin * kLaProjCols + part * (kLaHeads * kLaKd));
-    for (int row = row_begin; row < row_end; ++row) {
-        float4 cur[3] = {nxt[0], nxt[1], nxt[2]};
-        if (row + 1 < row_end) {
-#pragma unroll
-            for (int part = 0; part < 3; ++part)
-                nxt[part] = *reinterpret_cast<const float4*>(mrow0 + (size_t)(row + 1) * kLaProjCols + part * (kLaHeads * kLaKd));
-        }
-        const int sidx = row_seq[row];
-        const bool fresh = sidx != cur_seq;      // first row of the run, or the run crosses into the next sequence
-        if (fresh) { cur_seq = sidx; sm = seqs[sidx]; }
-        const int t = row - sm.row0;             // index inside this call's chunk of the sequence
-        float res[3][4];
-#pragma unroll
-        for (int part = 0; part < 3; ++part) {
-            const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + 4 * lane;   // kd == vd == 128
-            if (fresh) {
-                const float* st = conv_state_layer + (size_t)sm.slot * conv_stride_slot;
-#pragma unroll
-                for (int b = 0; b < 3; ++b) {
-                    const int tt = t - 3 + b;
-                    const float* src = (tt >= 0) ? mixed + (size_t)(sm.row0 + tt) * kLaProjCols + ch
-                                                 : st + (size_t)(tt + 3) * kLaConvDim + ch;
-                    x[part][b] = *reinterpret_cast<const float4*>(src);
-                }
+        for (int i = 0; i < kConvRun + 3; ++i) {
+            const int tt = t0 - 3 + i;
+            if (i < n + 3) {
+                const float* src = (tt >= 0) ? mixed + (size_t)(sm.row0 + tt) * kLaProjCols + ch
+                                             : st + (size_t)(tt + 3) * kLaConvDim + ch;
+                x[i] = *reinterpret_cast<const float4*>(src);
             }
-            const float4 xn = cur[part];
-            const float x0[4] = {x[part][0].x, x[part][0].y, x[part][0].z, x[part][0].w};
-            const float x1[4] = {x[part][1].x, x[part][1].y, x[part][1].z, x[part][1].w};
-            const float x2[4] = {x[part][2].x, x[part][2].y, x[part][2].z, x[part][2].w};
-            const float x3[4] = {xn.x, xn.y, xn.z, xn.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                float s2 = w[part][i].w * x3[i];
-                s2 += w[part][i].x * x2[i];
-                s2 += w[part][i].y * x1[i];
-                s2 += w[part][i].z * x0[i];
-                res[part][i] = silu_f(s2);
-            }
-            x[part][0] = x[part][1]; x[part][1] = x[part][2]; x[part][2] = xn;
         }
-        float qs = 0.f, ksq = 0.f;
+    }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { qs += res[0][i] * res[0][i]; ksq += res[1][i] * res[1][i]; }
-        qs = sqrtf(warp_sum_f(qs) + 1e-6f);
-        ksq = sqrtf(warp_sum_f(ksq) + 1e-6f);
-        float4 q4, k4, v4;
-        float* qp = &q4.x; float* kp = &k4.x; float* vp = &v4.x;
+    for (int j = 0; j < kConvRun; ++j) {
+        if (j >= n) break;
+        const int row = row_begin + j;
+        float4 x0, x1, x2, x3;
+        if (s_first == s_last) {
+            x0 = x[j]; x1 = x[j + 1]; x2 = x[j + 2]; x3 = x[j + 3];
+        } else {
+            // the run crosses into another sequence (a length that is not a multiple of the run): fetch the four taps per row
+            sm = seqs[row_seq[row]];
+            const int t = row - sm.row0;
+            const float* st = conv_state_layer + (size_t)sm.slot * conv_stride_slot;
+            float4 xs[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int tt = t - 3 + b;
+                const float* src = (tt >= 0) ? mixed + (size_t)(sm.row0 + tt) * kLaProjCols + ch
+                                             : st + (size_t)(tt + 3) * kLaConvDim + ch;
+                xs[b] = *reinterpret_cast<const float4*>(src);
+            }
+            x0 = xs[0]; x1 = xs[1]; x2 = xs[2]; x3 = xs[3];
+        }
+        const float a0[4] = {x0.x, x0.y, x0.z, x0.w}, a1[4] = {x1.x, x1.y, x1.z, x1.w};
+        const float a2[4] = {x2.x, x2.y, x2.z, x2.w}, a3[4] = {x3.x, x3.y, x3.z, x3.w};
+        float res[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            qp[i] = __fdiv_rn(res[0][i], qs) * q_scale;
-            kp[i] = __fdiv_rn(res[1][i], ksq);
-            vp[i] = res[2][i];
+            float s2 = w[i].w * a3[i];
+            s2 += w[i].x * a2[i];
+            s2 += w[i].y * a1[i];
+            s2 += w[i].z * a0[i];
+            res[i] = silu_f(s2);
         }
         const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
-        if (q_out) *reinterpret_cast<float4*>(q_out + o) = q4;
-        if (k_out) *reinterpret_cast<float4*>(k_out + o) = k4;
-        if (qh_out) {
-            __half2 a = __floats2half2_rn(q4.x, q4.y), b = __floats2half2_rn(q4.z, q4.w);
-            __half2 c = __floats2half2_rn(k4.x, k4.y), d = __floats2half2_rn(k4.z, k4.w);
-            *reinterpret_cast<uint2*>(qh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-            *reinterpret_cast<uint2*>(kh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&c), *reinterpret_cast<uint32_t*>(&d));
+        if (part == 2) {
+            *reinterpret_cast<float4*>(v_out + o) = make_float4(res[0], res[1], res[2], res[3]);
+        } else {
+            float ss = res[0] * res[0] + res[1] * res[1] + res[2] * res[2] + res[3] * res[3];
+            ss = sqrtf(warp_sum_f(ss) + 1e-6f);
+            const float sc = (part == 0) ? q_scale : 1.0f;
+            float4 r4;
+            if (part == 0) {
+                r4 = make_float4(__fdiv_rn(res[0], ss) * sc, __fdiv_rn(res[1], ss) * sc, __fdiv_rn(res[2], ss) * sc,
+                                 __fdiv_rn(res[3], ss) * sc);
+            } else {
+                r4 = make_float4(__fdiv_rn(res[0], ss), __fdiv_rn(res[1], ss), __fdiv_rn(res[2], ss), __fdiv_rn(res[3], ss));
+            }
+            float* o32 = (part == 0) ? q_out : k_out;
+            __half* o16 = (part == 0) ? qh_out : kh_out;
+            if (o32) *reinterpret_cast<float4*>(o32 + o) = r4;
+            if (o16) {
+                __half2 a = __floats2half2_rn(r4.x, r4.y), b = __floats2half2_rn(r4.z, r4.w);
+                *reinterpret_cast<uint2*>(o16 + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+            }
         }
-        *reinterpret_cast<float4*>(v_out + o) = v4;
-        if (lane == 0) {
-            const float a = mixed[(size_t)row * kLaProjCols + kLaAOff + h];
-            const float b = mixed[(size_t)row * kLaProjCols + kLaBOff + h];
-            beta_out[row * kLaHeads + h] = sigmoid_f(b);
-            g_out[row * kLaHeads + h] = decay * softplus_f(a + dtb);
-        }
+    }
+    if (part == 2 && lane < n) {      // beta and log-decay of the run's rows, one row per lane
+        const int row = row_begin + lane;
+        const float a = mixed[(size_t)row * kLaProjCols + kLaAOff + h];
+        const float b = mixed[(size_t)row * kLaProjCols + kLaBOff + h];
+        beta_out[row * kLaHeads + h] = sigmoid_f(b);
+        g_out[row * kLaHeads + h] = -expf(a_log[h]) * softplus_f(a + dt_bias[h]);
     }
 }
 
@@ -364,7 +363,7 @@ __global__ void la_conv_export_kernel(const float* __restrict__ mine, float* __r
 int launch_la_conv_seq(const float* mixed, const int* d_row_seq, const LaSeqMeta* d_seqs, const float* conv_layer,
                        size_t conv_stride, const float* conv_w, const float* a_log, const float* dt_bias, int rows,
                        float* q, float* k, __half* qh, __half* kh, float* v, float* g, float* beta, cudaStream_t s) {
-    la_conv_seq_kernel<<<ceil_div(ceil_div(rows, kConvRun) * kLaHeads, 4), 128, 0, s>>>(mixed, d_row_seq, d_seqs, conv_layer, conv_stride,
+    la_conv_seq_kernel<<<ceil_div(ceil_div(rows, kConvRun) * kLaHeads * 3, 4), 128, 0, s>>>(mixed, d_row_seq, d_seqs, conv_layer, conv_stride,
                                                                   conv_w, a_log, dt_bias, rows, q, k, qh, kh, v, g, beta);
     B2_LAUNCH_CHECK();
     return 0;

@@ -117,17 +117,23 @@ rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const f
 
 // act = silu(gate) * up.  gu rows hold tiles of 64 columns: 32 gate columns followed by the 32 matching up columns
 // (the layout the decode-step GEMM epilogue consumes as well).  bf16.
-__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int inter, size_t n_pairs, __nv_bfloat16* __restrict__ act) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // index over (row, inter/2)
-    if (i >= n_pairs) return;
-    const size_t half_inter = inter / 2;
-    const size_t row = i / half_inter, c = (i % half_inter) * 2;      // output channel pair c, c+1
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int inter, size_t n_oct, __nv_bfloat16* __restrict__ act) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // index over (row, inter/8): eight outputs per thread
+    if (i >= n_oct) return;
+    const size_t per_row = inter / 8;
+    const size_t row = i / per_row, c = (i % per_row) * 8;            // output channels c .. c+7 (inside one 32-channel tile)
     const size_t gcol = (c / 32) * 64 + (c % 32);
-    const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(gu + row * 2 * inter + gcol);
-    const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(gu + row * 2 * inter + gcol + 32);
-    const float2 g = __bfloat1622float2(g2), u = __bfloat1622float2(u2);
-    const float a0 = g.x / (1.0f + expf(-g.x)) * u.x, a1 = g.y / (1.0f + expf(-g.y)) * u.y;
-    *reinterpret_cast<__nv_bfloat162*>(act + row * inter + c) = __floats2bfloat162_rn(a0, a1);
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gu + row * 2 * inter + gcol);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gu + row * 2 * inter + gcol + 32);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    __nv_bfloat162 o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
+        o[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(act + row * inter + c) = *reinterpret_cast<uint4*>(o);
 }
 
 // Greedy argmax over one row of logits (first maximum wins). grid rows, block 1024.
@@ -458,8 +464,8 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
             B2_TRY(gemm_tc_store(s, st->d_act, st->d_wdown[i], st->d_partials, rows, kHidden, inter, kHidden, pending, pstride, st->d_error));
         } else {
             B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_wgu[i], true, st->d_gu, true, rows, 2 * inter, kHidden));
-            const size_t pairs = (size_t)rows * inter / 2;
-            swiglu_kernel<<<(unsigned)((pairs + 255) / 256), 256, 0, s>>>(st->d_gu, inter, pairs, st->d_act);
+            const size_t octs = (size_t)rows * inter / 8;
+            swiglu_kernel<<<(unsigned)((octs + 255) / 256), 256, 0, s>>>(st->d_gu, inter, octs, st->d_act);
             B2_LAUNCH_CHECK();
             B2_TRY(gemm_xwT(s, st->d_act, true, st->d_wdown[i], true, st->d_h, false, rows, kHidden, inter, 1.0f));
             pending = 0;
