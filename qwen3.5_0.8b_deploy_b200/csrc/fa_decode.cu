@@ -392,27 +392,45 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
             last = __shfl_sync(0xffffffffu, last, 0);
             if (last) {                                // the last partial of the pair to arrive: combine them all
                 __threadfence();
-#pragma unroll 1
-                for (int head = 0; head < 4; ++head) {
-                    float mmax = -INFINITY;
-                    for (int sp = 0; sp < n_parts; ++sp) mmax = fmaxf(mmax, __ldcg(&part_ml[(pbase + sp * 4 + head) * 2]));
-                    float acc[8], lsum = 0.f;
+                // eight lanes per head, 32 consecutive output dims per lane: every part costs one round of independent
+                // 16-byte loads, so the whole combine is a few L2 latencies long
+                const int hd = lane >> 3, sub = lane & 7;
+                float mmax = -INFINITY;
+                for (int sp = 0; sp < n_parts; ++sp) mmax = fmaxf(mmax, __ldcg(&part_ml[(pbase + sp * 4 + hd) * 2]));
+                float4 acc[8];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-                    for (int sp = 0; sp < n_parts; ++sp) {
-                        const float wgt = exp2f(__ldcg(&part_ml[(pbase + sp * 4 + head) * 2]) - mmax);
-                        lsum += __ldcg(&part_ml[(pbase + sp * 4 + head) * 2 + 1]) * wgt;
-                        const float* po = part_o + (pbase + sp * 4 + head) * kHeadDim + lane;
+                for (int k = 0; k < 8; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+                float lsum = 0.f;
+                for (int sp = 0; sp < n_parts; ++sp) {
+                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(&part_ml[(pbase + sp * 4 + hd) * 2]));
+                    const float wgt = exp2f(ml.x - mmax);
+                    lsum += ml.y * wgt;
+                    const float4* po = reinterpret_cast<const float4*>(part_o + (pbase + sp * 4 + hd) * kHeadDim + sub * 32);
+                    float4 pv[8];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) acc[k] += __ldcg(po + 32 * k) * wgt;
-                    }
-                    const float inv = inv_boost / lsum;
+                    for (int k = 0; k < 8; ++k) pv[k] = __ldcg(po + k);
 #pragma unroll
                     for (int k = 0; k < 8; ++k) {
-                        const size_t oo = obase + (size_t)head * kHeadDim + lane + 32 * k;
-                        float r = acc[k] * inv;
-                        if (gate) r *= __half2float(gate[oo]);
-                        out[oo] = (OutT)r;
+                        acc[k].x += pv[k].x * wgt; acc[k].y += pv[k].y * wgt; acc[k].z += pv[k].z * wgt; acc[k].w += pv[k].w * wgt;
+                    }
+                }
+                const float inv = inv_boost / lsum;
+                const size_t oo = obase + (size_t)hd * kHeadDim + sub * 32;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    float r0 = acc[k].x * inv, r1 = acc[k].y * inv, r2 = acc[k].z * inv, r3 = acc[k].w * inv;
+                    if (gate) {
+                        const uint2 g2 = *reinterpret_cast<const uint2*>(gate + oo + 4 * k);
+                        const float2 ga = __half22float2(*reinterpret_cast<const __half2*>(&g2.x));
+                        const float2 gb = __half22float2(*reinterpret_cast<const __half2*>(&g2.y));
+                        r0 *= ga.x; r1 *= ga.y; r2 *= gb.x; r3 *= gb.y;
+                    }
+                    if constexpr (sizeof(OutT) == 4) {
+                        *reinterpret_cast<float4*>(out + oo + 4 * k) = make_float4(r0, r1, r2, r3);
+                    } else {
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(r0, r1), h1 = __floats2bfloat162_rn(r2, r3);
+                        *reinterpret_cast<uint2*>(out + oo + 4 * k) =
+                            make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
                     }
                 }
             }

@@ -30,6 +30,11 @@ constexpr uint32_t kOffXch = kOffBar + 256;          // row-maximum exchange [2 
 constexpr uint32_t kF1Smem = kOffXch + 2048;         // no alignment slack: the kernel checks its base instead
 constexpr int kF1Threads = 320;
 constexpr float kLog2eF = 1.4426950408889634f;
+__device__ __forceinline__ float ex2_fast(float x) {     // 2^x, one MUFU op; -inf -> 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 enum { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 15,
        BAR_OF = 17, BAR_COUNT = 18 };
@@ -87,18 +92,33 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
             for (int blk = 0; blk < 4; ++blk)
                 tma_load_3d(base + kOffQ + blk * (kBM * 128), &map_q, bar(BAR_Q), blk * 64, head, tile.q_row0);
-            for (int j = 0; j < n_kt; ++j) {
-                const int b = j & 1;
-                const uint32_t par = ((j >> 1) - 1) & 1;
-                const int row = tile.ctx_row0 + j * kBN;
-                if (j >= 2 && !mbar_wait(bar(BAR_KE + b), par, abort_flag)) break;
-                mbar_arrive_expect_tx(bar(BAR_KF + b), kKVBytes);
-                for (int blk = 0; blk < 4; ++blk)
-                    tma_load_3d(base + kOffK + b * kKVBytes + blk * (kBN * 128), &map_k, bar(BAR_KF + b), blk * 64, kvh, row);
-                if (j >= 2 && !mbar_wait(bar(BAR_VE + b), par, abort_flag)) break;
-                mbar_arrive_expect_tx(bar(BAR_VF + b), kKVBytes);
-                for (int blk = 0; blk < 4; ++blk)
-                    tma_load_3d(base + kOffV + b * kKVBytes + blk * (kBN * 128), &map_v, bar(BAR_VF + b), blk * 64, kvh, row);
+            // K and V buffers are refilled independently, each as soon as its own consumer (the S product, the PV
+            // product) has released it: a K tile is then requested two key tiles ahead of its use, not behind the V wait.
+            int jk = 0, jv = 0;
+            const uint64_t t0 = global_timer_ns();
+            uint32_t idle = 0;
+            while (jk < n_kt || jv < n_kt) {
+                bool progressed = false;
+                if (jk < n_kt && (jk < 2 || mbar_test_wait(bar(BAR_KE + (jk & 1)), ((jk >> 1) - 1) & 1))) {
+                    const int b = jk & 1, row = tile.ctx_row0 + jk * kBN;
+                    mbar_arrive_expect_tx(bar(BAR_KF + b), kKVBytes);
+                    for (int blk = 0; blk < 4; ++blk)
+                        tma_load_3d(base + kOffK + b * kKVBytes + blk * (kBN * 128), &map_k, bar(BAR_KF + b), blk * 64, kvh, row);
+                    ++jk;
+                    progressed = true;
+                }
+                if (jv < n_kt && (jv < 2 || mbar_test_wait(bar(BAR_VE + (jv & 1)), ((jv >> 1) - 1) & 1))) {
+                    const int b = jv & 1, row = tile.ctx_row0 + jv * kBN;
+                    mbar_arrive_expect_tx(bar(BAR_VF + b), kKVBytes);
+                    for (int blk = 0; blk < 4; ++blk)
+                        tma_load_3d(base + kOffV + b * kKVBytes + blk * (kBN * 128), &map_v, bar(BAR_VF + b), blk * 64, kvh, row);
+                    ++jv;
+                    progressed = true;
+                }
+                if (!progressed && ((++idle & 255u) == 0u)) {
+                    if (*abort_flag) break;
+                    if (global_timer_ns() - t0 > 2000000000ull) { *abort_flag = 1; break; }
+                }
             }
         }
     } else if (warp == 9) {
@@ -207,8 +227,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 uint32_t pk[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p0 = exp2f(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e]), sc, -m_ref));
-                    const float p1 = exp2f(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e + 1]), sc, -m_ref));
+                    const float p0 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e]), sc, -m_ref));
+                    const float p1 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e + 1]), sc, -m_ref));
                     lsum += p0 + p1;
                     pk[e] = pack_half2(p0, p1);
                 }
@@ -222,12 +242,20 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         x_l[hf * 128 + r] = l;
         asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
         l += x_l[(hf ^ 1) * 128 + r];
+        const bool valid = r < tile.n_rows;
+        const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
+        uint4 gpre[4][4];      // this thread's gate values, requested before the wait on the last PV product
+        if (gate && valid) {
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc)
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+                    gpre[cc][q4] = *reinterpret_cast<const uint4*>(gate + orow + (hf * 4 + cc) * 32 + q4 * 8);
+        }
         if (mbar_wait_warp(bar(BAR_OF), 0, abort_flag) && ok) {
             tc_fence_after();
             const float inv_l = 1.0f / l;
-            const bool valid = r < tile.n_rows;
-            const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
-#pragma unroll 1
+#pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 const int ch = hf * 4 + cc;
                 uint32_t orr[32];
@@ -238,10 +266,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
                     for (int c = 0; c < 32; ++c) vals[c] = __uint_as_float(orr[c]) * inv_l;
                     if (gate) {
-                        const uint4* gp = reinterpret_cast<const uint4*>(gate + orow + ch * 32);
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {
-                            const uint4 gv = gp[q4];
+                            const uint4 gv = gpre[cc][q4];
                             const __half2* gh = reinterpret_cast<const __half2*>(&gv);
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {

@@ -72,7 +72,7 @@ int launch_la_gated_norm(const float* core, const float* mixed, const float* nor
                          cudaStream_t s);
 int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max_seqs, float* rec_layer,
                      size_t rec_stride, float* conv_layer, size_t conv_stride, const float* conv_w, const float* a_log,
-                     const float* dt_bias, const float* norm_w, void* out, bool out_bf16, cudaStream_t s);
+                     const float* dt_bias, const float* norm_w, void* out, bool out_bf16, int* d_error, cudaStream_t s);
 int launch_la_conv_import(const float* ref_conv, float* mine, cudaStream_t s);
 int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
 

@@ -11,6 +11,7 @@
 #include "kernels.cuh"
 #include "ptx_utils.cuh"
 
+#include <algorithm>
 #include <cstdlib>
 
 namespace b200 {
@@ -229,12 +230,14 @@ la_gated_norm_kernel(const float* __restrict__ core, const float* __restrict__ m
 }
 
 // ---- R1: fused recurrent decode step ---------------------------------------------------------------------
-// grid (heads, n_seqs), block 256.  Per (sequence, head): conv update of the head's 384 channels,
+// grid (heads, n_seqs), block 32 * 128 / kRows.  Per (sequence, head): conv update of the head's 384 channels,
 // L2 norms, gates, then ONE pass over the 128x128 fp32 state: thread (warp r, lane c) keeps rows
-// 16r..16r+15 of columns 4c..4c+3 in registers between the read (kv = S^T k) and the write
+// kRows * r .. kRows * r + kRows - 1 of columns 4c..4c+3 in registers between the read (kv = S^T k) and the write
 // (S' = g S + k (x) delta, o = S'^T q), followed by the gated RMSNorm.
-template <typename OutT, int kMinBlocks>
-__global__ void __launch_bounds__(256, kMinBlocks)
+// kRows = 16: 256 threads, 2 or 3 CTAs per SM.  kRows = 8: 512 threads, 2 CTAs per SM = 1024 resident threads with half
+// the registers each, so 2048 units fill 296 slots 6.9 times instead of 444 slots 4.6 times (a fuller last wave).
+template <typename OutT, int kMinBlocks, int kRows>
+__global__ void __launch_bounds__(32 * 128 / kRows, kMinBlocks)
 la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots, int max_seqs,
                  float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
                  size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
@@ -244,7 +247,8 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
     const int slot = slots[b];
     if (slot < 0 || slot >= max_seqs) return;
     __shared__ __align__(16) float s_qkv[3][kLaKd];
-    __shared__ __align__(16) float s_part[8][kLaVd];
+    constexpr int kWarpsR = 128 / kRows, kThreadsR = 32 * kWarpsR;
+    __shared__ __align__(16) float s_part[kWarpsR][kLaVd];
     __shared__ float s_gb[2];
     __shared__ float s_red[4];
     const float* mrow = mixed + (size_t)b * kLaProjCols;
@@ -252,15 +256,15 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
     float* Sg = rec_layer + (size_t)slot * rec_stride_slot + (size_t)h * kLaKd * kLaVd;
 
     // Issue the state loads first: they are the long pole and do not depend on anything below.
-    float4 S[16];
-    const float* Sp = Sg + (size_t)(warp * 16) * kLaVd + 4 * lane;
+    float4 S[kRows];
+    const float* Sp = Sg + (size_t)(warp * kRows) * kLaVd + 4 * lane;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) S[i] = __ldcs(reinterpret_cast<const float4*>(Sp + (size_t)i * kLaVd));
+    for (int i = 0; i < kRows; ++i) S[i] = __ldcs(reinterpret_cast<const float4*>(Sp + (size_t)i * kLaVd));
     // The state was last written by this layer's previous step; everything read below comes from the preceding kernel.
     pdl_enter();
 
     // conv + SiLU + state shift for the head's q, k, v channels (384 values, 256 threads)
-    for (int i = tid; i < 3 * kLaKd; i += 256) {
+    for (int i = tid; i < 3 * kLaKd; i += kThreadsR) {
         const int part = i / kLaKd, d = i % kLaKd;
         const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + d;
         const float x = mrow[ch];
@@ -292,18 +296,18 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
     __syncthreads();
     const float gt = s_gb[0], bt = s_gb[1];
 
-    // pass 1 (registers): partial kv over this warp's 16 rows
+    // pass 1 (registers): partial kv over this warp's rows
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float kk = s_qkv[1][warp * 16 + i];
+    for (int i = 0; i < kRows; ++i) {
+        const float kk = s_qkv[1][warp * kRows + i];
         acc.x += S[i].x * kk; acc.y += S[i].y * kk; acc.z += S[i].z * kk; acc.w += S[i].w * kk;
     }
     *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
     __syncthreads();
     float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int w = 0; w < 8; ++w) {
+    for (int w = 0; w < kWarpsR; ++w) {
         const float4 p = *reinterpret_cast<const float4*>(&s_part[w][4 * lane]);
         kv.x += p.x; kv.y += p.y; kv.z += p.z; kv.w += p.w;
     }
@@ -315,11 +319,11 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
 
     // pass 2 (registers): update, write back, partial o
     acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float* Sw = Sg + (size_t)(warp * 16) * kLaVd + 4 * lane;
+    float* Sw = Sg + (size_t)(warp * kRows) * kLaVd + 4 * lane;
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float kk = s_qkv[1][warp * 16 + i];
-        const float qq = s_qkv[0][warp * 16 + i];
+    for (int i = 0; i < kRows; ++i) {
+        const float kk = s_qkv[1][warp * kRows + i];
+        const float qq = s_qkv[0][warp * kRows + i];
         float4 s = S[i];
         s.x = s.x * gt + kk * dl.x; s.y = s.y * gt + kk * dl.y;
         s.z = s.z * gt + kk * dl.z; s.w = s.w * gt + kk * dl.w;
@@ -333,7 +337,7 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
     if (tid < kLaVd) {
         float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) o += s_part[w][tid];
+        for (int w = 0; w < kWarpsR; ++w) o += s_part[w][tid];
         float ss = warp_sum_f(o * o);
         if (lane == 0) s_red[warp] = ss;
         // warps 0..3 all take this branch, so a named barrier over 128 threads is enough
@@ -343,6 +347,199 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
         const float z = mrow[kLaZOff + h * kLaVd + tid];
         out[(size_t)b * (kLaHeads * kLaVd) + h * kLaVd + tid] = (OutT)(o * inv * norm_w[tid] * silu_f(z));
     }
+}
+
+// ---- R1, streamed form -----------------------------------------------------------------------------------------
+// Same arithmetic as la_decode_kernel, organised as a persistent kernel (one CTA per SM) that walks its (sequence,
+// head) units round-robin.  A producer lane brings each unit's 64 KB state into a three-stage shared-memory ring with
+// one bulk (TMA) copy and writes it back with one bulk store, so two state loads are always in flight per SM while
+// the eight compute warps work on a third, and the last wave of a grid of independent CTAs disappears.  Opt-in
+// (B200ATTN_LA_DECODE=stream): it is bit-identical to la_decode_kernel but currently slower, see launch_la_decode.
+constexpr int kR1Stages = 3;
+constexpr uint32_t kR1StateBytes = kLaKd * kLaVd * 4;
+constexpr uint32_t kR1Smem = kR1Stages * kR1StateBytes + 128;
+constexpr int kR1Threads = 288;
+
+template <typename OutT>
+__global__ void __launch_bounds__(kR1Threads, 1)
+la_decode_stream_kernel(const float* __restrict__ mixed, const int* __restrict__ slots, int n_seqs, int max_seqs,
+                        float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
+                        size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
+                        const float* __restrict__ dt_bias, const float* __restrict__ norm_w, OutT* __restrict__ out,
+                        int* __restrict__ error_word) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(16) float s_qkv[3][kLaKd];
+    __shared__ __align__(16) float s_part[8][kLaVd];
+    __shared__ float s_gb[2];
+    __shared__ float s_red[4];
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t bar0 = smem_u32(smem + kR1Stages * kR1StateBytes);
+    auto full = [&](int s) { return bar0 + 8u * s; };
+    auto done = [&](int s) { return bar0 + 8u * (kR1Stages + s); };
+    const int n_units = n_seqs * kLaHeads;
+    const int n_my = ((int)blockIdx.x < n_units) ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    if (tid == 0) {
+        for (int s = 0; s < kR1Stages; ++s) { mbar_init(full(s), 1); mbar_init(done(s), 256); }
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    volatile int* abort_flag = &s_abort;
+    auto unit_state = [&](int i) -> float* {         // global address of unit i's state, or null for a slot out of range
+        const int u = blockIdx.x + i * gridDim.x;
+        const int slot = slots[u / kLaHeads];
+        if (slot < 0 || slot >= max_seqs) return nullptr;
+        return rec_layer + (size_t)slot * rec_stride_slot + (size_t)(u % kLaHeads) * kLaKd * kLaVd;
+    };
+
+    if (warp == 8) {
+        // ------------------------------ producer: state in, state out ------------------------------
+        if (lane == 0) {
+            auto load = [&](int i) {
+                const float* src = unit_state(i);
+                const int s = i % kR1Stages;
+                if (src) {
+                    mbar_arrive_expect_tx(full(s), kR1StateBytes);
+                    bulk_g2s(smem_u32(smem + s * kR1StateBytes), src, kR1StateBytes, full(s));
+                } else {
+                    mbar_arrive(full(s));        // nothing to load: the consumers skip the unit
+                }
+            };
+            // the states were written by this layer's previous step, not by the preceding kernel: request them first
+            for (int i = 0; i < n_my && i < kR1Stages; ++i) load(i);
+            pdl_enter();
+            for (int j = 0; j < n_my; ++j) {
+                const int s = j % kR1Stages;
+                if (!mbar_wait(done(s), (j / kR1Stages) & 1, abort_flag)) break;
+                if (*abort_flag) break;          // a compute warp gave up on this stage: it does not hold a valid state
+                float* dst = unit_state(j);
+                if (dst) {
+                    bulk_s2g(dst, smem_u32(smem + s * kR1StateBytes), kR1StateBytes);
+                    bulk_commit_group();
+                    bulk_wait_group_read0();     // the stage may be refilled
+                }
+                if (j + kR1Stages < n_my) load(j + kR1Stages);
+            }
+            bulk_wait_group0();
+        } else {
+            pdl_enter();
+        }
+    } else {
+        // ------------------------------ compute warps ------------------------------
+        pdl_enter();
+        bool ok = true;
+        for (int j = 0; j < n_my; ++j) {
+            const int u = blockIdx.x + j * gridDim.x;
+            const int b = u / kLaHeads, h = u % kLaHeads;
+            const int slot = slots[b];
+            const bool valid = slot >= 0 && slot < max_seqs;
+            const int s = j % kR1Stages;
+            const float* mrow = mixed + (size_t)b * kLaProjCols;
+            if (valid) {
+                // conv + SiLU + state shift for the head's q, k, v channels (384 values, 256 threads)
+                float* cst = conv_layer + (size_t)slot * conv_stride_slot;
+                for (int i = tid; i < 3 * kLaKd; i += 256) {
+                    const int part = i / kLaKd, d = i % kLaKd;
+                    const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + d;
+                    const float x = mrow[ch];
+                    const float s0 = cst[ch], s1 = cst[kLaConvDim + ch], s2 = cst[2 * kLaConvDim + ch];
+                    const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)ch * kLaConvK);
+                    float sv = w.w * x;
+                    sv += w.x * s2;
+                    sv += w.y * s1;
+                    sv += w.z * s0;
+                    s_qkv[part][d] = silu_f(sv);
+                    cst[ch] = s1;
+                    cst[kLaConvDim + ch] = s2;
+                    cst[2 * kLaConvDim + ch] = x;
+                }
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (valid) {
+                if (warp < 2) {   // warp 0: q, warp 1: k
+                    float4 x4 = *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]);
+                    float ss = x4.x * x4.x + x4.y * x4.y + x4.z * x4.z + x4.w * x4.w;
+                    ss = sqrtf(warp_sum_f(ss) + 1e-6f);
+                    const float sc = (warp == 0) ? 1.0f / sqrtf((float)kLaKd) : 1.0f;
+                    x4.x = __fdiv_rn(x4.x, ss) * sc; x4.y = __fdiv_rn(x4.y, ss) * sc;
+                    x4.z = __fdiv_rn(x4.z, ss) * sc; x4.w = __fdiv_rn(x4.w, ss) * sc;
+                    *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]) = x4;
+                } else if (tid == 64) {
+                    const float a = mrow[kLaAOff + h], bb = mrow[kLaBOff + h];
+                    s_gb[0] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+                    s_gb[1] = sigmoid_f(bb);
+                }
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (!mbar_wait_warp(full(s), (j / kR1Stages) & 1, abort_flag)) ok = false;
+            const bool work = valid && ok;
+            const float gt = s_gb[0], bt = s_gb[1];
+            float4* Ss = reinterpret_cast<float4*>(smem + s * kR1StateBytes) + (size_t)(warp * 16) * (kLaVd / 4) + lane;
+            float4 S[16];
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (work) {
+                // pass 1 (registers): partial kv over this warp's 16 rows
+#pragma unroll
+                for (int i = 0; i < 16; ++i) S[i] = Ss[i * (kLaVd / 4)];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float kk = s_qkv[1][warp * 16 + i];
+                    acc.x += S[i].x * kk; acc.y += S[i].y * kk; acc.z += S[i].z * kk; acc.w += S[i].w * kk;
+                }
+                *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (work) {
+                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    const float4 p = *reinterpret_cast<const float4*>(&s_part[w][4 * lane]);
+                    kv.x += p.x; kv.y += p.y; kv.z += p.z; kv.w += p.w;
+                }
+                const float4 v4 = *reinterpret_cast<const float4*>(&s_qkv[2][4 * lane]);
+                dl.x = (v4.x - gt * kv.x) * bt; dl.y = (v4.y - gt * kv.y) * bt;
+                dl.z = (v4.z - gt * kv.z) * bt; dl.w = (v4.w - gt * kv.w) * bt;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // s_part is reused below
+            if (work) {
+                // pass 2 (registers): update, back into the stage, partial o
+                acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float kk = s_qkv[1][warp * 16 + i];
+                    const float qq = s_qkv[0][warp * 16 + i];
+                    float4 sv = S[i];
+                    sv.x = sv.x * gt + kk * dl.x; sv.y = sv.y * gt + kk * dl.y;
+                    sv.z = sv.z * gt + kk * dl.z; sv.w = sv.w * gt + kk * dl.w;
+                    Ss[i * (kLaVd / 4)] = sv;
+                    acc.x += sv.x * qq; acc.y += sv.y * qq; acc.z += sv.z * qq; acc.w += sv.w * qq;
+                }
+                *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
+            }
+            fence_proxy_async_smem();
+            mbar_arrive(done(s));
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            // o[vd], gated RMSNorm over the head's 128 values
+            if (tid < kLaVd) {
+                float o = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) o += s_part[w][tid];
+                float ss = warp_sum_f(o * o);
+                if (lane == 0) s_red[warp] = ss;
+                asm volatile("bar.sync 2, 128;" ::: "memory");   // warps 0..3 all take this branch
+                if (work) {
+                    const float var = (s_red[0] + s_red[1] + s_red[2] + s_red[3]) / (float)kLaVd;
+                    const float inv = 1.0f / sqrtf(var + 1e-6f);
+                    const float z = mrow[kLaZOff + h * kLaVd + tid];
+                    out[(size_t)b * (kLaHeads * kLaVd) + h * kLaVd + tid] = (OutT)(o * inv * norm_w[tid] * silu_f(z));
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && s_abort) atomicExch(error_word, 6);
 }
 
 // ---- state import / export in the reference's layouts ------------------------------------------------------
@@ -395,17 +592,39 @@ int launch_la_gated_norm(const float* core, const float* mixed, const float* nor
 }
 int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max_seqs, float* rec_layer,
                      size_t rec_stride, float* conv_layer, size_t conv_stride, const float* conv_w, const float* a_log,
-                     const float* dt_bias, const float* norm_w, void* out, bool out_bf16, cudaStream_t s) {
-    dim3 grid(kLaHeads, n_seqs);
-    static int occ = 0;      // resident CTAs per SM the kernel is compiled for: 2 (123 registers) or 3 (80 registers)
-    if (occ == 0) {
-        const char* e = std::getenv("B200ATTN_LA_DECODE_OCC");
-        occ = (e && e[0] == '2') ? 2 : 3;
+                     const float* dt_bias, const float* norm_w, void* out, bool out_bf16, int* d_error, cudaStream_t s) {
+    // B200ATTN_LA_DECODE=stream selects the persistent kernel with the TMA state ring (read on every call so both can be
+    // compared).  Measured at 128 sequences: 73.7 us against 53.4 us for the one-CTA-per-unit kernel below: one compute
+    // group per SM works through its units one after the other and cannot hide the input-load and barrier latencies
+    // that three independent resident CTAs overlap, so it is not the default.
+    const char* mode = std::getenv("B200ATTN_LA_DECODE");
+    if (d_error && mode && mode[0] == 's') {
+        static int n_sm = 0;
+        if (n_sm == 0) {
+            int dev = 0;
+            B2_CUDA(cudaGetDevice(&dev));
+            B2_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+            B2_CUDA(cudaFuncSetAttribute(la_decode_stream_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1Smem));
+            B2_CUDA(cudaFuncSetAttribute(la_decode_stream_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1Smem));
+        }
+        const dim3 grid(std::min(n_sm, n_seqs * kLaHeads));
+        if (out_bf16)
+            launch_pdl(la_decode_stream_kernel<__nv_bfloat16>, grid, dim3(kR1Threads), kR1Smem, s, mixed, d_slots, n_seqs, max_seqs,
+                       rec_layer, rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (__nv_bfloat16*)out, d_error);
+        else
+            launch_pdl(la_decode_stream_kernel<float>, grid, dim3(kR1Threads), kR1Smem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
+                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (float*)out, d_error);
+        B2_LAUNCH_CHECK();
+        return 0;
     }
-#define LA_DEC(T, O) launch_pdl(la_decode_kernel<T, O>, grid, dim3(256), 0, s, mixed, d_slots, max_seqs, rec_layer, rec_stride, \
-                                conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out)
-    if (out_bf16) { if (occ == 2) LA_DEC(__nv_bfloat16, 2); else LA_DEC(__nv_bfloat16, 3); }
-    else          { if (occ == 2) LA_DEC(float, 2); else LA_DEC(float, 3); }
+    dim3 grid(kLaHeads, n_seqs);
+    // B200ATTN_LA_DECODE_OCC: 2 or 3 = 256-thread CTAs, that many per SM; default = 512-thread CTAs, two per SM
+    const char* e = std::getenv("B200ATTN_LA_DECODE_OCC");
+    const int occ = (e && (e[0] == '2' || e[0] == '3')) ? e[0] - '0' : 0;
+#define LA_DEC(T, O, R) launch_pdl(la_decode_kernel<T, O, R>, grid, dim3(32 * 128 / R), 0, s, mixed, d_slots, max_seqs, rec_layer, \
+                                   rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out)
+    if (out_bf16) { if (occ == 2) LA_DEC(__nv_bfloat16, 2, 16); else if (occ == 3) LA_DEC(__nv_bfloat16, 3, 16); else LA_DEC(__nv_bfloat16, 2, 8); }
+    else          { if (occ == 2) LA_DEC(float, 2, 16); else if (occ == 3) LA_DEC(float, 3, 16); else LA_DEC(float, 2, 8); }
 #undef LA_DEC
     B2_LAUNCH_CHECK();
     return 0;

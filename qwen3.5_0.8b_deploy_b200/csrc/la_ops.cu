@@ -316,7 +316,7 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
             ProfScope prof(PROF_LA_DECODE, s);
             B2_TRY(launch_la_decode(la->d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
                                     st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, la->d_gated,
-                                    bf16, s));
+                                    bf16, la->d_error, s));
         }
         return project_out(n_seqs);
     }
@@ -389,5 +389,6 @@ extern "C" int b200attn_la_decode_core(b200attn_la la, b200attn_la_state st, int
     float* conv_layer = st->d_conv + (size_t)layer * st->cfg.max_seqs * st->conv_stride_slot();
     ProfScope prof(PROF_LA_DECODE, s);
     return launch_la_decode(d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
-                            st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, d_out, false, s);
+                            st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, d_out, false,
+                            la->d_error, s);
 }

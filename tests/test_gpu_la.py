@@ -57,9 +57,12 @@ def test_layer_against_reference_fixture(ops, cuda, synth):
     np.testing.assert_allclose(conv.cpu().numpy(), g["conv"], rtol=1e-4, atol=1e-5)
 
 
-def test_decode_from_seeded_state(ops, cuda, oracle, synth):
+@pytest.mark.parametrize("kernel", ["stream", "classic"])
+def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel):
     """Recurrent decode: 4 sequences, state ~ N(0, 0.05) and a warm conv cache imported in the
-    reference's layouts, 24 single-token steps; outputs every step, state at the end."""
+    reference's layouts, 24 single-token steps; outputs every step, state at the end.  Both forms of the
+    decode kernel (persistent with a TMA state ring / one CTA per unit); the library reads the variable per call."""
+    monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
     torch = cuda
     w = synth.la_weights(52)
     n, steps = 4, 24
@@ -90,6 +93,41 @@ def test_decode_from_seeded_state(ops, cuda, oracle, synth):
         np.testing.assert_allclose(conv.cpu().numpy(), refs[i].conv_state, rtol=1e-4, atol=1e-5)
     rec0, _ = st.export_state(0, 0)          # the other layer was never touched
     assert not rec0.any()
+
+
+def test_streamed_decode_equals_classic_kernel(ops, cuda, synth, monkeypatch):
+    """72 sequences x 16 heads = 1152 units on 148 persistent CTAs: every CTA walks its state ring seven or eight
+    times (stage reuse, write-back, refill).  The two kernels do the same arithmetic in the same order, so outputs,
+    recurrent states and conv states must be identical bit for bit.  One slot is out of range and must be skipped."""
+    torch = cuda
+    n, steps = 72, 3
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=n, max_prefill_rows=64)
+    la.set_weights(synth.la_weights(57))
+    g = torch.Generator(device="cuda").manual_seed(57)
+    results = {}
+    for kernel in ("classic", "stream"):
+        monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
+        st = ops.LinearAttnState(1, n)
+        g.manual_seed(57)
+        for i in range(0, n, 9):
+            st.import_state(0, i, torch.randn((16, 128, 128), device="cuda", generator=g) * 0.05,
+                            torch.randn((6144, 3), device="cuda", generator=g) * 0.5)
+        slots = torch.arange(n, dtype=torch.int32, device="cuda")
+        slots[5] = -1
+        outs = []
+        for t in range(steps):
+            mixed = torch.randn((n, 8224), device="cuda", generator=g) * 0.6
+            outs.append(la.decode_core(mixed, st, 0, slots).clone())
+        states = [st.export_state(0, i) for i in (0, 5, 9, 36, 71)]
+        results[kernel] = (outs, states)
+        assert la.device_status() == 0
+    for a, b in zip(results["classic"][0], results["stream"][0]):
+        keep = torch.ones(n, dtype=torch.bool, device="cuda")
+        keep[5] = False                      # the skipped sequence's output rows are not written by either kernel
+        assert torch.equal(a[keep], b[keep])
+    for (ra, ca), (rb, cb) in zip(results["classic"][1], results["stream"][1]):
+        assert torch.equal(ra, rb) and torch.equal(ca, cb)
+    assert not results["stream"][1][1][0].any()      # slot 5's state was never touched
 
 
 def test_ragged_batch_and_continuation(ops, cuda, oracle, synth):
