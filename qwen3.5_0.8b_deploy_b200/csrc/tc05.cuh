@@ -98,7 +98,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         : "memory");
 }
 
-// ---- tiled TMA loads (no multicast) --------------------------------------------------------------------------------
+// ---- tiled TMA loads (every CTA fetches its own tiles) --------------------------------------------------------------
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int c0, int c1,
                                             int c2) {
     asm volatile(

@@ -57,12 +57,14 @@ def test_layer_against_reference_fixture(ops, cuda, synth):
     np.testing.assert_allclose(conv.cpu().numpy(), g["conv"], rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("kernel", ["stream", "classic"])
-def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel):
+@pytest.mark.parametrize("kernel,occ", [("classic", ""), ("classic", "512"), ("stream", "")])
+def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel, occ):
     """Recurrent decode: 4 sequences, state ~ N(0, 0.05) and a warm conv cache imported in the
-    reference's layouts, 24 single-token steps; outputs every step, state at the end.  Both forms of the
-    decode kernel (persistent with a TMA state ring / one CTA per unit); the library reads the variable per call."""
+    reference's layouts, 24 single-token steps; outputs every step, state at the end.  Every form of the decode
+    kernel: one CTA per unit with 256 threads (default) or 512 threads, and the persistent one with a TMA state
+    ring; the library reads the variables per call."""
     monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
+    monkeypatch.setenv("B200ATTN_LA_DECODE_OCC", occ)
     torch = cuda
     w = synth.la_weights(52)
     n, steps = 4, 24
@@ -97,14 +99,16 @@ def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel)
 
 def test_streamed_decode_equals_classic_kernel(ops, cuda, synth, monkeypatch):
     """72 sequences x 16 heads = 1152 units on 148 persistent CTAs: every CTA walks its state ring seven or eight
-    times (stage reuse, write-back, refill).  The two kernels do the same arithmetic in the same order, so outputs,
-    recurrent states and conv states must be identical bit for bit.  One slot is out of range and must be skipped."""
+    times (stage reuse, write-back, refill).  It does the same arithmetic in the same order as the 256-thread
+    one-CTA-per-unit kernel, so outputs, recurrent states and conv states must be identical bit for bit.  One slot is
+    out of range and must be skipped."""
     torch = cuda
     n, steps = 72, 3
     la = ops.LinearAttention(ops.PROJ_FP32, max_batch=n, max_prefill_rows=64)
     la.set_weights(synth.la_weights(57))
     g = torch.Generator(device="cuda").manual_seed(57)
     results = {}
+    monkeypatch.setenv("B200ATTN_LA_DECODE_OCC", "3")     # 256 threads, 16 state rows per warp, as in the persistent kernel
     for kernel in ("classic", "stream"):
         monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
         st = ops.LinearAttnState(1, n)
