@@ -193,7 +193,8 @@ static int decode_pages_per_warp(const b200attn_kv_pool pool) {
 int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
                     int n_seqs, const int* d_slots_in, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
                     float y_beta, DecodeOut* dout, cudaStream_t s) {
-    B2_CHECK_ARG(pool && d_x && d_y, "full attention: null argument");
+    const bool core_only = decode && dout && dout->core_only;
+    B2_CHECK_ARG(pool && (core_only || (d_x && d_y)), "full attention: null argument");
     B2_TRY(fa_check(fa, pool, layer));
     const KvView kv = pool->view();
     const bool bf16 = fa->cfg.proj_precision == B200ATTN_PROJ_BF16;
@@ -204,7 +205,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= fa->cfg.max_batch, "fa_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, fa->cfg.max_batch);
         const int ppw = decode_pages_per_warp(pool);
         const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
-        B2_TRY(fa_project_in(fa, d_x, x_is_bf16, n_seqs, true, pool->d_error, s));
+        if (!core_only) B2_TRY(fa_project_in(fa, d_x, x_is_bf16, n_seqs, true, pool->d_error, s));
         B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, n_seqs, fa->d_qnorm, fa->d_inv_freq, nullptr, d_slots_in,
                                     pool->d_lens + (size_t)layer * pool->cfg.max_seqs, kv.max_seqs, fa->d_q, fa->d_gate, s));
         B2_TRY(launch_kv_append(kv, layer, nullptr, n_seqs, d_slots_in, k_in, kFaQkvCols, v_in, kFaQkvCols, true, fa->d_knorm,
@@ -215,7 +216,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
                                     fa->d_part_ml, fa->d_counters, fa->d_attn, bf16, s));
         }
         B2_TRY(launch_kv_advance(kv, layer, d_slots_in, nullptr, n_seqs, s));
-        B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
+        if (!core_only) B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
         pool->lens_dirty = true;
         return 0;
     }

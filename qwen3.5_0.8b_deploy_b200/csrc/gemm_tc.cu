@@ -241,6 +241,10 @@ int launch_one(const CUtensorMap& mx, const CUtensorMap& mw, int M, int N, int K
 }
 }  // namespace
 
+int gemm_tc_map(const void* ptr, int rows, int cols, int box_rows, void* tensor_map_out) {
+    return bf16_map(ptr, rows, cols, box_rows, static_cast<CUtensorMap*>(tensor_map_out));
+}
+
 void gemm_tc_forget(const void* ptr) {     // drop cached maps of a buffer that is being freed
     std::lock_guard<std::mutex> lk(g_map_mu);
     for (auto it = g_maps.begin(); it != g_maps.end();)
@@ -252,7 +256,13 @@ void gemm_tc_forget(const void* ptr) {     // drop cached maps of a buffer that 
 // every call so one process can exercise both.
 bool gemm_tc_enabled() {
     const char* e = std::getenv("B200ATTN_DECODE_GEMM");
-    return e && std::string(e) == "tc";
+    return e && (std::string(e) == "tc" || std::string(e) == "fused");
+}
+// "fused": additionally, everything between two attention kernels of the decode step runs as one persistent kernel
+// (decode_chain.cu).
+bool gemm_fused_enabled() {
+    const char* e = std::getenv("B200ATTN_DECODE_GEMM");
+    return e && std::string(e) == "fused";
 }
 
 // Number of split-K slices a [M<=128, N] x K product is cut into when the caller can sum partial tiles.

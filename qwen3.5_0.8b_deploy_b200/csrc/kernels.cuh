@@ -79,6 +79,7 @@ int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
 // ---- tcgen05 skinny GEMMs for the decode step (gemm_tc.cu) ---------------------------------------------------------
 int gemm_tc_splits(int N, int K, int bn);
 bool gemm_tc_enabled();
+bool gemm_fused_enabled();
 int gemm_tc_store(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, float* Y, int M, int N, int K, int ld_out,
                   int splits, size_t split_stride, int* d_error);
 int gemm_tc_swiglu(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, __nv_bfloat16* act, int M, int N, int K,
@@ -86,12 +87,40 @@ int gemm_tc_swiglu(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* 
 int gemm_tc_argmax(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, unsigned long long* d_packed, int* tokens,
                    int M, int N, int K, int* d_error);
 void gemm_tc_forget(const void* ptr);
+
+// ---- decode-step layer chain (decode_chain.cu): several skinny GEMMs and RMSNorms of consecutive layers in ONE
+// persistent cooperative kernel with grid barriers between the phases.
+struct ChainGemmDesc {          // Y[rows, N] = X[rows, K] W[N, K]^T, 64-column tiles
+    const __nv_bfloat16* X;
+    const __nv_bfloat16* W;
+    int N, K;
+    int splits;                 // > 1: fp32 partial matrices `split_stride` floats apart in out_f32
+    int epi;                    // 0 = fp32 store, 1 = SwiGLU (interleaved 32 gate + 32 up rows of W) -> out_bf16
+    float* out_f32;
+    size_t split_stride;
+    int ld_out;
+    __nv_bfloat16* out_bf16;
+};
+struct ChainNormDesc {          // h[row] += sum of partials (written back); out = RMSNorm(h) * (1 + w) as bf16
+    float* h;
+    const float* w;
+    const float* partials;
+    int n_splits;
+    size_t split_stride;
+    __nv_bfloat16* out;
+    float eps;
+};
+struct ChainPhaseDesc { int is_gemm; ChainGemmDesc g; ChainNormDesc n; };
+int launch_decode_chain(cudaStream_t s, int rows, const ChainPhaseDesc* phases, int n_phases, unsigned* d_sync, int* d_error);
+int gemm_tc_map(const void* ptr, int rows, int cols, int box_rows, void* tensor_map_out);   // cached CUtensorMap of a bf16 matrix
 // Where a decode-step output projection leaves its result when the caller sums split-K partials itself (the stack's
 // next RMSNorm does): `n_splits` matrices [rows, hidden], `stride` floats apart.  n_splits is set by the operator.
 struct DecodeOut {
     float* partials;
     size_t stride;
     int n_splits;
+    bool core_only = false;     // run only the attention core on the operator's own buffers: the input projection has
+                                // already been written to them and the caller projects the output itself
 };
 
 // ---- operator internals shared with the stack ------------------------------------------------------------------------

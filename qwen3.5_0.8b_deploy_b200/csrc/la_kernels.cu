@@ -23,6 +23,9 @@ __device__ __forceinline__ float warp_sum_f(float v) {
 }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+// SiLU on the special-function unit (ex2.approx + rcp.approx, about 2 ulp): the sequence-form conv kernel evaluates it
+// 6144 times per token and is otherwise bound by these instructions, not by memory.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : logf(1.0f + expf(x)); }
 
 // ---- C1, sequence form -------------------------------------------------------------------------------
@@ -98,7 +101,7 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
             s2 += w[i].x * a2[i];
             s2 += w[i].y * a1[i];
             s2 += w[i].z * a0[i];
-            res[i] = silu_f(s2);
+            res[i] = silu_fast(s2);
         }
         const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
         if (part == 2) {
@@ -106,14 +109,8 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
         } else {
             float ss = res[0] * res[0] + res[1] * res[1] + res[2] * res[2] + res[3] * res[3];
             ss = sqrtf(warp_sum_f(ss) + 1e-6f);
-            const float sc = (part == 0) ? q_scale : 1.0f;
-            float4 r4;
-            if (part == 0) {
-                r4 = make_float4(__fdiv_rn(res[0], ss) * sc, __fdiv_rn(res[1], ss) * sc, __fdiv_rn(res[2], ss) * sc,
-                                 __fdiv_rn(res[3], ss) * sc);
-            } else {
-                r4 = make_float4(__fdiv_rn(res[0], ss), __fdiv_rn(res[1], ss), __fdiv_rn(res[2], ss), __fdiv_rn(res[3], ss));
-            }
+            const float inv = ((part == 0) ? q_scale : 1.0f) / ss;     // one division per row instead of one per channel
+            const float4 r4 = make_float4(res[0] * inv, res[1] * inv, res[2] * inv, res[3] * inv);
             float* o32 = (part == 0) ? q_out : k_out;
             __half* o16 = (part == 0) ? qh_out : kh_out;
             if (o32) *reinterpret_cast<float4*>(o32 + o) = r4;
@@ -542,6 +539,170 @@ la_decode_stream_kernel(const float* __restrict__ mixed, const int* __restrict__
     if (tid == 0 && s_abort) atomicExch(error_word, 6);
 }
 
+// ---- R1, prefetching form -------------------------------------------------------------------------------------
+// la_decode_kernel's arithmetic and thread layout with two changes that keep more state bytes in flight per SM: the
+// CTAs are persistent (three per SM, each walking its units round-robin, no relaunch between units) and every CTA
+// owns a 64 KB shared-memory buffer into which one bulk (TMA) copy brings the NEXT unit's state while the current one
+// is being computed from registers.  The copy is issued as soon as the buffer has been read, so a load is in flight
+// for almost the whole life of a CTA, not only during its load phase.
+constexpr uint32_t kR1pSmem = kLaKd * kLaVd * 4 + 16;
+
+template <typename OutT>
+__global__ void __launch_bounds__(256, 3)
+la_decode_prefetch_kernel(const float* __restrict__ mixed, const int* __restrict__ slots, int n_seqs, int max_seqs,
+                          float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
+                          size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
+                          const float* __restrict__ dt_bias, const float* __restrict__ norm_w, OutT* __restrict__ out,
+                          int* __restrict__ error_word) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ __align__(16) float s_qkv[3][kLaKd];
+    __shared__ __align__(16) float s_part[8][kLaVd];
+    __shared__ float s_gb[2];
+    __shared__ float s_red[4];
+    __shared__ int s_abort;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t full = smem_u32(smem + kLaKd * kLaVd * 4);
+    const int n_units = n_seqs * kLaHeads;
+    const int n_my = ((int)blockIdx.x < n_units) ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    if (tid == 0) {
+        mbar_init(full, 1);
+        s_abort = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    volatile int* abort_flag = &s_abort;
+    auto unit_state = [&](int i) -> float* {         // global address of unit i's state, or null for a slot out of range
+        const int u = blockIdx.x + i * gridDim.x;
+        const int slot = slots[u / kLaHeads];
+        if (slot < 0 || slot >= max_seqs) return nullptr;
+        return rec_layer + (size_t)slot * rec_stride_slot + (size_t)(u % kLaHeads) * kLaKd * kLaVd;
+    };
+    auto request = [&](int i) {                       // one thread: bring unit i's state into the buffer
+        const float* src = unit_state(i);
+        if (src) {
+            mbar_arrive_expect_tx(full, kLaKd * kLaVd * 4);
+            bulk_g2s(smem_u32(smem), src, kLaKd * kLaVd * 4, full);
+        } else {
+            mbar_arrive(full);
+        }
+    };
+    // the states were written by this layer's previous step, not by the preceding kernel: request the first one at once
+    if (tid == 0 && n_my > 0) request(0);
+    pdl_enter();
+    bool ok = true;
+    for (int j = 0; j < n_my; ++j) {
+        const int u = blockIdx.x + j * gridDim.x;
+        const int b = u / kLaHeads, h = u % kLaHeads;
+        const int slot = slots[b];
+        const bool valid = slot >= 0 && slot < max_seqs;
+        const float* mrow = mixed + (size_t)b * kLaProjCols;
+        float* Sg = rec_layer + (size_t)(valid ? slot : 0) * rec_stride_slot + (size_t)h * kLaKd * kLaVd;
+        if (valid) {
+            // conv + SiLU + state shift for the head's q, k, v channels (384 values, 256 threads)
+            float* cst = conv_layer + (size_t)slot * conv_stride_slot;
+            for (int i = tid; i < 3 * kLaKd; i += 256) {
+                const int part = i / kLaKd, d = i % kLaKd;
+                const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + d;
+                const float x = mrow[ch];
+                const float s0 = cst[ch], s1 = cst[kLaConvDim + ch], s2 = cst[2 * kLaConvDim + ch];
+                const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)ch * kLaConvK);
+                float sv = w.w * x;
+                sv += w.x * s2;
+                sv += w.y * s1;
+                sv += w.z * s0;
+                s_qkv[part][d] = silu_f(sv);
+                cst[ch] = s1;
+                cst[kLaConvDim + ch] = s2;
+                cst[2 * kLaConvDim + ch] = x;
+            }
+        }
+        __syncthreads();
+        if (valid) {
+            if (warp < 2) {   // warp 0: q, warp 1: k
+                float4 x4 = *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]);
+                float ss = x4.x * x4.x + x4.y * x4.y + x4.z * x4.z + x4.w * x4.w;
+                ss = sqrtf(warp_sum_f(ss) + 1e-6f);
+                const float sc = (warp == 0) ? 1.0f / sqrtf((float)kLaKd) : 1.0f;
+                x4.x = __fdiv_rn(x4.x, ss) * sc; x4.y = __fdiv_rn(x4.y, ss) * sc;
+                x4.z = __fdiv_rn(x4.z, ss) * sc; x4.w = __fdiv_rn(x4.w, ss) * sc;
+                *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]) = x4;
+            } else if (tid == 64) {
+                const float a = mrow[kLaAOff + h], bb = mrow[kLaBOff + h];
+                s_gb[0] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+                s_gb[1] = sigmoid_f(bb);
+            }
+        }
+        __syncthreads();
+        if (!mbar_wait_warp(full, j & 1, abort_flag)) ok = false;
+        const bool work = valid && ok;
+        const float gt = s_gb[0], bt = s_gb[1];
+        const float4* Ss = reinterpret_cast<const float4*>(smem) + (size_t)(warp * 16) * (kLaVd / 4) + lane;
+        float4 S[16];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (work) {
+            // pass 1 (registers): partial kv over this warp's 16 rows
+#pragma unroll
+            for (int i = 0; i < 16; ++i) S[i] = Ss[i * (kLaVd / 4)];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float kk = s_qkv[1][warp * 16 + i];
+                acc.x += S[i].x * kk; acc.y += S[i].y * kk; acc.z += S[i].z * kk; acc.w += S[i].w * kk;
+            }
+            *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
+        }
+        __syncthreads();
+        // every thread holds its part of the state in registers: the buffer is free for the next unit's state
+        if (tid == 0 && j + 1 < n_my && !*abort_flag) request(j + 1);
+        float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (work) {
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                const float4 p = *reinterpret_cast<const float4*>(&s_part[w][4 * lane]);
+                kv.x += p.x; kv.y += p.y; kv.z += p.z; kv.w += p.w;
+            }
+            const float4 v4 = *reinterpret_cast<const float4*>(&s_qkv[2][4 * lane]);
+            dl.x = (v4.x - gt * kv.x) * bt; dl.y = (v4.y - gt * kv.y) * bt;
+            dl.z = (v4.z - gt * kv.z) * bt; dl.w = (v4.w - gt * kv.w) * bt;
+        }
+        __syncthreads();   // s_part is reused below
+        if (work) {
+            // pass 2 (registers): update, write back, partial o
+            acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float* Sw = Sg + (size_t)(warp * 16) * kLaVd + 4 * lane;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float kk = s_qkv[1][warp * 16 + i];
+                const float qq = s_qkv[0][warp * 16 + i];
+                float4 sv = S[i];
+                sv.x = sv.x * gt + kk * dl.x; sv.y = sv.y * gt + kk * dl.y;
+                sv.z = sv.z * gt + kk * dl.z; sv.w = sv.w * gt + kk * dl.w;
+                __stcs(reinterpret_cast<float4*>(Sw + (size_t)i * kLaVd), sv);
+                acc.x += sv.x * qq; acc.y += sv.y * qq; acc.z += sv.z * qq; acc.w += sv.w * qq;
+            }
+            *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
+        }
+        __syncthreads();
+        // o[vd], gated RMSNorm over the head's 128 values
+        if (tid < kLaVd) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) o += s_part[w][tid];
+            float ss = warp_sum_f(o * o);
+            if (lane == 0) s_red[warp] = ss;
+            asm volatile("bar.sync 1, 128;" ::: "memory");   // warps 0..3 all take this branch
+            if (work) {
+                const float var = (s_red[0] + s_red[1] + s_red[2] + s_red[3]) / (float)kLaVd;
+                const float inv = 1.0f / sqrtf(var + 1e-6f);
+                const float z = mrow[kLaZOff + h * kLaVd + tid];
+                out[(size_t)b * (kLaHeads * kLaVd) + h * kLaVd + tid] = (OutT)(o * inv * norm_w[tid] * silu_f(z));
+            }
+        }
+    }
+    __syncthreads();
+    if (tid == 0 && s_abort) atomicExch(error_word, 6);
+}
+
 // ---- state import / export in the reference's layouts ------------------------------------------------------
 __global__ void la_conv_import_kernel(const float* __restrict__ ref_conv, float* __restrict__ mine) {
     const int d = blockIdx.x * blockDim.x + threadIdx.x;
@@ -598,6 +759,27 @@ int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max
     // group per SM works through its units one after the other and cannot hide the input-load and barrier latencies
     // that three independent resident CTAs overlap, so it is not the default.
     const char* mode = std::getenv("B200ATTN_LA_DECODE");
+    // "prefetch": persistent CTAs, next state brought in by TMA during compute.  Measured 61.5 us (one-CTA-per-unit: 53.5):
+    // keeping more state bytes in flight does not move the kernel either, so it stays opt-in like "stream".
+    if (d_error && mode && mode[0] == 'p') {
+        static int n_sm_p = 0;
+        if (n_sm_p == 0) {
+            int dev = 0;
+            B2_CUDA(cudaGetDevice(&dev));
+            B2_CUDA(cudaDeviceGetAttribute(&n_sm_p, cudaDevAttrMultiProcessorCount, dev));
+            B2_CUDA(cudaFuncSetAttribute(la_decode_prefetch_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1pSmem));
+            B2_CUDA(cudaFuncSetAttribute(la_decode_prefetch_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1pSmem));
+        }
+        const dim3 grid(std::min(3 * n_sm_p, n_seqs * kLaHeads));
+        if (out_bf16)
+            launch_pdl(la_decode_prefetch_kernel<__nv_bfloat16>, grid, dim3(256), kR1pSmem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
+                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (__nv_bfloat16*)out, d_error);
+        else
+            launch_pdl(la_decode_prefetch_kernel<float>, grid, dim3(256), kR1pSmem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
+                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (float*)out, d_error);
+        B2_LAUNCH_CHECK();
+        return 0;
+    }
     if (d_error && mode && mode[0] == 's') {
         static int n_sm = 0;
         if (n_sm == 0) {

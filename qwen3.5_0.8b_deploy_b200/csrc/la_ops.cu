@@ -278,7 +278,8 @@ static int la_recurrence(b200attn_la la, b200attn_la_state st, int layer, const 
 int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots, const int* h_counts, int n_seqs,
                     const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y, float y_beta,
                     DecodeOut* dout, cudaStream_t s) {
-    B2_CHECK_ARG(la && st && d_x && d_y, "linear attention: null argument");
+    const bool core_only = decode && dout && dout->core_only;
+    B2_CHECK_ARG(la && st && (core_only || (d_x && d_y)), "linear attention: null argument");
     if (!la->ready) B2_FAIL(B200ATTN_ERR_NOT_READY, "LinearAttention weights not set");
     B2_CHECK_ARG(layer >= 0 && layer < st->cfg.num_layers, "linear attention: layer %d out of range", layer);
     const bool bf16 = la->cfg.proj_precision == B200ATTN_PROJ_BF16;
@@ -311,14 +312,14 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
     if (decode) {
         B2_CHECK_ARG(d_slots, "la_decode: null slots");
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= la->cfg.max_batch, "la_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, la->cfg.max_batch);
-        B2_TRY(project_in(n_seqs));
+        if (!core_only) B2_TRY(project_in(n_seqs));
         {
             ProfScope prof(PROF_LA_DECODE, s);
             B2_TRY(launch_la_decode(la->d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
                                     st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, la->d_gated,
                                     bf16, la->d_error, s));
         }
-        return project_out(n_seqs);
+        return core_only ? 0 : project_out(n_seqs);
     }
     int rows = 0;
     std::vector<LaSeqMeta> seqs;

@@ -42,6 +42,7 @@ struct b200attn_stack_s {
     float* d_partials = nullptr;       // [kMaxSplits][128][hidden] split-K partials of the decode-step output projections
     unsigned long long* d_packed = nullptr;   // [128] running argmax words of the LM head
     int* d_error = nullptr;            // device status word of the stack's own tcgen05 GEMMs
+    unsigned* d_sync = nullptr;        // [2] grid-barrier words of the decode chain kernel
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
     int graph_nseqs = 0;
@@ -246,7 +247,7 @@ extern "C" int b200attn_stack_destroy(b200attn_stack st) {
     cudaFree(st->op_scratch.base);
     cudaFree(st->d_h); cudaFree(st->d_xb); cudaFree(st->d_gu); cudaFree(st->d_act); cudaFree(st->d_last);
     cudaFree(st->d_logits); cudaFree(st->d_tokens); cudaFree(st->d_slots);
-    cudaFree(st->d_partials); cudaFree(st->d_packed); cudaFree(st->d_error);
+    cudaFree(st->d_partials); cudaFree(st->d_packed); cudaFree(st->d_error); cudaFree(st->d_sync);
     delete st;
     return 0;
 }
@@ -318,6 +319,8 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
     ST_CUDA(cudaMemset(st->d_packed, 0, 128 * sizeof(unsigned long long)));
     ST_CUDA(cudaMalloc(&st->d_error, sizeof(int)));
     ST_CUDA(cudaMemset(st->d_error, 0, sizeof(int)));
+    ST_CUDA(cudaMalloc(&st->d_sync, 2 * sizeof(unsigned)));
+    ST_CUDA(cudaMemset(st->d_sync, 0, 2 * sizeof(unsigned)));
     iota_kernel<<<ceil_div(cfg->max_seqs, 128), 128>>>(st->d_slots, cfg->max_seqs);
     ST_CUDA(cudaDeviceSynchronize());
 #undef ST_CUDA
@@ -423,6 +426,7 @@ extern "C" int b200attn_stack_reset(b200attn_stack st, b200attn_stream stream) {
     B2_CHECK_ARG(st, "stack_reset: null stack");
     if (st->pool) B2_TRY(b200attn_kv_clear(st->pool, stream));
     if (st->state) B2_TRY(b200attn_la_state_clear(st->state, -1, stream));
+    B2_CUDA(cudaMemsetAsync(st->d_sync, 0, 2 * sizeof(unsigned), b200::as_stream(stream)));   // grid-barrier words of the decode chain
     return 0;
 }
 
@@ -444,6 +448,50 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
     const bool tc = decode && rows <= 128 && gemm_tc_enabled();          // weight-streaming tcgen05 GEMMs with fused epilogues
     const size_t pstride = (size_t)128 * kHidden;
     int pending = 0;
+    if (tc && gemm_fused_enabled()) {
+        // One persistent kernel per layer boundary: out-proj(i), norm, gate/up + SwiGLU, down, norm(i+1), in-proj(i+1).
+        // The attention operators run core-only on their own projection buffers.
+        const int L = st->cfg.num_layers;
+        auto in_w = [&](int i) { return st->layer_kind[i] ? st->fa[st->layer_sub[i]]->d_wqkv_bf16 : st->la[st->layer_sub[i]]->d_win_bf16; };
+        auto in_buf = [&](int i) { return st->layer_kind[i] ? st->fa[st->layer_sub[i]]->d_qkv_raw : st->la[st->layer_sub[i]]->d_mixed; };
+        auto in_cols = [&](int i) { return st->layer_kind[i] ? kFaQkvCols : kLaProjCols; };
+        auto out_x = [&](int i) { return st->layer_kind[i] ? (const __nv_bfloat16*)st->fa[st->layer_sub[i]]->d_attn : (const __nv_bfloat16*)st->la[st->layer_sub[i]]->d_gated; };
+        auto out_w = [&](int i) { return st->layer_kind[i] ? st->fa[st->layer_sub[i]]->d_wo_bf16 : st->la[st->layer_sub[i]]->d_wout_bf16; };
+        const int attn_cols = 2048;                       // 8 x 256 = 16 x 128
+        const int s_out = gemm_tc_splits(kHidden, attn_cols, 64), s_down = std::min(kMaxSplits, gemm_tc_splits(kHidden, inter, 64));
+        launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[0], st->cfg.rms_eps, rows, st->d_xb, nullptr,
+                   st->d_partials, 0, pstride);
+        B2_LAUNCH_CHECK();
+        B2_TRY(gemm_tc_store(s, st->d_xb, in_w(0), in_buf(0), rows, in_cols(0), kHidden, in_cols(0), 1, 0, st->d_error));
+        for (int i = 0; i < L; ++i) {
+            DecodeOut core{nullptr, 0, 0, true};
+            if (st->layer_kind[i])
+                B2_TRY(fa_forward_rows(st->fa[st->layer_sub[i]], st->pool, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots, true,
+                                       nullptr, true, nullptr, 1.0f, &core, s));
+            else
+                B2_TRY(la_forward_rows(st->la[st->layer_sub[i]], st->state, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots, true,
+                                       nullptr, true, nullptr, 1.0f, &core, s));
+            ChainPhaseDesc ph[6] = {};
+            int np = 0;
+            ph[np].is_gemm = 1;
+            ph[np++].g = ChainGemmDesc{out_x(i), out_w(i), kHidden, attn_cols, s_out, 0, st->d_partials, pstride, kHidden, nullptr};
+            ph[np].is_gemm = 0;
+            ph[np++].n = ChainNormDesc{st->d_h, st->d_post_norm[i], st->d_partials, s_out, pstride, st->d_xb, st->cfg.rms_eps};
+            ph[np].is_gemm = 1;
+            ph[np++].g = ChainGemmDesc{st->d_xb, st->d_wgu[i], 2 * inter, kHidden, 1, 1, nullptr, 0, inter, st->d_act};
+            ph[np].is_gemm = 1;
+            ph[np++].g = ChainGemmDesc{st->d_act, st->d_wdown[i], kHidden, inter, s_down, 0, st->d_partials, pstride, kHidden, nullptr};
+            if (i + 1 < L) {
+                ph[np].is_gemm = 0;
+                ph[np++].n = ChainNormDesc{st->d_h, st->d_in_norm[i + 1], st->d_partials, s_down, pstride, st->d_xb, st->cfg.rms_eps};
+                ph[np].is_gemm = 1;
+                ph[np++].g = ChainGemmDesc{st->d_xb, in_w(i + 1), in_cols(i + 1), kHidden, 1, 0, in_buf(i + 1), 0, in_cols(i + 1), nullptr};
+            }
+            B2_TRY(launch_decode_chain(s, rows, ph, np, st->d_sync, st->d_error));
+        }
+        *pending_out = s_down;
+        return 0;
+    }
     for (int i = 0; i < st->cfg.num_layers; ++i) {
         launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
                                                         st->d_partials, pending, pstride);

@@ -57,12 +57,12 @@ def test_layer_against_reference_fixture(ops, cuda, synth):
     np.testing.assert_allclose(conv.cpu().numpy(), g["conv"], rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("kernel,occ", [("classic", ""), ("classic", "512"), ("stream", "")])
+@pytest.mark.parametrize("kernel,occ", [("classic", ""), ("classic", "512"), ("stream", ""), ("prefetch", "")])
 def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel, occ):
     """Recurrent decode: 4 sequences, state ~ N(0, 0.05) and a warm conv cache imported in the
     reference's layouts, 24 single-token steps; outputs every step, state at the end.  Every form of the decode
-    kernel: one CTA per unit with 256 threads (default) or 512 threads, and the persistent one with a TMA state
-    ring; the library reads the variables per call."""
+    kernel: one CTA per unit with 256 threads or 512 threads, the persistent one with a TMA state ring, and the
+    persistent one that prefetches the next state by TMA; the library reads the variables per call."""
     monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
     monkeypatch.setenv("B200ATTN_LA_DECODE_OCC", occ)
     torch = cuda
@@ -97,9 +97,9 @@ def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel,
     assert not rec0.any()
 
 
-def test_streamed_decode_equals_classic_kernel(ops, cuda, synth, monkeypatch):
-    """72 sequences x 16 heads = 1152 units on 148 persistent CTAs: every CTA walks its state ring seven or eight
-    times (stage reuse, write-back, refill).  It does the same arithmetic in the same order as the 256-thread
+def test_persistent_decode_kernels_equal_classic_kernel(ops, cuda, synth, monkeypatch):
+    """72 sequences x 16 heads = 1152 units on 148 (state ring) or 444 (prefetch) persistent CTAs: every CTA walks
+    several units (stage reuse, write-back, refill).  They do the same arithmetic in the same order as the 256-thread
     one-CTA-per-unit kernel, so outputs, recurrent states and conv states must be identical bit for bit.  One slot is
     out of range and must be skipped."""
     torch = cuda
@@ -109,7 +109,7 @@ def test_streamed_decode_equals_classic_kernel(ops, cuda, synth, monkeypatch):
     g = torch.Generator(device="cuda").manual_seed(57)
     results = {}
     monkeypatch.setenv("B200ATTN_LA_DECODE_OCC", "3")     # 256 threads, 16 state rows per warp, as in the persistent kernel
-    for kernel in ("classic", "stream"):
+    for kernel in ("classic", "stream", "prefetch"):
         monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
         st = ops.LinearAttnState(1, n)
         g.manual_seed(57)
@@ -125,13 +125,14 @@ def test_streamed_decode_equals_classic_kernel(ops, cuda, synth, monkeypatch):
         states = [st.export_state(0, i) for i in (0, 5, 9, 36, 71)]
         results[kernel] = (outs, states)
         assert la.device_status() == 0
-    for a, b in zip(results["classic"][0], results["stream"][0]):
-        keep = torch.ones(n, dtype=torch.bool, device="cuda")
-        keep[5] = False                      # the skipped sequence's output rows are not written by either kernel
-        assert torch.equal(a[keep], b[keep])
-    for (ra, ca), (rb, cb) in zip(results["classic"][1], results["stream"][1]):
-        assert torch.equal(ra, rb) and torch.equal(ca, cb)
-    assert not results["stream"][1][1][0].any()      # slot 5's state was never touched
+    keep = torch.ones(n, dtype=torch.bool, device="cuda")
+    keep[5] = False                          # the skipped sequence's output rows are not written by any kernel
+    for other in ("stream", "prefetch"):
+        for a, b in zip(results["classic"][0], results[other][0]):
+            assert torch.equal(a[keep], b[keep]), other
+        for (ra, ca), (rb, cb) in zip(results["classic"][1], results[other][1]):
+            assert torch.equal(ra, rb) and torch.equal(ca, cb), other
+        assert not results[other][1][1][0].any()     # slot 5's state was never touched
 
 
 def test_ragged_batch_and_continuation(ops, cuda, oracle, synth):

@@ -18,10 +18,11 @@ def _build(ops, synth, weights, max_seqs=4, max_seq_len=128, kv_dtype=1):
     return st
 
 
-@pytest.fixture(params=["cublas", "tc"])
+@pytest.fixture(params=["cublas", "tc", "fused"])
 def decode_gemm(request, monkeypatch):
-    """Both implementations of the decode-step projections: cuBLAS + separate SwiGLU / argmax kernels, and the
-    tcgen05 skinny GEMM with fused epilogues.  The library reads the variable on every call."""
+    """Every implementation of the decode-step projections: cuBLAS + separate SwiGLU / argmax kernels, the tcgen05
+    skinny GEMM with fused epilogues, and the persistent per-layer chain kernel (projections and norms between two
+    attention kernels in one cooperative launch).  The library reads the variable on every call."""
     monkeypatch.setenv("B200ATTN_DECODE_GEMM", request.param)
     return request.param
 
@@ -82,7 +83,7 @@ def test_graph_replay_equals_eager_decode(ops, cuda, synth, decode_gemm):
             st.launch_decode(1)
             replayed.append(st.get_tokens(n))
         side.synchronize()
-        assert ops.launch_count() > D * 20
+        assert ops.launch_count() > D * 10             # every replay counts its kernel nodes (17 per step in the fused mode)
     for a, b in zip(eager, replayed):
         assert torch.equal(a, b)
     assert st.device_status() == 0
