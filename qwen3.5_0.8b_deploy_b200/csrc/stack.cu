@@ -11,6 +11,7 @@
 #include "ptx_utils.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -530,7 +531,10 @@ static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int
                                                       d_hidden_out ? d_hidden_out : nullptr, st->d_partials, pending,
                                                       (size_t)128 * kHidden);
     B2_LAUNCH_CHECK();
-    if (n_seqs <= 128 && gemm_tc_enabled())    // LM head with the argmax in the GEMM epilogue: the logits never reach memory
+    // LM head with the argmax in the GEMM epilogue (the logits never reach memory): 103 us per step against 112 + 31 us for
+    // the cuBLAS GEMM and the argmax kernel.  B200ATTN_LM_HEAD=cublas selects the latter.
+    const char* lm = std::getenv("B200ATTN_LM_HEAD");
+    if (n_seqs <= 128 && !(lm && lm[0] == 'c'))
         return gemm_tc_argmax(s, st->d_xb, st->d_embed, st->d_packed, d_next, n_seqs, st->cfg.vocab_size, kHidden, st->d_error);
     B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_embed, true, st->d_logits, false, n_seqs, st->cfg.vocab_size, kHidden));
     argmax_kernel<<<n_seqs, 1024, 0, s>>>(st->d_logits, st->cfg.vocab_size, d_next);
