@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import concurrent.futures as cf
 import os
+import shlex
 import subprocess
 import sys
 
@@ -20,6 +21,7 @@ SOURCES = ["gemm.cu", "kv_cache.cu", "fa_decode.cu", "fa_prefill.cu", "fa_ops.cu
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+FLAGS += shlex.split(os.environ.get("B200ATTN_NVCC_EXTRA", ""))      # e.g. "-DNAME" to try a compile-time variant
 
 
 def _newest_header() -> float:

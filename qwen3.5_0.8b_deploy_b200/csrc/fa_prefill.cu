@@ -1,6 +1,6 @@
 // F1: causal flash-attention prefill for head_dim 256 on tcgen05 tensor cores.
 //
-// One CTA per (128-query tile of one sequence, q head).  Warp roles: warps 0-7 = softmax (two threads per query
+// Persistent CTAs, each walking (128-query tile of one sequence, q head) work items.  Warp roles: warps 0-7 = softmax (two threads per query
 // row = TMEM lane, each owning 32 of the 64 key columns of a tile and half of the output columns; the pair
 // exchanges its row maxima through shared memory), warp 8 = TMA producer, warp 9 = MMA issuer and TMEM owner.
 //   S[128x64]  = Q[128x256] K_j^T      tcgen05.mma kind::f16 (fp16 operands), A and B K-major, TMEM cols [0,128) double-buffered
@@ -36,13 +36,17 @@ __device__ __forceinline__ float ex2_fast(float x) {     // 2^x, one MUFU op; -i
     return y;
 }
 
-enum { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SE = 11, BAR_PF = 13, BAR_PV = 15,
-       BAR_OF = 17, BAR_COUNT = 18 };
+enum { BAR_Q = 0, BAR_QE = 1, BAR_KF = 2, BAR_KE = 4, BAR_VF = 6, BAR_VE = 8, BAR_SF = 10, BAR_SE = 12, BAR_PF = 14, BAR_PV = 16,
+       BAR_OF = 18, BAR_OD = 19, BAR_COUNT = 20 };
 
+// Persistent: grid = min(number of SMs, tiles x heads); CTA c walks the work items c, c + grid, ... (item w = tile w / 8,
+// head w % 8; the tile list is sorted longest context first, so the round-robin is balanced).  All ring barriers run on a
+// step counter that continues across items, so the K / V / Q loads and the first S products of the next item are under
+// way while the softmax warps still read the finished item's output out of TMEM.
 template <typename OutT>
 __global__ void __launch_bounds__(kF1Threads, 1)
 fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const PrefillTile* __restrict__ tiles,
+                     const __grid_constant__ CUtensorMap map_v, const PrefillTile* __restrict__ tiles, int n_items,
                      const __half* __restrict__ gate, OutT* __restrict__ out, int* __restrict__ error_word) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
@@ -57,15 +61,20 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t bar0 = base + kOffBar;
     auto bar = [&](int i) { return bar0 + 8u * i; };
 
-    if (*reinterpret_cast<volatile int*>(error_word) != 0) return;   // an earlier CTA gave up: do not queue more bounded waits
+    if (*reinterpret_cast<volatile int*>(error_word) != 0) return;   // an earlier launch gave up: do not queue more bounded waits
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const PrefillTile tile = tiles[blockIdx.x];
-    const int head = blockIdx.y, kvh = head >> 2;
-    const int n_kt = (tile.q_pos0 + tile.n_rows + kBN - 1) / kBN;   // key tiles 0..n_kt-1 cover positions <= last query
+    const int cta = blockIdx.x, n_cta = gridDim.x;
+    const int n_my = (cta < n_items) ? (n_items - cta + n_cta - 1) / n_cta : 0;
+    auto item_tile = [&](int i, int& head) -> PrefillTile {
+        const int w = cta + i * n_cta;
+        head = w & 7;
+        return tiles[w >> 3];
+    };
+    auto key_tiles = [](const PrefillTile& t) { return (t.q_pos0 + t.n_rows + kBN - 1) / kBN; };   // tiles 0..n-1 cover positions <= last query
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < BAR_COUNT; ++i) {
-            const bool many = (i == BAR_SE || i == BAR_SE + 1 || i == BAR_PF || i == BAR_PF + 1);
+            const bool many = (i == BAR_SE || i == BAR_SE + 1 || i == BAR_PF || i == BAR_PF + 1 || i == BAR_OD);
             mbar_init(bar(i), many ? 256 : 1);
         }
         *abort_flag = 0;
@@ -88,36 +97,49 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     if (warp == 8) {
         // ------------------------------ TMA producer ------------------------------
+        // Three independent streams, each advanced as soon as its consumer has released the buffer: Q (one tile per item),
+        // K and V (one tile per key step, double-buffered, steps counted across items).
         if (lane == 0) {
-            mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
-            for (int blk = 0; blk < 4; ++blk)
-                tma_load_3d(base + kOffQ + blk * (kBM * 128), &map_q, bar(BAR_Q), blk * 64, head, tile.q_row0);
-            // K and V buffers are refilled independently, each as soon as its own consumer (the S product, the PV
-            // product) has released it: a K tile is then requested two key tiles ahead of its use, not behind the V wait.
-            int jk = 0, jv = 0;
+            int iq = 0;
+            int ik = 0, jk = 0, gk = 0, iv = 0, jv = 0, gv = 0;
+            int hk = 0, hv = 0;
+            PrefillTile tk = {}, tv = {};
+            int nk = 0, nv = 0;
+            if (n_my > 0) { tk = item_tile(0, hk); tv = tk; hv = hk; nk = nv = key_tiles(tk); }
             const uint64_t t0 = global_timer_ns();
             uint32_t idle = 0;
-            while (jk < n_kt || jv < n_kt) {
+            while (iq < n_my || ik < n_my || iv < n_my) {
                 bool progressed = false;
-                if (jk < n_kt && (jk < 2 || mbar_test_wait(bar(BAR_KE + (jk & 1)), ((jk >> 1) - 1) & 1))) {
-                    const int b = jk & 1, row = tile.ctx_row0 + jk * kBN;
-                    mbar_arrive_expect_tx(bar(BAR_KF + b), kKVBytes);
+                if (iq < n_my && (iq == 0 || mbar_test_wait(bar(BAR_QE), (iq - 1) & 1))) {
+                    int hq;
+                    const PrefillTile tq = item_tile(iq, hq);
+                    mbar_arrive_expect_tx(bar(BAR_Q), kQBytes);
                     for (int blk = 0; blk < 4; ++blk)
-                        tma_load_3d(base + kOffK + b * kKVBytes + blk * (kBN * 128), &map_k, bar(BAR_KF + b), blk * 64, kvh, row);
-                    ++jk;
+                        tma_load_3d(base + kOffQ + blk * (kBM * 128), &map_q, bar(BAR_Q), blk * 64, hq, tq.q_row0);
+                    ++iq;
                     progressed = true;
                 }
-                if (jv < n_kt && (jv < 2 || mbar_test_wait(bar(BAR_VE + (jv & 1)), ((jv >> 1) - 1) & 1))) {
-                    const int b = jv & 1, row = tile.ctx_row0 + jv * kBN;
+                if (ik < n_my && (gk < 2 || mbar_test_wait(bar(BAR_KE + (gk & 1)), ((gk >> 1) - 1) & 1))) {
+                    const int b = gk & 1, row = tk.ctx_row0 + jk * kBN;
+                    mbar_arrive_expect_tx(bar(BAR_KF + b), kKVBytes);
+                    for (int blk = 0; blk < 4; ++blk)
+                        tma_load_3d(base + kOffK + b * kKVBytes + blk * (kBN * 128), &map_k, bar(BAR_KF + b), blk * 64, hk >> 2, row);
+                    ++gk;
+                    if (++jk == nk) { jk = 0; if (++ik < n_my) { tk = item_tile(ik, hk); nk = key_tiles(tk); } }
+                    progressed = true;
+                }
+                if (iv < n_my && (gv < 2 || mbar_test_wait(bar(BAR_VE + (gv & 1)), ((gv >> 1) - 1) & 1))) {
+                    const int b = gv & 1, row = tv.ctx_row0 + jv * kBN;
                     mbar_arrive_expect_tx(bar(BAR_VF + b), kKVBytes);
                     for (int blk = 0; blk < 4; ++blk)
-                        tma_load_3d(base + kOffV + b * kKVBytes + blk * (kBN * 128), &map_v, bar(BAR_VF + b), blk * 64, kvh, row);
-                    ++jv;
+                        tma_load_3d(base + kOffV + b * kKVBytes + blk * (kBN * 128), &map_v, bar(BAR_VF + b), blk * 64, hv >> 2, row);
+                    ++gv;
+                    if (++jv == nv) { jv = 0; if (++iv < n_my) { tv = item_tile(iv, hv); nv = key_tiles(tv); } }
                     progressed = true;
                 }
                 if (!progressed && ((++idle & 255u) == 0u)) {
                     if (*abort_flag) break;
-                    if (global_timer_ns() - t0 > 2000000000ull) { *abort_flag = 1; break; }
+                    if (global_timer_ns() - t0 > 4000000000ull) { *abort_flag = 1; break; }
                 }
             }
         }
@@ -126,41 +148,61 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc(kFmtF16, kBM, kBN, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc(kFmtF16, kBM, kHeadDim, 0, 1);
-            auto issue_pv = [&](int i) -> bool {
-                const int b = i & 1;
-                const uint32_t par = (i >> 1) & 1;
+            // PV product of global step g; `first`: first key step of its item (overwrites O, which the previous item's
+            // epilogue must have read), `last`: last key step of its item (O is final afterwards)
+            auto issue_pv = [&](int g, bool first, bool last, int item) -> bool {
+                const int b = g & 1;
+                const uint32_t par = (g >> 1) & 1;
                 if (!mbar_wait(bar(BAR_VF + b), par, abort_flag)) return false;
                 if (!mbar_wait(bar(BAR_PF + b), par, abort_flag)) return false;
+                if (first && item > 0 && !mbar_wait(bar(BAR_OD), (item - 1) & 1, abort_flag)) return false;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 4; ++ks) {
                     const uint64_t a = umma_smem_desc(base + kOffP + b * kPBytes + ks * 32, 16, 1024);
                     const uint64_t bd = umma_smem_desc(base + kOffV + b * kKVBytes + ks * 2048, kBN * 128, 1024);
-                    umma_f16(tmem_o, a, bd, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_f16(tmem_o, a, bd, idesc_pv, (!first || ks > 0) ? 1u : 0u);
                 }
                 umma_commit(bar(BAR_PV + b));
                 umma_commit(bar(BAR_VE + b));
+                if (last) umma_commit(bar(BAR_OF));
                 return true;
             };
-            bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag);
-            for (int j = 0; ok && j < n_kt; ++j) {
-                const int b = j & 1;
-                if (!mbar_wait(bar(BAR_KF + b), (j >> 1) & 1, abort_flag)) { ok = false; break; }
-                if (j >= 2 && !mbar_wait(bar(BAR_SE + b), ((j >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll
-                for (int ks = 0; ks < 16; ++ks) {
-                    const uint32_t off = (ks >> 2) * 0 + (ks & 3) * 32;
-                    const uint64_t a = umma_smem_desc(base + kOffQ + (ks >> 2) * (kBM * 128) + off, 16, 1024);
-                    const uint64_t bd = umma_smem_desc(base + kOffK + b * kKVBytes + (ks >> 2) * (kBN * 128) + off, 16, 1024);
-                    umma_f16(tmem + b * kBN, a, bd, idesc_s, ks > 0 ? 1u : 0u);
+            bool ok = true, pending = false;
+            int pg = 0, pitem = 0;
+            bool pfirst = false, plast = false;
+            int gs = 0;
+            for (int i = 0; ok && i < n_my; ++i) {
+                int head;
+                const PrefillTile tile = item_tile(i, head);
+                const int n_kt = key_tiles(tile);
+                // the previous item's last PV product goes out before the wait for this item's Q tile, so that its
+                // epilogue runs while Q and the first S product are on their way
+                if (pending) {
+                    if (!issue_pv(pg, pfirst, plast, pitem)) { ok = false; break; }
+                    pending = false;
                 }
-                umma_commit(bar(BAR_SF + b));
-                umma_commit(bar(BAR_KE + b));
-                if (j >= 1 && !issue_pv(j - 1)) { ok = false; break; }
+                if (!mbar_wait(bar(BAR_Q), i & 1, abort_flag)) { ok = false; break; }
+                for (int j = 0; j < n_kt; ++j, ++gs) {
+                    const int b = gs & 1;
+                    if (!mbar_wait(bar(BAR_KF + b), (gs >> 1) & 1, abort_flag)) { ok = false; break; }
+                    if (gs >= 2 && !mbar_wait(bar(BAR_SE + b), ((gs >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 16; ++ks) {
+                        const uint32_t off = (ks & 3) * 32;
+                        const uint64_t a = umma_smem_desc(base + kOffQ + (ks >> 2) * (kBM * 128) + off, 16, 1024);
+                        const uint64_t bd = umma_smem_desc(base + kOffK + b * kKVBytes + (ks >> 2) * (kBN * 128) + off, 16, 1024);
+                        umma_f16(tmem + b * kBN, a, bd, idesc_s, ks > 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar(BAR_SF + b));
+                    umma_commit(bar(BAR_KE + b));
+                    if (j == n_kt - 1) umma_commit(bar(BAR_QE));      // the Q tile is free once this item's S products are done
+                    if (pending && !issue_pv(pg, pfirst, plast, pitem)) { ok = false; break; }
+                    pending = true; pg = gs; pfirst = (j == 0); plast = (j == n_kt - 1); pitem = i;
+                }
             }
-            if (ok) ok = issue_pv(n_kt - 1);
-            if (ok) umma_commit(bar(BAR_OF));
+            if (ok && pending) issue_pv(pg, pfirst, plast, pitem);
         }
     } else {
         // ------------------------------ softmax / correction / epilogue ------------------------------
@@ -169,90 +211,97 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const int pair_bar = 1 + (warp & 3);             // named barrier shared by the two warps that cover the same rows
         float* x_mx = reinterpret_cast<float*>(sm + kOffXch);          // [2][2][128]
-        float* x_l = x_mx + (n_kt & 1) * 256;                           // [2][128]: the slot the last tile does not use
-        const int q_pos = tile.q_pos0 + r;
         const float sc = kLog2eF / 16.0f;
-        float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_kt; ++j) {
-            const int b = j & 1;
-            if (!mbar_wait_warp(bar(BAR_SF + b), (j >> 1) & 1, abort_flag)) ok = false;
-            tc_fence_after();
-            uint32_t sr[32];
-            tmem_ld32(tmem + lane_base + b * kBN + hf * 32, sr);
-            tmem_wait_ld();
-            tc_fence_before();
-            mbar_arrive(bar(BAR_SE + b));
-            const int col0 = j * kBN + hf * 32;
-            const bool diag = (col0 + 31 > tile.q_pos0);   // warp-uniform: this half tile may cross a diagonal
-            float mx = -INFINITY;
+        int gs = 0;
+        for (int it = 0; it < n_my; ++it) {
+            int head;
+            const PrefillTile tile = item_tile(it, head);
+            const int n_kt = key_tiles(tile);
+            const int q_pos = tile.q_pos0 + r;
+            float m_ref = -INFINITY, l = 0.f;
+            for (int j = 0; j < n_kt; ++j, ++gs) {
+                const int b = gs & 1;
+                if (!mbar_wait_warp(bar(BAR_SF + b), (gs >> 1) & 1, abort_flag)) ok = false;
+                tc_fence_after();
+                uint32_t sr[32];
+                tmem_ld32(tmem + lane_base + b * kBN + hf * 32, sr);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(bar(BAR_SE + b));
+                const int col0 = j * kBN + hf * 32;
+                const bool diag = (col0 + 31 > tile.q_pos0);   // warp-uniform: this half tile may cross a diagonal
+                float mx = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                float v = __uint_as_float(sr[c]);
-                if (diag && (col0 + c > q_pos)) v = -INFINITY;
-                sr[c] = __float_as_uint(v);
-                mx = fmaxf(mx, v);
-            }
-            x_mx[(b * 2 + hf) * 128 + r] = mx;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            mx = fmaxf(mx, x_mx[(b * 2 + (hf ^ 1)) * 128 + r]) * sc;
-            const float m_new = fmaxf(m_ref, mx);            // finite: key 0 is visible to every row
-            const bool need = (m_new - m_ref > 8.0f);        // also true on the first tile (m_ref = -inf)
-            if (__any_sync(0xffffffffu, need)) {             // same decision in both warps of the pair: same rows, same values
-                if (j > 0) {
-                    if (!mbar_wait_warp(bar(BAR_PV + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag)) ok = false;
-                    tc_fence_after();
-                    const float alpha = exp2f(m_ref - m_new);
-                    l *= alpha;
+                for (int c = 0; c < 32; ++c) {
+                    float v = __uint_as_float(sr[c]);
+                    if (diag && (col0 + c > q_pos)) v = -INFINITY;
+                    sr[c] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+                x_mx[(b * 2 + hf) * 128 + r] = mx;
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                mx = fmaxf(mx, x_mx[(b * 2 + (hf ^ 1)) * 128 + r]) * sc;
+                const float m_new = fmaxf(m_ref, mx);            // finite: key 0 is visible to every row
+                const bool need = (m_new - m_ref > 8.0f);        // also true on the first tile (m_ref = -inf)
+                if (__any_sync(0xffffffffu, need)) {             // same decision in both warps of the pair: same rows, same values
+                    if (j > 0) {
+                        if (!mbar_wait_warp(bar(BAR_PV + ((gs - 1) & 1)), ((gs - 1) >> 1) & 1, abort_flag)) ok = false;
+                        tc_fence_after();
+                        const float alpha = exp2f(m_ref - m_new);
+                        l *= alpha;
 #pragma unroll 1
-                    for (int cc = 0; cc < 4; ++cc) {
-                        const int ch = hf * 4 + cc;
-                        uint32_t orr[32];
-                        tmem_ld32(tmem_o + lane_base + ch * 32, orr);
-                        tmem_wait_ld();
+                        for (int cc = 0; cc < 4; ++cc) {
+                            const int ch = hf * 4 + cc;
+                            uint32_t orr[32];
+                            tmem_ld32(tmem_o + lane_base + ch * 32, orr);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) orr[c] = __float_as_uint(__uint_as_float(orr[c]) * alpha);
-                        tmem_st32(tmem_o + lane_base + ch * 32, orr);
+                            for (int c = 0; c < 32; ++c) orr[c] = __float_as_uint(__uint_as_float(orr[c]) * alpha);
+                            tmem_st32(tmem_o + lane_base + ch * 32, orr);
+                        }
+                        tmem_wait_st();
                     }
-                    tmem_wait_st();
+                    m_ref = m_new;
                 }
-                m_ref = m_new;
-            }
-            // P = 2^(s * scale - m_ref) as fp16 into the swizzled K-major A tile
-            if (j >= 2 && !mbar_wait_warp(bar(BAR_PV + b), ((j >> 1) - 1) & 1, abort_flag)) ok = false;
-            unsigned char* prow = sm + kOffP + b * kPBytes + r * 128;
-            float lsum = 0.f;
+                // P = 2^(s * scale - m_ref) as fp16 into the swizzled K-major A tile
+                if (gs >= 2 && !mbar_wait_warp(bar(BAR_PV + b), ((gs >> 1) - 1) & 1, abort_flag)) ok = false;
+                unsigned char* prow = sm + kOffP + b * kPBytes + r * 128;
+                float lsum = 0.f;
 #pragma unroll
-            for (int c8 = 0; c8 < 4; ++c8) {
-                uint32_t pk[4];
+                for (int c8 = 0; c8 < 4; ++c8) {
+                    uint32_t pk[4];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e]), sc, -m_ref));
-                    const float p1 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e + 1]), sc, -m_ref));
-                    lsum += p0 + p1;
-                    pk[e] = pack_half2(p0, p1);
+                    for (int e = 0; e < 4; ++e) {
+                        const float p0 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e]), sc, -m_ref));
+                        const float p1 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e + 1]), sc, -m_ref));
+                        lsum += p0 + p1;
+                        pk[e] = pack_half2(p0, p1);
+                    }
+                    *reinterpret_cast<uint4*>(prow + (((hf * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
-                *reinterpret_cast<uint4*>(prow + (((hf * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                l += lsum;
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(bar(BAR_PF + b));
             }
-            l += lsum;
-            fence_proxy_async_smem();
-            tc_fence_before();
-            mbar_arrive(bar(BAR_PF + b));
-        }
-        x_l[hf * 128 + r] = l;
-        asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-        l += x_l[(hf ^ 1) * 128 + r];
-        const bool valid = r < tile.n_rows;
-        const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
-        uint4 gpre[4][4];      // this thread's gate values, requested before the wait on the last PV product
-        if (gate && valid) {
+            // row sums of the two halves: through the exchange slot the next step will use, hence the second barrier
+            float* x_l = x_mx + (gs & 1) * 256;
+            x_l[hf * 128 + r] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            l += x_l[(hf ^ 1) * 128 + r];
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            const bool valid = r < tile.n_rows;
+            const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
+            uint4 gpre[4][4];      // this thread's gate values, requested before the wait on the last PV product
+            if (gate && valid) {
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc)
+                for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)
-                    gpre[cc][q4] = *reinterpret_cast<const uint4*>(gate + orow + (hf * 4 + cc) * 32 + q4 * 8);
-        }
-        if (mbar_wait_warp(bar(BAR_OF), 0, abort_flag) && ok) {
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        gpre[cc][q4] = *reinterpret_cast<const uint4*>(gate + orow + (hf * 4 + cc) * 32 + q4 * 8);
+            }
+            if (!mbar_wait_warp(bar(BAR_OF), it & 1, abort_flag)) ok = false;
             tc_fence_after();
             const float inv_l = 1.0f / l;
 #pragma unroll
@@ -261,7 +310,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 uint32_t orr[32];
                 tmem_ld32(tmem_o + lane_base + ch * 32, orr);
                 tmem_wait_ld();
-                if (valid) {
+                if (valid && ok) {
                     float vals[32];
 #pragma unroll
                     for (int c = 0; c < 32; ++c) vals[c] = __uint_as_float(orr[c]) * inv_l;
@@ -295,6 +344,8 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     }
                 }
             }
+            tc_fence_before();
+            mbar_arrive(bar(BAR_OD));      // this thread has read its part of O: the next item's first PV may overwrite it
         }
     }
     tc_fence_before();
@@ -419,11 +470,18 @@ int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const 
         B2_CUDA(cudaFuncSetAttribute(fa_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF1Smem));
         attr_done = true;
     }
-    dim3 grid(n_tiles, kFaHeads);
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        B2_CUDA(cudaGetDevice(&dev));
+        B2_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const int n_items = n_tiles * kFaHeads;
+    dim3 grid(std::min(n_items, n_sm));
     if (out_bf16)
-        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (__nv_bfloat16*)out, d_error);
+        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, n_items, gate, (__nv_bfloat16*)out, d_error);
     else
-        fa_prefill_tc_kernel<float><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, gate, (float*)out, d_error);
+        fa_prefill_tc_kernel<float><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, n_items, gate, (float*)out, d_error);
     B2_LAUNCH_CHECK();
     return 0;
 }

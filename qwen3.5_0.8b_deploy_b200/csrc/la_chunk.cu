@@ -51,6 +51,13 @@ constexpr int kG1Threads = 288;
 enum { G_KQ_FULL0 = 0, G_KQ_FULL1, G_A_DONE, G_B1, G_C1, G_B2, G_C2, G_B3, G_C3, G_BAR_COUNT };
 
 __device__ __forceinline__ void named_sync_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// 2^x on the special-function unit (about 2 ulp); the decay matrices need 64 x 64 of them per chunk and head.
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+constexpr float kLog2e = 1.4426950408889634f;
 
 // dst(16x16 block at dr,dc) (+)= sign * A(16x16 at ar,ac) * B(16x16 at br,bc); matrices 64x64 fp32 row-major in
 // shared memory; 256 threads, one output each.
@@ -230,11 +237,11 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (warp == 1) s_b[tid] += s_b[31];
             named_sync_256();
             if (tid < 64) {
-                s_eb[tid] = expf(s_b[tid]);
-                s_ebc[tid] = expf(s_b[63] - s_b[tid]);
+                s_eb[tid] = ex2_approx(s_b[tid] * kLog2e);
+                s_ebc[tid] = ex2_approx((s_b[63] - s_b[tid]) * kLog2e);
             }
             named_sync_256();
-            const float e_bc = expf(s_b[63]);
+            const float e_bc = ex2_approx(s_b[63] * kLog2e);
             // ---- this thread's half column of beta V ----
             float vcol[32];
 #pragma unroll
@@ -283,7 +290,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int j = hf * 32 + j4 * 4 + e;
-                            a4[e] = (j < r) ? be * expf(bi - s_b[j]) * __uint_as_float(d1[j4 * 4 + e]) : 0.f;
+                            a4[e] = (j < r) ? be * ex2_approx((bi - s_b[j]) * kLog2e) * __uint_as_float(d1[j4 * 4 + e]) : 0.f;
                         }
                         *reinterpret_cast<float4*>(AM + r * 64 + hf * 32 + j4 * 4) = make_float4(a4[0], a4[1], a4[2], a4[3]);
                     }
@@ -297,8 +304,8 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const int j0 = hf * 32 + cc * 8 + 2 * e, j1 = j0 + 1;
-                            const float m0 = (j0 <= i) ? expf(bi - s_b[j0]) * __uint_as_float(d1[cc * 8 + 2 * e]) : 0.f;
-                            const float m1 = (j1 <= i) ? expf(bi - s_b[j1]) * __uint_as_float(d1[cc * 8 + 2 * e + 1]) : 0.f;
+                            const float m0 = (j0 <= i) ? ex2_approx((bi - s_b[j0]) * kLog2e) * __uint_as_float(d1[cc * 8 + 2 * e]) : 0.f;
+                            const float m1 = (j1 <= i) ? ex2_approx((bi - s_b[j1]) * kLog2e) * __uint_as_float(d1[cc * 8 + 2 * e + 1]) : 0.f;
                             pk[e] = pack_half2(m0, m1);
                         }
                         *reinterpret_cast<uint4*>(row_ptr + (((hf * 4 + cc) ^ (i & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
