@@ -231,14 +231,15 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 mbar_arrive(bar(BAR_SE + b));
                 const int col0 = j * kBN + hf * 32;
                 const bool diag = (col0 + 31 > tile.q_pos0);   // warp-uniform: this half tile may cross a diagonal
-                float mx = -INFINITY;
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four short chains instead of one long one
 #pragma unroll
                 for (int c = 0; c < 32; ++c) {
                     float v = __uint_as_float(sr[c]);
                     if (diag && (col0 + c > q_pos)) v = -INFINITY;
                     sr[c] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                    mx4[c & 3] = fmaxf(mx4[c & 3], v);
                 }
+                float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
                 x_mx[(b * 2 + hf) * 128 + r] = mx;
                 asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
                 mx = fmaxf(mx, x_mx[(b * 2 + (hf ^ 1)) * 128 + r]) * sc;
@@ -267,7 +268,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 // P = 2^(s * scale - m_ref) as fp16 into the swizzled K-major A tile
                 if (gs >= 2 && !mbar_wait_warp(bar(BAR_PV + b), ((gs >> 1) - 1) & 1, abort_flag)) ok = false;
                 unsigned char* prow = sm + kOffP + b * kPBytes + r * 128;
-                float lsum = 0.f;
+                float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int c8 = 0; c8 < 4; ++c8) {
                     uint32_t pk[4];
@@ -275,12 +276,12 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     for (int e = 0; e < 4; ++e) {
                         const float p0 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e]), sc, -m_ref));
                         const float p1 = ex2_fast(fmaf(__uint_as_float(sr[c8 * 8 + 2 * e + 1]), sc, -m_ref));
-                        lsum += p0 + p1;
+                        ls4[e] += p0 + p1;
                         pk[e] = pack_half2(p0, p1);
                     }
                     *reinterpret_cast<uint4*>(prow + (((hf * 4 + c8) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
-                l += lsum;
+                l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(bar(BAR_PF + b));
