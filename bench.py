@@ -53,6 +53,23 @@ def algo_la_prefill_flops(n_seqs: int, length: int) -> float:
     return n_seqs * 16 * length * 3.0 * 2 * 128 * 128                     # serial recurrence: 3 passes of 128x128 MACs per token-head
 
 
+def ncu_traffic(kernel: str, scale: float):
+    """DRAM bytes (read + write) of one launch of `kernel` from the committed ncu summary of its small case
+    (profiles/<kernel>_kernel_small_case.md, last captured launch), scaled by `scale` = units of a bench launch /
+    units of the captured launch.  None if the summary is missing."""
+    path = os.path.join(ROOT, "profiles", f"{kernel}_kernel_small_case.md")
+    if not os.path.exists(path):
+        return None
+    unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+    total, seen = 0.0, 0
+    for line in open(path):
+        cells = [c.strip() for c in line.split("|")]
+        if len(cells) >= 4 and cells[1] in ("`dram__bytes_read.sum`", "`dram__bytes_write.sum`") and cells[3] in unit:
+            total += float(cells[2].replace(",", "")) * unit[cells[3]]
+            seen += 1
+    return total * scale if seen == 2 else None
+
+
 def read_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -383,8 +400,14 @@ def main():
             fa_prefill=dict(bound="tensor", achieved=algo_fa_prefill_flops(seqs_per_chunk, P) / (per["fa_prefill"] * 1e-3) / 1e12, peak=peaks["tflops_sustained"], unit="TFLOP/s"),
             la_prefill=dict(bound="tensor", achieved=algo_la_prefill_flops(seqs_per_chunk, P) / (per["la_prefill"] * 1e-3) / 1e12, peak=peaks["tflops_sustained"], unit="TFLOP/s"),
         )
+        # units of one bench launch / units of the launch captured under ncu (kernel_bench.py commands in profiles/):
+        # la_decode 128 sequences; fa_decode 128 sequences x 1280 cached tokens; fa_prefill 16 and la_prefill 10 sequences x 1024
+        traffic_scale = dict(la_decode=B / 128.0, fa_decode=(B / 128.0) * (ctx_avg / 1280.0), fa_prefill=seqs_per_chunk * P / (16.0 * 1024),
+                             la_prefill=seqs_per_chunk * P / (10.0 * 1024))
         for k, r in roof.items():
-            r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], timing=(timing if k.endswith("decode") else "eager launches"), job_ms=job_ms[k], traffic=None, peak_source=peaks["source"])
+            r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], timing=(timing if k.endswith("decode") else "eager launches"), job_ms=job_ms[k],
+                     traffic=ncu_traffic(k, traffic_scale[k]), traffic_source="ncu capture of the small case in profiles/, scaled by the units one bench launch processes",
+                     peak_source=peaks["source"])
         dominant = max(job_ms, key=job_ms.get)
         cpu = None
         if not args.no_cpu_baseline:

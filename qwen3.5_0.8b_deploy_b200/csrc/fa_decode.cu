@@ -214,6 +214,22 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                 qf[ks][1] = (g < 4) ? v.y : 0u;
             }
         }
+        // INT8 cache: the K codes enter the MMA as code + 1152 (one instruction less per pair of values); the logits are
+        // corrected by 1152 * sum_dim q[dim, head], which is computed here once per (sequence, kv head) pair
+        float corr0 = 0.f, corr1 = 0.f;
+        if constexpr (!kFp16) {
+            float qs = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 16; ++ks) {
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&qf[ks][0]));
+                const float2 b2 = __half22float2(*reinterpret_cast<const __half2*>(&qf[ks][1]));
+                qs += (a.x + a.y) + (b2.x + b2.y);
+            }
+            qs += __shfl_xor_sync(0xffffffffu, qs, 1);
+            qs += __shfl_xor_sync(0xffffffffu, qs, 2);           // lanes of one g now hold the sum over all 256 dims of head g
+            corr0 = 1152.0f * __shfl_sync(0xffffffffu, qs, (2 * t) * 4);
+            corr1 = 1152.0f * __shfl_sync(0xffffffffu, qs, (2 * t + 1) * 4);
+        }
         float o[16][4];
 #pragma unroll
         for (int j = 0; j < 16; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
@@ -254,8 +270,8 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
 #pragma unroll
                         for (int ss = 0; ss < 4; ++ss) {
                             uint32_t r0, r2, r1, r3;
-                            cvt_s8x4_half2x2(wl[ss], r0, r2);
-                            cvt_s8x4_half2x2(wh[ss], r1, r3);
+                            cvt_s8x4_half2x2_biased(wl[ss], r0, r2);
+                            cvt_s8x4_half2x2_biased(wh[ss], r1, r3);
                             mma_16816(s[w], r0, r1, r2, r3, qf[4 * blk + ss][0], qf[4 * blk + ss][1]);
                         }
                     }
@@ -270,10 +286,10 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                 const int tok_lo = 16 * (g >> 1) + 4 * w + (g & 1);
                 const int tok_hi = tok_lo + 2;
                 const bool val_lo = page_pos0 + tok_lo < L, val_hi = page_pos0 + tok_hi < L;
-                s[w][0] = val_lo ? s[w][0] * kl[w] : -INFINITY;
-                s[w][1] = val_lo ? s[w][1] * kl[w] : -INFINITY;
-                s[w][2] = val_hi ? s[w][2] * kh[w] : -INFINITY;
-                s[w][3] = val_hi ? s[w][3] * kh[w] : -INFINITY;
+                s[w][0] = val_lo ? (s[w][0] - corr0) * kl[w] : -INFINITY;      // corr = 0 for the FP16 cache
+                s[w][1] = val_lo ? (s[w][1] - corr1) * kl[w] : -INFINITY;
+                s[w][2] = val_hi ? (s[w][2] - corr0) * kh[w] : -INFINITY;
+                s[w][3] = val_hi ? (s[w][3] - corr1) * kh[w] : -INFINITY;
                 mx0 = fmaxf(mx0, fmaxf(s[w][0], s[w][2]));
                 mx1 = fmaxf(mx1, fmaxf(s[w][1], s[w][3]));
             }

@@ -139,4 +139,12 @@ __device__ __forceinline__ void cvt_s8x4_half2x2(uint32_t x, uint32_t& lo, uint3
     hi = *reinterpret_cast<uint32_t*>(&hh);
 }
 
+// Four signed bytes -> two half2 holding b + 1152 (exact integers 1024..1279): the same byte placement without the
+// subtraction.  For a dot product with a vector q the caller subtracts 1152 * sum(q) once instead.
+__device__ __forceinline__ void cvt_s8x4_half2x2_biased(uint32_t x, uint32_t& lo, uint32_t& hi) {
+    x ^= 0x80808080u;
+    lo = __byte_perm(x, 0x64646464u, 0x4140);
+    hi = __byte_perm(x, 0x64646464u, 0x4342);
+}
+
 }  // namespace b200

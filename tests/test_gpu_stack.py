@@ -89,6 +89,43 @@ def test_graph_replay_equals_eager_decode(ops, cuda, synth, decode_gemm):
     assert st.device_status() == 0
 
 
+def test_plain_stream_order_gives_the_same_tokens(ops, cuda, synth, monkeypatch):
+    """The decode kernels are launched as programmatic dependents (they may start while their predecessor drains and
+    wait before touching its results).  With the attribute switched off every launch waits for the previous one to
+    finish; both must produce identical tokens, eagerly and from the captured graph."""
+    torch = cuda
+    from oracle import cpu_stack
+    weights = cpu_stack.make_stack_weights(synth, 63, L, INTER, VOCAB, int8=True)
+    n, T, D = 4, 50, 5
+    tokens = torch.from_numpy(synth.rng(63, "tokens").integers(0, VOCAB, (n, T)).astype(np.int32)).cuda()
+    runs = {}
+    for pdl in ("1", "0"):
+        monkeypatch.setenv("B200ATTN_PDL", pdl)
+        st = _build(ops, synth, weights)
+        cur = st.forward_batch_prefill(tokens)
+        eager = [cur.clone()]
+        for _ in range(D):
+            cur = st.forward_batch_decode(cur)
+            eager.append(cur.clone())
+        st.reset_cache()
+        first = st.forward_batch_prefill(tokens)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            st.set_tokens(first)
+            st.capture_decode(n)
+            replay = []
+            for _ in range(D):
+                st.launch_decode(1)
+                replay.append(st.get_tokens(n))
+            side.synchronize()
+        for a, b in zip(eager[1:], replay):
+            assert torch.equal(a, b)
+        assert st.device_status() == 0
+        runs[pdl] = eager
+    for a, b in zip(runs["1"], runs["0"]):
+        assert torch.equal(a, b)
+
+
 def test_stack_errors(ops, cuda, synth):
     torch = cuda
     st = ops.HybridStack(num_layers=L, intermediate_size=INTER, vocab_size=VOCAB, max_seqs=2, max_seq_len=64,
