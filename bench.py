@@ -408,6 +408,21 @@ def main():
             r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], timing=(timing if k.endswith("decode") else "eager launches"), job_ms=job_ms[k],
                      traffic=ncu_traffic(k, traffic_scale[k]), traffic_source="ncu capture of the small case in profiles/, scaled by the units one bench launch processes",
                      peak_source=peaks["source"])
+        # The same two decode kernels timed as back-to-back launches on caches of their own (no event pair per launch, no
+        # neighbours): what the kernel itself does, next to what it does inside the step.
+        try:
+            import importlib.util
+            spec = importlib.util.spec_from_file_location("b200_kernel_bench", os.path.join(ROOT, "qwen3.5_0.8b_deploy_b200", "kernel_bench.py"))
+            kb = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(kb)
+            with torch.cuda.stream(stream):
+                iso = dict(la_decode=kb.measure("la_decode", seqs=B, layers=4, iters=40),
+                           fa_decode=kb.measure("fa_decode", seqs=B, ctx=int(ctx_avg), kv="fp16", layers=2, iters=40))
+            for k, m in iso.items():
+                roof[k]["isolated"] = dict(ms_per_launch=m["ms"], achieved=m["achieved"], frac=m["frac"],
+                                           note="back-to-back launches through the core entry" + ("; includes its query-conversion launch" if k == "fa_decode" else ""))
+        except Exception as e:          # the job's own numbers stand without it
+            roof["la_decode"]["isolated"] = dict(error=str(e)[:200])
         dominant = max(job_ms, key=job_ms.get)
         cpu = None
         if not args.no_cpu_baseline:

@@ -45,19 +45,11 @@ def time_ms(fn, iters, warmup):
     return a.elapsed_time(b) / iters
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--kernel", required=True, choices=["la_decode", "fa_decode", "fa_prefill", "la_prefill"])
-    ap.add_argument("--seqs", type=int, default=128)
-    ap.add_argument("--ctx", type=int, default=1024)
-    ap.add_argument("--kv", default="fp16", choices=["fp16", "int8"])
-    ap.add_argument("--layers", type=int, default=4, help="independent caches to rotate over (decode kernels)")
-    ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--serial", action="store_true", help="la_prefill / fa_prefill: run the plain cross-check kernel instead")
-    args = ap.parse_args()
+def measure(kernel: str, seqs: int = 128, ctx: int = 1024, kv: str = "fp16", layers: int = 4, iters: int = 20, warmup: int = 3,
+            serial: bool = False) -> dict:
+    """Times `iters` back-to-back launches of one kernel class on the current device and returns its roofline record."""
+    args = argparse.Namespace(kernel=kernel, seqs=seqs, ctx=ctx, kv=kv, layers=layers, iters=iters, warmup=warmup, serial=serial)
     ops = entry.load_ops()
-    torch.cuda.set_device(0)
     g = torch.Generator(device="cuda").manual_seed(1)
     hbm, tfl, src = peaks()
     n, L = args.seqs, args.ctx
@@ -130,7 +122,22 @@ def main():
                    note="time includes two fp32->fp16 conversion launches and a status read of the core entry")
     out["frac"] = out["achieved"] / out["peak"]
     out["peak_source"] = src
-    print(json.dumps(out))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True, choices=["la_decode", "fa_decode", "fa_prefill", "la_prefill"])
+    ap.add_argument("--seqs", type=int, default=128)
+    ap.add_argument("--ctx", type=int, default=1024)
+    ap.add_argument("--kv", default="fp16", choices=["fp16", "int8"])
+    ap.add_argument("--layers", type=int, default=4, help="independent caches to rotate over (decode kernels)")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--serial", action="store_true", help="la_prefill / fa_prefill: run the plain cross-check kernel instead")
+    a = ap.parse_args()
+    torch.cuda.set_device(0)
+    print(json.dumps(measure(a.kernel, a.seqs, a.ctx, a.kv, a.layers, a.iters, a.warmup, a.serial)))
 
 
 if __name__ == "__main__":
