@@ -206,16 +206,15 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
         const int ppw = decode_pages_per_warp(pool);
         const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
         if (!core_only) B2_TRY(fa_project_in(fa, d_x, x_is_bf16, n_seqs, true, pool->d_error, s));
-        B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, n_seqs, fa->d_qnorm, fa->d_inv_freq, nullptr, d_slots_in,
-                                    pool->d_lens + (size_t)layer * pool->cfg.max_seqs, kv.max_seqs, fa->d_q, fa->d_gate, s));
-        B2_TRY(launch_kv_append(kv, layer, nullptr, n_seqs, d_slots_in, k_in, kFaQkvCols, v_in, kFaQkvCols, true, fa->d_knorm,
-                                fa->d_inv_freq, nullptr, nullptr, nullptr, true, s));
+        // q / gate epilogue, append of the new token's K and V, and the length increment in one launch; the attention
+        // kernel then sees the new length already
+        B2_TRY(launch_fa_decode_pre(kv, layer, d_slots_in, n_seqs, fa->d_qkv_raw, fa->d_qnorm, fa->d_knorm, fa->d_inv_freq, fa->d_q,
+                                    fa->d_gate, s));
         {
             ProfScope prof(PROF_FA_DECODE, s);
-            B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, 1, fa->d_q, fa->d_gate, ppw, splits, fa->d_part_o,
+            B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, 0, fa->d_q, fa->d_gate, ppw, splits, fa->d_part_o,
                                     fa->d_part_ml, fa->d_counters, fa->d_attn, bf16, s));
         }
-        B2_TRY(launch_kv_advance(kv, layer, d_slots_in, nullptr, n_seqs, s));
         if (!core_only) B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
         pool->lens_dirty = true;
         return 0;

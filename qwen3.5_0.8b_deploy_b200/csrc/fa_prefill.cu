@@ -46,8 +46,9 @@ enum { BAR_Q = 0, BAR_QE = 1, BAR_KF = 2, BAR_KE = 4, BAR_VF = 6, BAR_VE = 8, BA
 template <typename OutT>
 __global__ void __launch_bounds__(kF1Threads, 1)
 fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const PrefillTile* __restrict__ tiles, int n_items,
-                     const __half* __restrict__ gate, OutT* __restrict__ out, int* __restrict__ error_word) {
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                     const PrefillTile* __restrict__ tiles, int n_items, const __half* __restrict__ gate, OutT* __restrict__ out,
+                     int* __restrict__ error_word) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     unsigned char* sm = smem_raw;
@@ -88,6 +89,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         tma_prefetch_desc(&map_q);
         tma_prefetch_desc(&map_k);
         tma_prefetch_desc(&map_v);
+        if constexpr (sizeof(OutT) == 2) tma_prefetch_desc(&map_o);
     }
     tc_fence_before();
     __syncthreads();
@@ -220,6 +222,12 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const int n_kt = key_tiles(tile);
             const int q_pos = tile.q_pos0 + r;
             float m_ref = -INFINITY, l = 0.f;
+            // this row's gate values (512 bytes, read in the epilogue) start their way from DRAM to L2 now
+            if (gate && r < tile.n_rows) {
+                const __half* grow = gate + ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim + hf * 128;
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(grow));
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(grow + 64));
+            }
             for (int j = 0; j < n_kt; ++j, ++gs) {
                 const int b = gs & 1;
                 if (!mbar_wait_warp(bar(BAR_SF + b), (gs >> 1) & 1, abort_flag)) ok = false;
@@ -294,47 +302,59 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
             const bool valid = r < tile.n_rows;
             const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
-            uint4 gpre[4][4];      // this thread's gate values, requested before the wait on the last PV product
+            // Output columns of this thread: round k (0, 1) covers columns [128k, 128k + 128); in it the thread owns the two
+            // 32-column chunks k*4 + hf*2 + {0, 1}.  Gate values are requested before the wait on the last PV product.
+            uint4 gpre[4][4];
             if (gate && valid) {
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc)
 #pragma unroll
                     for (int q4 = 0; q4 < 4; ++q4)
-                        gpre[cc][q4] = *reinterpret_cast<const uint4*>(gate + orow + (hf * 4 + cc) * 32 + q4 * 8);
+                        gpre[cc][q4] = *reinterpret_cast<const uint4*>(gate + orow + ((cc >> 1) * 4 + hf * 2 + (cc & 1)) * 32 + q4 * 8);
             }
             if (!mbar_wait_warp(bar(BAR_OF), it & 1, abort_flag)) ok = false;
             tc_fence_after();
             const float inv_l = 1.0f / l;
+            // bf16 output of a full tile leaves through shared memory and two tiled TMA stores per round (the P buffers are
+            // idle between the last PV product and the next item's first P tile); anything else is stored from registers
+            const bool via_tma = (sizeof(OutT) == 2) && (tile.n_rows == kBM);
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
-                const int ch = hf * 4 + cc;
+                const int ch = (cc >> 1) * 4 + hf * 2 + (cc & 1);
                 uint32_t orr[32];
                 tmem_ld32(tmem_o + lane_base + ch * 32, orr);
                 tmem_wait_ld();
-                if (valid && ok) {
-                    float vals[32];
+                float vals[32];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) vals[c] = __uint_as_float(orr[c]) * inv_l;
-                    if (gate) {
+                for (int c = 0; c < 32; ++c) vals[c] = __uint_as_float(orr[c]) * inv_l;
+                if (gate && valid) {
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            const uint4 gv = gpre[cc][q4];
-                            const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const uint4 gv = gpre[cc][q4];
+                        const __half2* gh = reinterpret_cast<const __half2*>(&gv);
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float2 gf = __half22float2(gh[e]);
-                                vals[q4 * 8 + 2 * e] *= gf.x;
-                                vals[q4 * 8 + 2 * e + 1] *= gf.y;
-                            }
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 gf = __half22float2(gh[e]);
+                            vals[q4 * 8 + 2 * e] *= gf.x;
+                            vals[q4 * 8 + 2 * e + 1] *= gf.y;
                         }
                     }
-                    OutT* dst = out + orow + ch * 32;          // 32 consecutive outputs of this row: 16-byte stores
-                    if constexpr (sizeof(OutT) == 4) {
+                }
+                if constexpr (sizeof(OutT) == 2) {
+                    if (via_tma) {
+                        // staging tile of round cc>>1: two boxes [128 rows][64 columns] bf16, 128-byte swizzle
+                        const int col = (hf * 2 + (cc & 1)) * 32;              // column inside the round's 128
+                        unsigned char* srow = sm + kOffP + (col >> 6) * kPBytes + r * 128;
 #pragma unroll
-                        for (int q4 = 0; q4 < 8; ++q4)
-                            *reinterpret_cast<float4*>(dst + 4 * q4) =
-                                make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
-                    } else {
+                        for (int q8 = 0; q8 < 4; ++q8) {
+                            __nv_bfloat162 h[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
+                            const int chunk16 = ((col & 63) >> 3) + q8;
+                            *reinterpret_cast<uint4*>(srow + ((chunk16 ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(h);
+                        }
+                    } else if (valid && ok) {
+                        OutT* dst = out + orow + ch * 32;
 #pragma unroll
                         for (int q8 = 0; q8 < 4; ++q8) {
                             __nv_bfloat162 h[4];
@@ -343,12 +363,39 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                             *reinterpret_cast<uint4*>(dst + 8 * q8) = *reinterpret_cast<uint4*>(h);
                         }
                     }
+                } else {
+                    if (valid && ok) {
+                        OutT* dst = out + orow + ch * 32;          // 32 consecutive outputs of this row: 16-byte stores
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4)
+                            *reinterpret_cast<float4*>(dst + 4 * q4) =
+                                make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
+                    }
+                }
+                if constexpr (sizeof(OutT) == 2) {
+                    if (via_tma && (cc & 1)) {
+                        // the round's 128 columns are staged: one thread sends them, everybody waits until the staging tile
+                        // has been read before it is written again (next round, or the next item's P tiles)
+                        fence_proxy_async_smem();
+                        asm volatile("bar.sync 5, 256;" ::: "memory");
+                        if (threadIdx.x == 0) {
+                            if (ok) {
+                                const int c0 = (cc >> 1) * 128;
+                                tma_store_3d(&map_o, base + kOffP, c0, head, tile.q_row0);
+                                tma_store_3d(&map_o, base + kOffP + kPBytes, c0 + 64, head, tile.q_row0);
+                                bulk_commit_group();
+                            }
+                            bulk_wait_group_read0();
+                        }
+                        asm volatile("bar.sync 5, 256;" ::: "memory");
+                    }
                 }
             }
             tc_fence_before();
             mbar_arrive(bar(BAR_OD));      // this thread has read its part of O: the next item's first PV may overwrite it
         }
     }
+    if (threadIdx.x == 0) bulk_wait_group0();      // this thread's TMA stores have reached global memory
     tc_fence_before();
     __syncthreads();
     if (warp == 9) {
@@ -465,6 +512,13 @@ int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const 
         B2_TRY(make_tensor_map(&mk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, kstage, dims, str, box));
         B2_TRY(make_tensor_map(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, vstage, dims, str, box));
     }
+    CUtensorMap mo = mq;      // only the bf16 kernel uses it
+    if (out_bf16) {
+        const uint64_t dims[3] = {(uint64_t)kHeadDim, (uint64_t)kFaHeads, (uint64_t)rows};
+        const uint64_t str[2] = {(uint64_t)kHeadDim * 2, (uint64_t)kFaHeads * kHeadDim * 2};
+        const uint32_t box[3] = {64, 1, (uint32_t)kBM};
+        B2_TRY(make_tensor_map(&mo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, dims, str, box));
+    }
     static bool attr_done = false;
     if (!attr_done) {
         B2_CUDA(cudaFuncSetAttribute(fa_prefill_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF1Smem));
@@ -480,9 +534,9 @@ int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const 
     const int n_items = n_tiles * kFaHeads;
     dim3 grid(std::min(n_items, n_sm));
     if (out_bf16)
-        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, n_items, gate, (__nv_bfloat16*)out, d_error);
+        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, mo, d_tiles, n_items, gate, (__nv_bfloat16*)out, d_error);
     else
-        fa_prefill_tc_kernel<float><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, d_tiles, n_items, gate, (float*)out, d_error);
+        fa_prefill_tc_kernel<float><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, mo, d_tiles, n_items, gate, (float*)out, d_error);
     B2_LAUNCH_CHECK();
     return 0;
 }

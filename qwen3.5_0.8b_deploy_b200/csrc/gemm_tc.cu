@@ -147,23 +147,26 @@ gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     }
                 }
             } else if constexpr (EPI == kEpiSwiglu) {
-                static_assert(EPI != kEpiSwiglu || BN == 64, "SwiGLU tiles are 32 gate + 32 up columns");
-                uint32_t gt[32], up[32];
-                tmem_ld32(tmem + lane_base, gt);
-                tmem_ld32(tmem + lane_base + 32, up);
-                tmem_wait_ld();
-                if (m < M) {
-                    __nv_bfloat16* dst = out_bf16 + (size_t)m * ld_out + blockIdx.x * 32;
+                static_assert(EPI != kEpiSwiglu || BN % 64 == 0, "SwiGLU tiles are groups of 32 gate + 32 up columns");
+#pragma unroll 1
+                for (int grp = 0; grp < BN / 64; ++grp) {       // each 64-column group: 32 gate columns, then the 32 matching up columns
+                    uint32_t gt[32], up[32];
+                    tmem_ld32(tmem + lane_base + grp * 64, gt);
+                    tmem_ld32(tmem + lane_base + grp * 64 + 32, up);
+                    tmem_wait_ld();
+                    if (m < M && n0 + grp * 64 < N) {
+                        __nv_bfloat16* dst = out_bf16 + (size_t)m * ld_out + (n0 >> 1) + grp * 32;
 #pragma unroll
-                    for (int c8 = 0; c8 < 4; ++c8) {
-                        __nv_bfloat162 h[4];
+                        for (int c8 = 0; c8 < 4; ++c8) {
+                            __nv_bfloat162 h[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float g0 = __uint_as_float(gt[8 * c8 + 2 * e]), g1 = __uint_as_float(gt[8 * c8 + 2 * e + 1]);
-                            const float u0 = __uint_as_float(up[8 * c8 + 2 * e]), u1 = __uint_as_float(up[8 * c8 + 2 * e + 1]);
-                            h[e] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                            for (int e = 0; e < 4; ++e) {
+                                const float g0 = __uint_as_float(gt[8 * c8 + 2 * e]), g1 = __uint_as_float(gt[8 * c8 + 2 * e + 1]);
+                                const float u0 = __uint_as_float(up[8 * c8 + 2 * e]), u1 = __uint_as_float(up[8 * c8 + 2 * e + 1]);
+                                h[e] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                            }
+                            *reinterpret_cast<uint4*>(dst + 8 * c8) = *reinterpret_cast<uint4*>(h);
                         }
-                        *reinterpret_cast<uint4*>(dst + 8 * c8) = *reinterpret_cast<uint4*>(h);
                     }
                 }
             } else {
@@ -295,8 +298,10 @@ int gemm_tc_swiglu(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* 
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N % 64 == 0, "gemm_tc_swiglu: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
     B2_TRY(bf16_map(X, M, K, 128, &mx));
-    B2_TRY(bf16_map(W, N, K, 64, &mw));
-    return launch_one<64, kEpiSwiglu>(mx, mw, M, N, K, 1, nullptr, N / 2, 0, act, nullptr, d_error, s);
+    // 128-column tiles (two gate/up groups): half as many CTAs re-read the activations, and 56 SMs still stream the
+    // 14.7 MB of gate/up weights of the model's FFN faster than HBM delivers them
+    B2_TRY(bf16_map(W, N, K, 128, &mw));
+    return launch_one<128, kEpiSwiglu>(mx, mw, M, N, K, 1, nullptr, N / 2, 0, act, nullptr, d_error, s);
 }
 
 // tokens[m] = argmax_n X[m] . W[n]   (d_packed: M zeroed 64-bit words, left zeroed again).

@@ -18,6 +18,8 @@ int launch_kv_append(const KvView& kv, int layer, const AppendTile* d_tiles, int
                      const float* kin, int k_stride, const float* vin, int v_stride, bool do_norm_rope,
                      const float* k_norm_w, const float* inv_freq, __half* kstage, __half* vstage,
                      const int* d_stage_row0, bool decode_mode, cudaStream_t s);
+int launch_fa_decode_pre(const KvView& kv, int layer, const int* d_slots, int n_seqs, const float* qkv_raw, const float* q_norm_w,
+                         const float* k_norm_w, const float* inv_freq, __half* q_out, __half* gate_out, cudaStream_t s);
 int launch_kv_advance(const KvView& kv, int layer, const int* d_slots, const int* d_counts, int n_seqs, cudaStream_t s);
 int launch_fa_q_epilogue(const float* qkv_raw, int rows, const float* q_norm_w, const float* inv_freq,
                          const int* d_row_pos, const int* d_slots, const int* d_lens_layer, int max_seqs, __half* q_out,

@@ -220,6 +220,85 @@ fa_q_epilogue_kernel(const float* __restrict__ qkv_raw, int rows, const float* _
     *reinterpret_cast<uint4*>(gate_out + o) = *reinterpret_cast<uint4*>(hg);
 }
 
+// Decode step, everything between the fused qkv projection and the attention kernel in ONE launch: one CTA per sequence,
+// twelve warps = 8 q heads (norm, RoPE, gate: fa_q_epilogue_kernel's work), 2 K heads and 2 V heads of the new token
+// (norm / RoPE / quantise-on-append: kv_append_kernel's work for one token), then the sequence's length on this layer
+// goes up by one (kv_advance_kernel's work) -- after every warp of the CTA has read the old length, and no other CTA
+// touches this sequence.  The attention kernel that follows therefore runs with len_add = 0.
+template <bool kFp16>
+__global__ void __launch_bounds__(384)
+fa_decode_pre_kernel(KvView kv, int layer, const int* __restrict__ slots, const float* __restrict__ qkv_raw,
+                     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
+                     __half* __restrict__ q_out, __half* __restrict__ gate_out) {
+    using VT = typename std::conditional<kFp16, __half, int8_t>::type;
+    pdl_enter();
+    const int seq = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = slots[seq];
+    if (slot < 0 || slot >= kv.max_seqs) {
+        if (threadIdx.x == 0) atomicExch(kv.error, 1);
+        return;
+    }
+    const int pos = kv.lens[layer * kv.max_seqs + slot];
+    const bool room = pos + 1 <= kv.capacity[slot];
+    const float* rowp = qkv_raw + (size_t)seq * kFaQkvCols;
+    if (warp < kFaHeads) {
+        const int h = warp;
+        const float* src = rowp + h * 2 * kHeadDim + 8 * lane;
+        float x[8], g[8];
+        load8(src, x);
+        load8(src + kHeadDim, g);
+        norm_rope8(x, q_norm_w, inv_freq, pos, lane);
+        __half hq[8], hg[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            hq[i] = __float2half_rn(x[i]);
+            hg[i] = __float2half_rn(1.0f / (1.0f + expf(-g[i])));
+        }
+        const size_t o = ((size_t)seq * kFaHeads + h) * kHeadDim + 8 * lane;
+        *reinterpret_cast<uint4*>(q_out + o) = *reinterpret_cast<uint4*>(hq);
+        *reinterpret_cast<uint4*>(gate_out + o) = *reinterpret_cast<uint4*>(hg);
+    } else if (room) {
+        const bool is_v = warp >= kFaHeads + kFaKvHeads;
+        const int kvh = (warp - kFaHeads) % kFaKvHeads;
+        const int page = kv.block_table[slot * kv.max_pages_per_seq + pos / kPageTokens];
+        const int t = pos % kPageTokens;
+        const size_t head_base = ((size_t)(layer * kv.num_pages + page) * kFaKvHeads + kvh);
+        float x[8];
+        load8(rowp + kFaHeads * kHeadDim * 2 + (is_v ? kFaKvHeads * kHeadDim : 0) + kvh * kHeadDim + 8 * lane, x);
+        if (!is_v) norm_rope8(x, k_norm_w, inv_freq, pos, lane);
+        VT* pg = reinterpret_cast<VT*>(is_v ? kv.v : kv.k) + head_base * (kPageTokens * kHeadDim);
+        if constexpr (kFp16) {
+            __half hx[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) hx[i] = __float2half_rn(x[i]);
+            if (!is_v) {
+                *reinterpret_cast<uint4*>(pg + t * kHeadDim + 8 * lane) = *reinterpret_cast<uint4*>(hx);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) pg[(8 * lane + i) * kPageTokens + t] = hx[i];     // token-minor V
+            }
+        } else {
+            int c[8];
+            const float sc = quantize8(x, c);
+            if (lane == 0) (is_v ? kv.vs : kv.ks)[head_base * kPageTokens + t] = sc;
+            if (!is_v) {
+                int8_t b[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) b[i] = (int8_t)c[i];
+                *reinterpret_cast<uint2*>(pg + t * kHeadDim + 8 * lane) = *reinterpret_cast<uint2*>(b);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) pg[(8 * lane + i) * kPageTokens + t] = (int8_t)c[i];
+            }
+        }
+    }
+    __syncthreads();      // every warp has used the old length
+    if (threadIdx.x == 0) {
+        if (room) kv.lens[layer * kv.max_seqs + slot] = pos + 1;
+        else atomicExch(kv.error, 2);               // page not reserved: nothing was written, the length stays
+    }
+}
+
 // Export one sequence's cache on one layer as token-major arrays. grid (len, kv_heads), block 256.
 template <bool kFp16>
 __global__ void kv_export_kernel(KvView kv, int layer, int slot, int len, void* k_out, void* v_out,
@@ -277,6 +356,18 @@ int launch_kv_append(const KvView& kv, int layer, const AppendTile* d_tiles, int
     else
         launch_pdl(kv_append_kernel<false>, grid, dim3(256), 0, s, kv, layer, d_tiles, d_slots, kin, k_stride, vin, v_stride,
                    do_norm_rope, k_norm_w, inv_freq, kstage, vstage, d_stage_row0, decode_mode);
+    B2_LAUNCH_CHECK();
+    return 0;
+}
+
+int launch_fa_decode_pre(const KvView& kv, int layer, const int* d_slots, int n_seqs, const float* qkv_raw, const float* q_norm_w,
+                         const float* k_norm_w, const float* inv_freq, __half* q_out, __half* gate_out, cudaStream_t s) {
+    if (kv.is_fp16)
+        launch_pdl(fa_decode_pre_kernel<true>, dim3(n_seqs), dim3(384), 0, s, kv, layer, d_slots, qkv_raw, q_norm_w, k_norm_w, inv_freq,
+                   q_out, gate_out);
+    else
+        launch_pdl(fa_decode_pre_kernel<false>, dim3(n_seqs), dim3(384), 0, s, kv, layer, d_slots, qkv_raw, q_norm_w, k_norm_w, inv_freq,
+                   q_out, gate_out);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -464,6 +555,33 @@ extern "C" int b200attn_kv_seq_free(b200attn_kv_pool p, int slot) {
     p->seq_pages[slot].clear();
     p->slot_used[slot] = 0;
     p->h_capacity[slot] = 0;
+    return pool_push_tables(p, slot);
+}
+
+extern "C" int b200attn_kv_seq_shrink(b200attn_kv_pool p, int slot, int new_len) {
+    B2_CHECK_ARG(p, "kv_seq_shrink: null pool");
+    B2_CHECK_ARG(slot >= 0 && slot < p->cfg.max_seqs && p->slot_used[slot], "kv_seq_shrink: slot %d is not allocated", slot);
+    B2_CHECK_ARG(new_len >= 0, "kv_seq_shrink: negative length");
+    B2_TRY(p->sync_lens());
+    // every layer's length drops to new_len (layers that hold fewer tokens keep theirs); a longer new_len changes nothing
+    bool changed = false;
+    for (int l = 0; l < p->cfg.num_layers; ++l) {
+        int& len = p->h_lens[(size_t)l * p->cfg.max_seqs + slot];
+        if (new_len < len) {
+            len = new_len;
+            changed = true;
+            B2_CUDA(cudaMemcpy(p->d_lens + (size_t)l * p->cfg.max_seqs + slot, &len, sizeof(int), cudaMemcpyHostToDevice));
+        }
+    }
+    if (!changed) return 0;
+    // pages past the new end go back to the pool; like the reference, a sequence keeps at least one page
+    auto& pages = p->seq_pages[slot];
+    const int keep = std::max(1, ceil_div(new_len, kPageTokens));
+    while ((int)pages.size() > keep) {
+        p->free_pages.push_back(pages.back());
+        pages.pop_back();
+    }
+    p->h_capacity[slot] = (int)pages.size() * kPageTokens;
     return pool_push_tables(p, slot);
 }
 

@@ -57,28 +57,71 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
     const int s_first = row_seq[row_begin], s_last = row_seq[row_begin + n - 1];
     float4 x[kConvRun + 3];  // the window: x[i] = input at (first row of the run) - 3 + i
     LaSeqMeta sm = seqs[s_first];
-    if (s_first == s_last) {
+    if (s_first == s_last && n == kConvRun) {
         const int t0 = row_begin - sm.row0;             // index of the run's first row inside this call's chunk of the sequence
         const float* st = conv_state_layer + (size_t)sm.slot * conv_stride_slot;
 #pragma unroll
         for (int i = 0; i < kConvRun + 3; ++i) {
             const int tt = t0 - 3 + i;
-            if (i < n + 3) {
-                const float* src = (tt >= 0) ? mixed + (size_t)(sm.row0 + tt) * kLaProjCols + ch
-                                             : st + (size_t)(tt + 3) * kLaConvDim + ch;
-                x[i] = *reinterpret_cast<const float4*>(src);
-            }
+            const float* src = (tt >= 0) ? mixed + (size_t)(sm.row0 + tt) * kLaProjCols + ch
+                                         : st + (size_t)(tt + 3) * kLaConvDim + ch;
+            x[i] = *reinterpret_cast<const float4*>(src);
         }
     }
+    // conv + SiLU of this lane's four channels for one row, from the four taps oldest .. newest
+    auto conv_row = [&](const float4& x0, const float4& x1, const float4& x2, const float4& x3, float (&res)[4]) {
+        const float a0[4] = {x0.x, x0.y, x0.z, x0.w}, a1[4] = {x1.x, x1.y, x1.z, x1.w};
+        const float a2[4] = {x2.x, x2.y, x2.z, x2.w}, a3[4] = {x3.x, x3.y, x3.z, x3.w};
 #pragma unroll
-    for (int j = 0; j < kConvRun; ++j) {
-        if (j >= n) break;
-        const int row = row_begin + j;
-        float4 x0, x1, x2, x3;
-        if (s_first == s_last) {
-            x0 = x[j]; x1 = x[j + 1]; x2 = x[j + 2]; x3 = x[j + 3];
-        } else {
-            // the run crosses into another sequence (a length that is not a multiple of the run): fetch the four taps per row
+        for (int i = 0; i < 4; ++i) {
+            float s2 = w[i].w * a3[i];
+            s2 += w[i].x * a2[i];
+            s2 += w[i].y * a1[i];
+            s2 += w[i].z * a0[i];
+            res[i] = silu_fast(s2);
+        }
+    };
+    auto store_row = [&](int row, const float (&res)[4], float ss_total) {
+        const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
+        if (part == 2) {
+            *reinterpret_cast<float4*>(v_out + o) = make_float4(res[0], res[1], res[2], res[3]);
+            return;
+        }
+        const float inv = ((part == 0) ? q_scale : 1.0f) / sqrtf(ss_total + 1e-6f);     // one division per row, not per channel
+        const float4 r4 = make_float4(res[0] * inv, res[1] * inv, res[2] * inv, res[3] * inv);
+        float* o32 = (part == 0) ? q_out : k_out;
+        __half* o16 = (part == 0) ? qh_out : kh_out;
+        if (o32) *reinterpret_cast<float4*>(o32 + o) = r4;
+        if (o16) {
+            __half2 a = __floats2half2_rn(r4.x, r4.y), b = __floats2half2_rn(r4.z, r4.w);
+            *reinterpret_cast<uint2*>(o16 + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+        }
+    };
+    if (s_first == s_last && n == kConvRun) {
+        // whole run inside one sequence: straight-line code, eight rows at a time so that the eight row-norm reductions
+        // (five shuffle steps each) interleave instead of forming eight serial chains
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            float res[8][4], ss[8];
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) {
+                const int j = half * 8 + jj;
+                conv_row(x[j], x[j + 1], x[j + 2], x[j + 3], res[jj]);
+                ss[jj] = res[jj][0] * res[jj][0] + res[jj][1] * res[jj][1] + res[jj][2] * res[jj][2] + res[jj][3] * res[jj][3];
+            }
+            if (part != 2) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                    for (int jj = 0; jj < 8; ++jj) ss[jj] += __shfl_xor_sync(0xffffffffu, ss[jj], off);
+            }
+#pragma unroll
+            for (int jj = 0; jj < 8; ++jj) store_row(row_begin + half * 8 + jj, res[jj], ss[jj]);
+        }
+    } else {
+        for (int j = 0; j < n; ++j) {
+            // short run or a run that crosses into another sequence (a length that is not a multiple of the run): four taps per row
+            const int row = row_begin + j;
             sm = seqs[row_seq[row]];
             const int t = row - sm.row0;
             const float* st = conv_state_layer + (size_t)sm.slot * conv_stride_slot;
@@ -90,34 +133,11 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
                                              : st + (size_t)(tt + 3) * kLaConvDim + ch;
                 xs[b] = *reinterpret_cast<const float4*>(src);
             }
-            x0 = xs[0]; x1 = xs[1]; x2 = xs[2]; x3 = xs[3];
-        }
-        const float a0[4] = {x0.x, x0.y, x0.z, x0.w}, a1[4] = {x1.x, x1.y, x1.z, x1.w};
-        const float a2[4] = {x2.x, x2.y, x2.z, x2.w}, a3[4] = {x3.x, x3.y, x3.z, x3.w};
-        float res[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float s2 = w[i].w * a3[i];
-            s2 += w[i].x * a2[i];
-            s2 += w[i].y * a1[i];
-            s2 += w[i].z * a0[i];
-            res[i] = silu_fast(s2);
-        }
-        const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
-        if (part == 2) {
-            *reinterpret_cast<float4*>(v_out + o) = make_float4(res[0], res[1], res[2], res[3]);
-        } else {
+            float res[4];
+            conv_row(xs[0], xs[1], xs[2], xs[3], res);
             float ss = res[0] * res[0] + res[1] * res[1] + res[2] * res[2] + res[3] * res[3];
-            ss = sqrtf(warp_sum_f(ss) + 1e-6f);
-            const float inv = ((part == 0) ? q_scale : 1.0f) / ss;     // one division per row instead of one per channel
-            const float4 r4 = make_float4(res[0] * inv, res[1] * inv, res[2] * inv, res[3] * inv);
-            float* o32 = (part == 0) ? q_out : k_out;
-            __half* o16 = (part == 0) ? qh_out : kh_out;
-            if (o32) *reinterpret_cast<float4*>(o32 + o) = r4;
-            if (o16) {
-                __half2 a = __floats2half2_rn(r4.x, r4.y), b = __floats2half2_rn(r4.z, r4.w);
-                *reinterpret_cast<uint2*>(o16 + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
-            }
+            if (part != 2) ss = warp_sum_f(ss);
+            store_row(row, res, ss);
         }
     }
     if (part == 2 && lane < n) {      // beta and log-decay of the run's rows, one row per lane

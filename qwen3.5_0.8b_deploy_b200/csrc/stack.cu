@@ -512,6 +512,8 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
             pending = std::min(kMaxSplits, gemm_tc_splits(kHidden, inter, 64));
             B2_TRY(gemm_tc_store(s, st->d_act, st->d_wdown[i], st->d_partials, rows, kHidden, inter, kHidden, pending, pstride, st->d_error));
         } else {
+            // (the tcgen05 gate/up GEMM with the SwiGLU in its epilogue was measured here as well: 2.39 ms per decode step
+            // against 2.31 ms for cuBLAS followed by the SwiGLU kernel)
             B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_wgu[i], true, st->d_gu, true, rows, 2 * inter, kHidden));
             const size_t octs = (size_t)rows * inter / 8;
             swiglu_kernel<<<(unsigned)((octs + 255) / 256), 256, 0, s>>>(st->d_gu, inter, octs, st->d_act);

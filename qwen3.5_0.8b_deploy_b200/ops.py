@@ -25,7 +25,7 @@ KV_INT8, KV_FP16 = 0, 1
 ABI_SYMBOLS = [
     "b200attn_last_error", "b200attn_abi_version", "b200attn_launch_count",
     "b200attn_kv_pool_create", "b200attn_kv_pool_destroy", "b200attn_kv_seq_alloc", "b200attn_kv_seq_reserve",
-    "b200attn_kv_seq_free", "b200attn_kv_clear", "b200attn_kv_seq_len", "b200attn_kv_pages", "b200attn_kv_append",
+    "b200attn_kv_seq_free", "b200attn_kv_seq_shrink", "b200attn_kv_clear", "b200attn_kv_seq_len", "b200attn_kv_pages", "b200attn_kv_append",
     "b200attn_kv_export", "b200attn_kv_device_status",
     "b200attn_fa_create", "b200attn_fa_destroy", "b200attn_fa_set_weights", "b200attn_fa_prefill", "b200attn_fa_decode",
     "b200attn_fa_decode_core", "b200attn_fa_decode_core_static", "b200attn_fa_prefill_core",
@@ -181,6 +181,10 @@ class KVCache:
 
     def release_sequence(self, slot: int) -> None:
         _check(_lib.b200attn_kv_seq_free(self.h, C.c_int(slot)))
+
+    def shrink_sequence(self, slot: int, new_len: int) -> None:
+        """PagedKVCache::shrink_sequence: truncate to new_len tokens in every layer, pages behind the end go back to the pool."""
+        _check(_lib.b200attn_kv_seq_shrink(self.h, C.c_int(slot), C.c_int(new_len)))
 
     def clear(self) -> None:
         _check(_lib.b200attn_kv_clear(self.h, _stream()))

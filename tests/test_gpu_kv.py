@@ -99,6 +99,40 @@ def test_page_bookkeeping(ops, cuda):
         kv.length(0, 99)
 
 
+def test_shrink_sequence_truncates_and_returns_pages(ops, cuda, oracle, synth):
+    """PagedKVCache::shrink_sequence semantics (one page is always kept, a longer length is a no-op), and the cache
+    content after a shrink + re-append equals a cache that was filled that way from the start (INT8 codes bit-exact)."""
+    torch = cuda
+    kv = ops.KVCache(2, 2, 512, ops.KV_INT8, num_pages=16)
+    s = kv.allocate_sequence(0)
+    k = torch.from_numpy(synth.normal(71, "k", (200, 512), 1.0)).cuda()
+    v = torch.from_numpy(synth.normal(71, "v", (200, 512), 0.6)).cuda()
+    for layer in range(2):
+        kv.append(layer, [s], [200], k, v)
+    assert kv.pages() == (16, 4) and kv.length(0, s) == 200 and kv.length(1, s) == 200
+    kv.shrink_sequence(s, 300)                      # not shorter: nothing happens
+    assert kv.pages() == (16, 4) and kv.length(0, s) == 200
+    kv.shrink_sequence(s, 70)                       # 2 pages stay
+    assert kv.pages() == (16, 2) and kv.length(0, s) == 70 and kv.length(1, s) == 70
+    kv.append(0, [s], [30], k[100:130], v[100:130])  # positions 70..99 again, with other rows
+    assert kv.length(0, s) == 100 and kv.length(1, s) == 70
+    got = kv.export(0, s)
+    ref = ops.KVCache(1, 1, 512, ops.KV_INT8, num_pages=4)
+    r = ref.allocate_sequence(0)
+    ref.append(0, [r], [70], k[:70], v[:70])
+    ref.append(0, [r], [30], k[100:130], v[100:130])
+    want = ref.export(0, r)
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    kv.shrink_sequence(s, 0)
+    assert kv.pages() == (16, 1) and kv.length(0, s) == 0
+    with pytest.raises(ops.InvalidArgument):
+        kv.shrink_sequence(s, -1)
+    with pytest.raises(ops.InvalidArgument):
+        kv.shrink_sequence(1 - s, 0)               # the other slot was never allocated
+    assert kv.device_status() == 0
+
+
 def test_append_rejects_bad_batches(ops, cuda):
     torch = cuda
     kv = ops.KVCache(1, 2, 64, ops.KV_INT8)
