@@ -117,6 +117,32 @@ rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const f
     if (out_f32) *reinterpret_cast<float4*>(out_f32 + (size_t)row * kHidden + 4 * t) = make_float4(r0, r1, r2, r3);
 }
 
+// The same RMSNorm for many rows without pending partials (prefill): one warp per row, 32 values per lane, four rows per
+// block, so that a pass over 131072 rows is 32768 blocks of useful size instead of 131072 blocks of one float4 per thread.
+__global__ void __launch_bounds__(128)
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int rows, __nv_bfloat16* __restrict__ out_bf16) {
+    const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * kHidden);
+    float4 v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        v[i] = src[32 * i + lane];
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    ss = wsum(ss);
+    const float rms = sqrtf(ss / (float)kHidden + eps);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float4 ww = *reinterpret_cast<const float4*>(w + 4 * (32 * i + lane));
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[i].x / rms * (1.0f + ww.x), v[i].y / rms * (1.0f + ww.y));
+        __nv_bfloat162 b = __floats2bfloat162_rn(v[i].z / rms * (1.0f + ww.z), v[i].w / rms * (1.0f + ww.w));
+        *reinterpret_cast<uint2*>(out_bf16 + (size_t)row * kHidden + 4 * (32 * i + lane)) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+    }
+}
+
 // act = silu(gate) * up.  gu rows hold tiles of 64 columns: 32 gate columns followed by the 32 matching up columns
 // (the layout the decode-step GEMM epilogue consumes as well).  bf16.
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int inter, size_t n_oct, __nv_bfloat16* __restrict__ act) {
@@ -493,9 +519,13 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
         *pending_out = s_down;
         return 0;
     }
+    const bool many_rows = !decode && rows > 128;      // prefill: no pending partials, warp-per-row norm
     for (int i = 0; i < st->cfg.num_layers; ++i) {
-        launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
-                                                        st->d_partials, pending, pstride);
+        if (many_rows)
+            rmsnorm_rows_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb);
+        else
+            launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
+                       st->d_partials, pending, pstride);
         B2_LAUNCH_CHECK();
         DecodeOut dout{st->d_partials, pstride, 0};
         if (st->layer_kind[i])
@@ -504,8 +534,11 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
         else
             B2_TRY(la_forward_rows(st->la[st->layer_sub[i]], st->state, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots,
                                    decode, st->d_xb, true, st->d_h, 1.0f, tc ? &dout : nullptr, s));
-        launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
-                                                        st->d_partials, dout.n_splits, pstride);
+        if (many_rows)
+            rmsnorm_rows_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb);
+        else
+            launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
+                       st->d_partials, dout.n_splits, pstride);
         B2_LAUNCH_CHECK();
         if (tc) {
             B2_TRY(gemm_tc_swiglu(s, st->d_xb, st->d_wgu[i], st->d_act, rows, 2 * inter, kHidden, st->d_error));

@@ -32,7 +32,7 @@ def test_prefill_and_decode_against_cpu_composition(ops, cuda, oracle, synth, de
     from oracle import cpu_stack
     weights = cpu_stack.make_stack_weights(synth, 61, L, INTER, VOCAB, int8=True)
     qw = cpu_stack.quantized_view(weights)
-    n, T, D = 3, 40, 4
+    n, T, D = 3, 48, 4            # 144 prefill rows: the many-row form of the norm kernel is on the path
     tokens = synth.rng(61, "tokens").integers(0, VOCAB, (n, T)).astype(np.int32)
     st = _build(ops, synth, weights)
     nxt, hid = st.forward_batch_prefill(torch.from_numpy(tokens).cuda(), want_hidden=True)
