@@ -133,6 +133,44 @@ def test_decode_core_against_float64(ops, cuda, oracle, synth, kv_dtype, lengths
             assert err <= 2e-3, f"seq {i} (L={L}) group {g}: max abs err {err:.3e}"
 
 
+@pytest.mark.parametrize("kv_dtype", [0, 1])
+def test_decode_core_full_batch_against_float64(ops, cuda, kv_dtype):
+    """The decode configuration at full size: 128 sequences with ragged caches of 1025 .. 1536 tokens (INT8 and FP16),
+    one decode step, every sequence checked against a float64 softmax over the exported cache contents (so the check
+    does not depend on the append path, which has its own bit-exact tests).  At this size every consumer warp of the
+    persistent kernel works through several (sequence, kv head) pairs and most pairs are split between warps."""
+    torch = cuda
+    n = 128
+    g = torch.Generator(device="cuda").manual_seed(43)
+    lengths = (1025 + torch.randint(0, 512, (n,), generator=g, device="cuda")).tolist()
+    lengths[0], lengths[1], lengths[2] = 1025, 1536, 1088
+    fa = ops.FullAttention(ops.PROJ_FP32, max_batch=n, max_prefill_rows=64)
+    kv = ops.KVCache(1, n, 1536, kv_dtype)
+    slots = [kv.allocate_sequence(0) for _ in range(n)]
+    for s0 in range(0, n, 16):
+        cnt = lengths[s0:s0 + 16]
+        k = torch.randn((sum(cnt), 512), device="cuda", generator=g)
+        v = torch.randn((sum(cnt), 512), device="cuda", generator=g) * 0.6
+        kv.append(0, slots[s0:s0 + 16], cnt, k, v)
+    q = torch.randn((n, 8, 256), device="cuda", generator=g)
+    out = fa.decode_core(q, kv, 0, torch.tensor(slots, dtype=torch.int32, device="cuda"))
+    assert kv.device_status() == 0
+    q64 = q.half().double()
+    worst = 0.0
+    for i in range(n):
+        kc, vc, ksc, vsc = kv.export(0, slots[i])
+        kd, vd = kc.double(), vc.double()
+        if ksc is not None:
+            kd, vd = kd * ksc.double()[..., None], vd * vsc.double()[..., None]
+        assert kd.shape[0] == lengths[i]
+        for grp in range(2):
+            sc = q64[i, 4 * grp:4 * grp + 4] @ kd[:, grp].T / 16.0
+            p = torch.softmax(sc, dim=1)
+            want = p @ vd[:, grp]
+            worst = max(worst, float((out[i, 4 * grp:4 * grp + 4].double() - want).abs().max()))
+    assert worst <= 2e-3, f"max abs err {worst:.3e}"
+
+
 @pytest.mark.parametrize("counts", [[1], [64], [65, 128], [200, 3, 129]])
 def test_prefill_core_against_float64(ops, cuda, synth, counts):
     torch = cuda

@@ -97,6 +97,37 @@ def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel,
     assert not rec0.any()
 
 
+def test_decode_full_batch_against_oracle(ops, cuda, oracle, synth):
+    """The recurrent-decode configuration at full batch: 128 sequences (2048 (sequence, head) units, several waves of
+    CTAs) with seeded states and conv caches, two single-token steps through the whole layer, every sequence against
+    the CPU oracle; states of a sample of sequences at the end."""
+    torch = cuda
+    w = synth.la_weights(58)
+    n, steps = 128, 2
+    la = ops.LinearAttention(ops.PROJ_FP32, max_batch=n, max_prefill_rows=64)
+    la.set_weights(w)
+    st = ops.LinearAttnState(1, n)
+    refs = []
+    for i in range(n):
+        r = oracle.OracleLinearAttention(w)
+        r.recurrent[:] = synth.normal(58, f"state.{i}", (16, 128, 128), 0.05)
+        r.conv_state[:] = synth.normal(58, f"conv.{i}", (6144, 3), 0.5)
+        st.import_state(0, i, torch.from_numpy(r.recurrent).cuda(), torch.from_numpy(r.conv_state).cuda())
+        refs.append(r)
+    d_slots = torch.arange(n, dtype=torch.int32, device="cuda")
+    for t in range(steps):
+        x = synth.hidden_states(58, f"step.{t}", n)
+        got = la.forward(torch.from_numpy(x).cuda(), st, 0, d_slots).cpu().numpy()
+        want = np.stack([refs[i].forward(x[i]) for i in range(n)])
+        ok, msg = allclose_report(got, want, ATOL, RTOL)
+        assert ok, f"step {t}: {msg}"
+    for i in (0, 1, 63, 64, 127):
+        rec, conv = st.export_state(0, i)
+        assert _rel(rec.cpu().numpy(), refs[i].recurrent) <= STATE_REL
+        np.testing.assert_allclose(conv.cpu().numpy(), refs[i].conv_state, rtol=1e-4, atol=1e-5)
+    assert la.device_status() == 0
+
+
 def test_persistent_decode_kernels_equal_classic_kernel(ops, cuda, synth, monkeypatch):
     """72 sequences x 16 heads = 1152 units on 148 (state ring) or 444 (prefetch) persistent CTAs: every CTA walks
     several units (stage reuse, write-back, refill).  They do the same arithmetic in the same order as the 256-thread
