@@ -64,7 +64,7 @@ __device__ __forceinline__ int find_seq(const int* s_pref, int n_seqs, int x) { 
 // grid (number of SMs).  max_parts = partial slots per (sequence, kv head) in part_o / part_ml (>= 3).
 template <bool kFp16, typename OutT>
 __global__ void __launch_bounds__(DecodeCfg<kFp16>::kThreads, 1)
-fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int n_seqs, int len_add,
+fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int n_seqs,
                        const __half* __restrict__ q, const __half* __restrict__ gate, int max_parts,
                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
                        OutT* __restrict__ out) {
@@ -92,7 +92,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
     for (int i = threadIdx.x; i < n_seqs; i += Cfg::kThreads) {
         const int slot = slots[i];
         int pages = 0;
-        if (slot >= 0 && slot < kv.max_seqs) pages = (kv.lens[layer * kv.max_seqs + slot] + len_add + kPageTokens - 1) / kPageTokens;
+        if (slot >= 0 && slot < kv.max_seqs) pages = (kv.lens[layer * kv.max_seqs + slot] + kPageTokens - 1) / kPageTokens;
         s_pref[i + 1] = pages;
         if (pages == 0 && blockIdx.x == 0 && slot >= 0 && slot < kv.max_seqs)    // no cached token: the output is defined as zero
             for (int idx = 0; idx < kFaHeads * kHeadDim; ++idx) out[(size_t)i * kFaHeads * kHeadDim + idx] = (OutT)0.f;
@@ -201,7 +201,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
         const int seg_pages = s_pref[seq + 1] - s_pref[seq];
         const int seg_begin = 2 * s_pref[seq] + kvh * seg_pages;
         const int n_my = min(x_end, seg_begin + seg_pages) - x;
-        const int L = kv.lens[layer * kv.max_seqs + slots[seq]] + len_add;
+        const int L = kv.lens[layer * kv.max_seqs + slots[seq]];
         // Q^T B-fragments: k-step ks = 4*blk + s covers dims 64*blk + 16*t + 4*s + {0,1 | 2,3}; head = g (< 4).
         uint32_t qf[16][2];
         {
@@ -458,14 +458,10 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
     if (*abort_flag && threadIdx.x == 0) atomicExch(kv.error, 3);
 }
 
-// Partial slots per (sequence, kv head) the kernel may use; callers size part_o / part_ml with it.
-int fa_decode_max_splits(bool, int, int) { return 16; }
-
-// pages_per_warp is unused (ranges are balanced on the device); max_splits = partial slots per pair in the scratch.
-int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, int len_add, const __half* q,
-                     const __half* gate, int pages_per_warp, int max_splits, float* part_o, float* part_ml, int* counters,
+// max_splits = partial slots per (sequence, kv head) pair in part_o / part_ml (kFaDecodeParts in the callers' scratch).
+int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, const __half* q,
+                     const __half* gate, int max_splits, float* part_o, float* part_ml, int* counters,
                      void* out, bool out_bf16, cudaStream_t s) {
-    (void)pages_per_warp;
     B2_CHECK_ARG(n_seqs > 0 && n_seqs <= kDecodeMaxSeqs, "decode attention: %d sequences outside (0, %d]", n_seqs, kDecodeMaxSeqs);
     B2_CHECK_ARG(max_splits >= 3, "decode attention: scratch for %d partials per head group, need >= 3", max_splits);
     static int n_sm = 0;
@@ -483,7 +479,7 @@ int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs
     dim3 grid(n_sm);
 #define FA_DEC_LAUNCH(F16, T)                                                                                          \
     launch_pdl(fa_decode_split_kernel<F16, T>, grid, dim3(DecodeCfg<F16>::kThreads), DecodeCfg<F16>::kSmemBytes, s,    \
-               kv, layer, d_slots, n_seqs, len_add, q, gate, max_splits, part_o, part_ml, counters, (T*)out)
+               kv, layer, d_slots, n_seqs, q, gate, max_splits, part_o, part_ml, counters, (T*)out)
     if (kv.is_fp16) { if (out_bf16) FA_DEC_LAUNCH(true, __nv_bfloat16); else FA_DEC_LAUNCH(true, float); }
     else            { if (out_bf16) FA_DEC_LAUNCH(false, __nv_bfloat16); else FA_DEC_LAUNCH(false, float); }
 #undef FA_DEC_LAUNCH

@@ -70,10 +70,6 @@ extern "C" int b200attn_fa_decode_core_static(b200attn_kv_pool pool, int layer, 
                  "fa_decode_core_static: block table of %d pages per sequence, the built-in scratch is sized for %d",
                  pool->cfg.max_pages_per_seq, kStaticMaxPages);
     const KvView kv = pool->view();
-    int ppw = kv.is_fp16 ? 2 : 1;
-    if (const char* e = std::getenv("B200ATTN_DECODE_PPW")) { const int v = std::atoi(e); if (v > 0) ppw = v; }
-    while (fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw) > kStaticMaxSplits) ++ppw;
-    const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
     unsigned char* base = nullptr;
     B2_TRY(static_scratch_ptr(&base));
     __half* q16 = reinterpret_cast<__half*>(base);
@@ -83,5 +79,5 @@ extern "C" int b200attn_fa_decode_core_static(b200attn_kv_pool pool, int layer, 
     cudaStream_t s = as_stream(stream);
     B2_CUDA(cudaMemsetAsync(counters, 0, kStaticCounterBytes, s));
     B2_TRY(f32_to_f16(s, d_q, q16, (size_t)n_seqs * kFaHeads * kHeadDim));
-    return launch_fa_decode(kv, layer, d_slots, n_seqs, 0, q16, nullptr, ppw, splits, part_o, part_ml, counters, d_out, false, s);
+    return launch_fa_decode(kv, layer, d_slots, n_seqs, q16, nullptr, kStaticMaxSplits, part_o, part_ml, counters, d_out, false, s);
 }

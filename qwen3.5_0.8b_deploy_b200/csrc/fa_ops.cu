@@ -12,7 +12,7 @@
 
 namespace b200 {
 
-constexpr int kMaxSplitsCap = 16;
+constexpr int kMaxSplitsCap = kFaDecodeParts;
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -179,14 +179,6 @@ static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, bool
     return gemm_xwT(s, fa->d_attn, false, fa->d_wo_f32, false, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
 }
 
-static int decode_pages_per_warp(const b200attn_kv_pool pool) {
-    const bool fp16 = pool->cfg.kv_dtype == B200ATTN_KV_FP16;
-    int ppw = fp16 ? 8 : 4;
-    if (const char* e = std::getenv("B200ATTN_DECODE_PPW")) { const int v = std::atoi(e); if (v > 0) ppw = v; }
-    while (fa_decode_max_splits(fp16, pool->cfg.max_pages_per_seq, ppw) > kMaxSplitsCap) ++ppw;
-    return ppw;
-}
-
 // One pass of the layer over a batch of rows.  decode == false: host-described varlen batch (h_slots /
 // h_counts), causal prefill through the tensor-core kernel.  decode == true: one row per sequence, slots
 // on the device, no host synchronisation or allocation (capture-safe).  d_y = beta * d_y + attn W_o^T.
@@ -203,8 +195,6 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
     if (decode) {
         B2_CHECK_ARG(d_slots_in, "fa_decode: null slots");
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= fa->cfg.max_batch, "fa_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, fa->cfg.max_batch);
-        const int ppw = decode_pages_per_warp(pool);
-        const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
         if (!core_only) B2_TRY(fa_project_in(fa, d_x, x_is_bf16, n_seqs, true, pool->d_error, s));
         // q / gate epilogue, append of the new token's K and V, and the length increment in one launch; the attention
         // kernel then sees the new length already
@@ -212,7 +202,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
                                     fa->d_gate, s));
         {
             ProfScope prof(PROF_FA_DECODE, s);
-            B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, 0, fa->d_q, fa->d_gate, ppw, splits, fa->d_part_o,
+            B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, fa->d_q, fa->d_gate, kMaxSplitsCap, fa->d_part_o,
                                     fa->d_part_ml, fa->d_counters, fa->d_attn, bf16, s));
         }
         if (!core_only) B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
@@ -253,14 +243,13 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
     B2_CUDA(cudaMemcpyAsync(d_ptiles, ptiles.data(), ptiles.size() * sizeof(PrefillTile), cudaMemcpyHostToDevice, s));
 
     B2_TRY(fa_project_in(fa, d_x, x_is_bf16, rows, false, pool->d_error, s));
-    B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, rows, fa->d_qnorm, fa->d_inv_freq, d_row_pos, nullptr, nullptr, kv.max_seqs,
-                                fa->d_q, fa->d_gate, s));
+    B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, rows, fa->d_qnorm, fa->d_inv_freq, d_row_pos, fa->d_q, fa->d_gate, s));
     for (int i = 0; i < n_seqs; ++i)
         B2_TRY(launch_kv_stage_gather(kv, layer, h_slots[i], base[i], ctx0[i], fa->d_kstage, fa->d_vstage, s));
     {
         ProfScope prof(PROF_KV_APPEND, s);
         B2_TRY(launch_kv_append(kv, layer, d_atiles, (int)atiles.size(), d_slots, k_in, kFaQkvCols, v_in, kFaQkvCols, true,
-                                fa->d_knorm, fa->d_inv_freq, fa->d_kstage, fa->d_vstage, d_ctx0, false, s));
+                                fa->d_knorm, fa->d_inv_freq, fa->d_kstage, fa->d_vstage, d_ctx0, s));
     }
     {
         ProfScope prof(PROF_FA_PREFILL, s);
@@ -292,11 +281,9 @@ extern "C" int b200attn_fa_decode_core(b200attn_fa fa, b200attn_kv_pool pool, in
     B2_CHECK_ARG(n_seqs > 0 && n_seqs <= fa->cfg.max_batch, "fa_decode_core: n_seqs %d outside (0, max_batch %d]", n_seqs, fa->cfg.max_batch);
     cudaStream_t s = as_stream(stream);
     const KvView kv = pool->view();
-    const int ppw = decode_pages_per_warp(pool);
-    const int splits = fa_decode_max_splits(kv.is_fp16, pool->cfg.max_pages_per_seq, ppw);
     B2_TRY(f32_to_f16(s, d_q, fa->d_q, (size_t)n_seqs * kFaHeads * kHeadDim));
     ProfScope prof(PROF_FA_DECODE, s);
-    return launch_fa_decode(kv, layer, d_slots, n_seqs, 0, fa->d_q, nullptr, ppw, splits, fa->d_part_o, fa->d_part_ml, fa->d_counters,
+    return launch_fa_decode(kv, layer, d_slots, n_seqs, fa->d_q, nullptr, kMaxSplitsCap, fa->d_part_o, fa->d_part_ml, fa->d_counters,
                             d_out, false, s);
 }
 

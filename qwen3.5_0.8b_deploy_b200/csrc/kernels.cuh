@@ -17,13 +17,12 @@ struct AppendTile {  // the tokens of one sequence that land in one cache page
 int launch_kv_append(const KvView& kv, int layer, const AppendTile* d_tiles, int n_tiles, const int* d_slots,
                      const float* kin, int k_stride, const float* vin, int v_stride, bool do_norm_rope,
                      const float* k_norm_w, const float* inv_freq, __half* kstage, __half* vstage,
-                     const int* d_stage_row0, bool decode_mode, cudaStream_t s);
+                     const int* d_stage_row0, cudaStream_t s);
 int launch_fa_decode_pre(const KvView& kv, int layer, const int* d_slots, int n_seqs, const float* qkv_raw, const float* q_norm_w,
                          const float* k_norm_w, const float* inv_freq, __half* q_out, __half* gate_out, cudaStream_t s);
 int launch_kv_advance(const KvView& kv, int layer, const int* d_slots, const int* d_counts, int n_seqs, cudaStream_t s);
 int launch_fa_q_epilogue(const float* qkv_raw, int rows, const float* q_norm_w, const float* inv_freq,
-                         const int* d_row_pos, const int* d_slots, const int* d_lens_layer, int max_seqs, __half* q_out,
-                         __half* gate_out, cudaStream_t s);
+                         const int* d_row_pos, __half* q_out, __half* gate_out, cudaStream_t s);
 int launch_kv_stage_gather(const KvView& kv, int layer, int slot, int base, int stage_row0, __half* kstage,
                            __half* vstage, cudaStream_t s);
 void build_append_tiles(const std::vector<int>& base, const int* h_counts, int n_seqs, std::vector<AppendTile>& tiles);
@@ -32,9 +31,9 @@ int pool_prepare_append(b200attn_kv_pool p, int layer, const int* h_slots, const
 int ensure_meta(int** d_meta, int* cap, int need);
 
 // ---- decode attention (fa_decode.cu) -----------------------------------------------------------------------
-int fa_decode_max_splits(bool fp16, int max_pages_per_seq, int pages_per_warp);
-int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, int len_add, const __half* q,
-                     const __half* gate, int pages_per_warp, int max_splits, float* part_o, float* part_ml, int* counters,
+constexpr int kFaDecodeParts = 16;      // partial slots per (sequence, kv head) pair the decode kernel may use; sizes part_o / part_ml
+int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, const __half* q,
+                     const __half* gate, int max_splits, float* part_o, float* part_ml, int* counters,
                      void* out, bool out_bf16, cudaStream_t s);
 
 // ---- prefill attention (fa_prefill.cu) -----------------------------------------------------------------------

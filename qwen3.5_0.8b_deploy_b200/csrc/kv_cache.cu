@@ -75,34 +75,23 @@ __device__ __forceinline__ float quantize8(const float (&x)[8], int (&code)[8]) 
 
 // grid (n_tiles, kv_heads), block 256.
 // Input rows: K from kin[row*k_stride + kvh*256 ..], V from vin[row*v_stride + kvh*256 ..].
-// decode_mode: tile i is sequence i with one token at position lens[slot]; tiles == nullptr.
 template <bool kFp16>
 __global__ void __launch_bounds__(256)
 kv_append_kernel(KvView kv, int layer, const AppendTile* __restrict__ tiles, const int* __restrict__ slots,
                  const float* __restrict__ kin, int k_stride, const float* __restrict__ vin, int v_stride,
                  int do_norm_rope, const float* __restrict__ k_norm_w, const float* __restrict__ inv_freq,
-                 __half* __restrict__ kstage, __half* __restrict__ vstage, const int* __restrict__ stage_row0,
-                 int decode_mode) {
+                 __half* __restrict__ kstage, __half* __restrict__ vstage, const int* __restrict__ stage_row0) {
     using VT = typename std::conditional<kFp16, __half, int8_t>::type;
     __shared__ __align__(16) VT sV[kHeadDim][kPageTokens + (kFp16 ? 8 : 16)];
     const int kvh = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_enter();
-    AppendTile tile;
-    if (decode_mode) {
-        tile.seq = blockIdx.x;
-        tile.first_row = blockIdx.x;
-        tile.ntok = 1;
-        tile.first_pos = 0;
-    } else {
-        tile = tiles[blockIdx.x];
-    }
+    const AppendTile tile = tiles[blockIdx.x];
     const int slot = slots[tile.seq];
     if (slot < 0 || slot >= kv.max_seqs) {
         if (threadIdx.x == 0) atomicExch(kv.error, 1);
         return;
     }
-    if (decode_mode) tile.first_pos = kv.lens[layer * kv.max_seqs + slot];
     if (tile.first_pos + tile.ntok > kv.capacity[slot]) {
         if (threadIdx.x == 0) atomicExch(kv.error, 2);   // page not reserved: skip the write
         return;
@@ -186,24 +175,17 @@ __global__ void kv_advance_kernel(KvView kv, int layer, const int* __restrict__ 
 // Q / gate epilogue of the fused qkv projection: one warp per (row, q head).
 // qkv_raw row layout: head h -> [h*512, h*512+256) q, [h*512+256, h*512+512) gate
 // (language_full_attn.cpp:133-140).  Writes q (normalised, rotated) and sigmoid(gate) as half.
-// pos: row_pos[row] if given, else lens[layer][slots[row]] (decode: row == sequence).
+// pos = row_pos[row].  (The decode step does this work inside fa_decode_pre_kernel.)
 __global__ void __launch_bounds__(128)
 fa_q_epilogue_kernel(const float* __restrict__ qkv_raw, int rows, const float* __restrict__ q_norm_w,
                      const float* __restrict__ inv_freq, const int* __restrict__ row_pos,
-                     const int* __restrict__ slots, const int* __restrict__ lens_layer, int max_seqs,
                      __half* __restrict__ q_out, __half* __restrict__ gate_out) {
     pdl_enter();
     const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (gw >= rows * kFaHeads) return;
     const int row = gw / kFaHeads, h = gw % kFaHeads;
-    int pos;
-    if (row_pos) {
-        pos = row_pos[row];
-    } else {
-        const int slot = slots[row];
-        pos = (slot >= 0 && slot < max_seqs) ? lens_layer[slot] : 0;
-    }
+    const int pos = row_pos[row];
     const float* src = qkv_raw + (size_t)row * kFaQkvCols + h * 2 * kHeadDim + 8 * lane;
     float x[8], g[8];
     load8(src, x);
@@ -224,7 +206,7 @@ fa_q_epilogue_kernel(const float* __restrict__ qkv_raw, int rows, const float* _
 // twelve warps = 8 q heads (norm, RoPE, gate: fa_q_epilogue_kernel's work), 2 K heads and 2 V heads of the new token
 // (norm / RoPE / quantise-on-append: kv_append_kernel's work for one token), then the sequence's length on this layer
 // goes up by one (kv_advance_kernel's work) -- after every warp of the CTA has read the old length, and no other CTA
-// touches this sequence.  The attention kernel that follows therefore runs with len_add = 0.
+// touches this sequence.  The attention kernel that follows therefore sees the new length.
 template <bool kFp16>
 __global__ void __launch_bounds__(384)
 fa_decode_pre_kernel(KvView kv, int layer, const int* __restrict__ slots, const float* __restrict__ qkv_raw,
@@ -347,15 +329,15 @@ __global__ void kv_stage_gather_kernel(KvView kv, int layer, int slot, int base,
 int launch_kv_append(const KvView& kv, int layer, const AppendTile* d_tiles, int n_tiles, const int* d_slots,
                      const float* kin, int k_stride, const float* vin, int v_stride, bool do_norm_rope,
                      const float* k_norm_w, const float* inv_freq, __half* kstage, __half* vstage,
-                     const int* d_stage_row0, bool decode_mode, cudaStream_t s) {
+                     const int* d_stage_row0, cudaStream_t s) {
     if (n_tiles <= 0) return 0;
     dim3 grid(n_tiles, kFaKvHeads);
     if (kv.is_fp16)
         launch_pdl(kv_append_kernel<true>, grid, dim3(256), 0, s, kv, layer, d_tiles, d_slots, kin, k_stride, vin, v_stride,
-                   do_norm_rope, k_norm_w, inv_freq, kstage, vstage, d_stage_row0, decode_mode);
+                   do_norm_rope, k_norm_w, inv_freq, kstage, vstage, d_stage_row0);
     else
         launch_pdl(kv_append_kernel<false>, grid, dim3(256), 0, s, kv, layer, d_tiles, d_slots, kin, k_stride, vin, v_stride,
-                   do_norm_rope, k_norm_w, inv_freq, kstage, vstage, d_stage_row0, decode_mode);
+                   do_norm_rope, k_norm_w, inv_freq, kstage, vstage, d_stage_row0);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -380,11 +362,10 @@ int launch_kv_advance(const KvView& kv, int layer, const int* d_slots, const int
 }
 
 int launch_fa_q_epilogue(const float* qkv_raw, int rows, const float* q_norm_w, const float* inv_freq,
-                         const int* d_row_pos, const int* d_slots, const int* d_lens_layer, int max_seqs,
-                         __half* q_out, __half* gate_out, cudaStream_t s) {
+                         const int* d_row_pos, __half* q_out, __half* gate_out, cudaStream_t s) {
     const int warps = rows * kFaHeads;
     launch_pdl(fa_q_epilogue_kernel, dim3(ceil_div(warps, 4)), dim3(128), 0, s, qkv_raw, rows, q_norm_w, inv_freq, d_row_pos,
-               d_slots, d_lens_layer, max_seqs, q_out, gate_out);
+               q_out, gate_out);
     B2_LAUNCH_CHECK();
     return 0;
 }
@@ -675,7 +656,7 @@ extern "C" int b200attn_kv_append(b200attn_kv_pool p, int layer, const int* h_sl
     B2_CUDA(cudaStreamSynchronize(s));   // host vectors go out of scope
     const int w = kFaKvHeads * kHeadDim;
     B2_TRY(launch_kv_append(p->view(), layer, d_tiles, (int)tiles.size(), d_slots, d_k, w, d_v, w, false, nullptr,
-                            nullptr, nullptr, nullptr, nullptr, false, s));
+                            nullptr, nullptr, nullptr, nullptr, s));
     B2_TRY(launch_kv_advance(p->view(), layer, d_slots, d_counts, n_seqs, s));
     for (int i = 0; i < n_seqs; ++i) p->h_lens[(size_t)layer * p->cfg.max_seqs + h_slots[i]] += h_counts[i];
     return 0;
