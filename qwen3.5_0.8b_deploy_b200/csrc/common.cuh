@@ -106,6 +106,9 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 int gemm_xwT(cudaStream_t stream, const void* X, bool x_bf16, const void* W, bool w_bf16, void* Y,
              bool y_bf16, int rows, int out, int in, float beta = 0.f);
 int cublas_init();   // creates the per-process handle and its capture-safe workspace
+constexpr int kGemmLanes = 4;
+int cublas_init_lanes(int n);      // handles 0..n-1, one per concurrent stream of GEMMs
+void gemm_set_lane(int lane);      // handle the calling thread's next gemm_xwT calls use
 
 // ---- small elementwise helpers (elementwise.cu) ----------------------------------------------------
 int f32_to_bf16(cudaStream_t s, const float* in, __nv_bfloat16* out, size_t n);

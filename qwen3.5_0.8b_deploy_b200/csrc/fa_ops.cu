@@ -28,7 +28,6 @@ size_t fa_scratch_bytes(const b200attn_fa_config& c) {
     n += align_up(B * kFaKvHeads * kMaxSplitsCap * 4 * kHeadDim * 4, 256);   // part_o
     n += align_up(B * kFaKvHeads * kMaxSplitsCap * 4 * 2 * 4, 256);          // part_ml
     n += align_up((4 * R + 65536) * 4, 256);                // meta
-    n += align_up(B * kFaKvHeads * 4, 256);                 // split arrival counters
     return n;
 }
 
@@ -50,7 +49,6 @@ void fa_carve_scratch(b200attn_fa fa) {
     fa->d_part_ml = (float*)take(B * kFaKvHeads * kMaxSplitsCap * 4 * 2 * 4);
     fa->meta_cap = (int)(4 * R + 65536);
     fa->d_meta = (int*)take((size_t)fa->meta_cap * 4);
-    fa->d_counters = (int*)take(B * kFaKvHeads * 4);
     fa->max_splits = kMaxSplitsCap;
 }
 
@@ -79,7 +77,11 @@ int fa_create_internal(const b200attn_fa_config* cfg, const Scratch* shared, b20
         fa->scratch.owned = true;
     }
     fa_carve_scratch(fa);
-    if (cudaMemset(fa->d_counters, 0, (size_t)cfg->max_batch * kFaKvHeads * 4) != cudaSuccess) {
+    // The arrival counters must read zero at every launch, so they are an allocation of their own: operators of one stack
+    // overlay their working buffers on one scratch area, and counters inside it would be overwritten by another
+    // operator's data.
+    if (cudaMalloc(&fa->d_counters, (size_t)cfg->max_batch * kFaKvHeads * 4) != cudaSuccess ||
+        cudaMemset(fa->d_counters, 0, (size_t)cfg->max_batch * kFaKvHeads * 4) != cudaSuccess) {
         b200attn_fa_destroy(fa);
         B2_FAIL(B200ATTN_ERR_CUDA, "fa_create: clearing the split counters failed");
     }
@@ -109,6 +111,7 @@ extern "C" int b200attn_fa_destroy(b200attn_fa fa) {
     cudaFree(fa->d_wqkv_f32); cudaFree(fa->d_wqkv_bf16); cudaFree(fa->d_wo_f32); cudaFree(fa->d_wo_bf16);
     cudaFree(fa->d_qnorm); cudaFree(fa->d_knorm); cudaFree(fa->d_inv_freq);
     if (fa->scratch.owned) cudaFree(fa->scratch.base);
+    cudaFree(fa->d_counters);
     delete fa;
     return 0;
 }

@@ -45,39 +45,53 @@ void prof_end(ProfKind k, cudaStream_t s) {
     g_prof[k].open = nullptr;
 }
 
-static cublasHandle_t g_handle = nullptr;
-static void* g_workspace = nullptr;
-static constexpr size_t kWorkspaceBytes = 64ull << 20;
+// One handle per lane, each with its own fixed workspace: GEMMs issued on different lanes may run at the same time
+// (the decode step's branches), and two cuBLAS kernels must never share split-K workspace.  Lane 0 serves everything else.
+static cublasHandle_t g_handle[kGemmLanes] = {};
+static void* g_workspace[kGemmLanes] = {};
+static constexpr size_t kWorkspaceBytes = 64ull << 20, kLaneWorkspaceBytes = 16ull << 20;
 static std::mutex g_mu;
+thread_local int g_gemm_lane = 0;
 
-int cublas_init() {
+void gemm_set_lane(int lane) { g_gemm_lane = (lane >= 0 && lane < kGemmLanes) ? lane : 0; }
+
+static int cublas_init_lane(int lane) {
     std::lock_guard<std::mutex> lk(g_mu);
-    if (g_handle) return 0;
-    cublasStatus_t st = cublasCreate(&g_handle);
+    if (g_handle[lane]) return 0;
+    cublasStatus_t st = cublasCreate(&g_handle[lane]);
     if (st != CUBLAS_STATUS_SUCCESS) {
-        g_handle = nullptr;
+        g_handle[lane] = nullptr;
         B2_FAIL(B200ATTN_ERR_CUDA, "cublasCreate failed with status %d", (int)st);
     }
-    B2_CUDA(cudaMalloc(&g_workspace, kWorkspaceBytes));
+    const size_t bytes = lane == 0 ? kWorkspaceBytes : kLaneWorkspaceBytes;
+    B2_CUDA(cudaMalloc(&g_workspace[lane], bytes));
     // A fixed workspace keeps cuBLAS from allocating inside stream capture.
-    st = cublasSetWorkspace(g_handle, g_workspace, kWorkspaceBytes);
+    st = cublasSetWorkspace(g_handle[lane], g_workspace[lane], bytes);
     if (st != CUBLAS_STATUS_SUCCESS) B2_FAIL(B200ATTN_ERR_CUDA, "cublasSetWorkspace failed with status %d", (int)st);
-    cublasSetMathMode(g_handle, CUBLAS_DEFAULT_MATH);
+    cublasSetMathMode(g_handle[lane], CUBLAS_DEFAULT_MATH);
+    return 0;
+}
+
+int cublas_init() { return cublas_init_lane(0); }
+int cublas_init_lanes(int n) {
+    for (int i = 0; i < n && i < kGemmLanes; ++i) B2_TRY(cublas_init_lane(i));
     return 0;
 }
 
 int gemm_xwT(cudaStream_t stream, const void* X, bool x_bf16, const void* W, bool w_bf16, void* Y, bool y_bf16, int rows,
              int out, int in, float beta) {
     if (rows <= 0) return 0;
-    B2_TRY(cublas_init());
+    const int lane = g_gemm_lane;
+    B2_TRY(cublas_init_lane(lane));
+    cublasHandle_t handle = g_handle[lane];
     if (x_bf16 != w_bf16) B2_FAIL(B200ATTN_ERR_INVALID, "gemm: activation and weight types must match");
-    cublasStatus_t st = cublasSetStream(g_handle, stream);
+    cublasStatus_t st = cublasSetStream(handle, stream);
     if (st != CUBLAS_STATUS_SUCCESS) B2_FAIL(B200ATTN_ERR_CUDA, "cublasSetStream failed with status %d", (int)st);
     const float alpha = 1.0f;
     const cudaDataType_t in_t = x_bf16 ? CUDA_R_16BF : CUDA_R_32F;
     const cudaDataType_t out_t = y_bf16 ? CUDA_R_16BF : CUDA_R_32F;
     // Row-major Y[rows,out] = X[rows,in] W[out,in]^T  ==  column-major Y^T[out,rows] = W^T(op T) X^T.
-    st = cublasGemmEx(g_handle, CUBLAS_OP_T, CUBLAS_OP_N, out, rows, in, &alpha, W, in_t, in, X, in_t, in, &beta, Y, out_t,
+    st = cublasGemmEx(handle, CUBLAS_OP_T, CUBLAS_OP_N, out, rows, in, &alpha, W, in_t, in, X, in_t, in, &beta, Y, out_t,
                       out, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
     if (st != CUBLAS_STATUS_SUCCESS) B2_FAIL(B200ATTN_ERR_CUDA, "cublasGemmEx(%d,%d,%d) failed with status %d", rows, out, in, (int)st);
     count_launch();

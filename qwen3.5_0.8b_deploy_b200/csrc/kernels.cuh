@@ -129,6 +129,10 @@ size_t fa_scratch_bytes(const b200attn_fa_config& c);
 int fa_create_internal(const b200attn_fa_config* cfg, const Scratch* shared, b200attn_fa* out);
 size_t la_scratch_bytes(const b200attn_la_config& c);
 int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b200attn_la* out);
+// Point the operator's working buffers into its `scratch` (sized by *_scratch_bytes of its cfg).  The stack uses these to
+// make per-branch views of one operator: same weights, different working buffers.
+void fa_carve_scratch(b200attn_fa fa);
+void la_carve_scratch(b200attn_la la);
 // Operator bodies that take activations in the stack's own formats (see stack.cu).
 int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
                     int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y,

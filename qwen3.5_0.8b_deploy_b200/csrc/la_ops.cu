@@ -26,11 +26,10 @@ size_t la_scratch_bytes(const b200attn_la_config& c) {
     n += align_up(R * kHidden * 2, 256);                // xb
     n += align_up(R * kLaHeads * kLaVd * 4, 256);       // gated
     n += align_up((2 * R + 65536) * 4, 256);            // meta
-    n += 256;                                            // device status word
     return n;
 }
 
-static void la_carve_scratch(b200attn_la la) {
+void la_carve_scratch(b200attn_la la) {
     const b200attn_la_config& c = la->cfg;
     const size_t R = (size_t)std::max(c.max_batch, c.max_prefill_rows);
     char* p = la->scratch.base;
@@ -49,7 +48,6 @@ static void la_carve_scratch(b200attn_la la) {
     la->d_gated = take(R * kLaHeads * kLaVd * 4);
     la->meta_cap = (int)(2 * R + 65536);
     la->d_meta = (int*)take((size_t)la->meta_cap * 4);
-    la->d_error = (int*)take(256);
 }
 
 int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b200attn_la* out) {
@@ -76,7 +74,9 @@ int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b20
         la->scratch.owned = true;
     }
     la_carve_scratch(la);
-    if (cudaMemset(la->d_error, 0, sizeof(int)) != cudaSuccess) {
+    // The status word is an allocation of its own: operators of one stack overlay their working buffers on one scratch
+    // area, and a word inside it would be overwritten by another operator's data.
+    if (cudaMalloc(&la->d_error, 256) != cudaSuccess || cudaMemset(la->d_error, 0, 256) != cudaSuccess) {
         b200attn_la_destroy(la);
         B2_FAIL(B200ATTN_ERR_CUDA, "la_create: clearing the status word failed");
     }
@@ -99,6 +99,7 @@ extern "C" int b200attn_la_destroy(b200attn_la la) {
     cudaFree(la->d_win_f32); cudaFree(la->d_win_bf16); cudaFree(la->d_wout_f32); cudaFree(la->d_wout_bf16);
     cudaFree(la->d_conv_w); cudaFree(la->d_a_log); cudaFree(la->d_dt_bias); cudaFree(la->d_norm);
     if (la->scratch.owned) cudaFree(la->scratch.base);
+    cudaFree(la->d_error);
     delete la;
     return 0;
 }

@@ -44,6 +44,15 @@ struct b200attn_stack_s {
     unsigned long long* d_packed = nullptr;   // [128] running argmax words of the LM head
     int* d_error = nullptr;            // device status word of the stack's own tcgen05 GEMMs
     unsigned* d_sync = nullptr;        // [2] grid-barrier words of the decode chain kernel
+    // Decode branches: the step's sequences are cut into up to kMaxBranches groups that walk the layers independently on
+    // streams of their own (branch 0 on the caller's), so one group's dependent chain of small launches fills the gaps of
+    // another's and runs under its bandwidth-bound attention kernels.  Each extra branch has its own operator working
+    // buffers, split counters and cuBLAS lane.
+    static constexpr int kMaxBranches = 4;
+    cudaStream_t br_stream[kMaxBranches - 1] = {};
+    cudaEvent_t ev_fork = nullptr, ev_join[kMaxBranches - 1] = {};
+    b200::Scratch br_fa_scratch[kMaxBranches - 1], br_la_scratch[kMaxBranches - 1];
+    int* br_counters[kMaxBranches - 1] = {};
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
     int graph_nseqs = 0;
@@ -235,6 +244,7 @@ __global__ void quantize_rows_kernel(float* __restrict__ w, int rows, int cols) 
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr int kMaxSplits = 16;
+constexpr int kDefaultDecodeBranches = 1;
 
 // Uploads a host fp32 matrix as bf16, optionally through the INT8 fake quantiser.
 static int upload_matrix(const float* h, int rows, int cols, bool int8, __nv_bfloat16** out) {
@@ -272,6 +282,12 @@ extern "C" int b200attn_stack_destroy(b200attn_stack st) {
     b200attn_kv_pool_destroy(st->pool);
     b200attn_la_state_destroy(st->state);
     cudaFree(st->op_scratch.base);
+    for (int b = 0; b < b200attn_stack_s::kMaxBranches - 1; ++b) {
+        if (st->br_stream[b]) cudaStreamDestroy(st->br_stream[b]);
+        if (st->ev_join[b]) cudaEventDestroy(st->ev_join[b]);
+        cudaFree(st->br_fa_scratch[b].base); cudaFree(st->br_la_scratch[b].base); cudaFree(st->br_counters[b]);
+    }
+    if (st->ev_fork) cudaEventDestroy(st->ev_fork);
     cudaFree(st->d_h); cudaFree(st->d_xb); cudaFree(st->d_gu); cudaFree(st->d_act); cudaFree(st->d_last);
     cudaFree(st->d_logits); cudaFree(st->d_tokens); cudaFree(st->d_slots);
     cudaFree(st->d_partials); cudaFree(st->d_packed); cudaFree(st->d_error); cudaFree(st->d_sync);
@@ -330,6 +346,22 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
             if ((rc = la_create_internal(&lc, &st->op_scratch, &l)) != 0) return fail(rc);
             st->la.push_back(l);
         }
+    }
+    {   // working buffers of the extra decode branches (decode only: one row per sequence)
+        b200attn_fa_config fd = fc; fd.max_prefill_rows = 0;
+        b200attn_la_config ld = lc; ld.max_prefill_rows = 0;
+        ST_CUDA(cudaEventCreateWithFlags(&st->ev_fork, cudaEventDisableTiming));
+        for (int b = 0; b < b200attn_stack_s::kMaxBranches - 1; ++b) {
+            ST_CUDA(cudaStreamCreateWithFlags(&st->br_stream[b], cudaStreamNonBlocking));
+            ST_CUDA(cudaEventCreateWithFlags(&st->ev_join[b], cudaEventDisableTiming));
+            st->br_fa_scratch[b].bytes = fa_scratch_bytes(fd);
+            st->br_la_scratch[b].bytes = la_scratch_bytes(ld);
+            ST_CUDA(cudaMalloc(&st->br_fa_scratch[b].base, st->br_fa_scratch[b].bytes));
+            ST_CUDA(cudaMalloc(&st->br_la_scratch[b].base, st->br_la_scratch[b].bytes));
+            ST_CUDA(cudaMalloc(&st->br_counters[b], (size_t)cfg->max_seqs * kFaKvHeads * 4));
+            ST_CUDA(cudaMemset(st->br_counters[b], 0, (size_t)cfg->max_seqs * kFaKvHeads * 4));
+        }
+        if ((rc = cublas_init_lanes(b200attn_stack_s::kMaxBranches)) != 0) return fail(rc);
     }
     const size_t R = st->max_rows;
     ST_CUDA(cudaMalloc(&st->d_h, R * kHidden * 4));
@@ -467,6 +499,15 @@ static int stack_ready(b200attn_stack st) {
     return 0;
 }
 
+// Number of groups the decode step's sequences are cut into (B200ATTN_DECODE_BRANCHES, read on every call so one process
+// can compare settings); every group keeps at least 16 sequences.
+static int decode_branches(int rows) {
+    const char* e = std::getenv("B200ATTN_DECODE_BRANCHES");
+    int nb = e ? std::atoi(e) : kDefaultDecodeBranches;
+    nb = std::max(1, std::min(nb, (int)b200attn_stack_s::kMaxBranches));
+    return std::max(1, std::min(nb, rows / 16));
+}
+
 // All layers over `rows` rows already embedded in d_h.  Returns through *pending the number of split-K partial
 // matrices of the last output projection that still have to be added to d_h (decode path only).
 static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const int* h_counts, int n_seqs, const int* d_slots,
@@ -518,6 +559,71 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
         }
         *pending_out = s_down;
         return 0;
+    }
+    const int nb = (decode && !tc) ? decode_branches(rows) : 1;
+    if (nb > 1) {
+        // Fork: every extra branch waits for what precedes the layers on the caller's stream (the embedding gather).
+        int r0[b200attn_stack_s::kMaxBranches + 1];
+        for (int b = 0; b <= nb; ++b) r0[b] = (int)((long long)rows * b / nb);
+        B2_CUDA(cudaEventRecord(st->ev_fork, s));
+        for (int b = 1; b < nb; ++b) B2_CUDA(cudaStreamWaitEvent(st->br_stream[b - 1], st->ev_fork, 0));
+        int rc = 0;
+        for (int i = 0; i < st->cfg.num_layers && rc == 0; ++i) {
+            for (int b = 0; b < nb && rc == 0; ++b) {
+                const int n = r0[b + 1] - r0[b];
+                cudaStream_t bs = b ? st->br_stream[b - 1] : s;
+                float* h = st->d_h + (size_t)r0[b] * kHidden;
+                __nv_bfloat16* xb = st->d_xb + (size_t)r0[b] * kHidden;
+                __nv_bfloat16* gu = st->d_gu + (size_t)r0[b] * 2 * inter;
+                __nv_bfloat16* act = st->d_act + (size_t)r0[b] * inter;
+                gemm_set_lane(b);
+                rc = [&]() -> int {
+                    launch_pdl(rmsnorm_kernel, dim3(n), dim3(256), 0, bs, h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, n, xb, nullptr,
+                               st->d_partials, 0, pstride);
+                    B2_LAUNCH_CHECK();
+                    if (st->layer_kind[i]) {
+                        b200attn_fa_s view = *st->fa[st->layer_sub[i]];      // same weights, the branch's working buffers
+                        if (b) {
+                            view.scratch = st->br_fa_scratch[b - 1];
+                            view.cfg.max_prefill_rows = 0;
+                            fa_carve_scratch(&view);
+                            view.d_counters = st->br_counters[b - 1];
+                        }
+                        B2_TRY(fa_forward_rows(&view, st->pool, st->layer_sub[i], nullptr, nullptr, n, d_slots + r0[b], true, xb, true, h,
+                                               1.0f, nullptr, bs));
+                    } else {
+                        b200attn_la_s view = *st->la[st->layer_sub[i]];
+                        if (b) {
+                            view.scratch = st->br_la_scratch[b - 1];
+                            view.cfg.max_prefill_rows = 0;
+                            la_carve_scratch(&view);
+                        }
+                        B2_TRY(la_forward_rows(&view, st->state, st->layer_sub[i], nullptr, nullptr, n, d_slots + r0[b], true, xb, true, h,
+                                               1.0f, nullptr, bs));
+                    }
+                    launch_pdl(rmsnorm_kernel, dim3(n), dim3(256), 0, bs, h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, n, xb, nullptr,
+                               st->d_partials, 0, pstride);
+                    B2_LAUNCH_CHECK();
+                    B2_TRY(gemm_xwT(bs, xb, true, st->d_wgu[i], true, gu, true, n, 2 * inter, kHidden));
+                    const size_t octs = (size_t)n * inter / 8;
+                    swiglu_kernel<<<(unsigned)((octs + 255) / 256), 256, 0, bs>>>(gu, inter, octs, act);
+                    B2_LAUNCH_CHECK();
+                    return gemm_xwT(bs, act, true, st->d_wdown[i], true, h, false, n, kHidden, inter, 1.0f);
+                }();
+            }
+        }
+        gemm_set_lane(0);
+        // Join even after a failed launch, so that a capture in progress can be ended by the caller.
+        for (int b = 1; b < nb; ++b) {
+            cudaError_t e1 = cudaEventRecord(st->ev_join[b - 1], st->br_stream[b - 1]);
+            cudaError_t e2 = cudaStreamWaitEvent(s, st->ev_join[b - 1], 0);
+            if (rc == 0 && (e1 != cudaSuccess || e2 != cudaSuccess)) {
+                set_error("decode branches: join failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+                rc = B200ATTN_ERR_CUDA;
+            }
+        }
+        *pending_out = 0;
+        return rc;
     }
     const bool many_rows = !decode && rows > 128;      // prefill: no pending partials, warp-per-row norm
     for (int i = 0; i < st->cfg.num_layers; ++i) {

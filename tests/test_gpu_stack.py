@@ -126,6 +126,88 @@ def test_plain_stream_order_gives_the_same_tokens(ops, cuda, synth, monkeypatch)
         assert torch.equal(a, b)
 
 
+def test_decode_after_a_prefill_that_fills_the_working_buffers(ops, cuda, oracle, synth):
+    """The operators of one stack overlay their working buffers on one area.  A prefill that uses (nearly) every row of
+    it must leave nothing behind that the decode step depends on: the split counters and status words live outside it.
+    Four pages of context per sequence make the decode attention combine several partials per head."""
+    torch = cuda
+    from oracle import cpu_stack
+    weights = cpu_stack.make_stack_weights(synth, 65, L, INTER, VOCAB, int8=True)
+    qw = cpu_stack.quantized_view(weights)
+    n, T, D = 2, 250, 4
+    tokens_np = synth.rng(65, "tokens").integers(0, VOCAB, (n, T)).astype(np.int32)
+    st = _build(ops, synth, weights, max_seqs=n, max_seq_len=256)      # 2 x 256 rows of working space, 500 used
+    cur = st.forward_batch_prefill(torch.from_numpy(tokens_np).cuda())
+    picks = [cur.cpu().numpy()]
+    for _ in range(D):
+        cur = st.forward_batch_decode(cur)
+        picks.append(cur.cpu().numpy())
+    assert st.device_status() == 0
+    for i in range(n):
+        seq = cpu_stack.OracleStackSequence(qw, T + D + 1, kv_mode=2)
+        for t in range(T):
+            _, logits = seq.forward_token(int(tokens_np[i, t]), want_logits=(t == T - 1))
+        for d in range(D + 1):
+            assert logits[picks[d][i]] >= logits.max() - 0.05 * (logits.max() - logits.mean()), f"seq {i} step {d}"
+            if d < D:
+                _, logits = seq.forward_token(int(picks[d][i]))
+
+
+@pytest.mark.parametrize("branches", ["2", "3"])
+def test_decode_branches_against_single_chain_and_cpu(ops, cuda, oracle, synth, monkeypatch, branches):
+    """B200ATTN_DECODE_BRANCHES cuts the step's sequences into groups that walk the layers on streams of their own.  The
+    groups' GEMMs have fewer rows than the single chain's, so the library may sum in another order: tokens are compared
+    with the single chain by agreement on the first step (identical inputs), exactly between eager launches and the
+    captured graph, and against the CPU composition for one sequence of every group."""
+    torch = cuda
+    from oracle import cpu_stack
+    weights = cpu_stack.make_stack_weights(synth, 64, L, INTER, VOCAB, int8=True)
+    qw = cpu_stack.quantized_view(weights)
+    n, T, D = 48, 24, 3
+    tokens_np = synth.rng(64, "tokens").integers(0, VOCAB, (n, T)).astype(np.int32)
+    tokens = torch.from_numpy(tokens_np).cuda()
+    st = _build(ops, synth, weights, max_seqs=n, max_seq_len=64)
+
+    def eager_run():
+        st.reset_cache()
+        cur = st.forward_batch_prefill(tokens)
+        out = [cur.clone()]
+        for _ in range(D):
+            cur = st.forward_batch_decode(cur)
+            out.append(cur.clone())
+        return out
+
+    monkeypatch.setenv("B200ATTN_DECODE_BRANCHES", "1")
+    single = eager_run()
+    monkeypatch.setenv("B200ATTN_DECODE_BRANCHES", branches)
+    ops.launch_count(reset=True)
+    split = eager_run()
+    assert torch.equal(single[0], split[0])                       # prefill does not branch
+    agree = (single[1] == split[1]).float().mean().item()
+    assert agree >= 0.9, f"first decode step: {agree:.2f} of the tokens agree with the single chain"
+    st.reset_cache()
+    first = st.forward_batch_prefill(tokens)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        st.set_tokens(first)
+        st.capture_decode(n)
+        for d in range(D):
+            st.launch_decode(1)
+            assert torch.equal(st.get_tokens(n), split[d + 1]), f"replayed step {d}"
+        side.synchronize()
+    assert st.device_status() == 0
+    # one sequence of each group (and the last one) against the CPU composition, fed with the GPU's own tokens
+    picks = [s.cpu().numpy() for s in split]
+    for i in sorted({0, n // 2, n - 1}):
+        seq = cpu_stack.OracleStackSequence(qw, T + D + 1, kv_mode=2)
+        for t in range(T):
+            _, logits = seq.forward_token(int(tokens_np[i, t]), want_logits=(t == T - 1))
+        for d in range(D + 1):
+            assert logits[picks[d][i]] >= logits.max() - 0.05 * (logits.max() - logits.mean()), f"seq {i} step {d}"
+            if d < D:
+                _, logits = seq.forward_token(int(picks[d][i]))
+
+
 def test_stack_errors(ops, cuda, synth):
     torch = cuda
     st = ops.HybridStack(num_layers=L, intermediate_size=INTER, vocab_size=VOCAB, max_seqs=2, max_seq_len=64,
