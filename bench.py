@@ -263,7 +263,6 @@ def main():
     stream = torch.cuda.Stream()
     h_tokens = torch.from_numpy(synth.rng(77 + rank, "bench.tokens").integers(0, VOCAB, (B, P)).astype(np.int32)).pin_memory()
     d_tokens = h_tokens.cuda()
-    h_out = torch.empty(B, dtype=torch.int32).pin_memory()
 
     def barrier():
         torch.cuda.synchronize()
@@ -278,18 +277,29 @@ def main():
         st.set_tokens(first)
         st.launch_decode(G)          # G captured decode steps; the cache ends at P + G tokens
 
+    h_ring = [torch.empty(B, dtype=torch.int32).pin_memory() for _ in range(2)]
+    ring_ev = [torch.cuda.Event() for _ in range(2)]
+    e2e_check = [0]
+
     def job_e2e():
-        """Same job through the public API with host buffers: prompt ids H2D, generated ids D2H every step."""
+        """Same job through the public API with host buffers: prompt ids H2D, generated ids D2H every step.  The ids of
+        step i are read on the host while step i + 1 runs (two pinned buffers, one event each), as a serving loop that
+        streams tokens out would do; every step's ids do reach the host inside the timed region."""
+        cur = torch.cuda.current_stream()
         st.reset_cache()
         dev = h_tokens.to("cuda", non_blocking=True)
         first = st.forward_batch_prefill(dev)
         st.set_tokens(first)
-        h_out.copy_(first, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        for _ in range(G):
+        h_ring[0].copy_(first, non_blocking=True)
+        ring_ev[0].record(cur)
+        for i in range(1, G + 1):
             st.launch_decode(1)
-            h_out.copy_(st.get_tokens(B), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            h_ring[i & 1].copy_(st.get_tokens(B), non_blocking=True)
+            ring_ev[i & 1].record(cur)
+            ring_ev[(i - 1) & 1].synchronize()                  # the previous step's ids are on the host now
+            e2e_check[0] ^= int(h_ring[(i - 1) & 1][0])
+        ring_ev[G & 1].synchronize()
+        e2e_check[0] ^= int(h_ring[G & 1][0])
 
     with torch.cuda.stream(stream):
         # one eager pass warms cuBLAS heuristics and kernel attributes, then the decode step is captured once

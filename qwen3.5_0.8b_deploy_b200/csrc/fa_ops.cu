@@ -159,7 +159,7 @@ static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_bf16, int ro
             B2_TRY(f32_to_bf16(s, (const float*)d_x, fa->d_xb, (size_t)rows * kHidden));
             xb = fa->d_xb;
         }
-        if (decode && rows <= 128 && gemm_tc_enabled())   // weight-streaming tcgen05 GEMM
+        if (decode && rows <= 128 && gemm_tc_inproj_enabled())   // weight-streaming tcgen05 GEMM
             return gemm_tc_store(s, (const __nv_bfloat16*)xb, fa->d_wqkv_bf16, fa->d_qkv_raw, rows, kFaQkvCols, kHidden, kFaQkvCols, 1, 0, d_error);
         return gemm_xwT(s, xb, true, fa->d_wqkv_bf16, true, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden);
     }

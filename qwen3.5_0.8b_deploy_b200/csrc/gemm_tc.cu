@@ -261,6 +261,13 @@ bool gemm_tc_enabled() {
     const char* e = std::getenv("B200ATTN_DECODE_GEMM");
     return e && (std::string(e) == "tc" || std::string(e) == "fused");
 }
+// "inproj": only the input projection of each attention layer (the GEMM in front of the attention kernel) runs on the
+// kernel above.  It lets its dependents start early, so the attention kernel that follows is resident and has its
+// state / cache loads in flight while the projection still runs; every other projection stays on cuBLAS.
+bool gemm_tc_inproj_enabled() {
+    const char* e = std::getenv("B200ATTN_DECODE_GEMM");
+    return e && (std::string(e) == "tc" || std::string(e) == "fused" || std::string(e) == "inproj");
+}
 // "fused": additionally, everything between two attention kernels of the decode step runs as one persistent kernel
 // (decode_chain.cu).
 bool gemm_fused_enabled() {

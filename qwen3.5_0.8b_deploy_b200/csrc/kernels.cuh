@@ -80,6 +80,7 @@ int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
 // ---- tcgen05 skinny GEMMs for the decode step (gemm_tc.cu) ---------------------------------------------------------
 int gemm_tc_splits(int N, int K, int bn);
 bool gemm_tc_enabled();
+bool gemm_tc_inproj_enabled();
 bool gemm_fused_enabled();
 int gemm_tc_store(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, float* Y, int M, int N, int K, int ld_out,
                   int splits, size_t split_stride, int* d_error);

@@ -291,7 +291,7 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
         if (bf16) {
             const void* xb = d_x;
             if (!x_is_bf16) { B2_TRY(f32_to_bf16(s, (const float*)d_x, la->d_xb, (size_t)rows * kHidden)); xb = la->d_xb; }
-            if (decode && rows <= 128 && gemm_tc_enabled())   // weight-streaming tcgen05 GEMM
+            if (decode && rows <= 128 && gemm_tc_inproj_enabled())   // weight-streaming tcgen05 GEMM
                 return gemm_tc_store(s, (const __nv_bfloat16*)xb, la->d_win_bf16, la->d_mixed, rows, kLaProjCols, kHidden, kLaProjCols, 1, 0, la->d_error);
             return gemm_xwT(s, xb, true, la->d_win_bf16, true, la->d_mixed, false, rows, kLaProjCols, kHidden);
         }

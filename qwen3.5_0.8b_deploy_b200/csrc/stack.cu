@@ -560,7 +560,7 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
         *pending_out = s_down;
         return 0;
     }
-    const int nb = (decode && !tc) ? decode_branches(rows) : 1;
+    const int nb = (decode && !tc && !gemm_tc_inproj_enabled()) ? decode_branches(rows) : 1;
     if (nb > 1) {
         // Fork: every extra branch waits for what precedes the layers on the caller's stream (the embedding gather).
         int r0[b200attn_stack_s::kMaxBranches + 1];

@@ -18,9 +18,10 @@ def _build(ops, synth, weights, max_seqs=4, max_seq_len=128, kv_dtype=1):
     return st
 
 
-@pytest.fixture(params=["cublas", "tc", "fused"])
+@pytest.fixture(params=["cublas", "inproj", "tc", "fused"])
 def decode_gemm(request, monkeypatch):
-    """Every implementation of the decode-step projections: cuBLAS + separate SwiGLU / argmax kernels, the tcgen05
+    """Every implementation of the decode-step projections: cuBLAS + separate SwiGLU / argmax kernels, cuBLAS with only
+    the input projection of each attention layer on the tcgen05 kernel, the tcgen05
     skinny GEMM with fused epilogues, and the persistent per-layer chain kernel (projections and norms between two
     attention kernels in one cooperative launch).  The library reads the variable on every call."""
     monkeypatch.setenv("B200ATTN_DECODE_GEMM", request.param)
