@@ -584,7 +584,7 @@ la_decode_prefetch_kernel(const float* __restrict__ mixed, const int* __restrict
                           float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
                           size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
                           const float* __restrict__ dt_bias, const float* __restrict__ norm_w, OutT* __restrict__ out,
-                          int* __restrict__ error_word) {
+                          int* __restrict__ error_word, unsigned stagger_ns, unsigned n_sms) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ __align__(16) float s_qkv[3][kLaKd];
     __shared__ __align__(16) float s_part[8][kLaVd];
@@ -592,6 +592,10 @@ la_decode_prefetch_kernel(const float* __restrict__ mixed, const int* __restrict
     __shared__ float s_red[4];
     __shared__ int s_abort;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (stagger_ns && blockIdx.x >= n_sms) {          // same start offset between the CTAs of an SM as in la_decode_kernel
+        const unsigned long long t0 = global_timer_ns(), span = (unsigned long long)(blockIdx.x / n_sms) * stagger_ns;
+        while (global_timer_ns() - t0 < span) __nanosleep(100);
+    }
     const uint32_t full = smem_u32(smem + kLaKd * kLaVd * 4);
     const int n_units = n_seqs * kLaHeads;
     const int n_my = ((int)blockIdx.x < n_units) ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -802,12 +806,14 @@ int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max
             B2_CUDA(cudaFuncSetAttribute(la_decode_prefetch_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1pSmem));
         }
         const dim3 grid(std::min(3 * n_sm_p, n_seqs * kLaHeads));
+        const char* sgp = std::getenv("B200ATTN_LA_DECODE_STAGGER_NS");
+        const unsigned stagger_p = (sgp && (int)grid.x == 3 * n_sm_p) ? (unsigned)std::min(20000, std::max(0, std::atoi(sgp))) : 0u;
         if (out_bf16)
             launch_pdl(la_decode_prefetch_kernel<__nv_bfloat16>, grid, dim3(256), kR1pSmem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
-                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (__nv_bfloat16*)out, d_error);
+                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (__nv_bfloat16*)out, d_error, stagger_p, (unsigned)n_sm_p);
         else
             launch_pdl(la_decode_prefetch_kernel<float>, grid, dim3(256), kR1pSmem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
-                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (float*)out, d_error);
+                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (float*)out, d_error, stagger_p, (unsigned)n_sm_p);
         B2_LAUNCH_CHECK();
         return 0;
     }
