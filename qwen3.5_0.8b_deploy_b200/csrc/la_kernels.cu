@@ -259,7 +259,7 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
                  float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
                  size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
                  const float* __restrict__ dt_bias, const float* __restrict__ norm_w, OutT* __restrict__ out,
-                 unsigned stagger_ns, unsigned n_sms) {
+                 unsigned stagger_ns, unsigned n_sms, unsigned l2_ahead) {
     const int h = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int slot = slots[b];
@@ -288,6 +288,16 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
     const float* Sp = Sg + (size_t)(warp * kRows) * kLaVd + 4 * lane;
 #pragma unroll
     for (int i = 0; i < kRows; ++i) S[i] = __ldcs(reinterpret_cast<const float4*>(Sp + (size_t)i * kLaVd));
+    if (l2_ahead && tid == 0) {
+        // Ask L2 for the state of the unit that will run `l2_ahead` units later (about one wave): its CTA then finds the
+        // state in L2, and HBM keeps streaming while the resident CTAs compute.
+        const unsigned nxt = blockIdx.y * gridDim.x + blockIdx.x + l2_ahead;
+        if (nxt < gridDim.x * gridDim.y) {
+            const int slot2 = slots[nxt / gridDim.x];
+            if (slot2 >= 0 && slot2 < max_seqs)
+                bulk_prefetch_l2(rec_layer + (size_t)slot2 * rec_stride_slot + (size_t)(nxt % gridDim.x) * kLaKd * kLaVd, kLaKd * kLaVd * 4);
+        }
+    }
     // The state was last written by this layer's previous step; everything read below comes from the preceding kernel.
     pdl_enter();
 
@@ -855,8 +865,10 @@ int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max
     const char* sg = std::getenv("B200ATTN_LA_DECODE_STAGGER_NS");
     unsigned stagger_ns = sg ? (unsigned)std::min(20000, std::max(0, std::atoi(sg))) : 2750u;
     if (n_seqs * kLaHeads < 2 * (occ == 3 ? 3 : 2) * n_sm_c) stagger_ns = 0;
+    const char* pf = std::getenv("B200ATTN_LA_DECODE_L2_AHEAD");
+    const unsigned l2_ahead = pf ? (unsigned)std::min(4096, std::max(0, std::atoi(pf))) : 0u;
 #define LA_DEC(T, O, R) launch_pdl(la_decode_kernel<T, O, R>, grid, dim3(32 * 128 / R), 0, s, mixed, d_slots, max_seqs, rec_layer, \
-                                   rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out, stagger_ns, (unsigned)n_sm_c)
+                                   rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out, stagger_ns, (unsigned)n_sm_c, l2_ahead)
     if (out_bf16) { if (occ == 2) LA_DEC(__nv_bfloat16, 2, 16); else if (occ == 3) LA_DEC(__nv_bfloat16, 3, 16); else LA_DEC(__nv_bfloat16, 2, 8); }
     else          { if (occ == 2) LA_DEC(float, 2, 16); else if (occ == 3) LA_DEC(float, 3, 16); else LA_DEC(float, 2, 8); }
 #undef LA_DEC
