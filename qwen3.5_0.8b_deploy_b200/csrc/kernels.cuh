@@ -81,6 +81,7 @@ int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
 int gemm_tc_splits(int N, int K, int bn);
 bool gemm_tc_enabled();
 bool gemm_tc_inproj_enabled();
+int la_decode_l2_ahead();     // look-ahead (in units) of the L2 state prefetch of the DeltaNet decode kernel, 0 = off
 bool gemm_fused_enabled();
 int gemm_tc_store(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, float* Y, int M, int N, int K, int ld_out,
                   int splits, size_t split_stride, int* d_error);
