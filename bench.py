@@ -7,7 +7,8 @@ One "step" = one whole job on one batch: prefill 1024 tokens then greedy-decode 
 sequences per GPU (24 layers = 6 x [3 Gated DeltaNet + 1 gated full attention], INT8-quantised
 weights, FP16 paged KV cache), synthetic token ids, random-init weights.  Sequences are partitioned
 across ranks (one process per GPU, model replicated, no collective on the data path), so N GPUs run
-N x 128 sequences: weak scaling.  Rank 0 prints ONE JSON line.
+N x 128 sequences: weak scaling.  The same line also carries `strong`: one batch of 128 sequences
+partitioned s mod N over the ranks (128 / N per GPU).  Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
 
@@ -50,7 +51,10 @@ def algo_fa_prefill_flops(n_seqs: int, length: int) -> float:
 
 
 def algo_la_prefill_flops(n_seqs: int, length: int) -> float:
-    return n_seqs * 16 * length * 3.0 * 2 * 128 * 128                     # serial recurrence: 3 passes of 128x128 MACs per token-head
+    # chunk-64 gated delta rule, per (chunk, head): five 64x64x128 products (K K^T, Q K^T, T K, T V, A V_new), three
+    # 64x128x128 products (W S, Q S, K^T V_new) and the triangular solve: 11.6 MFLOP
+    per_chunk_head = 5 * 2 * 64 * 64 * 128 + 3 * 2 * 64 * 128 * 128 + 64 ** 3 / 3
+    return n_seqs * 16 * (-(-length // 64)) * per_chunk_head
 
 
 def ncu_traffic(kernel: str, scale: float):
@@ -197,7 +201,7 @@ def run_reference_arm(args):
 
 def workload_config(args) -> dict:
     return dict(workload="24-layer hybrid stack (18 Gated DeltaNet + 6 gated full attention, FFN 3584, vocab 248320, tied "
-                         "embeddings), INT8 per-output-channel weights, FP16 paged KV, greedy decode",
+                         "embeddings), fp16 weights carrying INT8 per-output-channel quantised values, FP16 paged KV, greedy decode",
                 batch_per_gpu=args.batch, prompt_len=args.prompt, gen_len=args.gen,
                 parallelism=f"replica per GPU, sequences partitioned ({args.batch} per GPU)",
                 l2="inputs larger than L2: each decode step streams 4.8 GB of DeltaNet state and the KV cache")
@@ -212,7 +216,6 @@ def prefill_chunk_seqs(args) -> int:
 
 
 def build_stack(ops, synth, args, seed=1234):
-    from oracle import cpu_stack  # weight generator only (numpy); nothing from the checker is executed on the timed path
     st = ops.HybridStack(num_layers=NUM_LAYERS, intermediate_size=INTER, vocab_size=VOCAB, max_seqs=args.batch,
                          max_seq_len=args.prompt + args.gen, prefill_chunk_seqs=prefill_chunk_seqs(args),
                          kv_dtype=ops.KV_FP16, int8_weights=True)
@@ -345,38 +348,43 @@ def main():
         ms_e2e = ev2.elapsed_time(ev3)
 
         # per-kernel device times (rank 0): the prefill kernels in an eager pass (milliseconds each, launch gaps do not
-        # matter), the decode kernels inside a captured decode step with event nodes around them and programmatic
-        # dependent launch off, so that an event pair sees exactly one kernel and no CPU launch gap.
-        prof, phases, timing = {}, {}, ""
+        # matter), the decode kernels inside a captured decode step with event-record nodes around them, so that an
+        # event pair sees exactly one kernel and no CPU launch gap.  The decode attention kernel is read twice: in the
+        # first steps after the prompt (cache length P + 2) and in the middle of the job (P + G / 2).
+        prof, phases, timing, fa_mid = {}, {}, "", None
         if rank == 0:
-            os.environ["B200ATTN_PDL"] = "0"
             st.reset_cache()
             ops.profile_reset(); ops.profile_enable(True)
             first = st.forward_batch_prefill(d_tokens)
-            st.set_tokens(first)
-            st.capture_decode(B)
-            st.launch_decode(8)
             stream.synchronize()
-            ops.profile_enable(False)
-            for name in ("fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append"):
+            for name in ("fa_prefill", "la_prefill", "kv_append"):
                 prof[name] = ops.profile_read(name)
             ops.profile_reset()
-            timing = "event nodes inside the captured decode step"
-            if prof["la_decode"][1] == 0 or prof["fa_decode"][1] == 0:
-                # events recorded by graph nodes gave no time on this driver: eager decode steps instead (the event
-                # pairs then also see the CPU launch gap in front of each kernel)
-                timing = "eager launches"
-                ops.profile_enable(True)
-                cur = first
-                for _ in range(8):
-                    cur = st.forward_batch_decode(cur)
+            st.set_tokens(first)
+            st.capture_decode(B)                       # the captured attention kernels carry time-stamp slots
+            ops.profile_enable(False)
+
+            def read_steps(k):
+                acc = dict(fa_decode=[0.0, 0], la_decode=[0.0, 0])
                 stream.synchronize()
-                ops.profile_enable(False)
-                for name in ("fa_decode", "la_decode", "kv_append"):
-                    prof[name] = ops.profile_read(name)
-                ops.profile_reset()
-            del os.environ["B200ATTN_PDL"]
-            st.capture_decode(B)
+                for name in acc:                       # a read arms the slots again: drop what earlier replays left
+                    ops.profile_read(name)
+                for _ in range(k):
+                    st.launch_decode(1)
+                    stream.synchronize()
+                    for name in acc:
+                        ms, cnt = ops.profile_read(name)
+                        acc[name][0] += ms; acc[name][1] += cnt
+                return {k2: tuple(v) for k2, v in acc.items()}
+            early = read_steps(4)
+            timing = "in-kernel time stamps (first CTA past its dependency wait .. last CTA done) inside the captured decode step, programmatic dependent launch on"
+            if early["la_decode"][1] == 0 or early["fa_decode"][1] == 0:
+                raise RuntimeError("the stamped decode step returned no times")
+            prof.update(early)
+            st.launch_decode(G // 2 - 6)
+            fa_mid = read_steps(4)["fa_decode"]
+            st.capture_decode(B)                       # back to the plain graph before the events go away
+            ops.profile_reset()
             # where the job time goes: prefill pass vs captured decode steps
             job_device()
             ea, eb, ec = (torch.cuda.Event(enable_timing=True) for _ in range(3))
@@ -390,9 +398,46 @@ def main():
             stream.synchronize()
             phases = dict(prefill_ms=ea.elapsed_time(eb), decode_step_ms=eb.elapsed_time(ec) / G)
 
+        # The contract's split of ONE batch: sequence s belongs to rank s mod N, so every rank runs B / N sequences of
+        # the same job (its own pages, states and captured step).  Timed like the headline: max over ranks.
+        strong = None
+        if world > 1:
+            mine = list(replica.partition(B, world, rank))
+            ns = len(mine)
+            d_tok_s = d_tokens[:ns].contiguous()
+
+            def job_strong():
+                st.reset_cache()
+                f = st.forward_batch_prefill(d_tok_s)
+                st.set_tokens(f)
+                st.launch_decode(G)
+            st.reset_cache()
+            f = st.forward_batch_prefill(d_tok_s)
+            st.set_tokens(f)
+            st.capture_decode(ns)
+            job_strong()
+            stream.synchronize()
+            barrier()
+            es = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            es[0].record(stream)
+            job_strong()
+            es[1].record(stream)
+            stream.synchronize()
+            barrier()
+            st.reset_cache()
+            es[2].record(stream)
+            f = st.forward_batch_prefill(d_tok_s)
+            st.set_tokens(f)
+            es[3].record(stream)
+            stream.synchronize()
+            strong = [es[0].elapsed_time(es[1]), es[2].elapsed_time(es[3]), float(ns)]
+
     # NCCL: the only collective of the run, and only on the counters (max of the times, sum of the tokens)
     tokens_per_job = B * (P + G)
-    (ms_total, ms_e2e), (tokens_all,) = replica.reduce_counters([ms_total, ms_e2e], [float(tokens_per_job * args.steps)], "cuda")
+    mx = [ms_total, ms_e2e] + (strong[:2] if strong else [])
+    sm = [float(tokens_per_job * args.steps)] + ([strong[2]] if strong else [])
+    mx, sm = replica.reduce_counters(mx, sm, "cuda")
+    ms_total, ms_e2e, tokens_all = mx[0], mx[1], sm[0]
     value = replica.job_throughput(tokens_all, ms_total)
     e2e_value = replica.job_throughput(tokens_all, ms_e2e)
 
@@ -402,7 +447,7 @@ def main():
         # share of one whole job spent in each kernel class (launch counts of a full job x measured ms per launch)
         job_ms = dict(la_decode=per["la_decode"] * 18 * G, fa_decode=per["fa_decode"] * 6 * G,
                       fa_prefill=prof["fa_prefill"][0], la_prefill=prof["la_prefill"][0])
-        ctx_avg = P + (8 if timing.startswith("event") else 4.5)           # cache length the timed decode launches saw
+        ctx_avg = P + 2.5                                                # cache length the first timed decode launches saw
         seqs_per_chunk = B / max(chunks, 1)
         roof = dict(
             la_decode=dict(bound="hbm", achieved=algo_la_decode_bytes(B) / (per["la_decode"] * 1e-3) / 1e9, peak=peaks["hbm_gbs"], unit="GB/s"),
@@ -416,21 +461,28 @@ def main():
                              la_prefill=seqs_per_chunk * P / (10.0 * 1024))
         for k, r in roof.items():
             r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], timing=(timing if k.endswith("decode") else "eager launches"), job_ms=job_ms[k],
+                     ctx_len=(ctx_avg if k == "fa_decode" else None),
                      traffic=ncu_traffic(k, traffic_scale[k]), traffic_source="ncu capture of the small case in profiles/, scaled by the units one bench launch processes",
                      peak_source=peaks["source"])
         # The same two decode kernels timed as back-to-back launches on caches of their own (no event pair per launch, no
         # neighbours): what the kernel itself does, next to what it does inside the step.
+        if fa_mid and fa_mid[1]:
+            ms_mid, ctx_mid = fa_mid[0] / fa_mid[1], P + G // 2
+            a_mid = algo_fa_decode_bytes(B, ctx_mid, True) / (ms_mid * 1e-3) / 1e9
+            roof["fa_decode"]["mid_job"] = dict(ctx_len=ctx_mid, ms_per_launch=ms_mid, achieved=a_mid, frac=a_mid / peaks["hbm_gbs"], timing=timing)
+        extra = []
         try:
-            import importlib.util
-            spec = importlib.util.spec_from_file_location("b200_kernel_bench", os.path.join(ROOT, "qwen3.5_0.8b_deploy_b200", "kernel_bench.py"))
-            kb = importlib.util.module_from_spec(spec)
-            spec.loader.exec_module(kb)
+            import kernel_bench as kb
             with torch.cuda.stream(stream):
                 iso = dict(la_decode=kb.measure("la_decode", seqs=B, layers=4, iters=40),
-                           fa_decode=kb.measure("fa_decode", seqs=B, ctx=int(ctx_avg), kv="fp16", layers=2, iters=40))
+                           fa_decode=kb.measure("fa_decode", seqs=B, ctx=P + G // 2, kv="fp16", layers=2, iters=40))
+                i8 = kb.measure("fa_decode", seqs=B, ctx=P + G // 2, kv="int8", layers=2, iters=40)
             for k, m in iso.items():
-                roof[k]["isolated"] = dict(ms_per_launch=m["ms"], achieved=m["achieved"], frac=m["frac"],
+                roof[k]["isolated"] = dict(ms_per_launch=m["ms"], achieved=m["achieved"], frac=m["frac"], ctx_len=m.get("ctx"),
                                            note="back-to-back launches through the core entry" + ("; includes its query-conversion launch" if k == "fa_decode" else ""))
+            extra.append(dict(kernel="fa_decode_int8", bound="hbm", achieved=i8["achieved"], peak=peaks["hbm_gbs"], unit="GB/s", frac=i8["achieved"] / peaks["hbm_gbs"],
+                              ms_per_launch=i8["ms"], ctx_len=P + G // 2, timing="back-to-back launches through the core entry on an INT8 cache "
+                              "(includes its query-conversion launch); the job itself runs the FP16 cache", traffic=None, peak_source=peaks["source"]))
         except Exception as e:          # the job's own numbers stand without it
             roof["la_decode"]["isolated"] = dict(error=str(e)[:200])
         dominant = max(job_ms, key=job_ms.get)
@@ -439,11 +491,16 @@ def main():
             arm = CpuArm(args.cpu_prompt, args.cpu_gen, os.cpu_count() or 1)
             cpu = dict(value=arm.step(), unit=UNIT, cores=arm.threads, kind=arm.kind, sample=arm.sample)
         line = dict(metric=METRIC, value=value, unit=UNIT, n_gpus=world, steps=args.steps, warmup=args.warmup,
-                    ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+                    ms_per_step=ms_total / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="fp16",
                     data="synthetic", config=workload_config(args), clocks=clk,
                     e2e=dict(value=e2e_value, unit=UNIT, h2d_bytes_per_step=B * P * 4, d2h_bytes_per_step=B * G * 4),
-                    gpu_launches=launches, phases=phases, roofline=roof[dominant], roofline_other=[roof[k] for k in roof if k != dominant],
+                    gpu_launches=launches, phases=phases, roofline=roof[dominant], roofline_other=[roof[k] for k in roof if k != dominant] + extra,
                     cpu_baseline=cpu)
+        if strong:
+            ms_job, ms_pre, nseq = mx[2], mx[3], sm[1]
+            line["strong"] = dict(scaling="strong", sequences_total=int(nseq), sequences_per_gpu=int(nseq) // world, tok_s=nseq * (P + G) / (ms_job * 1e-3),
+                                  ms_per_job=ms_job, prefill_ms=ms_pre, decode_step_ms=(ms_job - ms_pre) / G,
+                                  note="one batch of %d sequences partitioned s mod N; max over ranks; speed-up = tok_s / the N = 1 line's value" % int(nseq))
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -44,7 +44,7 @@ typedef enum {
 /* Precision of the projection GEMMs around the attention cores. */
 typedef enum {
     B200ATTN_PROJ_FP32 = 0, /* fp32 weights and activations (parity runs against the fp32 CPU reference) */
-    B200ATTN_PROJ_BF16 = 1  /* bf16 weights and activations, fp32 accumulation (throughput runs)         */
+    B200ATTN_PROJ_FP16 = 1  /* fp16 weights and activations, fp32 accumulation (throughput runs)         */
 } b200attn_proj_precision;
 
 /* Storage type of the paged KV cache. */
@@ -310,8 +310,9 @@ typedef struct {
     int max_seq_len;       /* prompt + generated tokens per sequence */
     int prefill_chunk_seqs; /* sequences per prefill pass (bounds activation scratch) */
     int kv_dtype;          /* b200attn_kv_dtype */
-    int int8_weights;      /* 1: matrices are quantised per output channel to INT8 and the GEMMs use
-                              code*scale (src/backend/cuda/kernels/mlp_cuda.cu:22-39) */
+    int int8_weights;      /* 1: every matrix is quantised per output channel to INT8 codes (scale = absmax/127,
+                              roundf; src/backend/cuda/kernels/mlp_cuda.cu:22-39) and the GEMMs use code*scale,
+                              stored as fp16: the values are the INT8 ones, the bytes streamed are fp16 */
     float rms_eps;         /* 1e-6 */
 } b200attn_stack_config;
 
@@ -349,7 +350,8 @@ int b200attn_stack_reset(b200attn_stack st, b200attn_stream stream);
 /* CudaEngine::forward_batch_prefill (cuda_engine.cu:354-389) for n_seqs sequences of prompt_len
  * tokens each (slots 0..n_seqs-1): d_tokens int32 [n_seqs, prompt_len]; writes the greedy next
  * token of every sequence to d_next int32 [n_seqs].  d_hidden_out (optional) receives the final
- * normalised hidden state of each sequence's last token, fp32 [n_seqs, hidden]. */
+ * normalised hidden state of each sequence's last token, fp32 [n_seqs, hidden].  Asynchronous on `stream` (no
+ * allocation, no host synchronisation); device-side failures show in b200attn_stack_device_status. */
 int b200attn_stack_prefill(b200attn_stack st, int n_seqs, int prompt_len, const int* d_tokens,
                            int* d_next, float* d_hidden_out, b200attn_stream stream);
 /* One decode step for n_seqs sequences, eager: CudaEngine::forward_batch_decode
@@ -374,24 +376,17 @@ long long b200attn_launch_count(int reset);
 
 /* ------------------------------------------------------------------------------------------------
  * Per-kernel device timing (the reference's LatencyStats over cudaEvent pairs,
- * src/backend/cuda/performance_test.cu:60-97, applied per kernel class).  While enabled, every launch
- * of the named kernel classes is bracketed by an event pair on its own stream (do not enable during
- * stream capture).  Names: "fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append".
- * b200attn_profile_read synchronises the device and returns the summed device time and launch count.
+ * src/backend/cuda/performance_test.cu:60-97, applied per kernel class).  While enabled, the prefill kernels and the
+ * append are bracketed by an event pair on their own stream, and every launch of the two decode kernels gets a
+ * device-side stamp slot (first CTA past its dependency wait .. last CTA done, on the GPU's global timer).  Stamps
+ * also work for launches captured by b200attn_decode_graph_capture while profiling is on: every replay fills its
+ * slots again, b200attn_profile_read sums and re-arms them.  Names: "fa_prefill", "fa_decode", "la_prefill",
+ * "la_decode", "kv_append".  b200attn_profile_read synchronises the device and returns the summed device time and
+ * launch count; b200attn_profile_reset forgets all pairs and slots (re-capture a graph that carried stamps).
  * ---------------------------------------------------------------------------------------------- */
 int b200attn_profile_enable(int on);
 int b200attn_profile_reset(void);
 int b200attn_profile_read(const char* name, double* total_ms_out, long long* launches_out);
-
-/* ------------------------------------------------------------------------------------------------
- * Self-test of the tcgen05 / TMA building blocks: D[M,N] = A[M,K] * B^T on one CTA with the
- * operand formats the prefill kernels use.  variant: 0 = fp16 K-major A and B, 1 = fp16 K-major A,
- * MN-major B, 2 = tf32 K-major A and B (3, tf32 with an MN-major B, returns B200ATTN_ERR_UNSUPPORTED).
- * d_a fp32 [128, K], d_b fp32 [N, K] (variants 0, 2) or [K, N] (variant 1), d_d fp32 [128, N]; K a
- * multiple of 64 (fp16) or 32 (tf32), N in {64, 128, 256}.  No reference counterpart.
- * ---------------------------------------------------------------------------------------------- */
-int b200attn_selftest_umma(int variant, int n, int k, const float* d_a, const float* d_b, float* d_d,
-                           b200attn_stream stream);
 
 #ifdef __cplusplus
 }

@@ -1,10 +1,10 @@
 """Times ONE kernel class of the attention path in isolation (CUDA events around the C-ABI `*_core` entry)
 and prints its roofline line.  Sized by flags so the same command serves as a small profiler target:
 
-    python qwen3.5_0.8b_deploy_b200/kernel_bench.py --kernel la_decode  --seqs 128
-    python qwen3.5_0.8b_deploy_b200/kernel_bench.py --kernel fa_decode  --seqs 128 --ctx 1280 --kv fp16
-    python qwen3.5_0.8b_deploy_b200/kernel_bench.py --kernel fa_prefill --seqs 16  --ctx 1024
-    python qwen3.5_0.8b_deploy_b200/kernel_bench.py --kernel la_prefill --seqs 10  --ctx 1024
+    python kernel_bench.py --kernel la_decode  --seqs 128
+    python kernel_bench.py --kernel fa_decode  --seqs 128 --ctx 1280 --kv fp16
+    python kernel_bench.py --kernel fa_prefill --seqs 16  --ctx 1024
+    python kernel_bench.py --kernel la_prefill --seqs 10  --ctx 1024
 
 Inputs are synthetic (unit-RMS q/k, N(0, 0.6) v, decays as in the model) and stay larger than L2 for the
 decode kernels by rotating over `--layers` independent caches.
@@ -19,7 +19,7 @@ import sys
 import numpy as np
 import torch
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
@@ -56,7 +56,7 @@ def measure(kernel: str, seqs: int = 128, ctx: int = 1024, kv: str = "fp16", lay
     out = dict(kernel=args.kernel, seqs=n, ctx=L)
 
     if args.kernel == "la_decode":
-        la = ops.LinearAttention(ops.PROJ_BF16, max_batch=n, max_prefill_rows=64)
+        la = ops.LinearAttention(ops.PROJ_FP16, max_batch=n, max_prefill_rows=64)
         la.set_weights(entry.load_package().synth.la_weights(3))
         st = ops.LinearAttnState(args.layers, n)
         mixed = torch.randn((n, 8224), device="cuda", generator=g) * 0.6
@@ -71,7 +71,7 @@ def measure(kernel: str, seqs: int = 128, ctx: int = 1024, kv: str = "fp16", lay
         out.update(ms=ms, achieved=byts / ms / 1e6, unit="GB/s", peak=hbm, bound="hbm")
     elif args.kernel == "fa_decode":
         fp16 = args.kv == "fp16"
-        fa = ops.FullAttention(ops.PROJ_BF16, max_batch=n, max_prefill_rows=64)
+        fa = ops.FullAttention(ops.PROJ_FP16, max_batch=n, max_prefill_rows=64)
         kv = ops.KVCache(args.layers, n, max(L, 64), ops.KV_FP16 if fp16 else ops.KV_INT8)
         slots = [kv.allocate_sequence(L) for _ in range(n)]
         for layer in range(args.layers):
@@ -95,7 +95,7 @@ def measure(kernel: str, seqs: int = 128, ctx: int = 1024, kv: str = "fp16", lay
         assert kv.device_status() == 0
     elif args.kernel == "fa_prefill":
         rows = n * L
-        fa = ops.FullAttention(ops.PROJ_BF16, max_batch=4, max_prefill_rows=rows)
+        fa = ops.FullAttention(ops.PROJ_FP16, max_batch=4, max_prefill_rows=rows)
         q = torch.randn((rows, 8, 256), device="cuda", generator=g)
         k = torch.randn((rows, 2, 256), device="cuda", generator=g)
         v = torch.randn((rows, 2, 256), device="cuda", generator=g) * 0.6
@@ -105,7 +105,7 @@ def measure(kernel: str, seqs: int = 128, ctx: int = 1024, kv: str = "fp16", lay
                    note="time includes three fp32->fp16 conversion launches and a status read of the core entry")
     else:
         rows = n * L
-        la = ops.LinearAttention(ops.PROJ_BF16, max_batch=4, max_prefill_rows=rows)
+        la = ops.LinearAttention(ops.PROJ_FP16, max_batch=4, max_prefill_rows=rows)
         st = ops.LinearAttnState(1, n)
         q = torch.randn((rows, 16, 128), device="cuda", generator=g)
         q = q / q.norm(dim=-1, keepdim=True) / 128 ** 0.5

@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libb200attn.so")
 OBJ = os.path.join(HERE, "build")
 SOURCES = ["gemm.cu", "kv_cache.cu", "fa_decode.cu", "fa_prefill.cu", "fa_ops.cu", "la_kernels.cu", "la_chunk.cu",
-           "la_ops.cu", "stack.cu", "selftest.cu", "fa_decode_static.cu", "gemm_tc.cu", "decode_chain.cu"]
+           "la_ops.cu", "stack.cu", "fa_decode_static.cu", "gemm_tc.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
          "--expt-relaxed-constexpr", "-Xptxas", "-v"]

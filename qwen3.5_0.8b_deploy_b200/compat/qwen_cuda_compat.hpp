@@ -113,7 +113,7 @@ class CudaLinearAttention {
   protected:
     int hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_;
     b200attn_la op_ = nullptr;
-    int proj_precision_ = B200ATTN_PROJ_BF16;   // the reference rounds these weights to bf16 at load
+    int proj_precision_ = B200ATTN_PROJ_FP16;   // the reference rounds these weights to fp16 at load
 };
 
 // Same operator with fp32 weights and an explicit stream on forward_batch (linear_attention_v2.cuh:10-33).

@@ -1,7 +1,6 @@
 // Shared internals of libb200attn: status plumbing, handle structs, launch counter.
 #pragma once
 
-#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <cublas_v2.h>
@@ -72,18 +71,50 @@ enum ProfKind { PROF_FA_PREFILL = 0, PROF_FA_DECODE, PROF_LA_PREFILL, PROF_LA_DE
 extern bool g_prof_on;
 void prof_begin(ProfKind k, cudaStream_t s);
 void prof_end(ProfKind k, cudaStream_t s);
+// Device-side stamps for kernels that carry a stamp argument (the decode kernels): while profiling is on, every launch
+// gets a two-word slot [first CTA past its dependency wait, last CTA done] in a device buffer; works for eager
+// launches and for launches captured into a graph (every replay overwrites its slots).  nullptr when profiling is off.
+unsigned long long* prof_stamp_slot(ProfKind k);
 struct ProfScope {   // brackets the launches issued during its lifetime when profiling is enabled
     ProfKind k; cudaStream_t s;
     ProfScope(ProfKind kind, cudaStream_t st) : k(kind), s(st) { if (g_prof_on) prof_begin(k, s); }
     ~ProfScope() { if (g_prof_on) prof_end(k, s); }
 };
 
+// ---- process-wide switches -------------------------------------------------------------------------------
+// Read from the environment by refresh_runtime_flags(), which every *_create entry calls: a process picks its variants
+// before it builds its operators, and no launch path touches the environment.
+struct RuntimeFlags {
+    bool pdl = true;                 // B200ATTN_PDL=0: ordinary stream order instead of programmatic dependent launch
+    bool decode_gemm_tc = false;     // B200ATTN_DECODE_GEMM=tc: tcgen05 skinny GEMMs with fused epilogues in the decode step (default: library GEMMs)
+    bool lm_head_cublas = false;     // B200ATTN_LM_HEAD=cublas: library GEMM + argmax kernel instead of the fused epilogue
+    bool la_prefill_serial = false;  // B200ATTN_LA_PREFILL=serial: token-serial fp32 recurrence instead of the chunked tensor-core kernels
+    unsigned la_stagger_ns = 2750;   // B200ATTN_LA_DECODE_STAGGER_NS
+    unsigned la_l2_ahead = 185;      // B200ATTN_LA_DECODE_L2_AHEAD
+};
+extern RuntimeFlags g_flags;
+void refresh_runtime_flags();
+
+// ---- per-device facts and one-time set-up -------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+int device_sm_count(int* out);          // multiprocessor count of the current device (cached per device)
+// Runs `fn` (returning 0 or a status) once per device for the call site that owns `done`: kernel attributes such as the
+// opt-in shared-memory size belong to the device's context, so a second GPU in the same process needs its own call.
+struct PerDeviceOnce { bool done[kMaxDevices] = {}; };
+int per_device_once_begin(PerDeviceOnce& o, int* dev_out, bool* need_out);
+void per_device_once_end(PerDeviceOnce& o, int dev);
+#define B2_PER_DEVICE_ONCE(once, ...)                                   \
+    do {                                                                \
+        int _dev = 0; bool _need = false;                               \
+        B2_TRY(::b200::per_device_once_begin(once, &_dev, &_need));     \
+        if (_need) { __VA_ARGS__; ::b200::per_device_once_end(once, _dev); } \
+    } while (0)
+
 // Launch with the programmatic-stream-serialization attribute: the kernel may become resident while the previous
 // kernel of the stream drains; it must call pdl_wait() before touching anything that kernel produced or still reads.
-// B200ATTN_PDL=0 turns the attribute off (ordinary stream order).
-bool pdl_enabled();
+// `on` = false (or B200ATTN_PDL=0) gives the ordinary stream order.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+inline cudaError_t launch_pdl_if(bool on, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -93,27 +124,31 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = (on && g_flags.pdl) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    return launch_pdl_if(true, kernel, grid, block, smem, s, static_cast<Args&&>(args)...);
 }
 
 inline cudaStream_t as_stream(b200attn_stream s) { return reinterpret_cast<cudaStream_t>(s); }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // ---- GEMM (cuBLAS) --------------------------------------------------------------------------------
-// Y[rows, out] = X[rows, in] * W[out, in]^T, row-major.  x_bf16/w_bf16/y_bf16 select the storage
+// Y[rows, out] = X[rows, in] * W[out, in]^T, row-major.  x_fp16/w_fp16/y_fp16 select the storage
 // types; accumulation is fp32.  fp32 inputs use full fp32 math (no TF32).
-int gemm_xwT(cudaStream_t stream, const void* X, bool x_bf16, const void* W, bool w_bf16, void* Y,
-             bool y_bf16, int rows, int out, int in, float beta = 0.f);
+// Y = alpha * X W^T + beta * Y; ld_out > 0 gives the row pitch of Y (elements) when it is a column block of a wider matrix.
+int gemm_xwT(cudaStream_t stream, const void* X, bool x_fp16, const void* W, bool w_fp16, void* Y,
+             bool y_fp16, int rows, int out, int in, float beta = 0.f, float alpha = 1.f, int ld_out = 0);
 int cublas_init();   // creates the per-process handle and its capture-safe workspace
-constexpr int kGemmLanes = 4;
-int cublas_init_lanes(int n);      // handles 0..n-1, one per concurrent stream of GEMMs
-void gemm_set_lane(int lane);      // handle the calling thread's next gemm_xwT calls use
 
 // ---- small elementwise helpers (elementwise.cu) ----------------------------------------------------
-int f32_to_bf16(cudaStream_t s, const float* in, __nv_bfloat16* out, size_t n);
+int f32_to_f16(cudaStream_t s, const float* in, __half* out, size_t n);
+constexpr float kLoScale = 2048.0f;     // low-order fp16 terms are stored times 2^11 to stay clear of fp16 subnormals
+int f32_split_f16(cudaStream_t s, const float* in, __half* hi, __half* lo, size_t n);   // hi = fp16(x), lo = fp16((x - hi) * kLoScale)
 int upload_f32(const float* h, float** d_out, size_t n);                       // cudaMalloc + H2D
-int upload_bf16_from_f32(const float* h, __nv_bfloat16** d_out, size_t n);      // cudaMalloc + convert
+int upload_f16_from_f32(const float* h, __half** d_out, size_t n);      // cudaMalloc + convert
 
 // ---- paged KV pool ---------------------------------------------------------------------------------
 struct KvView {            // what kernels need, passed by value
@@ -172,9 +207,10 @@ struct b200attn_fa_s {
     b200attn_fa_config cfg{};
     bool ready = false;
     float* d_wqkv_f32 = nullptr;           // [5120, 1024]  (fp32 mode)
-    __nv_bfloat16* d_wqkv_bf16 = nullptr;  //               (bf16 mode)
+    __half* d_wqkv_fp16 = nullptr;  //               (fp16 mode)
+    __half* d_wkv_lo = nullptr;     // [1024, 1024] low-order halves of the K | V rows, times kLoScale (fp16 mode)
     float* d_wo_f32 = nullptr;             // [1024, 2048]
-    __nv_bfloat16* d_wo_bf16 = nullptr;
+    __half* d_wo_fp16 = nullptr;
     float* d_qnorm = nullptr;
     float* d_knorm = nullptr;
     float* d_inv_freq = nullptr;           // [rotary_dim/2]
@@ -186,8 +222,9 @@ struct b200attn_fa_s {
     __half* d_gate = nullptr;              // [max_rows, 8, 256]  sigmoid(gate)
     __half* d_kstage = nullptr;            // [max_rows, 2, 256]
     __half* d_vstage = nullptr;
-    __nv_bfloat16* d_xb = nullptr;         // [max_rows, 1024]
-    void* d_attn = nullptr;                // [max_rows, 2048] fp32 or bf16
+    __half* d_xb = nullptr;         // [max_rows, 1024]
+    __half* d_xlo = nullptr;        // [max_rows, 1024] low-order halves of the activations, times kLoScale
+    void* d_attn = nullptr;                // [max_rows, 2048] fp32 or fp16
     float* d_part_o = nullptr;             // split-KV partials
     float* d_part_ml = nullptr;
     int* d_counters = nullptr;             // split arrival counters [max_batch][kv_heads], zero between launches
@@ -210,9 +247,9 @@ struct b200attn_la_s {
     b200attn_la_config cfg{};
     bool ready = false;
     float* d_win_f32 = nullptr;            // [8224, 1024] rows: qkv | z | a | b
-    __nv_bfloat16* d_win_bf16 = nullptr;
+    __half* d_win_fp16 = nullptr;
     float* d_wout_f32 = nullptr;           // [1024, 2048]
-    __nv_bfloat16* d_wout_bf16 = nullptr;
+    __half* d_wout_fp16 = nullptr;
     float* d_conv_w = nullptr;             // [6144, 4]
     float* d_a_log = nullptr;
     float* d_dt_bias = nullptr;
@@ -229,8 +266,8 @@ struct b200attn_la_s {
     float* d_g = nullptr;                  // [max_rows, 16]
     float* d_beta = nullptr;
     float* d_core = nullptr;               // [max_rows, 16, 128]
-    __nv_bfloat16* d_xb = nullptr;
-    void* d_gated = nullptr;               // [max_rows, 2048] fp32 or bf16
+    __half* d_xb = nullptr;
+    void* d_gated = nullptr;               // [max_rows, 2048] fp32 or fp16
     int* d_meta = nullptr;
     int meta_cap = 0;
 };

@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(DecodeCfg<kFp16>::kThreads, 1)
 fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int n_seqs,
                        const __half* __restrict__ q, const __half* __restrict__ gate, int max_parts,
                        float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ counters,
-                       OutT* __restrict__ out) {
+                       OutT* __restrict__ out, unsigned long long* stamp) {
     using Cfg = DecodeCfg<kFp16>;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_pref[kDecodeMaxSeqs + 1];      // s_pref[i] = pages of the sequences before i
@@ -85,6 +85,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
         mbar_fence_init();
     }
     pdl_enter();
+    stamp_begin(stamp);
     __shared__ int s_stop;
     if (threadIdx.x == 0) s_stop = (*reinterpret_cast<volatile int*>(kv.error) == 3);   // an earlier launch gave up: queue no more bounded waits
 
@@ -444,7 +445,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                     if constexpr (sizeof(OutT) == 4) {
                         *reinterpret_cast<float4*>(out + oo + 4 * k) = make_float4(r0, r1, r2, r3);
                     } else {
-                        __nv_bfloat162 h0 = __floats2bfloat162_rn(r0, r1), h1 = __floats2bfloat162_rn(r2, r3);
+                        __half2 h0 = __floats2half2_rn(r0, r1), h1 = __floats2half2_rn(r2, r3);
                         *reinterpret_cast<uint2*>(out + oo + 4 * k) =
                             make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
                     }
@@ -455,33 +456,31 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
         }   // pairs of this range
     }
     __syncthreads();
+    stamp_end(stamp);
     if (*abort_flag && threadIdx.x == 0) atomicExch(kv.error, 3);
 }
 
 // max_splits = partial slots per (sequence, kv head) pair in part_o / part_ml (kFaDecodeParts in the callers' scratch).
 int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, const __half* q,
                      const __half* gate, int max_splits, float* part_o, float* part_ml, int* counters,
-                     void* out, bool out_bf16, cudaStream_t s) {
+                     void* out, bool out_fp16, cudaStream_t s) {
     B2_CHECK_ARG(n_seqs > 0 && n_seqs <= kDecodeMaxSeqs, "decode attention: %d sequences outside (0, %d]", n_seqs, kDecodeMaxSeqs);
     B2_CHECK_ARG(max_splits >= 3, "decode attention: scratch for %d partials per head group, need >= 3", max_splits);
-    static int n_sm = 0;
-    static bool attr_done = false;
-    if (!attr_done) {
-        int dev = 0;
-        B2_CUDA(cudaGetDevice(&dev));
-        B2_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    int n_sm = 0;
+    B2_TRY(device_sm_count(&n_sm));
+    static PerDeviceOnce once;
+    B2_PER_DEVICE_ONCE(once,
         B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<true, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<true>::kSmemBytes));
-        B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<true, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<true>::kSmemBytes));
+        B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<true, __half>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<true>::kSmemBytes));
         B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<false, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<false>::kSmemBytes));
-        B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<false, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<false>::kSmemBytes));
-        attr_done = true;
-    }
+        B2_CUDA(cudaFuncSetAttribute(fa_decode_split_kernel<false, __half>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<false>::kSmemBytes)));
     dim3 grid(n_sm);
+    unsigned long long* stamp = prof_stamp_slot(PROF_FA_DECODE);
 #define FA_DEC_LAUNCH(F16, T)                                                                                          \
     launch_pdl(fa_decode_split_kernel<F16, T>, grid, dim3(DecodeCfg<F16>::kThreads), DecodeCfg<F16>::kSmemBytes, s,    \
-               kv, layer, d_slots, n_seqs, q, gate, max_splits, part_o, part_ml, counters, (T*)out)
-    if (kv.is_fp16) { if (out_bf16) FA_DEC_LAUNCH(true, __nv_bfloat16); else FA_DEC_LAUNCH(true, float); }
-    else            { if (out_bf16) FA_DEC_LAUNCH(false, __nv_bfloat16); else FA_DEC_LAUNCH(false, float); }
+               kv, layer, d_slots, n_seqs, q, gate, max_splits, part_o, part_ml, counters, (T*)out, stamp)
+    if (kv.is_fp16) { if (out_fp16) FA_DEC_LAUNCH(true, __half); else FA_DEC_LAUNCH(true, float); }
+    else            { if (out_fp16) FA_DEC_LAUNCH(false, __half); else FA_DEC_LAUNCH(false, float); }
 #undef FA_DEC_LAUNCH
     B2_LAUNCH_CHECK();
     return 0;

@@ -36,7 +36,6 @@ constexpr size_t kStaticBytes = kStaticQBytes + kStaticPartOBytes + kStaticPartM
 // In host code this name is only a handle for cudaGetSymbolAddress, never a pointer to hand to a kernel.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
 
-constexpr int kMaxDevices = 64;
 static unsigned char* g_static_ptr[kMaxDevices] = {};
 static std::mutex g_static_mu;
 

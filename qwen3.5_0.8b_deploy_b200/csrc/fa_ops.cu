@@ -6,7 +6,6 @@
 
 #include <algorithm>
 #include <cmath>
-#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -23,7 +22,7 @@ size_t fa_scratch_bytes(const b200attn_fa_config& c) {
     n += align_up(R * kFaQkvCols * 4, 256);                 // qkv_raw
     n += 2 * align_up(R * kFaHeads * kHeadDim * 2, 256);    // q, gate
     n += 2 * align_up(R * kFaKvHeads * kHeadDim * 2, 256);  // kstage, vstage
-    n += align_up(R * kHidden * 2, 256);                    // xb
+    n += 2 * align_up(R * kHidden * 2, 256);                // xb, xlo
     n += align_up(R * kFaHeads * kHeadDim * 4, 256);        // attn
     n += align_up(B * kFaKvHeads * kMaxSplitsCap * 4 * kHeadDim * 4, 256);   // part_o
     n += align_up(B * kFaKvHeads * kMaxSplitsCap * 4 * 2 * 4, 256);          // part_ml
@@ -43,7 +42,8 @@ void fa_carve_scratch(b200attn_fa fa) {
     fa->d_gate = (__half*)take(R * kFaHeads * kHeadDim * 2);
     fa->d_kstage = (__half*)take(R * kFaKvHeads * kHeadDim * 2);
     fa->d_vstage = (__half*)take(R * kFaKvHeads * kHeadDim * 2);
-    fa->d_xb = (__nv_bfloat16*)take(R * kHidden * 2);
+    fa->d_xb = (__half*)take(R * kHidden * 2);
+    fa->d_xlo = (__half*)take(R * kHidden * 2);
     fa->d_attn = take(R * kFaHeads * kHeadDim * 4);
     fa->d_part_o = (float*)take(B * kFaKvHeads * kMaxSplitsCap * 4 * kHeadDim * 4);
     fa->d_part_ml = (float*)take(B * kFaKvHeads * kMaxSplitsCap * 4 * 2 * 4);
@@ -60,8 +60,9 @@ int fa_create_internal(const b200attn_fa_config* cfg, const Scratch* shared, b20
                 "fa_create: kernels are built for hidden=1024, heads=8, kv_heads=2, head_dim=256, rotary_dim=64");
     B2_CHECK_ARG(cfg->hidden_size > 0 && cfg->num_heads > 0 && cfg->num_kv_heads > 0, "All dimensions must be > 0");
     B2_CHECK_ARG(cfg->max_batch > 0 && cfg->max_prefill_rows >= 0, "fa_create: max_batch must be > 0");
-    B2_CHECK_ARG(cfg->proj_precision == B200ATTN_PROJ_FP32 || cfg->proj_precision == B200ATTN_PROJ_BF16,
+    B2_CHECK_ARG(cfg->proj_precision == B200ATTN_PROJ_FP32 || cfg->proj_precision == B200ATTN_PROJ_FP16,
                  "fa_create: bad proj_precision");
+    refresh_runtime_flags();
     auto* fa = new (std::nothrow) b200attn_fa_s();
     if (!fa) B2_FAIL(B200ATTN_ERR_NOMEM, "fa_create: host allocation failed");
     fa->cfg = *cfg;
@@ -108,7 +109,7 @@ extern "C" int b200attn_fa_create(const b200attn_fa_config* cfg, b200attn_fa* ou
 
 extern "C" int b200attn_fa_destroy(b200attn_fa fa) {
     if (!fa) return 0;
-    cudaFree(fa->d_wqkv_f32); cudaFree(fa->d_wqkv_bf16); cudaFree(fa->d_wo_f32); cudaFree(fa->d_wo_bf16);
+    cudaFree(fa->d_wqkv_f32); cudaFree(fa->d_wqkv_fp16); cudaFree(fa->d_wkv_lo); cudaFree(fa->d_wo_f32); cudaFree(fa->d_wo_fp16);
     cudaFree(fa->d_qnorm); cudaFree(fa->d_knorm); cudaFree(fa->d_inv_freq);
     if (fa->scratch.owned) cudaFree(fa->scratch.base);
     cudaFree(fa->d_counters);
@@ -124,15 +125,24 @@ extern "C" int b200attn_fa_set_weights(b200attn_fa fa, const b200attn_fa_weights
     std::memcpy(cat.data(), w->q_proj, nq * 4);
     std::memcpy(cat.data() + nq, w->k_proj, nkv * 4);
     std::memcpy(cat.data() + nq + nkv, w->v_proj, nkv * 4);
-    cudaFree(fa->d_wqkv_f32); cudaFree(fa->d_wqkv_bf16); cudaFree(fa->d_wo_f32); cudaFree(fa->d_wo_bf16);
+    cudaFree(fa->d_wqkv_f32); cudaFree(fa->d_wqkv_fp16); cudaFree(fa->d_wkv_lo); cudaFree(fa->d_wo_f32); cudaFree(fa->d_wo_fp16);
     cudaFree(fa->d_qnorm); cudaFree(fa->d_knorm);
-    fa->d_wqkv_f32 = nullptr; fa->d_wqkv_bf16 = nullptr; fa->d_wo_f32 = nullptr; fa->d_wo_bf16 = nullptr;
+    fa->d_wqkv_f32 = nullptr; fa->d_wqkv_fp16 = nullptr; fa->d_wkv_lo = nullptr; fa->d_wo_f32 = nullptr; fa->d_wo_fp16 = nullptr;
     fa->d_qnorm = nullptr; fa->d_knorm = nullptr;
     fa->ready = false;
     const size_t no = (size_t)kHidden * kFaHeads * kHeadDim;
-    if (fa->cfg.proj_precision == B200ATTN_PROJ_BF16) {
-        B2_TRY(upload_bf16_from_f32(cat.data(), &fa->d_wqkv_bf16, cat.size()));
-        B2_TRY(upload_bf16_from_f32(w->o_proj, &fa->d_wo_bf16, no));
+    if (fa->cfg.proj_precision == B200ATTN_PROJ_FP16) {
+        B2_TRY(upload_f16_from_f32(cat.data(), &fa->d_wqkv_fp16, cat.size()));
+        B2_TRY(upload_f16_from_f32(w->o_proj, &fa->d_wo_fp16, no));
+        // Low-order halves of the K and V rows, w = fp16(w) + lo / kLoScale: an INT8 cache quantises K and V, and a
+        // projection error of 2^-12 would move about one code in two hundred across a rounding boundary (a change of a
+        // whole quantisation step), so for such caches the K / V columns are computed with compensated operands.
+        std::vector<float> lo(2 * nkv);
+        for (size_t i = 0; i < 2 * nkv; ++i) {
+            const float v = cat[nq + i];
+            lo[i] = (v - __half2float(__float2half_rn(v))) * kLoScale;
+        }
+        B2_TRY(upload_f16_from_f32(lo.data(), &fa->d_wkv_lo, lo.size()));
     } else {
         B2_TRY(upload_f32(cat.data(), &fa->d_wqkv_f32, cat.size()));
         B2_TRY(upload_f32(w->o_proj, &fa->d_wo_f32, no));
@@ -152,33 +162,43 @@ static int fa_check(b200attn_fa fa, b200attn_kv_pool pool, int layer) {
     return 0;
 }
 
-static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_bf16, int rows, bool decode, int* d_error, cudaStream_t s) {
-    if (fa->cfg.proj_precision == B200ATTN_PROJ_BF16) {
+static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_fp16, int rows, bool decode, bool kv_int8, int* d_error, cudaStream_t s) {
+    if (fa->cfg.proj_precision == B200ATTN_PROJ_FP16) {
         const void* xb = d_x;
-        if (!x_is_bf16) {
-            B2_TRY(f32_to_bf16(s, (const float*)d_x, fa->d_xb, (size_t)rows * kHidden));
+        const bool compensate = kv_int8 && !x_is_fp16;      // fp32 activations at hand and a quantising cache behind K / V
+        if (!x_is_fp16) {
+            if (compensate) B2_TRY(f32_split_f16(s, (const float*)d_x, fa->d_xb, fa->d_xlo, (size_t)rows * kHidden));
+            else B2_TRY(f32_to_f16(s, (const float*)d_x, fa->d_xb, (size_t)rows * kHidden));
             xb = fa->d_xb;
         }
-        if (decode && rows <= 128 && gemm_tc_inproj_enabled())   // weight-streaming tcgen05 GEMM
-            return gemm_tc_store(s, (const __nv_bfloat16*)xb, fa->d_wqkv_bf16, fa->d_qkv_raw, rows, kFaQkvCols, kHidden, kFaQkvCols, 1, 0, d_error);
-        return gemm_xwT(s, xb, true, fa->d_wqkv_bf16, true, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden);
+        if (decode && rows <= 128 && gemm_tc_enabled() && !compensate)   // weight-streaming tcgen05 GEMM
+            return gemm_tc_store(s, (const __half*)xb, fa->d_wqkv_fp16, fa->d_qkv_raw, rows, kFaQkvCols, kHidden, kFaQkvCols, 1, 0, d_error);
+        B2_TRY(gemm_xwT(s, xb, true, fa->d_wqkv_fp16, true, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden));
+        if (compensate) {
+            // K | V columns += (x_lo W_hi^T + x_hi W_lo^T) / kLoScale
+            const int q_cols = kFaHeads * kHeadDim * 2, kv_cols = 2 * kFaKvHeads * kHeadDim;
+            const __half* w_kv_hi = fa->d_wqkv_fp16 + (size_t)q_cols * kHidden;
+            B2_TRY(gemm_xwT(s, fa->d_xlo, true, w_kv_hi, true, fa->d_qkv_raw + q_cols, false, rows, kv_cols, kHidden, 1.0f, 1.0f / kLoScale, kFaQkvCols));
+            B2_TRY(gemm_xwT(s, xb, true, fa->d_wkv_lo, true, fa->d_qkv_raw + q_cols, false, rows, kv_cols, kHidden, 1.0f, 1.0f / kLoScale, kFaQkvCols));
+        }
+        return 0;
     }
-    if (x_is_bf16) B2_FAIL(B200ATTN_ERR_INVALID, "full attention: bf16 activations need the bf16 projection mode");
+    if (x_is_fp16) B2_FAIL(B200ATTN_ERR_INVALID, "full attention: fp16 activations need the fp16 projection mode");
     return gemm_xwT(s, d_x, false, fa->d_wqkv_f32, false, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden);
 }
 
 static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, bool decode, DecodeOut* dout, int* d_error, cudaStream_t s) {
-    if (fa->cfg.proj_precision == B200ATTN_PROJ_BF16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || beta == 0.f)) {
+    if (fa->cfg.proj_precision == B200ATTN_PROJ_FP16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || beta == 0.f)) {
         const int K = kFaHeads * kHeadDim;
         if (dout) {
             dout->n_splits = gemm_tc_splits(kHidden, K, 64);
-            return gemm_tc_store(s, (const __nv_bfloat16*)fa->d_attn, fa->d_wo_bf16, dout->partials, rows, kHidden, K, kHidden,
+            return gemm_tc_store(s, (const __half*)fa->d_attn, fa->d_wo_fp16, dout->partials, rows, kHidden, K, kHidden,
                                  dout->n_splits, dout->stride, d_error);
         }
-        return gemm_tc_store(s, (const __nv_bfloat16*)fa->d_attn, fa->d_wo_bf16, d_y, rows, kHidden, K, kHidden, 1, 0, d_error);
+        return gemm_tc_store(s, (const __half*)fa->d_attn, fa->d_wo_fp16, d_y, rows, kHidden, K, kHidden, 1, 0, d_error);
     }
-    if (fa->cfg.proj_precision == B200ATTN_PROJ_BF16)
-        return gemm_xwT(s, fa->d_attn, true, fa->d_wo_bf16, true, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
+    if (fa->cfg.proj_precision == B200ATTN_PROJ_FP16)
+        return gemm_xwT(s, fa->d_attn, true, fa->d_wo_fp16, true, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
     return gemm_xwT(s, fa->d_attn, false, fa->d_wo_f32, false, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
 }
 
@@ -186,29 +206,25 @@ static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, bool
 // h_counts), causal prefill through the tensor-core kernel.  decode == true: one row per sequence, slots
 // on the device, no host synchronisation or allocation (capture-safe).  d_y = beta * d_y + attn W_o^T.
 int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
-                    int n_seqs, const int* d_slots_in, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
+                    int n_seqs, const int* d_slots_in, bool decode, const void* d_x, bool x_is_fp16, float* d_y,
                     float y_beta, DecodeOut* dout, cudaStream_t s) {
-    const bool core_only = decode && dout && dout->core_only;
-    B2_CHECK_ARG(pool && (core_only || (d_x && d_y)), "full attention: null argument");
+    B2_CHECK_ARG(pool && d_x && d_y, "full attention: null argument");
     B2_TRY(fa_check(fa, pool, layer));
     const KvView kv = pool->view();
-    const bool bf16 = fa->cfg.proj_precision == B200ATTN_PROJ_BF16;
+    const bool fp16 = fa->cfg.proj_precision == B200ATTN_PROJ_FP16;
     const float* k_in = fa->d_qkv_raw + kFaHeads * kHeadDim * 2;
     const float* v_in = k_in + kFaKvHeads * kHeadDim;
     if (decode) {
         B2_CHECK_ARG(d_slots_in, "fa_decode: null slots");
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= fa->cfg.max_batch, "fa_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, fa->cfg.max_batch);
-        if (!core_only) B2_TRY(fa_project_in(fa, d_x, x_is_bf16, n_seqs, true, pool->d_error, s));
+        B2_TRY(fa_project_in(fa, d_x, x_is_fp16, n_seqs, true, !kv.is_fp16, pool->d_error, s));
         // q / gate epilogue, append of the new token's K and V, and the length increment in one launch; the attention
         // kernel then sees the new length already
         B2_TRY(launch_fa_decode_pre(kv, layer, d_slots_in, n_seqs, fa->d_qkv_raw, fa->d_qnorm, fa->d_knorm, fa->d_inv_freq, fa->d_q,
                                     fa->d_gate, s));
-        {
-            ProfScope prof(PROF_FA_DECODE, s);
-            B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, fa->d_q, fa->d_gate, kMaxSplitsCap, fa->d_part_o,
-                                    fa->d_part_ml, fa->d_counters, fa->d_attn, bf16, s));
-        }
-        if (!core_only) B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
+        B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, fa->d_q, fa->d_gate, kMaxSplitsCap, fa->d_part_o,
+                                fa->d_part_ml, fa->d_counters, fa->d_attn, fp16, s));
+        B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
         pool->lens_dirty = true;
         return 0;
     }
@@ -245,7 +261,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
     B2_CUDA(cudaMemcpyAsync(d_atiles, atiles.data(), atiles.size() * sizeof(AppendTile), cudaMemcpyHostToDevice, s));
     B2_CUDA(cudaMemcpyAsync(d_ptiles, ptiles.data(), ptiles.size() * sizeof(PrefillTile), cudaMemcpyHostToDevice, s));
 
-    B2_TRY(fa_project_in(fa, d_x, x_is_bf16, rows, false, pool->d_error, s));
+    B2_TRY(fa_project_in(fa, d_x, x_is_fp16, rows, false, !kv.is_fp16, pool->d_error, s));
     B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, rows, fa->d_qnorm, fa->d_inv_freq, d_row_pos, fa->d_q, fa->d_gate, s));
     for (int i = 0; i < n_seqs; ++i)
         B2_TRY(launch_kv_stage_gather(kv, layer, h_slots[i], base[i], ctx0[i], fa->d_kstage, fa->d_vstage, s));
@@ -257,7 +273,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
     {
         ProfScope prof(PROF_FA_PREFILL, s);
         B2_TRY(launch_fa_prefill_tc(fa->d_q, rows, fa->d_kstage, fa->d_vstage, ctx_rows, d_ptiles, (int)ptiles.size(),
-                                    fa->d_gate, fa->d_attn, bf16, pool->d_error, s));
+                                    fa->d_gate, fa->d_attn, fp16, pool->d_error, s));
     }
     B2_TRY(launch_kv_advance(kv, layer, d_slots, d_counts, n_seqs, s));
     B2_TRY(fa_project_out(fa, d_y, y_beta, rows, false, nullptr, pool->d_error, s));
@@ -285,7 +301,6 @@ extern "C" int b200attn_fa_decode_core(b200attn_fa fa, b200attn_kv_pool pool, in
     cudaStream_t s = as_stream(stream);
     const KvView kv = pool->view();
     B2_TRY(f32_to_f16(s, d_q, fa->d_q, (size_t)n_seqs * kFaHeads * kHeadDim));
-    ProfScope prof(PROF_FA_DECODE, s);
     return launch_fa_decode(kv, layer, d_slots, n_seqs, fa->d_q, nullptr, kMaxSplitsCap, fa->d_part_o, fa->d_part_ml, fa->d_counters,
                             d_out, false, s);
 }

@@ -315,7 +315,7 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (!mbar_wait_warp(bar(BAR_OF), it & 1, abort_flag)) ok = false;
             tc_fence_after();
             const float inv_l = 1.0f / l;
-            // bf16 output of a full tile leaves through shared memory and two tiled TMA stores per round (the P buffers are
+            // fp16 output of a full tile leaves through shared memory and two tiled TMA stores per round (the P buffers are
             // idle between the last PV product and the next item's first P tile); anything else is stored from registers
             const bool via_tma = (sizeof(OutT) == 2) && (tile.n_rows == kBM);
 #pragma unroll
@@ -342,14 +342,14 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 if constexpr (sizeof(OutT) == 2) {
                     if (via_tma) {
-                        // staging tile of round cc>>1: two boxes [128 rows][64 columns] bf16, 128-byte swizzle
+                        // staging tile of round cc>>1: two boxes [128 rows][64 columns] fp16, 128-byte swizzle
                         const int col = (hf * 2 + (cc & 1)) * 32;              // column inside the round's 128
                         unsigned char* srow = sm + kOffP + (col >> 6) * kPBytes + r * 128;
 #pragma unroll
                         for (int q8 = 0; q8 < 4; ++q8) {
-                            __nv_bfloat162 h[4];
+                            __half2 h[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
                             const int chunk16 = ((col & 63) >> 3) + q8;
                             *reinterpret_cast<uint4*>(srow + ((chunk16 ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(h);
                         }
@@ -357,9 +357,9 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         OutT* dst = out + orow + ch * 32;
 #pragma unroll
                         for (int q8 = 0; q8 < 4; ++q8) {
-                            __nv_bfloat162 h[4];
+                            __half2 h[4];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
+                            for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
                             *reinterpret_cast<uint4*>(dst + 8 * q8) = *reinterpret_cast<uint4*>(h);
                         }
                     }
@@ -456,16 +456,6 @@ fa_prefill_simt_kernel(const __half* __restrict__ q, const __half* __restrict__ 
     }
 }
 
-__global__ void f32_to_f16_kernel(const float* __restrict__ in, __half* __restrict__ out, size_t n) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = __float2half_rn(in[i]);
-}
-int f32_to_f16(cudaStream_t s, const float* in, __half* out, size_t n) {
-    if (n == 0) return 0;
-    f32_to_f16_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(in, out, n);
-    B2_LAUNCH_CHECK();
-    return 0;
-}
 
 // ---- host: tensor maps + launch -------------------------------------------------------------------------------
 int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
@@ -495,7 +485,7 @@ int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const
 
 // q [rows][8][256], kstage/vstage [ctx_rows][2][256] fp16.  d_tiles: device copy of the tile list.
 int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const __half* vstage, int ctx_rows,
-                         const PrefillTile* d_tiles, int n_tiles, const __half* gate, void* out, bool out_bf16,
+                         const PrefillTile* d_tiles, int n_tiles, const __half* gate, void* out, bool out_fp16,
                          int* d_error, cudaStream_t s) {
     if (n_tiles <= 0) return 0;
     CUtensorMap mq, mk, mv;
@@ -512,29 +502,23 @@ int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const 
         B2_TRY(make_tensor_map(&mk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, kstage, dims, str, box));
         B2_TRY(make_tensor_map(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, vstage, dims, str, box));
     }
-    CUtensorMap mo = mq;      // only the bf16 kernel uses it
-    if (out_bf16) {
+    CUtensorMap mo = mq;      // only the fp16 kernel uses it
+    if (out_fp16) {
         const uint64_t dims[3] = {(uint64_t)kHeadDim, (uint64_t)kFaHeads, (uint64_t)rows};
         const uint64_t str[2] = {(uint64_t)kHeadDim * 2, (uint64_t)kFaHeads * kHeadDim * 2};
         const uint32_t box[3] = {64, 1, (uint32_t)kBM};
-        B2_TRY(make_tensor_map(&mo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, out, dims, str, box));
+        B2_TRY(make_tensor_map(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, out, dims, str, box));
     }
-    static bool attr_done = false;
-    if (!attr_done) {
+    static PerDeviceOnce once;
+    B2_PER_DEVICE_ONCE(once,
         B2_CUDA(cudaFuncSetAttribute(fa_prefill_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF1Smem));
-        B2_CUDA(cudaFuncSetAttribute(fa_prefill_tc_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF1Smem));
-        attr_done = true;
-    }
-    static int n_sm = 0;
-    if (n_sm == 0) {
-        int dev = 0;
-        B2_CUDA(cudaGetDevice(&dev));
-        B2_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-    }
+        B2_CUDA(cudaFuncSetAttribute(fa_prefill_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kF1Smem)));
+    int n_sm = 0;
+    B2_TRY(device_sm_count(&n_sm));
     const int n_items = n_tiles * kFaHeads;
     dim3 grid(std::min(n_items, n_sm));
-    if (out_bf16)
-        fa_prefill_tc_kernel<__nv_bfloat16><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, mo, d_tiles, n_items, gate, (__nv_bfloat16*)out, d_error);
+    if (out_fp16)
+        fa_prefill_tc_kernel<__half><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, mo, d_tiles, n_items, gate, (__half*)out, d_error);
     else
         fa_prefill_tc_kernel<float><<<grid, kF1Threads, kF1Smem, s>>>(mq, mk, mv, mo, d_tiles, n_items, gate, (float*)out, d_error);
     B2_LAUNCH_CHECK();
@@ -542,12 +526,12 @@ int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const 
 }
 
 int launch_fa_prefill_simt(const __half* q, const __half* kstage, const __half* vstage, const int* d_row_pos,
-                           const int* d_row_ctx0, int rows, const __half* gate, void* out, bool out_bf16,
+                           const int* d_row_ctx0, int rows, const __half* gate, void* out, bool out_fp16,
                            cudaStream_t s) {
     const int blocks = ceil_div(rows * kFaHeads, 4);
-    if (out_bf16)
-        fa_prefill_simt_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(q, kstage, vstage, d_row_pos, d_row_ctx0, rows, gate,
-                                                                    (__nv_bfloat16*)out);
+    if (out_fp16)
+        fa_prefill_simt_kernel<__half><<<blocks, 128, 0, s>>>(q, kstage, vstage, d_row_pos, d_row_ctx0, rows, gate,
+                                                                    (__half*)out);
     else
         fa_prefill_simt_kernel<float><<<blocks, 128, 0, s>>>(q, kstage, vstage, d_row_pos, d_row_ctx0, rows, gate, (float*)out);
     B2_LAUNCH_CHECK();

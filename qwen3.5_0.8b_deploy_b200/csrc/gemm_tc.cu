@@ -1,18 +1,17 @@
-// Skinny GEMM for the decode step on tcgen05: Y[M <= 128, N] = X[M, K] W[N, K]^T with bf16 operands and fp32
+// Skinny GEMM for the decode step on tcgen05: Y[M <= 128, N] = X[M, K] W[N, K]^T with fp16 operands and fp32
 // accumulation in TMEM.  At 128 rows the projections are pure weight streaming (every weight byte is used once),
 // so the kernel is a TMA -> shared-memory ring -> tcgen05.mma pipeline with one 128 x BN output tile per CTA and
 // optional split-K, sized so a launch puts about one CTA on every SM.  Epilogues:
 //   kEpiStore   fp32 tile store (also used for split-K partials, which the following norm kernel sums);
-//   kEpiSwiglu  the tile holds BN/2 gate columns then the BN/2 matching up columns: act = silu(gate) * up, bf16;
+//   kEpiSwiglu  the tile holds BN/2 gate columns then the BN/2 matching up columns: act = silu(gate) * up, fp16;
 //   kEpiArgmax  running per-row argmax over all tiles (64-bit atomicMax on {ordered value, ~index}).
-// Replaces the reference's thread-per-output projection kernels at decode (linear_proj_bf16_kernel,
+// Replaces the reference's thread-per-output projection kernels at decode (linear_proj_fp16_kernel,
 // src/backend/cuda/kernels/linear_attention_cuda.cu:33-45; fused_q_path_kernel's GEMV loop,
 // full_attention_cuda.cu:31-76; output_proj_kernel :161-172) and the 128 sequential LM-head GEMVs plus host
 // argmax of the benchmark driver (src/backend/cuda/performance_test.cu:313-319).
 #include "kernels.cuh"
 #include "tc05.cuh"
 
-#include <cstdlib>
 #include <map>
 #include <string>
 #include <mutex>
@@ -24,7 +23,7 @@ enum { kEpiStore = 0, kEpiSwiglu = 1, kEpiArgmax = 2 };
 
 template <int BN>
 struct GemmCfg {
-    static constexpr uint32_t kABytes = 128 * 128;          // 128 rows x 64 bf16
+    static constexpr uint32_t kABytes = 128 * 128;          // 128 rows x 64 fp16
     static constexpr uint32_t kBBytes = BN * 128;
     static constexpr uint32_t kStage = kABytes + kBBytes;
     static constexpr int kStages = (8 * kStage <= 200 * 1024) ? 8 : (int)(200 * 1024 / kStage);   // ring depth
@@ -46,7 +45,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(192)
 gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, int M, int N,
                     int k_steps_per_split, int k_steps_total, float* __restrict__ out_f32, int ld_out, size_t split_stride,
-                    __nv_bfloat16* __restrict__ out_bf16, unsigned long long* __restrict__ argmax_out,
+                    __half* __restrict__ out_fp16, unsigned long long* __restrict__ argmax_out,
                     int* __restrict__ error_word) {
     using Cfg = GemmCfg<BN>;
     constexpr int kStages = Cfg::kStages;
@@ -106,7 +105,7 @@ gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     }
     if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(kFmtBF16, 128, BN, 0, 0);
+            constexpr uint32_t idesc = umma_idesc(kFmtF16, 128, BN, 0, 0);
             bool ok = true;
             for (int ks = 0; ks < nk; ++ks) {
                 const int st = ks % kStages;
@@ -155,15 +154,15 @@ gemm_small_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     tmem_ld32(tmem + lane_base + grp * 64 + 32, up);
                     tmem_wait_ld();
                     if (m < M && n0 + grp * 64 < N) {
-                        __nv_bfloat16* dst = out_bf16 + (size_t)m * ld_out + (n0 >> 1) + grp * 32;
+                        __half* dst = out_fp16 + (size_t)m * ld_out + (n0 >> 1) + grp * 32;
 #pragma unroll
                         for (int c8 = 0; c8 < 4; ++c8) {
-                            __nv_bfloat162 h[4];
+                            __half2 h[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const float g0 = __uint_as_float(gt[8 * c8 + 2 * e]), g1 = __uint_as_float(gt[8 * c8 + 2 * e + 1]);
                                 const float u0 = __uint_as_float(up[8 * c8 + 2 * e]), u1 = __uint_as_float(up[8 * c8 + 2 * e + 1]);
-                                h[e] = __floats2bfloat162_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
+                                h[e] = __floats2half2_rn(g0 / (1.0f + expf(-g0)) * u0, g1 / (1.0f + expf(-g1)) * u1);
                             }
                             *reinterpret_cast<uint4*>(dst + 8 * c8) = *reinterpret_cast<uint4*>(h);
                         }
@@ -211,9 +210,9 @@ namespace {
 std::mutex g_map_mu;
 std::map<std::tuple<const void*, int, int, int>, CUtensorMap> g_maps;
 
-// Tensor map of a row-major bf16 matrix [rows, cols] with a {64 cols, box_rows} box (128-byte swizzle); cached per
+// Tensor map of a row-major fp16 matrix [rows, cols] with a {64 cols, box_rows} box (128-byte swizzle); cached per
 // (pointer, shape) since weights and activation buffers keep their addresses.
-int bf16_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+int fp16_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
     std::lock_guard<std::mutex> lk(g_map_mu);
     const auto key = std::make_tuple(ptr, rows, cols, box_rows);
     auto it = g_maps.find(key);
@@ -221,31 +220,28 @@ int bf16_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out
     const uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
     const uint64_t str[1] = {(uint64_t)cols * 2};
     const uint32_t box[2] = {64, (uint32_t)box_rows};
-    B2_TRY(make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, str, box));
+    B2_TRY(make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ptr, dims, str, box));
     g_maps[key] = *out;
     return 0;
 }
 
 template <int BN, int EPI>
 int launch_one(const CUtensorMap& mx, const CUtensorMap& mw, int M, int N, int K, int splits, float* out_f32, int ld_out,
-               size_t split_stride, __nv_bfloat16* out_bf16, unsigned long long* argmax_out, int* d_error, cudaStream_t s) {
-    static bool attr_done = false;
-    if (!attr_done) {
-        B2_CUDA(cudaFuncSetAttribute(gemm_small_m_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmem));
-        attr_done = true;
-    }
+               size_t split_stride, __half* out_fp16, unsigned long long* argmax_out, int* d_error, cudaStream_t s) {
+    static PerDeviceOnce once;
+    B2_PER_DEVICE_ONCE(once, B2_CUDA(cudaFuncSetAttribute(gemm_small_m_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmem)));
     const int k_steps = K / 64;
     const int per = ceil_div(k_steps, splits);
     dim3 grid(ceil_div(N, BN), ceil_div(k_steps, per));
     launch_pdl(gemm_small_m_kernel<BN, EPI>, grid, dim3(192), GemmCfg<BN>::kSmem, s, mx, mw, M, N, per, k_steps, out_f32, ld_out,
-               split_stride, out_bf16, argmax_out, d_error);
+               split_stride, out_fp16, argmax_out, d_error);
     B2_LAUNCH_CHECK();
     return 0;
 }
 }  // namespace
 
 int gemm_tc_map(const void* ptr, int rows, int cols, int box_rows, void* tensor_map_out) {
-    return bf16_map(ptr, rows, cols, box_rows, static_cast<CUtensorMap*>(tensor_map_out));
+    return fp16_map(ptr, rows, cols, box_rows, static_cast<CUtensorMap*>(tensor_map_out));
 }
 
 void gemm_tc_forget(const void* ptr) {     // drop cached maps of a buffer that is being freed
@@ -254,26 +250,9 @@ void gemm_tc_forget(const void* ptr) {     // drop cached maps of a buffer that 
         it = (std::get<0>(it->first) == ptr) ? g_maps.erase(it) : std::next(it);
 }
 
-// B200ATTN_DECODE_GEMM selects the projections of the decode step: "tc" = the kernel above with its fused epilogues,
-// "cublas" (default: measured faster end to end so far) = cuBLAS GEMMs with separate SwiGLU / argmax kernels.  Read on
-// every call so one process can exercise both.
-bool gemm_tc_enabled() {
-    const char* e = std::getenv("B200ATTN_DECODE_GEMM");
-    return e && (std::string(e) == "tc" || std::string(e) == "fused");
-}
-// "inproj": only the input projection of each attention layer (the GEMM in front of the attention kernel) runs on the
-// kernel above.  It lets its dependents start early, so the attention kernel that follows is resident and has its
-// state / cache loads in flight while the projection still runs; every other projection stays on cuBLAS.
-bool gemm_tc_inproj_enabled() {
-    const char* e = std::getenv("B200ATTN_DECODE_GEMM");
-    return e && (std::string(e) == "tc" || std::string(e) == "fused" || std::string(e) == "inproj");
-}
-// "fused": additionally, everything between two attention kernels of the decode step runs as one persistent kernel
-// (decode_chain.cu).
-bool gemm_fused_enabled() {
-    const char* e = std::getenv("B200ATTN_DECODE_GEMM");
-    return e && std::string(e) == "fused";
-}
+// B200ATTN_DECODE_GEMM=tc selects this kernel with its fused epilogues for the projections of the decode step; the
+// default is cuBLAS with separate SwiGLU / argmax kernels.
+bool gemm_tc_enabled() { return g_flags.decode_gemm_tc; }
 
 // Number of split-K slices a [M<=128, N] x K product is cut into when the caller can sum partial tiles.
 int gemm_tc_splits(int N, int K, int bn) {
@@ -284,40 +263,40 @@ int gemm_tc_splits(int N, int K, int bn) {
 }
 
 // Y tile store (fp32).  splits > 1 writes `splits` partial matrices split_stride floats apart.
-int gemm_tc_store(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, float* Y, int M, int N, int K, int ld_out,
+int gemm_tc_store(cudaStream_t s, const __half* X, const __half* W, float* Y, int M, int N, int K, int ld_out,
                   int splits, size_t split_stride, int* d_error) {
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N > 0, "gemm_tc: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
-    B2_TRY(bf16_map(X, M, K, 128, &mx));
+    B2_TRY(fp16_map(X, M, K, 128, &mx));
     // Without split-K every CTA reads all of X from L2, so wide N (the input projections) takes 128-column tiles:
     // half as many CTAs pull the activations, and 40-65 SMs still stream the weights faster than HBM delivers them.
     if (splits <= 1 && N >= 2048) {
-        B2_TRY(bf16_map(W, N, K, 128, &mw));
+        B2_TRY(fp16_map(W, N, K, 128, &mw));
         return launch_one<128, kEpiStore>(mx, mw, M, N, K, 1, Y, ld_out, split_stride, nullptr, nullptr, d_error, s);
     }
-    B2_TRY(bf16_map(W, N, K, 64, &mw));
+    B2_TRY(fp16_map(W, N, K, 64, &mw));
     return launch_one<64, kEpiStore>(mx, mw, M, N, K, splits, Y, ld_out, split_stride, nullptr, nullptr, d_error, s);
 }
 
 // act[M, N/2] = silu(gate) * up with W rows arranged in tiles of 32 gate rows followed by the 32 matching up rows.
-int gemm_tc_swiglu(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, __nv_bfloat16* act, int M, int N, int K,
+int gemm_tc_swiglu(cudaStream_t s, const __half* X, const __half* W, __half* act, int M, int N, int K,
                    int* d_error) {
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N % 64 == 0, "gemm_tc_swiglu: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
-    B2_TRY(bf16_map(X, M, K, 128, &mx));
+    B2_TRY(fp16_map(X, M, K, 128, &mx));
     // 128-column tiles (two gate/up groups): half as many CTAs re-read the activations, and 56 SMs still stream the
     // 14.7 MB of gate/up weights of the model's FFN faster than HBM delivers them
-    B2_TRY(bf16_map(W, N, K, 128, &mw));
+    B2_TRY(fp16_map(W, N, K, 128, &mw));
     return launch_one<128, kEpiSwiglu>(mx, mw, M, N, K, 1, nullptr, N / 2, 0, act, nullptr, d_error, s);
 }
 
 // tokens[m] = argmax_n X[m] . W[n]   (d_packed: M zeroed 64-bit words, left zeroed again).
-int gemm_tc_argmax(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, unsigned long long* d_packed, int* tokens,
+int gemm_tc_argmax(cudaStream_t s, const __half* X, const __half* W, unsigned long long* d_packed, int* tokens,
                    int M, int N, int K, int* d_error) {
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N > 0, "gemm_tc_argmax: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
-    B2_TRY(bf16_map(X, M, K, 128, &mx));
-    B2_TRY(bf16_map(W, N, K, 256, &mw));
+    B2_TRY(fp16_map(X, M, K, 128, &mx));
+    B2_TRY(fp16_map(W, N, K, 256, &mw));
     B2_TRY((launch_one<256, kEpiArgmax>(mx, mw, M, N, K, 1, nullptr, 0, 0, nullptr, d_packed, d_error, s)));
     launch_pdl(argmax_unpack_kernel, dim3(ceil_div(M, 128)), dim3(128), 0, s, d_packed, M, tokens);
     B2_LAUNCH_CHECK();

@@ -34,7 +34,7 @@ int ensure_meta(int** d_meta, int* cap, int need);
 constexpr int kFaDecodeParts = 16;      // partial slots per (sequence, kv head) pair the decode kernel may use; sizes part_o / part_ml
 int launch_fa_decode(const KvView& kv, int layer, const int* d_slots, int n_seqs, const __half* q,
                      const __half* gate, int max_splits, float* part_o, float* part_ml, int* counters,
-                     void* out, bool out_bf16, cudaStream_t s);
+                     void* out, bool out_fp16, cudaStream_t s);
 
 // ---- prefill attention (fa_prefill.cu) -----------------------------------------------------------------------
 struct PrefillTile {
@@ -44,13 +44,12 @@ struct PrefillTile {
     int ctx_row0;  // staging row of the sequence's context position 0
 };
 int launch_fa_prefill_tc(const __half* q, int rows, const __half* kstage, const __half* vstage, int ctx_rows,
-                         const PrefillTile* d_tiles, int n_tiles, const __half* gate, void* out, bool out_bf16,
+                         const PrefillTile* d_tiles, int n_tiles, const __half* gate, void* out, bool out_fp16,
                          int* d_error, cudaStream_t s);
 int launch_fa_prefill_simt(const __half* q, const __half* kstage, const __half* vstage, const int* d_row_pos,
-                           const int* d_row_ctx0, int rows, const __half* gate, void* out, bool out_bf16, cudaStream_t s);
+                           const int* d_row_ctx0, int rows, const __half* gate, void* out, bool out_fp16, cudaStream_t s);
 void build_prefill_tiles(const std::vector<int>& base, const int* counts, const std::vector<int>& ctx0, int n_seqs,
                          std::vector<PrefillTile>& tiles);
-int f32_to_f16(cudaStream_t s, const float* in, __half* out, size_t n);
 
 // ---- Gated DeltaNet (la_kernels.cu, la_chunk.cu) -----------------------------------------------------------------
 struct LaSeqMeta {  // per sequence, device array
@@ -69,61 +68,31 @@ int launch_la_conv_state_update(const float* mixed, const LaSeqMeta* d_seqs, int
 int launch_la_recurrent_serial(const float* q, const float* k, const float* v, const float* g, const float* beta,
                                const LaSeqMeta* d_seqs, int n_seqs, float* rec_layer, size_t rec_stride, float* out,
                                cudaStream_t s);
-int launch_la_gated_norm(const float* core, const float* mixed, const float* norm_w, int rows, void* out, bool out_bf16,
+int launch_la_gated_norm(const float* core, const float* mixed, const float* norm_w, int rows, void* out, bool out_fp16,
                          cudaStream_t s);
 int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max_seqs, float* rec_layer,
                      size_t rec_stride, float* conv_layer, size_t conv_stride, const float* conv_w, const float* a_log,
-                     const float* dt_bias, const float* norm_w, void* out, bool out_bf16, int* d_error, cudaStream_t s);
+                     const float* dt_bias, const float* norm_w, void* out, bool out_fp16, bool early_state_loads, cudaStream_t s);
 int launch_la_conv_import(const float* ref_conv, float* mine, cudaStream_t s);
 int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
 
 // ---- tcgen05 skinny GEMMs for the decode step (gemm_tc.cu) ---------------------------------------------------------
 int gemm_tc_splits(int N, int K, int bn);
 bool gemm_tc_enabled();
-bool gemm_tc_inproj_enabled();
-int la_decode_l2_ahead();     // look-ahead (in units) of the L2 state prefetch of the DeltaNet decode kernel, 0 = off
-bool gemm_fused_enabled();
-int gemm_tc_store(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, float* Y, int M, int N, int K, int ld_out,
+int gemm_tc_store(cudaStream_t s, const __half* X, const __half* W, float* Y, int M, int N, int K, int ld_out,
                   int splits, size_t split_stride, int* d_error);
-int gemm_tc_swiglu(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, __nv_bfloat16* act, int M, int N, int K,
+int gemm_tc_swiglu(cudaStream_t s, const __half* X, const __half* W, __half* act, int M, int N, int K,
                    int* d_error);
-int gemm_tc_argmax(cudaStream_t s, const __nv_bfloat16* X, const __nv_bfloat16* W, unsigned long long* d_packed, int* tokens,
+int gemm_tc_argmax(cudaStream_t s, const __half* X, const __half* W, unsigned long long* d_packed, int* tokens,
                    int M, int N, int K, int* d_error);
 void gemm_tc_forget(const void* ptr);
 
-// ---- decode-step layer chain (decode_chain.cu): several skinny GEMMs and RMSNorms of consecutive layers in ONE
-// persistent cooperative kernel with grid barriers between the phases.
-struct ChainGemmDesc {          // Y[rows, N] = X[rows, K] W[N, K]^T, 64-column tiles
-    const __nv_bfloat16* X;
-    const __nv_bfloat16* W;
-    int N, K;
-    int splits;                 // > 1: fp32 partial matrices `split_stride` floats apart in out_f32
-    int epi;                    // 0 = fp32 store, 1 = SwiGLU (interleaved 32 gate + 32 up rows of W) -> out_bf16
-    float* out_f32;
-    size_t split_stride;
-    int ld_out;
-    __nv_bfloat16* out_bf16;
-};
-struct ChainNormDesc {          // h[row] += sum of partials (written back); out = RMSNorm(h) * (1 + w) as bf16
-    float* h;
-    const float* w;
-    const float* partials;
-    int n_splits;
-    size_t split_stride;
-    __nv_bfloat16* out;
-    float eps;
-};
-struct ChainPhaseDesc { int is_gemm; ChainGemmDesc g; ChainNormDesc n; };
-int launch_decode_chain(cudaStream_t s, int rows, const ChainPhaseDesc* phases, int n_phases, unsigned* d_sync, int* d_error);
-int gemm_tc_map(const void* ptr, int rows, int cols, int box_rows, void* tensor_map_out);   // cached CUtensorMap of a bf16 matrix
 // Where a decode-step output projection leaves its result when the caller sums split-K partials itself (the stack's
 // next RMSNorm does): `n_splits` matrices [rows, hidden], `stride` floats apart.  n_splits is set by the operator.
 struct DecodeOut {
     float* partials;
     size_t stride;
     int n_splits;
-    bool core_only = false;     // run only the attention core on the operator's own buffers: the input projection has
-                                // already been written to them and the caller projects the output itself
 };
 
 // ---- operator internals shared with the stack ------------------------------------------------------------------------
@@ -131,16 +100,15 @@ size_t fa_scratch_bytes(const b200attn_fa_config& c);
 int fa_create_internal(const b200attn_fa_config* cfg, const Scratch* shared, b200attn_fa* out);
 size_t la_scratch_bytes(const b200attn_la_config& c);
 int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b200attn_la* out);
-// Point the operator's working buffers into its `scratch` (sized by *_scratch_bytes of its cfg).  The stack uses these to
-// make per-branch views of one operator: same weights, different working buffers.
+// Point the operator's working buffers into its `scratch` (sized by *_scratch_bytes of its cfg).
 void fa_carve_scratch(b200attn_fa fa);
 void la_carve_scratch(b200attn_la la);
 // Operator bodies that take activations in the stack's own formats (see stack.cu).
 int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* h_slots, const int* h_counts,
-                    int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
+                    int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_fp16, float* d_y,
                     float y_beta, DecodeOut* dout, cudaStream_t s);
 int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots, const int* h_counts,
-                    int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y,
+                    int n_seqs, const int* d_slots, bool decode, const void* d_x, bool x_is_fp16, float* d_y,
                     float y_beta, DecodeOut* dout, cudaStream_t s);
 
 }  // namespace b200

@@ -414,6 +414,9 @@ b200::KvView b200attn_kv_pool_s::view() const {
 
 int b200attn_kv_pool_s::sync_lens() {
     if (!lens_dirty) return 0;
+    // Decode steps and graph replays advance the lengths on streams the pool does not know (non-blocking streams do not
+    // order against the legacy stream a plain cudaMemcpy uses), so wait for the whole device first.
+    B2_CUDA(cudaDeviceSynchronize());
     B2_CUDA(cudaMemcpy(h_lens.data(), d_lens, h_lens.size() * sizeof(int), cudaMemcpyDeviceToHost));
     lens_dirty = false;
     return 0;
@@ -477,11 +480,29 @@ extern "C" int b200attn_kv_pool_destroy(b200attn_kv_pool p) {
     return 0;
 }
 
+// Host -> device copy of small bookkeeping data that kernels on ANY stream may read next: a pageable cudaMemcpy may
+// return while its DMA is still in flight on the legacy stream, which non-blocking streams do not wait for, so the
+// copy is followed by a wait on that stream.
+static int push_ints(int* d_dst, const int* h_src, size_t n) {
+    B2_CUDA(cudaMemcpy(d_dst, h_src, n * sizeof(int), cudaMemcpyHostToDevice));
+    B2_CUDA(cudaStreamSynchronize(cudaStreamLegacy));
+    return 0;
+}
+
 static int pool_push_tables(b200attn_kv_pool p, int slot) {
     const int w = p->cfg.max_pages_per_seq;
-    B2_CUDA(cudaMemcpy(p->d_block_table + (size_t)slot * w, p->h_block_table.data() + (size_t)slot * w,
-                       w * sizeof(int), cudaMemcpyHostToDevice));
-    B2_CUDA(cudaMemcpy(p->d_capacity + slot, p->h_capacity.data() + slot, sizeof(int), cudaMemcpyHostToDevice));
+    B2_TRY(push_ints(p->d_block_table + (size_t)slot * w, p->h_block_table.data() + (size_t)slot * w, w));
+    return push_ints(p->d_capacity + slot, p->h_capacity.data() + slot, 1);
+}
+
+// Sets the slot's length to zero on every layer, on the host mirror and on the device.
+static int pool_zero_lens(b200attn_kv_pool p, int slot) {
+    B2_TRY(p->sync_lens());
+    const int zero = 0;
+    for (int l = 0; l < p->cfg.num_layers; ++l) {
+        p->h_lens[(size_t)l * p->cfg.max_seqs + slot] = 0;
+        B2_TRY(push_ints(p->d_lens + (size_t)l * p->cfg.max_seqs + slot, &zero, 1));
+    }
     return 0;
 }
 
@@ -517,11 +538,7 @@ extern "C" int b200attn_kv_seq_alloc(b200attn_kv_pool p, int reserve_tokens, int
     p->slot_used[slot] = 1;
     p->seq_pages[slot].clear();
     p->h_capacity[slot] = 0;
-    B2_TRY(p->sync_lens());
-    for (int l = 0; l < p->cfg.num_layers; ++l) p->h_lens[(size_t)l * p->cfg.max_seqs + slot] = 0;
-    std::vector<int> zeros(p->cfg.num_layers, 0);
-    for (int l = 0; l < p->cfg.num_layers; ++l)
-        B2_CUDA(cudaMemcpy(p->d_lens + (size_t)l * p->cfg.max_seqs + slot, zeros.data(), sizeof(int), cudaMemcpyHostToDevice));
+    B2_TRY(pool_zero_lens(p, slot));
     int st = b200attn_kv_seq_reserve(p, slot, reserve_tokens);
     if (st != 0) { p->slot_used[slot] = 0; return st; }
     if (reserve_tokens == 0) B2_TRY(pool_push_tables(p, slot));
@@ -532,6 +549,9 @@ extern "C" int b200attn_kv_seq_alloc(b200attn_kv_pool p, int reserve_tokens, int
 extern "C" int b200attn_kv_seq_free(b200attn_kv_pool p, int slot) {
     B2_CHECK_ARG(p, "kv_seq_free: null pool");
     B2_CHECK_ARG(slot >= 0 && slot < p->cfg.max_seqs && p->slot_used[slot], "kv_seq_free: slot %d is not allocated", slot);
+    // The slot's lengths go to zero first: a decode launch that still names the slot then writes its defined zero output
+    // instead of attending over pages that may already belong to another sequence.
+    B2_TRY(pool_zero_lens(p, slot));
     for (int pg : p->seq_pages[slot]) p->free_pages.push_back(pg);
     p->seq_pages[slot].clear();
     p->slot_used[slot] = 0;
@@ -551,7 +571,7 @@ extern "C" int b200attn_kv_seq_shrink(b200attn_kv_pool p, int slot, int new_len)
         if (new_len < len) {
             len = new_len;
             changed = true;
-            B2_CUDA(cudaMemcpy(p->d_lens + (size_t)l * p->cfg.max_seqs + slot, &len, sizeof(int), cudaMemcpyHostToDevice));
+            B2_TRY(push_ints(p->d_lens + (size_t)l * p->cfg.max_seqs + slot, &len, 1));
         }
     }
     if (!changed) return 0;

@@ -1,54 +1,49 @@
 // G1: chunk-64 gated delta rule (WY / UT form) on tcgen05 tensor cores.
 //
-// One CTA per (sequence, head) walks the sequence in chunks of C = 64 tokens.  With b_i the running sum of
-// the log decays g inside the chunk and S0 the state at the chunk start, the serial recurrence
+// One CTA per (sequence, head) walks the sequence in chunks of C = 64 tokens; two CTAs share an SM (106 KB of shared
+// memory and 256 TMEM columns each), so one CTA's CUDA-core phases run under the other's tensor-core phases.  With b_i
+// the running sum of the log decays g inside the chunk and S0 the state at the chunk start, the serial recurrence
 //     S_i = e^{g_i} S_{i-1} + k_i (x) beta_i (v_i - (e^{g_i} S_{i-1})^T k_i),   o_i = S_i^T q_i
 // (src/backend/cpu/core/attention/language_linear_attn.cpp:206-240 in the reference; its CUDA form is the
 // token-serial gated_delta_batch_fused_v2_kernel, linear_attention_v2.cu:492-595) is equivalent to
 //     A_ij  = beta_i e^{b_i-b_j} (k_i.k_j)  (j < i),     T = (I + A)^-1
 //     U     = T (beta V),   W = T (beta e^{b} K),        V_new = U - W S0
 //     O     = (Q e^{b}) S0 + tril(e^{b_i-b_j} (q_i.k_j)) V_new
-//     S_C   = e^{b_C} S0 + K^T (e^{b_C-b} V_new)
+//     S_C   = e^{b_C} S0 + (e^{b_C-b} K)^T V_new
 // Every decay factor is formed as exp(b_i - b_j) with i >= j, never as a quotient of products.
 //
 // All state-sized objects are kept TRANSPOSED in TMEM (lane = value dim or key dim, column = token), so every
-// tensor-core product has M = 128 and every tile a thread writes is one of its own rows:
+// tensor-core product has M = 128 and every tile a thread writes is one of its own rows.  The row scalings by beta and
+// beta e^b are folded into the columns of T, so that the K and V tiles go to the tensor core exactly as TMA delivered
+// them (as MN-major operands) and no transposed operand is ever built by scattered stores:
 //   (a)  D1  [128 x 64] = [K ; Q] K^T                         rows 0-63: K K^T, rows 64-127: Q K^T
-//   (uw) Ut  [vd x 64]  = (beta V)^T T^T,   Wt [kd x 64] = (beta e^b K)^T T^T     (T as an fp16 hi + lo pair)
+//   (uw) Ut  [vd x 64]  = V^T (T diag(beta))^T,   Wt [kd x 64] = K^T (T diag(beta e^b))^T     (T as an fp16 hi + lo pair)
 //   (ws) Ut -= S0^T W^T                                        -> V_new^T, accumulated in place (negated A operand)
 //   (o)  Ot  [vd x 64]  = S0^T (Q e^b)^T + V_new^T Mq^T       (Q is scaled in place in its TMA tile)
-//   (u)  D3  [vd x kd]  = e^{b_C} D3 + (e^{b_C-b} V_new)^T K  D3 holds S^T for the whole sequence
+//   (u)  D3  [vd x kd]  = e^{b_C} D3 + V_new^T (e^{b_C-b} K)  D3 holds S^T for the whole sequence; K is scaled in place
 // tcgen05.mma kind::f16: fp16 operands (the same 10-bit mantissa as tf32), fp32 accumulation; 128-byte swizzle.
 // T itself is built in fp32 in shared memory by a blocked inverse (16 x 16 blocks) on the CUDA cores.
 //
 // Eight compute warps (two threads per TMEM lane, each owning half of the 64 token columns) and one warp that
-// issues TMA loads (K/Q tiles double-buffered) and MMAs.  The chunk is split in a front half that does not need
-// the state (scalars, A, T, operand tiles -> B1) and a back half (S0 tile, W, V_new -> B2, B3); the front half of
-// chunk c+1 runs while the tensor core finishes (o) and (u) of chunk c, whose outputs are stored one chunk late.
-// All waits are bounded.
+// issues TMA loads and MMAs.  All waits are bounded.
 #include "kernels.cuh"
 #include "tc05.cuh"
 
 namespace b200 {
 
 constexpr int kC = 64;
-// shared-memory map (bytes from a 1024-aligned base)
-constexpr uint32_t kOffKQ = 0;        // 2 buffers x [2 blocks][128 rows][128 B]: rows 0-63 K chunk, rows 64-127 Q chunk
-constexpr uint32_t kOffAM = 65536;    // fp32 A [64][64]; its (zero) upper blocks double as scratch of the inverse
-constexpr uint32_t kOffTF = 81920;    // fp32 T [64][64]
-constexpr uint32_t kOffST = 65536;    // S0^T fp16 [2 blocks (64 kd)][128 vd rows][128 B], over A / T once T is converted
-constexpr uint32_t kOffRV = 98304;    // (beta V)^T [128 vd rows][64 tokens]            A of (uw)
-constexpr uint32_t kOffRK = 114688;   // (beta e^b K)^T [128 kd rows][64 tokens]        A of (uw)
-constexpr uint32_t kOffVN = 131072;   // V_new^T [128 vd rows][64 tokens]               A of (o)
-constexpr uint32_t kOffVS = 147456;   // (e^{b_C-b} V_new)^T                            A of (u)
-constexpr uint32_t kOffTT = 163840;   // T hi [64][64] fp16, then T lo                  B of (uw)
-constexpr uint32_t kOffWT = 163840;   // W [2 blocks][64 token rows][128 B], over T     B of (ws)
-constexpr uint32_t kOffMQ = 180224;   // 2 buffers x Mq [64][64] fp16                   B of (o)
-constexpr uint32_t kOffSC = 196608;   // 2 buffers x scalars: b[64], beta[64], eb[64], ebc[64]
-constexpr uint32_t kOffBarG = 198656;
+// shared-memory map (bytes from a 1024-aligned base); regions are reused as their contents die during a chunk
+constexpr uint32_t kOffKQ = 0;        // [2 blocks of 64 key dims][rows 0-63 K chunk, rows 64-127 Q chunk][128 B]
+constexpr uint32_t kOffV = 32768;     // V chunk [2 blocks of 64 value dims][64 tokens][128 B]; after (uw): V_new^T [128 vd][64 tokens]
+constexpr uint32_t kOffR = 49152;     // 32 KB: fp32 A [64][64] + fp32 T [64][64]  ->  T diag(beta) hi, lo, T diag(beta e^b) hi, lo
+                                      //        (four [64][64] fp16 tiles)  ->  S0^T fp16 [2 blocks of 64 kd][128 vd rows][128 B]
+constexpr uint32_t kOffW = 81920;     // W^T [128 kd rows][64 tokens] fp16                B of (ws), MN-major
+constexpr uint32_t kOffMQ = 98304;    // Mq [64][64] fp16                                 B of (o)
+constexpr uint32_t kOffSC = 106496;   // scalars: b[64], beta[64], eb[64], ebc[64]
+constexpr uint32_t kOffBarG = 107520;
 constexpr uint32_t kG1Smem = kOffBarG + 128 + 1024;
 constexpr int kG1Threads = 288;
-enum { G_KQ_FULL0 = 0, G_KQ_FULL1, G_A_DONE, G_B1, G_C1, G_B2, G_C2, G_B3, G_C3, G_BAR_COUNT };
+enum { G_FULL = 0, G_A_DONE, G_B1, G_C1, G_B2, G_C2, G_B3, G_C3, G_OT_FREE, G_BAR_COUNT };
 
 __device__ __forceinline__ void named_sync_256() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 // 2^x on the special-function unit (about 2 ulp); the decay matrices need 64 x 64 of them per chunk and head.
@@ -75,10 +70,10 @@ __device__ __forceinline__ void block_product(float* dst, int dr, int dc, const 
     *d = accumulate ? *d + v : v;
 }
 
-// grid (heads, n_seqs), block 288
-__global__ void __launch_bounds__(kG1Threads, 1)
+// grid (heads, n_seqs), block 288, two CTAs per SM
+__global__ void __launch_bounds__(kG1Threads, 2)
 la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const float* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
+                   const __grid_constant__ CUtensorMap map_v, const float* __restrict__ g, const float* __restrict__ beta,
                    const LaSeqMeta* __restrict__ seqs, float* __restrict__ rec_layer, size_t rec_stride_slot,
                    float* __restrict__ out, int* __restrict__ error_word) {
     extern __shared__ unsigned char smem_raw[];
@@ -89,8 +84,8 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + G_BAR_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     auto bar = [&](int i) { return base + kOffBarG + 8u * i; };
-    float* AM = reinterpret_cast<float*>(sm + kOffAM);
-    float* TF = reinterpret_cast<float*>(sm + kOffTF);
+    float* AM = reinterpret_cast<float*>(sm + kOffR);
+    float* TF = reinterpret_cast<float*>(sm + kOffR + 16384);
 
     const int h = blockIdx.x;
     const LaSeqMeta sq = seqs[blockIdx.y];
@@ -101,84 +96,87 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     float* Sg = rec_layer + (size_t)sq.slot * rec_stride_slot + (size_t)h * kLaKd * kLaVd;
 
     if (tid == 0) {
-        for (int i = 0; i < G_BAR_COUNT; ++i) mbar_init(bar(i), (i == G_B1 || i == G_B2 || i == G_B3) ? 256 : 1);
+        for (int i = 0; i < G_BAR_COUNT; ++i)
+            mbar_init(bar(i), (i == G_B1 || i == G_B2 || i == G_B3 || i == G_OT_FREE) ? 256 : 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
     if (warp == 8) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_alloc(smem_u32(tmem_slot), 256);
         tmem_relinquish();
-        if (lane == 0) { tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); }
+        if (lane == 0) { tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tm_d1 = tmem, tm_ut = tmem + 64, tm_wt = tmem + 128, tm_ot = tmem + 192, tm_d3 = tmem + 256;
+    // D3 = S^T (128 columns); X = D1, then W^T, then O^T (64 columns); Ut = U^T, then V_new^T (64 columns)
+    const uint32_t tm_d3 = tmem, tm_x = tmem + 128, tm_ut = tmem + 192;
 
     if (warp == 8) {
         // ------------------------------ TMA + MMA issuer ------------------------------
         if (lane == 0) {
             constexpr uint32_t id64 = umma_idesc(kFmtF16, 128, 64, 0, 0);
-            constexpr uint32_t id64_neg = id64 | (1u << 13);                  // negated A operand
-            constexpr uint32_t id_u = umma_idesc(kFmtF16, 128, 128, 0, 1);    // B MN-major, N = 128
-            auto load_kq = [&](int c) {
-                const uint32_t dst = base + kOffKQ + (c & 1) * 32768;
-                const uint32_t fb = bar(G_KQ_FULL0 + (c & 1));
+            constexpr uint32_t id64_amn = umma_idesc(kFmtF16, 128, 64, 1, 0);                    // A MN-major (a TMA tile as it came)
+            constexpr uint32_t id64_bmn_neg = umma_idesc(kFmtF16, 128, 64, 0, 1) | (1u << 13);   // B MN-major, negated A
+            constexpr uint32_t id_u = umma_idesc(kFmtF16, 128, 128, 0, 1);                       // B MN-major, N = 128
+            auto load_chunk = [&](int c) {
                 const int row = sq.row0 + c * kC;
-                mbar_arrive_expect_tx(fb, 32768);
+                mbar_arrive_expect_tx(bar(G_FULL), 49152);
                 for (int blk = 0; blk < 2; ++blk) {
-                    tma_load_3d(dst + blk * 16384, &map_k, fb, blk * 64, h, row);
-                    tma_load_3d(dst + blk * 16384 + 8192, &map_q, fb, blk * 64, h, row);
+                    tma_load_3d(base + kOffKQ + blk * 16384, &map_k, bar(G_FULL), blk * 64, h, row);
+                    tma_load_3d(base + kOffKQ + blk * 16384 + 8192, &map_q, bar(G_FULL), blk * 64, h, row);
+                    tma_load_3d(base + kOffV + blk * 8192, &map_v, bar(G_FULL), blk * 64, h, row);
                 }
             };
-            load_kq(0);
+            const uint32_t kq = base + kOffKQ;
+            load_chunk(0);
             for (int c = 0; c < n_chunks; ++c) {
                 const uint32_t par = c & 1;
-                const uint32_t kq = base + kOffKQ + (c & 1) * 32768;
-                if (!mbar_wait(bar(G_KQ_FULL0 + (c & 1)), (c >> 1) & 1, abort_flag)) break;
+                if (!mbar_wait(bar(G_FULL), par, abort_flag)) break;
+                if (c > 0 && !mbar_wait(bar(G_OT_FREE), (c - 1) & 1, abort_flag)) break;   // O^T of chunk c-1 has left TMEM
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {   // (a) D1 = [K;Q] K^T
                     const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                    umma_f16(tm_d1, umma_smem_desc(kq + off, 16, 1024), umma_smem_desc(kq + off, 16, 1024), id64, ks > 0 ? 1u : 0u);
+                    umma_f16(tm_x, umma_smem_desc(kq + off, 16, 1024), umma_smem_desc(kq + off, 16, 1024), id64, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(G_A_DONE));
-                // the other K/Q buffer was last read by (o) and (u) of chunk c-1 (its threads were done with it before B2)
-                if (c + 1 < n_chunks) {
-                    if (c >= 1 && !mbar_wait(bar(G_C3), (c - 1) & 1, abort_flag)) break;
-                    load_kq(c + 1);
-                }
                 if (!mbar_wait(bar(G_B1), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
-                for (int hl = 0; hl < 2; ++hl)    // (uw) with T = hi + lo
+                for (int hl = 0; hl < 2; ++hl)    // (uw): T diag(beta) and T diag(beta e^b) as hi + lo pairs
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks) {
-                        const uint64_t bt = umma_smem_desc(base + kOffTT + hl * 8192 + ks * 32, 16, 1024);
-                        umma_f16(tm_ut, umma_smem_desc(base + kOffRV + ks * 32, 16, 1024), bt, id64, (hl > 0 || ks > 0) ? 1u : 0u);
-                        umma_f16(tm_wt, umma_smem_desc(base + kOffRK + ks * 32, 16, 1024), bt, id64, (hl > 0 || ks > 0) ? 1u : 0u);
+                        const uint32_t acc = (hl > 0 || ks > 0) ? 1u : 0u;
+                        umma_f16(tm_ut, umma_smem_desc(base + kOffV + ks * 2048, 8192, 1024),
+                                 umma_smem_desc(base + kOffR + hl * 8192 + ks * 32, 16, 1024), id64_amn, acc);
+                        umma_f16(tm_x, umma_smem_desc(kq + ks * 2048, 16384, 1024),
+                                 umma_smem_desc(base + kOffR + 16384 + hl * 8192 + ks * 32, 16, 1024), id64_amn, acc);
                     }
                 umma_commit(bar(G_C1));
                 if (!mbar_wait(bar(G_B2), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {   // (ws) Ut -= S0^T W^T ; (o) Ot = S0^T (Q e^b)^T
-                    const uint64_t a = umma_smem_desc(base + kOffST + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-                    umma_f16(tm_ut, a, umma_smem_desc(base + kOffWT + (ks >> 2) * 8192 + (ks & 3) * 32, 16, 1024), id64_neg, 1u);
-                    umma_f16(tm_ot, a, umma_smem_desc(kq + 8192 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024), id64, ks > 0 ? 1u : 0u);
+                    const uint64_t a = umma_smem_desc(base + kOffR + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+                    umma_f16(tm_ut, a, umma_smem_desc(base + kOffW + ks * 2048, 8192, 1024), id64_bmn_neg, 1u);
+                    umma_f16(tm_x, a, umma_smem_desc(kq + 8192 + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024), id64, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(G_C2));
                 if (!mbar_wait(bar(G_B3), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {   // (o) Ot += V_new^T Mq^T ; (u) D3 += (e^{b_C-b} V_new)^T K
-                    umma_f16(tm_ot, umma_smem_desc(base + kOffVN + ks * 32, 16, 1024),
-                             umma_smem_desc(base + kOffMQ + (c & 1) * 8192 + ks * 32, 16, 1024), id64, 1u);
-                    umma_f16(tm_d3, umma_smem_desc(base + kOffVS + ks * 32, 16, 1024), umma_smem_desc(kq + ks * 2048, 16384, 1024),
-                             id_u, 1u);
+                for (int ks = 0; ks < 4; ++ks) {   // (o) Ot += V_new^T Mq^T ; (u) D3 += V_new^T (e^{b_C-b} K)
+                    const uint64_t a = umma_smem_desc(base + kOffV + ks * 32, 16, 1024);
+                    umma_f16(tm_x, a, umma_smem_desc(base + kOffMQ + ks * 32, 16, 1024), id64, 1u);
+                    umma_f16(tm_d3, a, umma_smem_desc(kq + ks * 2048, 16384, 1024), id_u, 1u);
                 }
                 umma_commit(bar(G_C3));
+                if (c + 1 < n_chunks) {            // every tile of this chunk has been read: fetch the next one
+                    if (!mbar_wait(bar(G_C3), par, abort_flag)) break;
+                    load_chunk(c + 1);
+                }
             }
         }
     } else {
@@ -186,6 +184,11 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const int r = tid & 127;     // TMEM lane: D1 row, value dim of Ut/Ot/D3, key dim of Wt; also this thread's tile row
         const int hf = tid >> 7;     // which 32 of the 64 token columns (or which half of the state columns) it handles
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+        float* s_b = reinterpret_cast<float*>(sm + kOffSC);
+        float* s_beta = s_b + 64;
+        float* s_eb = s_b + 128;
+        float* s_ebc = s_b + 192;
+        unsigned char* kq = sm + kOffKQ;
         // D3 <- S^T from the state pool: lane vd = r, column kd
 #pragma unroll 1
         for (int cc = 0; cc < 2; ++cc) {
@@ -196,35 +199,41 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             tmem_st32(tm_d3 + lane_base + ch * 32, sv);
         }
         tmem_wait_st();
-        // stores the outputs of chunk cp (Ot, lane = value dim) -> out[token][head][vd]
-        auto store_out = [&](int cp) {
+        bool ok = true;
+        // Outputs of chunk cp: O^T (lane = value dim) -> out[token][head][vd]; the TMEM columns are released as soon as
+        // they are in registers.
+        auto store_out = [&](int cp, bool do_store) {
             const int tok0 = cp * kC;
             const int n_valid = min(kC, sq.count - tok0);
             uint32_t ov[32];
-            tmem_ld32(tm_ot + lane_base + hf * 32, ov);
+            tmem_ld32(tm_x + lane_base + hf * 32, ov);
             tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(bar(G_OT_FREE));
+            if (!do_store) return;
             float* obase = out + ((size_t)(sq.row0 + tok0 + hf * 32) * kLaHeads + h) * kLaVd + r;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
                 if (hf * 32 + j < n_valid) obase[(size_t)j * kLaHeads * kLaVd] = __uint_as_float(ov[j]);
         };
-        bool ok = true;
         for (int c = 0; c < n_chunks; ++c) {   // after a failed wait the warp keeps the barrier protocol going, without waiting or storing
-            const uint32_t par = c & 1, prev = (c - 1) & 1;
+            const uint32_t par = c & 1;
             const int tok0 = c * kC;
             const int n_valid = min(kC, sq.count - tok0);
-            unsigned char* kq = sm + kOffKQ + (c & 1) * 32768;
-            float* s_b = reinterpret_cast<float*>(sm + kOffSC) + (c & 1) * 256;
-            float* s_beta = s_b + 64;
-            float* s_eb = s_b + 128;
-            float* s_ebc = s_b + 192;
-            // ======================= front half: needs nothing of the state =======================
+            // this chunk's decay and beta values are requested before the wait on the previous chunk's tensor-core work
+            float gv = 0.f, bv = 0.f;
+            if (tid < 64 && tid < n_valid) {
+                const size_t gi = (size_t)(sq.row0 + tok0 + tid) * kLaHeads + h;
+                gv = g[gi];
+                bv = beta[gi];
+            }
+            if (c > 0) {
+                if (!mbar_wait_warp(bar(G_C3), (c - 1) & 1, abort_flag)) ok = false;
+                tc_fence_after();
+                store_out(c - 1, ok);
+            }
             // ---- per-chunk scalars: b = cumsum(g), beta; padded tokens get g = 0, beta = 0 ----
             if (tid < 64) {
-                const bool val = tid < n_valid;
-                const size_t gi = (size_t)(sq.row0 + tok0 + tid) * kLaHeads + h;
-                float gv = val ? g[gi] : 0.f;
-                const float bv = val ? beta[gi] : 0.f;
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
                     const float t2 = __shfl_up_sync(0xffffffffu, gv, o);
@@ -242,45 +251,13 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             named_sync_256();
             const float e_bc = ex2_approx(s_b[63] * kLog2e);
-            // ---- this thread's half column of beta V ----
-            float vcol[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const int tk = hf * 32 + i;
-                vcol[i] = (tk < n_valid) ? s_beta[tk] * v[((size_t)(sq.row0 + tok0 + tk) * kLaHeads + h) * kLaVd + r] : 0.f;
-            }
-            // ---- (beta V)^T row r and (beta e^b K)^T row r, tokens of this half ----
-            if (!mbar_wait_warp(bar(G_KQ_FULL0 + (c & 1)), (c >> 1) & 1, abort_flag)) ok = false;
-            {
-                const unsigned char* kq_blk = kq + (r >> 6) * 16384;
-                const int tcol = r & 63;
-                unsigned char* rv_row = sm + kOffRV + r * 128;
-                unsigned char* rk_row = sm + kOffRK + r * 128;
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int c8 = hf * 4 + cc;
-                    uint32_t pv[4], pk[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int l0 = cc * 8 + 2 * e;                 // index into vcol
-                        const int i0 = c8 * 8 + 2 * e, i1 = i0 + 1;    // token
-                        const uint32_t sw0 = (((tcol >> 3) ^ (i0 & 7)) << 4) + (tcol & 7) * 2;
-                        const uint32_t sw1 = (((tcol >> 3) ^ (i1 & 7)) << 4) + (tcol & 7) * 2;
-                        const float k0 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i0 * 128 + sw0));
-                        const float k1 = __half2float(*reinterpret_cast<const __half*>(kq_blk + i1 * 128 + sw1));
-                        pv[e] = pack_half2(vcol[l0], vcol[l0 + 1]);
-                        pk[e] = pack_half2(s_beta[i0] * s_eb[i0] * k0, s_beta[i1] * s_eb[i1] * k1);
-                    }
-                    *reinterpret_cast<uint4*>(rv_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pv[0], pv[1], pv[2], pv[3]);
-                    *reinterpret_cast<uint4*>(rk_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                }
-            }
             // ---- D1 -> A matrix (rows 0-63) and masked, decayed Q K^T (rows 64-127); then Q *= e^b in place ----
+            if (!mbar_wait_warp(bar(G_FULL), par, abort_flag)) ok = false;
             if (!mbar_wait_warp(bar(G_A_DONE), par, abort_flag)) ok = false;
             tc_fence_after();
             {
                 uint32_t d1[32];
-                tmem_ld32(tm_d1 + lane_base + hf * 32, d1);
+                tmem_ld32(tm_x + lane_base + hf * 32, d1);
                 tmem_wait_ld();
                 if (r < 64) {
                     const float bi = s_b[r], be = s_beta[r];
@@ -297,7 +274,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 } else {
                     const int i = r - 64;
                     const float bi = s_b[i];
-                    unsigned char* row_ptr = sm + kOffMQ + (c & 1) * 8192 + i * 128;
+                    unsigned char* row_ptr = sm + kOffMQ + i * 128;
 #pragma unroll
                     for (int cc = 0; cc < 4; ++cc) {
                         uint32_t pk[4];
@@ -381,41 +358,49 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             named_sync_256();
             block_product(TF, 48, 0, TF, 48, 48, AM, 0, 48, -1.f, false, tid);
             named_sync_256();
-            {   // T -> fp16 hi + lo tiles (row = i, K = j)
+            {   // T diag(beta) and T diag(beta e^b) -> fp16 hi + lo tiles (row = i, K = j), written over A and T
                 const int i = tid >> 2, qd = tid & 3;
+                float tv[16];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(&TF[i * 64 + qd * 16 + 4 * e]);
+                    tv[4 * e] = t4.x; tv[4 * e + 1] = t4.y; tv[4 * e + 2] = t4.z; tv[4 * e + 3] = t4.w;
+                }
+                named_sync_256();     // every thread holds its part of T: the tiles may overwrite it
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
-                    uint32_t ph[4], pl[4];
+                    uint32_t uh[4], ul[4], wh[4], wl[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float2 t2 = *reinterpret_cast<const float2*>(&TF[i * 64 + qd * 16 + cc * 8 + 2 * e]);
-                        const float h0 = __half2float(__float2half_rn(t2.x)), h1 = __half2float(__float2half_rn(t2.y));
-                        ph[e] = pack_half2(h0, h1);
-                        pl[e] = pack_half2(t2.x - h0, t2.y - h1);
+                        const int j0 = qd * 16 + cc * 8 + 2 * e, j1 = j0 + 1;
+                        const float u0 = tv[cc * 8 + 2 * e] * s_beta[j0], u1 = tv[cc * 8 + 2 * e + 1] * s_beta[j1];
+                        const float w0 = u0 * s_eb[j0], w1 = u1 * s_eb[j1];
+                        const float uh0 = __half2float(__float2half_rn(u0)), uh1 = __half2float(__float2half_rn(u1));
+                        const float wh0 = __half2float(__float2half_rn(w0)), wh1 = __half2float(__float2half_rn(w1));
+                        uh[e] = pack_half2(uh0, uh1); ul[e] = pack_half2(u0 - uh0, u1 - uh1);
+                        wh[e] = pack_half2(wh0, wh1); wl[e] = pack_half2(w0 - wh0, w1 - wh1);
                     }
-                    const int chunk16 = qd * 2 + cc;
-                    *reinterpret_cast<uint4*>(sm + kOffTT + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                    *reinterpret_cast<uint4*>(sm + kOffTT + 8192 + i * 128 + ((chunk16 ^ (i & 7)) << 4)) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                    const uint32_t o16 = i * 128 + (((qd * 2 + cc) ^ (i & 7)) << 4);
+                    *reinterpret_cast<uint4*>(sm + kOffR + o16) = make_uint4(uh[0], uh[1], uh[2], uh[3]);
+                    *reinterpret_cast<uint4*>(sm + kOffR + 8192 + o16) = make_uint4(ul[0], ul[1], ul[2], ul[3]);
+                    *reinterpret_cast<uint4*>(sm + kOffR + 16384 + o16) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                    *reinterpret_cast<uint4*>(sm + kOffR + 24576 + o16) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                 }
             }
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(bar(G_B1));
-            named_sync_256();     // every thread is done reading A / T: their space becomes the S0 tile below
-            // ======================= back half: needs the state of the chunk start =======================
-            if (c > 0) {
-                if (!mbar_wait_warp(bar(G_C3), prev, abort_flag)) ok = false;
-                tc_fence_after();
-                if (ok) store_out(c - 1);
-            }
-            // ---- D3 (S^T of the chunk start) -> fp16 tile, and back to TMEM scaled by e^{b_C} ----
+            // ======================= the part that needs the state of the chunk start =======================
+            if (!mbar_wait_warp(bar(G_C1), par, abort_flag)) ok = false;    // (uw) is done: the T tiles are dead, W^T is in TMEM
+            tc_fence_after();
+            // ---- D3 (S^T of the chunk start) -> fp16 tile over the T tiles, and back to TMEM scaled by e^{b_C} ----
 #pragma unroll 1
             for (int cc = 0; cc < 2; ++cc) {
                 const int ch = hf * 2 + cc;
                 uint32_t sv[32];
                 tmem_ld32(tm_d3 + lane_base + ch * 32, sv);
                 tmem_wait_ld();
-                unsigned char* row_ptr = sm + kOffST + (ch >> 1) * 16384 + r * 128;
+                unsigned char* row_ptr = sm + kOffR + (ch >> 1) * 16384 + r * 128;
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
                     uint32_t pk[4];
@@ -429,48 +414,58 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 for (int c2 = 0; c2 < 32; ++c2) sv[c2] = __float_as_uint(__uint_as_float(sv[c2]) * e_bc);
                 tmem_st32(tm_d3 + lane_base + ch * 32, sv);
             }
-            tmem_wait_st();
-            // ---- W^T (lane = key dim) -> column r of the W tile (over T, which (uw) has finished reading) ----
-            if (!mbar_wait_warp(bar(G_C1), par, abort_flag)) ok = false;
-            tc_fence_after();
+            // ---- W^T (lane = key dim): row r of the W tile, this thread's 32 tokens ----
             {
                 uint32_t wv[32];
-                tmem_ld32(tm_wt + lane_base + hf * 32, wv);
+                tmem_ld32(tm_x + lane_base + hf * 32, wv);
                 tmem_wait_ld();
-                unsigned char* wt_blk = sm + kOffWT + (r >> 6) * 8192;
-                const int tcol = r & 63;
+                unsigned char* w_row = sm + kOffW + r * 128;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int i = hf * 32 + j;
-                    const __half hv = __float2half_rn(__uint_as_float(wv[j]));
-                    *reinterpret_cast<__half*>(wt_blk + i * 128 + (((tcol >> 3) ^ (i & 7)) << 4) + (tcol & 7) * 2) = hv;
+                for (int cc = 0; cc < 4; ++cc) {
+                    uint32_t pk[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        pk[e] = pack_half2(__uint_as_float(wv[cc * 8 + 2 * e]), __uint_as_float(wv[cc * 8 + 2 * e + 1]));
+                    *reinterpret_cast<uint4*>(w_row + (((hf * 4 + cc) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
             }
+            {   // K tile rows (token j): every element times e^{b_C - b_j} for the state update
+                const int j = tid >> 2;
+                const float sc = s_ebc[j];
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        uint4* p4 = reinterpret_cast<uint4*>(kq + blk * 16384 + j * 128 + (((tid & 3) * 2 + e) << 4));
+                        uint4 x = *p4;
+                        __half2* hx = reinterpret_cast<__half2*>(&x);
+#pragma unroll
+                        for (int w2 = 0; w2 < 4; ++w2) {
+                            const float2 f = __half22float2(hx[w2]);
+                            hx[w2] = __floats2half2_rn(f.x * sc, f.y * sc);
+                        }
+                        *p4 = x;
+                    }
+            }
+            tmem_wait_st();
             fence_proxy_async_smem();
             tc_fence_before();
             mbar_arrive(bar(G_B2));
-            // ---- V_new^T (lane = value dim): plain and decayed fp16 rows ----
+            // ---- V_new^T (lane = value dim) -> fp16 rows over the V tile ----
             if (!mbar_wait_warp(bar(G_C2), par, abort_flag)) ok = false;
             tc_fence_after();
             {
                 uint32_t uv[32];
                 tmem_ld32(tm_ut + lane_base + hf * 32, uv);
                 tmem_wait_ld();
-                unsigned char* vn_row = sm + kOffVN + r * 128;
-                unsigned char* vs_row = sm + kOffVS + r * 128;
+                unsigned char* vn_row = sm + kOffV + r * 128;
 #pragma unroll
                 for (int cc = 0; cc < 4; ++cc) {
-                    uint32_t pa[4], pb[4];
+                    uint32_t pa[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int l0 = cc * 8 + 2 * e, j0 = hf * 32 + l0;
-                        const float x0 = __uint_as_float(uv[l0]), x1 = __uint_as_float(uv[l0 + 1]);
-                        pa[e] = pack_half2(x0, x1);
-                        pb[e] = pack_half2(x0 * s_ebc[j0], x1 * s_ebc[j0 + 1]);
-                    }
-                    const int c8 = hf * 4 + cc;
-                    *reinterpret_cast<uint4*>(vn_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
-                    *reinterpret_cast<uint4*>(vs_row + ((c8 ^ (r & 7)) << 4)) = make_uint4(pb[0], pb[1], pb[2], pb[3]);
+                    for (int e = 0; e < 4; ++e)
+                        pa[e] = pack_half2(__uint_as_float(uv[cc * 8 + 2 * e]), __uint_as_float(uv[cc * 8 + 2 * e + 1]));
+                    *reinterpret_cast<uint4*>(vn_row + (((hf * 4 + cc) ^ (r & 7)) << 4)) = make_uint4(pa[0], pa[1], pa[2], pa[3]);
                 }
             }
             fence_proxy_async_smem();
@@ -480,7 +475,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // ---- last chunk's outputs and the final state: D3 (S^T) -> state pool ----
         if (ok && mbar_wait_warp(bar(G_C3), (n_chunks - 1) & 1, abort_flag)) {
             tc_fence_after();
-            store_out(n_chunks - 1);
+            store_out(n_chunks - 1, true);
 #pragma unroll 1
             for (int cc = 0; cc < 2; ++cc) {
                 const int ch = hf * 2 + cc;
@@ -496,28 +491,26 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     if (warp == 8) {
         tc_fence_after();
-        tmem_dealloc(tmem, 512);
+        tmem_dealloc(tmem, 256);
     }
     if (tid == 0 && *abort_flag) atomicExch(error_word, 6);
 }
 
-// q_h, k_h: fp16 [rows][16][128]; v fp32 [rows][16][128]; g, beta fp32 [rows][16].
-int launch_la_chunk_tc(const __half* q_h, const __half* k_h, const float* v, const float* g, const float* beta,
+// q_h, k_h, v_h: fp16 [rows][16][128]; g, beta fp32 [rows][16].
+int launch_la_chunk_tc(const __half* q_h, const __half* k_h, const __half* v_h, const float* g, const float* beta,
                        const LaSeqMeta* d_seqs, int n_seqs, int rows, float* rec_layer, size_t rec_stride, float* out,
                        int* d_error, cudaStream_t s) {
-    CUtensorMap mq, mk;
+    CUtensorMap mq, mk, mv;
     const uint64_t dims[3] = {(uint64_t)kLaKd, (uint64_t)kLaHeads, (uint64_t)rows};
     const uint64_t str[2] = {(uint64_t)kLaKd * 2, (uint64_t)kLaHeads * kLaKd * 2};
     const uint32_t box[3] = {64, 1, (uint32_t)kC};
     B2_TRY(make_tensor_map(&mq, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, q_h, dims, str, box));
     B2_TRY(make_tensor_map(&mk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, k_h, dims, str, box));
-    static bool attr_done = false;
-    if (!attr_done) {
-        B2_CUDA(cudaFuncSetAttribute(la_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kG1Smem));
-        attr_done = true;
-    }
+    B2_TRY(make_tensor_map(&mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, v_h, dims, str, box));
+    static PerDeviceOnce once;
+    B2_PER_DEVICE_ONCE(once, B2_CUDA(cudaFuncSetAttribute(la_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kG1Smem)));
     dim3 grid(kLaHeads, n_seqs);
-    la_chunk_tc_kernel<<<grid, kG1Threads, kG1Smem, s>>>(mq, mk, v, g, beta, d_seqs, rec_layer, rec_stride, out, d_error);
+    la_chunk_tc_kernel<<<grid, kG1Threads, kG1Smem, s>>>(mq, mk, mv, g, beta, d_seqs, rec_layer, rec_stride, out, d_error);
     B2_LAUNCH_CHECK();
     return 0;
 }

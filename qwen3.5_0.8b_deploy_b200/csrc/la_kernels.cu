@@ -251,15 +251,14 @@ la_gated_norm_kernel(const float* __restrict__ core, const float* __restrict__ m
 // L2 norms, gates, then ONE pass over the 128x128 fp32 state: thread (warp r, lane c) keeps rows
 // kRows * r .. kRows * r + kRows - 1 of columns 4c..4c+3 in registers between the read (kv = S^T k) and the write
 // (S' = g S + k (x) delta, o = S'^T q), followed by the gated RMSNorm.
-// kRows = 16: 256 threads, 2 or 3 CTAs per SM.  kRows = 8: 512 threads, 2 CTAs per SM = 1024 resident threads with half
-// the registers each, so 2048 units fill 296 slots 6.9 times instead of 444 slots 4.6 times (a fuller last wave).
+// kRows = 16: 256 threads, three CTAs per SM.
 template <typename OutT, int kMinBlocks, int kRows>
 __global__ void __launch_bounds__(32 * 128 / kRows, kMinBlocks)
 la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots, int max_seqs,
                  float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
                  size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
                  const float* __restrict__ dt_bias, const float* __restrict__ norm_w, OutT* __restrict__ out,
-                 unsigned stagger_ns, unsigned n_sms, unsigned l2_ahead) {
+                 unsigned stagger_ns, unsigned n_sms, unsigned l2_ahead, unsigned long long* stamp) {
     const int h = blockIdx.x, b = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int slot = slots[b];
@@ -300,6 +299,7 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
     }
     // The state was last written by this layer's previous step; everything read below comes from the preceding kernel.
     pdl_enter();
+    stamp_begin(stamp);
 
     // conv + SiLU + state shift for the head's q, k, v channels (384 values, 256 threads)
     for (int i = tid; i < 3 * kLaKd; i += kThreadsR) {
@@ -385,367 +385,10 @@ la_decode_kernel(const float* __restrict__ mixed, const int* __restrict__ slots,
         const float z = mrow[kLaZOff + h * kLaVd + tid];
         out[(size_t)b * (kLaHeads * kLaVd) + h * kLaVd + tid] = (OutT)(o * inv * norm_w[tid] * silu_f(z));
     }
-}
-
-// ---- R1, streamed form -----------------------------------------------------------------------------------------
-// Same arithmetic as la_decode_kernel, organised as a persistent kernel (one CTA per SM) that walks its (sequence,
-// head) units round-robin.  A producer lane brings each unit's 64 KB state into a three-stage shared-memory ring with
-// one bulk (TMA) copy and writes it back with one bulk store, so two state loads are always in flight per SM while
-// the eight compute warps work on a third, and the last wave of a grid of independent CTAs disappears.  Opt-in
-// (B200ATTN_LA_DECODE=stream): it is bit-identical to la_decode_kernel but currently slower, see launch_la_decode.
-constexpr int kR1Stages = 3;
-constexpr uint32_t kR1StateBytes = kLaKd * kLaVd * 4;
-constexpr uint32_t kR1Smem = kR1Stages * kR1StateBytes + 128;
-constexpr int kR1Threads = 288;
-
-template <typename OutT>
-__global__ void __launch_bounds__(kR1Threads, 1)
-la_decode_stream_kernel(const float* __restrict__ mixed, const int* __restrict__ slots, int n_seqs, int max_seqs,
-                        float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
-                        size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
-                        const float* __restrict__ dt_bias, const float* __restrict__ norm_w, OutT* __restrict__ out,
-                        int* __restrict__ error_word) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(16) float s_qkv[3][kLaKd];
-    __shared__ __align__(16) float s_part[8][kLaVd];
-    __shared__ float s_gb[2];
-    __shared__ float s_red[4];
-    __shared__ int s_abort;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t bar0 = smem_u32(smem + kR1Stages * kR1StateBytes);
-    auto full = [&](int s) { return bar0 + 8u * s; };
-    auto done = [&](int s) { return bar0 + 8u * (kR1Stages + s); };
-    const int n_units = n_seqs * kLaHeads;
-    const int n_my = ((int)blockIdx.x < n_units) ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    if (tid == 0) {
-        for (int s = 0; s < kR1Stages; ++s) { mbar_init(full(s), 1); mbar_init(done(s), 256); }
-        s_abort = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
-    volatile int* abort_flag = &s_abort;
-    auto unit_state = [&](int i) -> float* {         // global address of unit i's state, or null for a slot out of range
-        const int u = blockIdx.x + i * gridDim.x;
-        const int slot = slots[u / kLaHeads];
-        if (slot < 0 || slot >= max_seqs) return nullptr;
-        return rec_layer + (size_t)slot * rec_stride_slot + (size_t)(u % kLaHeads) * kLaKd * kLaVd;
-    };
-
-    if (warp == 8) {
-        // ------------------------------ producer: state in, state out ------------------------------
-        if (lane == 0) {
-            auto load = [&](int i) {
-                const float* src = unit_state(i);
-                const int s = i % kR1Stages;
-                if (src) {
-                    mbar_arrive_expect_tx(full(s), kR1StateBytes);
-                    bulk_g2s(smem_u32(smem + s * kR1StateBytes), src, kR1StateBytes, full(s));
-                } else {
-                    mbar_arrive(full(s));        // nothing to load: the consumers skip the unit
-                }
-            };
-            // the states were written by this layer's previous step, not by the preceding kernel: request them first
-            for (int i = 0; i < n_my && i < kR1Stages; ++i) load(i);
-            pdl_enter();
-            for (int j = 0; j < n_my; ++j) {
-                const int s = j % kR1Stages;
-                if (!mbar_wait(done(s), (j / kR1Stages) & 1, abort_flag)) break;
-                if (*abort_flag) break;          // a compute warp gave up on this stage: it does not hold a valid state
-                float* dst = unit_state(j);
-                if (dst) {
-                    bulk_s2g(dst, smem_u32(smem + s * kR1StateBytes), kR1StateBytes);
-                    bulk_commit_group();
-                    bulk_wait_group_read0();     // the stage may be refilled
-                }
-                if (j + kR1Stages < n_my) load(j + kR1Stages);
-            }
-            bulk_wait_group0();
-        } else {
-            pdl_enter();
-        }
-    } else {
-        // ------------------------------ compute warps ------------------------------
-        pdl_enter();
-        bool ok = true;
-        for (int j = 0; j < n_my; ++j) {
-            const int u = blockIdx.x + j * gridDim.x;
-            const int b = u / kLaHeads, h = u % kLaHeads;
-            const int slot = slots[b];
-            const bool valid = slot >= 0 && slot < max_seqs;
-            const int s = j % kR1Stages;
-            const float* mrow = mixed + (size_t)b * kLaProjCols;
-            if (valid) {
-                // conv + SiLU + state shift for the head's q, k, v channels (384 values, 256 threads)
-                float* cst = conv_layer + (size_t)slot * conv_stride_slot;
-                for (int i = tid; i < 3 * kLaKd; i += 256) {
-                    const int part = i / kLaKd, d = i % kLaKd;
-                    const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + d;
-                    const float x = mrow[ch];
-                    const float s0 = cst[ch], s1 = cst[kLaConvDim + ch], s2 = cst[2 * kLaConvDim + ch];
-                    const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)ch * kLaConvK);
-                    float sv = w.w * x;
-                    sv += w.x * s2;
-                    sv += w.y * s1;
-                    sv += w.z * s0;
-                    s_qkv[part][d] = silu_f(sv);
-                    cst[ch] = s1;
-                    cst[kLaConvDim + ch] = s2;
-                    cst[2 * kLaConvDim + ch] = x;
-                }
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (valid) {
-                if (warp < 2) {   // warp 0: q, warp 1: k
-                    float4 x4 = *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]);
-                    float ss = x4.x * x4.x + x4.y * x4.y + x4.z * x4.z + x4.w * x4.w;
-                    ss = sqrtf(warp_sum_f(ss) + 1e-6f);
-                    const float sc = (warp == 0) ? 1.0f / sqrtf((float)kLaKd) : 1.0f;
-                    x4.x = __fdiv_rn(x4.x, ss) * sc; x4.y = __fdiv_rn(x4.y, ss) * sc;
-                    x4.z = __fdiv_rn(x4.z, ss) * sc; x4.w = __fdiv_rn(x4.w, ss) * sc;
-                    *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]) = x4;
-                } else if (tid == 64) {
-                    const float a = mrow[kLaAOff + h], bb = mrow[kLaBOff + h];
-                    s_gb[0] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
-                    s_gb[1] = sigmoid_f(bb);
-                }
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            if (!mbar_wait_warp(full(s), (j / kR1Stages) & 1, abort_flag)) ok = false;
-            const bool work = valid && ok;
-            const float gt = s_gb[0], bt = s_gb[1];
-            float4* Ss = reinterpret_cast<float4*>(smem + s * kR1StateBytes) + (size_t)(warp * 16) * (kLaVd / 4) + lane;
-            float4 S[16];
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (work) {
-                // pass 1 (registers): partial kv over this warp's 16 rows
-#pragma unroll
-                for (int i = 0; i < 16; ++i) S[i] = Ss[i * (kLaVd / 4)];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float kk = s_qkv[1][warp * 16 + i];
-                    acc.x += S[i].x * kk; acc.y += S[i].y * kk; acc.z += S[i].z * kk; acc.w += S[i].w * kk;
-                }
-                *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (work) {
-                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int w = 0; w < 8; ++w) {
-                    const float4 p = *reinterpret_cast<const float4*>(&s_part[w][4 * lane]);
-                    kv.x += p.x; kv.y += p.y; kv.z += p.z; kv.w += p.w;
-                }
-                const float4 v4 = *reinterpret_cast<const float4*>(&s_qkv[2][4 * lane]);
-                dl.x = (v4.x - gt * kv.x) * bt; dl.y = (v4.y - gt * kv.y) * bt;
-                dl.z = (v4.z - gt * kv.z) * bt; dl.w = (v4.w - gt * kv.w) * bt;
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");   // s_part is reused below
-            if (work) {
-                // pass 2 (registers): update, back into the stage, partial o
-                acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float kk = s_qkv[1][warp * 16 + i];
-                    const float qq = s_qkv[0][warp * 16 + i];
-                    float4 sv = S[i];
-                    sv.x = sv.x * gt + kk * dl.x; sv.y = sv.y * gt + kk * dl.y;
-                    sv.z = sv.z * gt + kk * dl.z; sv.w = sv.w * gt + kk * dl.w;
-                    Ss[i * (kLaVd / 4)] = sv;
-                    acc.x += sv.x * qq; acc.y += sv.y * qq; acc.z += sv.z * qq; acc.w += sv.w * qq;
-                }
-                *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
-            }
-            fence_proxy_async_smem();
-            mbar_arrive(done(s));
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            // o[vd], gated RMSNorm over the head's 128 values
-            if (tid < kLaVd) {
-                float o = 0.f;
-#pragma unroll
-                for (int w = 0; w < 8; ++w) o += s_part[w][tid];
-                float ss = warp_sum_f(o * o);
-                if (lane == 0) s_red[warp] = ss;
-                asm volatile("bar.sync 2, 128;" ::: "memory");   // warps 0..3 all take this branch
-                if (work) {
-                    const float var = (s_red[0] + s_red[1] + s_red[2] + s_red[3]) / (float)kLaVd;
-                    const float inv = 1.0f / sqrtf(var + 1e-6f);
-                    const float z = mrow[kLaZOff + h * kLaVd + tid];
-                    out[(size_t)b * (kLaHeads * kLaVd) + h * kLaVd + tid] = (OutT)(o * inv * norm_w[tid] * silu_f(z));
-                }
-            }
-        }
-    }
-    __syncthreads();
-    if (tid == 0 && s_abort) atomicExch(error_word, 6);
-}
-
-// ---- R1, prefetching form -------------------------------------------------------------------------------------
-// la_decode_kernel's arithmetic and thread layout with two changes that keep more state bytes in flight per SM: the
-// CTAs are persistent (three per SM, each walking its units round-robin, no relaunch between units) and every CTA
-// owns a 64 KB shared-memory buffer into which one bulk (TMA) copy brings the NEXT unit's state while the current one
-// is being computed from registers.  The copy is issued as soon as the buffer has been read, so a load is in flight
-// for almost the whole life of a CTA, not only during its load phase.
-constexpr uint32_t kR1pSmem = kLaKd * kLaVd * 4 + 16;
-
-template <typename OutT>
-__global__ void __launch_bounds__(256, 3)
-la_decode_prefetch_kernel(const float* __restrict__ mixed, const int* __restrict__ slots, int n_seqs, int max_seqs,
-                          float* __restrict__ rec_layer, size_t rec_stride_slot, float* __restrict__ conv_layer,
-                          size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
-                          const float* __restrict__ dt_bias, const float* __restrict__ norm_w, OutT* __restrict__ out,
-                          int* __restrict__ error_word, unsigned stagger_ns, unsigned n_sms) {
-    extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ __align__(16) float s_qkv[3][kLaKd];
-    __shared__ __align__(16) float s_part[8][kLaVd];
-    __shared__ float s_gb[2];
-    __shared__ float s_red[4];
-    __shared__ int s_abort;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (stagger_ns && blockIdx.x >= n_sms) {          // same start offset between the CTAs of an SM as in la_decode_kernel
-        const unsigned long long t0 = global_timer_ns(), span = (unsigned long long)(blockIdx.x / n_sms) * stagger_ns;
-        while (global_timer_ns() - t0 < span) __nanosleep(100);
-    }
-    const uint32_t full = smem_u32(smem + kLaKd * kLaVd * 4);
-    const int n_units = n_seqs * kLaHeads;
-    const int n_my = ((int)blockIdx.x < n_units) ? (n_units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    if (tid == 0) {
-        mbar_init(full, 1);
-        s_abort = 0;
-        mbar_fence_init();
-    }
-    __syncthreads();
-    volatile int* abort_flag = &s_abort;
-    auto unit_state = [&](int i) -> float* {         // global address of unit i's state, or null for a slot out of range
-        const int u = blockIdx.x + i * gridDim.x;
-        const int slot = slots[u / kLaHeads];
-        if (slot < 0 || slot >= max_seqs) return nullptr;
-        return rec_layer + (size_t)slot * rec_stride_slot + (size_t)(u % kLaHeads) * kLaKd * kLaVd;
-    };
-    auto request = [&](int i) {                       // one thread: bring unit i's state into the buffer
-        const float* src = unit_state(i);
-        if (src) {
-            mbar_arrive_expect_tx(full, kLaKd * kLaVd * 4);
-            bulk_g2s(smem_u32(smem), src, kLaKd * kLaVd * 4, full);
-        } else {
-            mbar_arrive(full);
-        }
-    };
-    // the states were written by this layer's previous step, not by the preceding kernel: request the first one at once
-    if (tid == 0 && n_my > 0) request(0);
-    pdl_enter();
-    bool ok = true;
-    for (int j = 0; j < n_my; ++j) {
-        const int u = blockIdx.x + j * gridDim.x;
-        const int b = u / kLaHeads, h = u % kLaHeads;
-        const int slot = slots[b];
-        const bool valid = slot >= 0 && slot < max_seqs;
-        const float* mrow = mixed + (size_t)b * kLaProjCols;
-        float* Sg = rec_layer + (size_t)(valid ? slot : 0) * rec_stride_slot + (size_t)h * kLaKd * kLaVd;
-        if (valid) {
-            // conv + SiLU + state shift for the head's q, k, v channels (384 values, 256 threads)
-            float* cst = conv_layer + (size_t)slot * conv_stride_slot;
-            for (int i = tid; i < 3 * kLaKd; i += 256) {
-                const int part = i / kLaKd, d = i % kLaKd;
-                const int ch = part * (kLaHeads * kLaKd) + h * kLaKd + d;
-                const float x = mrow[ch];
-                const float s0 = cst[ch], s1 = cst[kLaConvDim + ch], s2 = cst[2 * kLaConvDim + ch];
-                const float4 w = *reinterpret_cast<const float4*>(conv_w + (size_t)ch * kLaConvK);
-                float sv = w.w * x;
-                sv += w.x * s2;
-                sv += w.y * s1;
-                sv += w.z * s0;
-                s_qkv[part][d] = silu_f(sv);
-                cst[ch] = s1;
-                cst[kLaConvDim + ch] = s2;
-                cst[2 * kLaConvDim + ch] = x;
-            }
-        }
+    if (stamp) {
         __syncthreads();
-        if (valid) {
-            if (warp < 2) {   // warp 0: q, warp 1: k
-                float4 x4 = *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]);
-                float ss = x4.x * x4.x + x4.y * x4.y + x4.z * x4.z + x4.w * x4.w;
-                ss = sqrtf(warp_sum_f(ss) + 1e-6f);
-                const float sc = (warp == 0) ? 1.0f / sqrtf((float)kLaKd) : 1.0f;
-                x4.x = __fdiv_rn(x4.x, ss) * sc; x4.y = __fdiv_rn(x4.y, ss) * sc;
-                x4.z = __fdiv_rn(x4.z, ss) * sc; x4.w = __fdiv_rn(x4.w, ss) * sc;
-                *reinterpret_cast<float4*>(&s_qkv[warp][4 * lane]) = x4;
-            } else if (tid == 64) {
-                const float a = mrow[kLaAOff + h], bb = mrow[kLaBOff + h];
-                s_gb[0] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
-                s_gb[1] = sigmoid_f(bb);
-            }
-        }
-        __syncthreads();
-        if (!mbar_wait_warp(full, j & 1, abort_flag)) ok = false;
-        const bool work = valid && ok;
-        const float gt = s_gb[0], bt = s_gb[1];
-        const float4* Ss = reinterpret_cast<const float4*>(smem) + (size_t)(warp * 16) * (kLaVd / 4) + lane;
-        float4 S[16];
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (work) {
-            // pass 1 (registers): partial kv over this warp's 16 rows
-#pragma unroll
-            for (int i = 0; i < 16; ++i) S[i] = Ss[i * (kLaVd / 4)];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float kk = s_qkv[1][warp * 16 + i];
-                acc.x += S[i].x * kk; acc.y += S[i].y * kk; acc.z += S[i].z * kk; acc.w += S[i].w * kk;
-            }
-            *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
-        }
-        __syncthreads();
-        // every thread holds its part of the state in registers: the buffer is free for the next unit's state
-        if (tid == 0 && j + 1 < n_my && !*abort_flag) request(j + 1);
-        float4 dl = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (work) {
-            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int w = 0; w < 8; ++w) {
-                const float4 p = *reinterpret_cast<const float4*>(&s_part[w][4 * lane]);
-                kv.x += p.x; kv.y += p.y; kv.z += p.z; kv.w += p.w;
-            }
-            const float4 v4 = *reinterpret_cast<const float4*>(&s_qkv[2][4 * lane]);
-            dl.x = (v4.x - gt * kv.x) * bt; dl.y = (v4.y - gt * kv.y) * bt;
-            dl.z = (v4.z - gt * kv.z) * bt; dl.w = (v4.w - gt * kv.w) * bt;
-        }
-        __syncthreads();   // s_part is reused below
-        if (work) {
-            // pass 2 (registers): update, write back, partial o
-            acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            float* Sw = Sg + (size_t)(warp * 16) * kLaVd + 4 * lane;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float kk = s_qkv[1][warp * 16 + i];
-                const float qq = s_qkv[0][warp * 16 + i];
-                float4 sv = S[i];
-                sv.x = sv.x * gt + kk * dl.x; sv.y = sv.y * gt + kk * dl.y;
-                sv.z = sv.z * gt + kk * dl.z; sv.w = sv.w * gt + kk * dl.w;
-                __stcs(reinterpret_cast<float4*>(Sw + (size_t)i * kLaVd), sv);
-                acc.x += sv.x * qq; acc.y += sv.y * qq; acc.z += sv.z * qq; acc.w += sv.w * qq;
-            }
-            *reinterpret_cast<float4*>(&s_part[warp][4 * lane]) = acc;
-        }
-        __syncthreads();
-        // o[vd], gated RMSNorm over the head's 128 values
-        if (tid < kLaVd) {
-            float o = 0.f;
-#pragma unroll
-            for (int w = 0; w < 8; ++w) o += s_part[w][tid];
-            float ss = warp_sum_f(o * o);
-            if (lane == 0) s_red[warp] = ss;
-            asm volatile("bar.sync 1, 128;" ::: "memory");   // warps 0..3 all take this branch
-            if (work) {
-                const float var = (s_red[0] + s_red[1] + s_red[2] + s_red[3]) / (float)kLaVd;
-                const float inv = 1.0f / sqrtf(var + 1e-6f);
-                const float z = mrow[kLaZOff + h * kLaVd + tid];
-                out[(size_t)b * (kLaHeads * kLaVd) + h * kLaVd + tid] = (OutT)(o * inv * norm_w[tid] * silu_f(z));
-            }
-        }
+        stamp_end(stamp);
     }
-    __syncthreads();
-    if (tid == 0 && s_abort) atomicExch(error_word, 6);
 }
 
 // ---- state import / export in the reference's layouts ------------------------------------------------------
@@ -787,10 +430,10 @@ int launch_la_recurrent_serial(const float* q, const float* k, const float* v, c
     return 0;
 }
 int launch_la_gated_norm(const float* core, const float* mixed, const float* norm_w, int rows, void* out,
-                         bool out_bf16, cudaStream_t s) {
+                         bool out_fp16, cudaStream_t s) {
     const int blocks = ceil_div(rows * kLaHeads, 4);
-    if (out_bf16)
-        la_gated_norm_kernel<__nv_bfloat16><<<blocks, 128, 0, s>>>(core, mixed, norm_w, rows, (__nv_bfloat16*)out);
+    if (out_fp16)
+        la_gated_norm_kernel<__half><<<blocks, 128, 0, s>>>(core, mixed, norm_w, rows, (__half*)out);
     else
         la_gated_norm_kernel<float><<<blocks, 128, 0, s>>>(core, mixed, norm_w, rows, (float*)out);
     B2_LAUNCH_CHECK();
@@ -798,89 +441,30 @@ int launch_la_gated_norm(const float* core, const float* mixed, const float* nor
 }
 int launch_la_decode(const float* mixed, const int* d_slots, int n_seqs, int max_seqs, float* rec_layer,
                      size_t rec_stride, float* conv_layer, size_t conv_stride, const float* conv_w, const float* a_log,
-                     const float* dt_bias, const float* norm_w, void* out, bool out_bf16, int* d_error, cudaStream_t s) {
-    // B200ATTN_LA_DECODE=stream selects the persistent kernel with the TMA state ring (read on every call so both can be
-    // compared).  Measured at 128 sequences: 73.7 us against 53.4 us for the one-CTA-per-unit kernel below: one compute
-    // group per SM works through its units one after the other and cannot hide the input-load and barrier latencies
-    // that three independent resident CTAs overlap, so it is not the default.
-    const char* mode = std::getenv("B200ATTN_LA_DECODE");
-    // "prefetch": persistent CTAs, next state brought in by TMA during compute.  Measured 61.5 us (one-CTA-per-unit: 53.5):
-    // keeping more state bytes in flight does not move the kernel either, so it stays opt-in like "stream".
-    if (d_error && mode && mode[0] == 'p') {
-        static int n_sm_p = 0;
-        if (n_sm_p == 0) {
-            int dev = 0;
-            B2_CUDA(cudaGetDevice(&dev));
-            B2_CUDA(cudaDeviceGetAttribute(&n_sm_p, cudaDevAttrMultiProcessorCount, dev));
-            B2_CUDA(cudaFuncSetAttribute(la_decode_prefetch_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1pSmem));
-            B2_CUDA(cudaFuncSetAttribute(la_decode_prefetch_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1pSmem));
-        }
-        const dim3 grid(std::min(3 * n_sm_p, n_seqs * kLaHeads));
-        const char* sgp = std::getenv("B200ATTN_LA_DECODE_STAGGER_NS");
-        const unsigned stagger_p = (sgp && (int)grid.x == 3 * n_sm_p) ? (unsigned)std::min(20000, std::max(0, std::atoi(sgp))) : 0u;
-        if (out_bf16)
-            launch_pdl(la_decode_prefetch_kernel<__nv_bfloat16>, grid, dim3(256), kR1pSmem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
-                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (__nv_bfloat16*)out, d_error, stagger_p, (unsigned)n_sm_p);
-        else
-            launch_pdl(la_decode_prefetch_kernel<float>, grid, dim3(256), kR1pSmem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
-                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (float*)out, d_error, stagger_p, (unsigned)n_sm_p);
-        B2_LAUNCH_CHECK();
-        return 0;
-    }
-    if (d_error && mode && mode[0] == 's') {
-        static int n_sm = 0;
-        if (n_sm == 0) {
-            int dev = 0;
-            B2_CUDA(cudaGetDevice(&dev));
-            B2_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-            B2_CUDA(cudaFuncSetAttribute(la_decode_stream_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1Smem));
-            B2_CUDA(cudaFuncSetAttribute(la_decode_stream_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kR1Smem));
-        }
-        const dim3 grid(std::min(n_sm, n_seqs * kLaHeads));
-        if (out_bf16)
-            launch_pdl(la_decode_stream_kernel<__nv_bfloat16>, grid, dim3(kR1Threads), kR1Smem, s, mixed, d_slots, n_seqs, max_seqs,
-                       rec_layer, rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (__nv_bfloat16*)out, d_error);
-        else
-            launch_pdl(la_decode_stream_kernel<float>, grid, dim3(kR1Threads), kR1Smem, s, mixed, d_slots, n_seqs, max_seqs, rec_layer,
-                       rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (float*)out, d_error);
-        B2_LAUNCH_CHECK();
-        return 0;
-    }
+                     const float* dt_bias, const float* norm_w, void* out, bool out_fp16, bool early_state_loads, cudaStream_t s) {
     dim3 grid(kLaHeads, n_seqs);
-    // B200ATTN_LA_DECODE_OCC: 3 (default) or 2 = 256-thread CTAs, that many per SM; 512 = 512-thread CTAs, two per SM.
-    // Measured at 128 sequences: 53.6 / 53.5 / 54.7 us, i.e. the kernel sits on a plateau that neither occupancy nor a
-    // fuller last wave moves.
-    const char* e = std::getenv("B200ATTN_LA_DECODE_OCC");
-    const int occ = (e && e[0] == '2') ? 2 : (e && e[0] == '5') ? 0 : 3;
-    static int n_sm_c = 0;
-    if (n_sm_c == 0) {
-        int dev = 0;
-        B2_CUDA(cudaGetDevice(&dev));
-        B2_CUDA(cudaDeviceGetAttribute(&n_sm_c, cudaDevAttrMultiProcessorCount, dev));
-    }
-    // B200ATTN_LA_DECODE_STAGGER_NS: start offset between the CTAs that share an SM in the first wave (0 = none).
+    unsigned long long* stamp = prof_stamp_slot(PROF_LA_DECODE);
+    int n_sm = 0;
+    B2_TRY(device_sm_count(&n_sm));
+    // Start offset between the CTAs that share an SM in the first wave (B200ATTN_LA_DECODE_STAGGER_NS, 0 = none).
     // Measured at 128 sequences inside the decode step: 2.317 ms per step without, 2.254 / 2.240 / 2.242 / 2.261 / 2.282
     // with 2000 / 2500 / 3000 / 3500 / 5000 ns; alone 52.8 -> 50.9 us per launch.  Only for launches of at least two
     // full waves: a smaller launch is latency-bound and a delayed start would only lengthen it.
-    const char* sg = std::getenv("B200ATTN_LA_DECODE_STAGGER_NS");
-    unsigned stagger_ns = sg ? (unsigned)std::min(20000, std::max(0, std::atoi(sg))) : 2750u;
-    if (n_seqs * kLaHeads < 2 * (occ == 3 ? 3 : 2) * n_sm_c) stagger_ns = 0;
-    const unsigned l2_ahead = (unsigned)la_decode_l2_ahead();
-#define LA_DEC(T, O, R) launch_pdl(la_decode_kernel<T, O, R>, grid, dim3(32 * 128 / R), 0, s, mixed, d_slots, max_seqs, rec_layer, \
-                                   rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out, stagger_ns, (unsigned)n_sm_c, l2_ahead)
-    if (out_bf16) { if (occ == 2) LA_DEC(__nv_bfloat16, 2, 16); else if (occ == 3) LA_DEC(__nv_bfloat16, 3, 16); else LA_DEC(__nv_bfloat16, 2, 8); }
-    else          { if (occ == 2) LA_DEC(float, 2, 16); else if (occ == 3) LA_DEC(float, 3, 16); else LA_DEC(float, 2, 8); }
+    unsigned stagger_ns = g_flags.la_stagger_ns;
+    if (n_seqs * kLaHeads < 2 * 3 * n_sm) stagger_ns = 0;
+    // How many units ahead of itself a CTA asks L2 for a state (B200ATTN_LA_DECODE_L2_AHEAD, 0 = off).  Measured at 128
+    // sequences with the start offset: 51.7 us without, 48.5 / 48.2 / 48.7 / 49.5 / 51.8 / 54.4 us at 148 / 222 / 296 /
+    // 444 / 592 / 888 units.
+    const unsigned l2_ahead = g_flags.la_l2_ahead;
+    // The kernel requests its state before the programmatic-launch wait.  That is only sound when another kernel that
+    // executes the wait runs between two writers of the same state (the decode step of a stack).  A caller that may
+    // launch this kernel twice in a row on one layer (the core entry) takes the ordinary stream order instead.
+#define LA_DEC(T) launch_pdl_if(early_state_loads, la_decode_kernel<T, 3, 16>, grid, dim3(256), 0, s, mixed, d_slots, max_seqs, rec_layer, \
+                                rec_stride, conv_layer, conv_stride, conv_w, a_log, dt_bias, norm_w, (T*)out, stagger_ns, (unsigned)n_sm, l2_ahead, stamp)
+    if (out_fp16) LA_DEC(__half); else LA_DEC(float);
 #undef LA_DEC
     B2_LAUNCH_CHECK();
     return 0;
-}
-// B200ATTN_LA_DECODE_L2_AHEAD: how many units ahead of itself a CTA of la_decode_kernel asks L2 for a state (0 = off).
-// Measured at 128 sequences with the start offset: 51.7 us without, 48.5 / 48.2 / 48.7 / 49.5 / 51.8 / 54.4 us at
-// 148 / 222 / 296 / 444 / 592 / 888 units; inside the decode step 2.235 ms without, 2.25 / 2.23 / 2.20 / 2.19 / 2.185 /
-// 2.183 / 2.21 at 48 / 74 / 111 / 148 / 185 / 222 / 296.
-int la_decode_l2_ahead() {
-    const char* pf = std::getenv("B200ATTN_LA_DECODE_L2_AHEAD");
-    return pf ? std::min(4096, std::max(0, std::atoi(pf))) : 185;
 }
 int launch_la_conv_import(const float* ref_conv, float* mine, cudaStream_t s) {
     la_conv_import_kernel<<<kLaConvDim / 256, 256, 0, s>>>(ref_conv, mine);

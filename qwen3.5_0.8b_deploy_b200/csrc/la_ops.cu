@@ -6,8 +6,6 @@
 #include "kernels.cuh"
 
 #include <algorithm>
-#include <cstdlib>
-#include <string>
 #include <new>
 #include <vector>
 
@@ -44,7 +42,7 @@ void la_carve_scratch(b200attn_la la) {
     la->d_g = (float*)take(R * kLaHeads * 4);
     la->d_beta = (float*)take(R * kLaHeads * 4);
     la->d_core = (float*)take(R * kLaHeads * kLaVd * 4);
-    la->d_xb = (__nv_bfloat16*)take(R * kHidden * 2);
+    la->d_xb = (__half*)take(R * kHidden * 2);
     la->d_gated = take(R * kLaHeads * kLaVd * 4);
     la->meta_cap = (int)(2 * R + 65536);
     la->d_meta = (int*)take((size_t)la->meta_cap * 4);
@@ -58,7 +56,8 @@ int la_create_internal(const b200attn_la_config* cfg, const Scratch* shared, b20
         cfg->conv_kernel != kLaConvK)
         B2_FAIL(B200ATTN_ERR_UNSUPPORTED, "la_create: kernels are built for hidden=1024, heads=16, key_dim=value_dim=128, conv_kernel=4");
     B2_CHECK_ARG(cfg->max_batch > 0 && cfg->max_prefill_rows >= 0, "la_create: max_batch must be > 0");
-    B2_CHECK_ARG(cfg->proj_precision == B200ATTN_PROJ_FP32 || cfg->proj_precision == B200ATTN_PROJ_BF16, "la_create: bad proj_precision");
+    B2_CHECK_ARG(cfg->proj_precision == B200ATTN_PROJ_FP32 || cfg->proj_precision == B200ATTN_PROJ_FP16, "la_create: bad proj_precision");
+    refresh_runtime_flags();
     auto* la = new (std::nothrow) b200attn_la_s();
     if (!la) B2_FAIL(B200ATTN_ERR_NOMEM, "la_create: host allocation failed");
     la->cfg = *cfg;
@@ -96,7 +95,7 @@ extern "C" int b200attn_la_create(const b200attn_la_config* cfg, b200attn_la* ou
 
 extern "C" int b200attn_la_destroy(b200attn_la la) {
     if (!la) return 0;
-    cudaFree(la->d_win_f32); cudaFree(la->d_win_bf16); cudaFree(la->d_wout_f32); cudaFree(la->d_wout_bf16);
+    cudaFree(la->d_win_f32); cudaFree(la->d_win_fp16); cudaFree(la->d_wout_f32); cudaFree(la->d_wout_fp16);
     cudaFree(la->d_conv_w); cudaFree(la->d_a_log); cudaFree(la->d_dt_bias); cudaFree(la->d_norm);
     if (la->scratch.owned) cudaFree(la->scratch.base);
     cudaFree(la->d_error);
@@ -114,15 +113,15 @@ extern "C" int b200attn_la_set_weights(b200attn_la la, const b200attn_la_weights
     std::memcpy(cat.data() + (size_t)kLaZOff * kHidden, w->in_proj_z, (size_t)kLaHeads * kLaVd * kHidden * 4);
     std::memcpy(cat.data() + (size_t)kLaAOff * kHidden, w->in_proj_a, (size_t)kLaHeads * kHidden * 4);
     std::memcpy(cat.data() + (size_t)kLaBOff * kHidden, w->in_proj_b, (size_t)kLaHeads * kHidden * 4);
-    cudaFree(la->d_win_f32); cudaFree(la->d_win_bf16); cudaFree(la->d_wout_f32); cudaFree(la->d_wout_bf16);
+    cudaFree(la->d_win_f32); cudaFree(la->d_win_fp16); cudaFree(la->d_wout_f32); cudaFree(la->d_wout_fp16);
     cudaFree(la->d_conv_w); cudaFree(la->d_a_log); cudaFree(la->d_dt_bias); cudaFree(la->d_norm);
-    la->d_win_f32 = nullptr; la->d_win_bf16 = nullptr; la->d_wout_f32 = nullptr; la->d_wout_bf16 = nullptr;
+    la->d_win_f32 = nullptr; la->d_win_fp16 = nullptr; la->d_wout_f32 = nullptr; la->d_wout_fp16 = nullptr;
     la->d_conv_w = nullptr; la->d_a_log = nullptr; la->d_dt_bias = nullptr; la->d_norm = nullptr;
     la->ready = false;
     const size_t no = (size_t)kHidden * kLaHeads * kLaVd;
-    if (la->cfg.proj_precision == B200ATTN_PROJ_BF16) {
-        B2_TRY(upload_bf16_from_f32(cat.data(), &la->d_win_bf16, cat.size()));
-        B2_TRY(upload_bf16_from_f32(w->out_proj, &la->d_wout_bf16, no));
+    if (la->cfg.proj_precision == B200ATTN_PROJ_FP16) {
+        B2_TRY(upload_f16_from_f32(cat.data(), &la->d_win_fp16, cat.size()));
+        B2_TRY(upload_f16_from_f32(w->out_proj, &la->d_wout_fp16, no));
     } else {
         B2_TRY(upload_f32(cat.data(), &la->d_win_f32, cat.size()));
         B2_TRY(upload_f32(w->out_proj, &la->d_wout_f32, no));
@@ -226,14 +225,7 @@ extern "C" int b200attn_la_state_export(b200attn_la_state st, int layer, int slo
 // ---- forward ---------------------------------------------------------------------------------------------------
 namespace b200 {
 
-static bool la_use_tensor_cores() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = std::getenv("B200ATTN_LA_PREFILL");
-        v = (e && std::string(e) == "serial") ? 0 : 1;
-    }
-    return v == 1;
-}
+static bool la_use_tensor_cores() { return !g_flags.la_prefill_serial; }
 
 static int la_build_meta(b200attn_la la, b200attn_la_state st, const int* h_slots, const int* h_counts, int n_seqs,
                          int* rows_out, std::vector<LaSeqMeta>& seqs, LaSeqMeta** d_seqs, int** d_row_seq, bool need_row_seq,
@@ -277,50 +269,46 @@ static int la_recurrence(b200attn_la la, b200attn_la_state st, int layer, const 
 }
 
 int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* h_slots, const int* h_counts, int n_seqs,
-                    const int* d_slots, bool decode, const void* d_x, bool x_is_bf16, float* d_y, float y_beta,
+                    const int* d_slots, bool decode, const void* d_x, bool x_is_fp16, float* d_y, float y_beta,
                     DecodeOut* dout, cudaStream_t s) {
-    const bool core_only = decode && dout && dout->core_only;
-    B2_CHECK_ARG(la && st && (core_only || (d_x && d_y)), "linear attention: null argument");
+    B2_CHECK_ARG(la && st && d_x && d_y, "linear attention: null argument");
     if (!la->ready) B2_FAIL(B200ATTN_ERR_NOT_READY, "LinearAttention weights not set");
     B2_CHECK_ARG(layer >= 0 && layer < st->cfg.num_layers, "linear attention: layer %d out of range", layer);
-    const bool bf16 = la->cfg.proj_precision == B200ATTN_PROJ_BF16;
-    if (x_is_bf16 && !bf16) B2_FAIL(B200ATTN_ERR_INVALID, "linear attention: bf16 activations need the bf16 projection mode");
+    const bool fp16 = la->cfg.proj_precision == B200ATTN_PROJ_FP16;
+    if (x_is_fp16 && !fp16) B2_FAIL(B200ATTN_ERR_INVALID, "linear attention: fp16 activations need the fp16 projection mode");
     float* rec_layer = st->d_recurrent + (size_t)layer * st->cfg.max_seqs * st->rec_stride_slot();
     float* conv_layer = st->d_conv + (size_t)layer * st->cfg.max_seqs * st->conv_stride_slot();
     auto project_in = [&](int rows) -> int {
-        if (bf16) {
+        if (fp16) {
             const void* xb = d_x;
-            if (!x_is_bf16) { B2_TRY(f32_to_bf16(s, (const float*)d_x, la->d_xb, (size_t)rows * kHidden)); xb = la->d_xb; }
-            if (decode && rows <= 128 && gemm_tc_inproj_enabled())   // weight-streaming tcgen05 GEMM
-                return gemm_tc_store(s, (const __nv_bfloat16*)xb, la->d_win_bf16, la->d_mixed, rows, kLaProjCols, kHidden, kLaProjCols, 1, 0, la->d_error);
-            return gemm_xwT(s, xb, true, la->d_win_bf16, true, la->d_mixed, false, rows, kLaProjCols, kHidden);
+            if (!x_is_fp16) { B2_TRY(f32_to_f16(s, (const float*)d_x, la->d_xb, (size_t)rows * kHidden)); xb = la->d_xb; }
+            if (decode && rows <= 128 && gemm_tc_enabled())   // weight-streaming tcgen05 GEMM
+                return gemm_tc_store(s, (const __half*)xb, la->d_win_fp16, la->d_mixed, rows, kLaProjCols, kHidden, kLaProjCols, 1, 0, la->d_error);
+            return gemm_xwT(s, xb, true, la->d_win_fp16, true, la->d_mixed, false, rows, kLaProjCols, kHidden);
         }
         return gemm_xwT(s, d_x, false, la->d_win_f32, false, la->d_mixed, false, rows, kLaProjCols, kHidden);
     };
     auto project_out = [&](int rows) -> int {
-        if (bf16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || y_beta == 0.f)) {
+        if (fp16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || y_beta == 0.f)) {
             const int K = kLaHeads * kLaVd;
             if (dout) {
                 dout->n_splits = gemm_tc_splits(kHidden, K, 64);
-                return gemm_tc_store(s, (const __nv_bfloat16*)la->d_gated, la->d_wout_bf16, dout->partials, rows, kHidden, K, kHidden,
+                return gemm_tc_store(s, (const __half*)la->d_gated, la->d_wout_fp16, dout->partials, rows, kHidden, K, kHidden,
                                      dout->n_splits, dout->stride, la->d_error);
             }
-            return gemm_tc_store(s, (const __nv_bfloat16*)la->d_gated, la->d_wout_bf16, d_y, rows, kHidden, K, kHidden, 1, 0, la->d_error);
+            return gemm_tc_store(s, (const __half*)la->d_gated, la->d_wout_fp16, d_y, rows, kHidden, K, kHidden, 1, 0, la->d_error);
         }
-        if (bf16) return gemm_xwT(s, la->d_gated, true, la->d_wout_bf16, true, d_y, false, rows, kHidden, kLaHeads * kLaVd, y_beta);
+        if (fp16) return gemm_xwT(s, la->d_gated, true, la->d_wout_fp16, true, d_y, false, rows, kHidden, kLaHeads * kLaVd, y_beta);
         return gemm_xwT(s, la->d_gated, false, la->d_wout_f32, false, d_y, false, rows, kHidden, kLaHeads * kLaVd, y_beta);
     };
     if (decode) {
         B2_CHECK_ARG(d_slots, "la_decode: null slots");
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= la->cfg.max_batch, "la_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, la->cfg.max_batch);
-        if (!core_only) B2_TRY(project_in(n_seqs));
-        {
-            ProfScope prof(PROF_LA_DECODE, s);
-            B2_TRY(launch_la_decode(la->d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
-                                    st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, la->d_gated,
-                                    bf16, la->d_error, s));
-        }
-        return core_only ? 0 : project_out(n_seqs);
+        B2_TRY(project_in(n_seqs));
+        B2_TRY(launch_la_decode(la->d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
+                                st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, la->d_gated,
+                                fp16, true, s));
+        return project_out(n_seqs);
     }
     int rows = 0;
     std::vector<LaSeqMeta> seqs;
@@ -336,7 +324,7 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
                               tc ? la->d_kh : nullptr, la->d_v, la->d_g, la->d_beta, s));
     B2_TRY(la_recurrence(la, st, layer, la->d_q, la->d_k, la->d_v, la->d_g, la->d_beta, d_seqs, n_seqs, rows, la->d_core, tc, s));
     B2_TRY(launch_la_conv_state_update(la->d_mixed, d_seqs, n_seqs, conv_layer, st->conv_stride_slot(), s));
-    B2_TRY(launch_la_gated_norm(la->d_core, la->d_mixed, la->d_norm, rows, la->d_gated, bf16, s));
+    B2_TRY(launch_la_gated_norm(la->d_core, la->d_mixed, la->d_norm, rows, la->d_gated, fp16, s));
     return project_out(rows);
 }
 
@@ -389,8 +377,7 @@ extern "C" int b200attn_la_decode_core(b200attn_la la, b200attn_la_state st, int
     cudaStream_t s = as_stream(stream);
     float* rec_layer = st->d_recurrent + (size_t)layer * st->cfg.max_seqs * st->rec_stride_slot();
     float* conv_layer = st->d_conv + (size_t)layer * st->cfg.max_seqs * st->conv_stride_slot();
-    ProfScope prof(PROF_LA_DECODE, s);
     return launch_la_decode(d_mixed, d_slots, n_seqs, st->cfg.max_seqs, rec_layer, st->rec_stride_slot(), conv_layer,
                             st->conv_stride_slot(), la->d_conv_w, la->d_a_log, la->d_dt_bias, la->d_norm, d_out, false,
-                            la->d_error, s);
+                            false, s);
 }

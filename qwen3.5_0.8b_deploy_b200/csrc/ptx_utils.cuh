@@ -17,6 +17,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
+// ---- in-kernel time stamps ------------------------------------------------------------------------------
+// slot[0] = earliest time a CTA of the launch passed its dependency wait, slot[1] = latest time a CTA finished
+// (armed as ~0 / 0 by the host).  slot == nullptr: off.  stamp_end must follow a CTA-wide barrier.
+__device__ __forceinline__ void stamp_begin(unsigned long long* slot) {
+    if (slot && threadIdx.x == 0) atomicMin(slot, (unsigned long long)global_timer_ns());
+}
+__device__ __forceinline__ void stamp_end(unsigned long long* slot) {
+    if (slot && threadIdx.x == 0) atomicMax(slot + 1, (unsigned long long)global_timer_ns());
+}
+
 // ---- mbarrier ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -6,12 +6,11 @@
 // Engine-level behaviour mirrors qwen::cuda::CudaEngine (src/backend/cuda/kernels/cuda_engine.cu:158-519):
 // per-layer weights, prefill over token batches, a decode step for the whole batch, reset_cache, and a
 // graph-captured step (there: prefill, :391-479; here: decode with device-resident lengths and tokens).
-// The residual stream is fp32; GEMM operands are bf16 with fp32 accumulation (cuBLAS).
+// The residual stream is fp32; GEMM operands are fp16 with fp32 accumulation (cuBLAS).
 #include "kernels.cuh"
 #include "ptx_utils.cuh"
 
 #include <algorithm>
-#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -23,9 +22,9 @@ struct b200attn_stack_s {
     std::vector<b200attn_fa> fa;
     std::vector<b200attn_la> la;
     std::vector<float*> d_in_norm, d_post_norm;
-    std::vector<__nv_bfloat16*> d_wgu, d_wdown;   // [2*inter, hidden], [hidden, inter]
+    std::vector<__half*> d_wgu, d_wdown;   // [2*inter, hidden], [hidden, inter]
     std::vector<char> layer_ready;
-    __nv_bfloat16* d_embed = nullptr;  // [vocab, hidden]
+    __half* d_embed = nullptr;  // [vocab, hidden]
     float* d_final_norm = nullptr;
     bool embed_ready = false;
     b200attn_kv_pool pool = nullptr;
@@ -33,9 +32,9 @@ struct b200attn_stack_s {
     b200::Scratch op_scratch;
     int max_rows = 0;
     float* d_h = nullptr;              // [max_rows, hidden] residual stream
-    __nv_bfloat16* d_xb = nullptr;     // [max_rows, hidden]
-    __nv_bfloat16* d_gu = nullptr;     // [max_rows, 2*inter]
-    __nv_bfloat16* d_act = nullptr;    // [max_rows, inter]
+    __half* d_xb = nullptr;     // [max_rows, hidden]
+    __half* d_gu = nullptr;     // [max_rows, 2*inter]
+    __half* d_act = nullptr;    // [max_rows, inter]
     float* d_last = nullptr;           // [max_seqs, hidden]
     float* d_logits = nullptr;         // [max_seqs, vocab]
     int* d_tokens = nullptr;           // [max_seqs] decode token buffer (in place)
@@ -43,16 +42,7 @@ struct b200attn_stack_s {
     float* d_partials = nullptr;       // [kMaxSplits][128][hidden] split-K partials of the decode-step output projections
     unsigned long long* d_packed = nullptr;   // [128] running argmax words of the LM head
     int* d_error = nullptr;            // device status word of the stack's own tcgen05 GEMMs
-    unsigned* d_sync = nullptr;        // [2] grid-barrier words of the decode chain kernel
-    // Decode branches: the step's sequences are cut into up to kMaxBranches groups that walk the layers independently on
-    // streams of their own (branch 0 on the caller's), so one group's dependent chain of small launches fills the gaps of
-    // another's and runs under its bandwidth-bound attention kernels.  Each extra branch has its own operator working
-    // buffers, split counters and cuBLAS lane.
-    static constexpr int kMaxBranches = 4;
-    cudaStream_t br_stream[kMaxBranches - 1] = {};
-    cudaEvent_t ev_fork = nullptr, ev_join[kMaxBranches - 1] = {};
-    b200::Scratch br_fa_scratch[kMaxBranches - 1], br_la_scratch[kMaxBranches - 1];
-    int* br_counters[kMaxBranches - 1] = {};
+    int* d_last_idx = nullptr;         // [max_seqs] row of every sequence's last prompt token inside a prefill pass
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
     int graph_nseqs = 0;
@@ -67,25 +57,25 @@ __device__ __forceinline__ float wsum(float v) {
     return v;
 }
 
-// h[row] = embed[token[row]] (bf16 -> fp32). grid rows, block 256 (4 elements per thread).
-__global__ void embed_gather_kernel(const int* __restrict__ tokens, const __nv_bfloat16* __restrict__ embed, int vocab,
+// h[row] = embed[token[row]] (fp16 -> fp32). grid rows, block 256 (4 elements per thread).
+__global__ void embed_gather_kernel(const int* __restrict__ tokens, const __half* __restrict__ embed, int vocab,
                                     float* __restrict__ h) {
     pdl_enter();
     const int row = blockIdx.x;
     int tok = tokens[row];
     tok = min(max(tok, 0), vocab - 1);
     const uint2 raw = *reinterpret_cast<const uint2*>(embed + (size_t)tok * kHidden + 4 * threadIdx.x);
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]);
+    const __half2* p = reinterpret_cast<const __half2*>(&raw);
+    const float2 a = __half22float2(p[0]), b = __half22float2(p[1]);
     *reinterpret_cast<float4*>(h + (size_t)row * kHidden + 4 * threadIdx.x) = make_float4(a.x, a.y, b.x, b.y);
 }
 
-// RMSNorm with (1 + w), fp32 in, bf16 out (and optional fp32 copy).  One 256-thread block per row, one float4 per
+// RMSNorm with (1 + w), fp32 in, fp16 out (and optional fp32 copy).  One 256-thread block per row, one float4 per
 // thread; optional row gather.  n_splits > 0: first x[row] += sum of the split-K partial rows (written back), i.e.
 // the residual add of the preceding output projection happens here; the partial loads are issued four at a time.
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w, float eps,
-               int rows, __nv_bfloat16* __restrict__ out_bf16, float* __restrict__ out_f32,
+               int rows, __half* __restrict__ out_fp16, float* __restrict__ out_f32,
                const float* __restrict__ partials, int n_splits, size_t split_stride) {
     __shared__ float s_part[8];
     const int row = blockIdx.x, t = threadIdx.x;
@@ -116,12 +106,12 @@ rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const f
     const float rms = sqrtf(ss / (float)kHidden + eps);
     const float r0 = v.x / rms * (1.0f + ww.x), r1 = v.y / rms * (1.0f + ww.y);
     const float r2 = v.z / rms * (1.0f + ww.z), r3 = v.w / rms * (1.0f + ww.w);
-    if (out_bf16) {
-        __nv_bfloat162 a = __floats2bfloat162_rn(r0, r1), b = __floats2bfloat162_rn(r2, r3);
+    if (out_fp16) {
+        __half2 a = __floats2half2_rn(r0, r1), b = __floats2half2_rn(r2, r3);
         uint2 pk;
         pk.x = *reinterpret_cast<uint32_t*>(&a);
         pk.y = *reinterpret_cast<uint32_t*>(&b);
-        *reinterpret_cast<uint2*>(out_bf16 + (size_t)row * kHidden + 4 * t) = pk;
+        *reinterpret_cast<uint2*>(out_fp16 + (size_t)row * kHidden + 4 * t) = pk;
     }
     if (out_f32) *reinterpret_cast<float4*>(out_f32 + (size_t)row * kHidden + 4 * t) = make_float4(r0, r1, r2, r3);
 }
@@ -129,7 +119,7 @@ rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const f
 // The same RMSNorm for many rows without pending partials (prefill): one warp per row, 32 values per lane, four rows per
 // block, so that a pass over 131072 rows is 32768 blocks of useful size instead of 131072 blocks of one float4 per thread.
 __global__ void __launch_bounds__(128)
-rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int rows, __nv_bfloat16* __restrict__ out_bf16) {
+rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int rows, __half* __restrict__ out_fp16) {
     const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (row >= rows) return;
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * kHidden);
@@ -145,16 +135,16 @@ rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, fl
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const float4 ww = *reinterpret_cast<const float4*>(w + 4 * (32 * i + lane));
-        __nv_bfloat162 a = __floats2bfloat162_rn(v[i].x / rms * (1.0f + ww.x), v[i].y / rms * (1.0f + ww.y));
-        __nv_bfloat162 b = __floats2bfloat162_rn(v[i].z / rms * (1.0f + ww.z), v[i].w / rms * (1.0f + ww.w));
-        *reinterpret_cast<uint2*>(out_bf16 + (size_t)row * kHidden + 4 * (32 * i + lane)) =
+        __half2 a = __floats2half2_rn(v[i].x / rms * (1.0f + ww.x), v[i].y / rms * (1.0f + ww.y));
+        __half2 b = __floats2half2_rn(v[i].z / rms * (1.0f + ww.z), v[i].w / rms * (1.0f + ww.w));
+        *reinterpret_cast<uint2*>(out_fp16 + (size_t)row * kHidden + 4 * (32 * i + lane)) =
             make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
     }
 }
 
 // act = silu(gate) * up.  gu rows hold tiles of 64 columns: 32 gate columns followed by the 32 matching up columns
-// (the layout the decode-step GEMM epilogue consumes as well).  bf16.
-__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int inter, size_t n_oct, __nv_bfloat16* __restrict__ act) {
+// (the layout the decode-step GEMM epilogue consumes as well).  fp16.
+__global__ void swiglu_kernel(const __half* __restrict__ gu, int inter, size_t n_oct, __half* __restrict__ act) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // index over (row, inter/8): eight outputs per thread
     if (i >= n_oct) return;
     const size_t per_row = inter / 8;
@@ -162,13 +152,13 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, int inter, s
     const size_t gcol = (c / 32) * 64 + (c % 32);
     const uint4 g4 = *reinterpret_cast<const uint4*>(gu + row * 2 * inter + gcol);
     const uint4 u4 = *reinterpret_cast<const uint4*>(gu + row * 2 * inter + gcol + 32);
-    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
-    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
-    __nv_bfloat162 o[4];
+    const __half2* gp = reinterpret_cast<const __half2*>(&g4);
+    const __half2* up = reinterpret_cast<const __half2*>(&u4);
+    __half2 o[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-        const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
-        o[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+        const float2 g = __half22float2(gp[e]), u = __half22float2(up[e]);
+        o[e] = __floats2half2_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
     }
     *reinterpret_cast<uint4*>(act + row * inter + c) = *reinterpret_cast<uint4*>(o);
 }
@@ -205,8 +195,8 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
     }
 }
 
-// Embedding ~ N(0, std) from a counter-based hash (Box-Muller), written as bf16.
-__global__ void init_normal_bf16_kernel(__nv_bfloat16* __restrict__ out, size_t n, uint64_t seed, float std_dev) {
+// Embedding ~ N(0, std) from a counter-based hash (Box-Muller), written as fp16.
+__global__ void init_normal_fp16_kernel(__half* __restrict__ out, size_t n, uint64_t seed, float std_dev) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     uint64_t z = seed + 0x9E3779B97F4A7C15ull * (i + 1);
@@ -215,7 +205,7 @@ __global__ void init_normal_bf16_kernel(__nv_bfloat16* __restrict__ out, size_t 
     z ^= z >> 31;
     const float u1 = ((uint32_t)(z & 0xffffffffu) + 1.0f) * (1.0f / 4294967296.0f);
     const float u2 = (uint32_t)(z >> 32) * (1.0f / 4294967296.0f);
-    out[i] = __float2bfloat16_rn(std_dev * sqrtf(-2.0f * logf(u1)) * cosf(6.283185307179586f * u2));
+    out[i] = __float2half_rn(std_dev * sqrtf(-2.0f * logf(u1)) * cosf(6.283185307179586f * u2));
 }
 
 __global__ void iota_kernel(int* p, int n) {
@@ -244,10 +234,9 @@ __global__ void quantize_rows_kernel(float* __restrict__ w, int rows, int cols) 
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 constexpr int kMaxSplits = 16;
-constexpr int kDefaultDecodeBranches = 1;
 
-// Uploads a host fp32 matrix as bf16, optionally through the INT8 fake quantiser.
-static int upload_matrix(const float* h, int rows, int cols, bool int8, __nv_bfloat16** out) {
+// Uploads a host fp32 matrix as fp16, optionally through the INT8 fake quantiser.
+static int upload_matrix(const float* h, int rows, int cols, bool int8, __half** out) {
     float* tmp = nullptr;
     B2_TRY(upload_f32(h, &tmp, (size_t)rows * cols));
     if (int8) {
@@ -257,7 +246,7 @@ static int upload_matrix(const float* h, int rows, int cols, bool int8, __nv_bfl
     cudaError_t e = cudaMalloc(out, (size_t)rows * cols * 2);
     int st = 0;
     if (e != cudaSuccess) { set_error("cudaMalloc failed: %s", cudaGetErrorString(e)); st = B200ATTN_ERR_NOMEM; }
-    if (st == 0) st = f32_to_bf16(0, tmp, *out, (size_t)rows * cols);
+    if (st == 0) st = f32_to_f16(0, tmp, *out, (size_t)rows * cols);
     e = cudaDeviceSynchronize();
     cudaFree(tmp);
     if (st == 0 && e != cudaSuccess) { set_error("weight upload failed: %s", cudaGetErrorString(e)); st = B200ATTN_ERR_CUDA; }
@@ -282,15 +271,9 @@ extern "C" int b200attn_stack_destroy(b200attn_stack st) {
     b200attn_kv_pool_destroy(st->pool);
     b200attn_la_state_destroy(st->state);
     cudaFree(st->op_scratch.base);
-    for (int b = 0; b < b200attn_stack_s::kMaxBranches - 1; ++b) {
-        if (st->br_stream[b]) cudaStreamDestroy(st->br_stream[b]);
-        if (st->ev_join[b]) cudaEventDestroy(st->ev_join[b]);
-        cudaFree(st->br_fa_scratch[b].base); cudaFree(st->br_la_scratch[b].base); cudaFree(st->br_counters[b]);
-    }
-    if (st->ev_fork) cudaEventDestroy(st->ev_fork);
     cudaFree(st->d_h); cudaFree(st->d_xb); cudaFree(st->d_gu); cudaFree(st->d_act); cudaFree(st->d_last);
     cudaFree(st->d_logits); cudaFree(st->d_tokens); cudaFree(st->d_slots);
-    cudaFree(st->d_partials); cudaFree(st->d_packed); cudaFree(st->d_error); cudaFree(st->d_sync);
+    cudaFree(st->d_partials); cudaFree(st->d_packed); cudaFree(st->d_error); cudaFree(st->d_last_idx);
     delete st;
     return 0;
 }
@@ -301,6 +284,7 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
                      cfg->max_seqs > 0 && cfg->max_seq_len > 0 && cfg->prefill_chunk_seqs > 0,
                  "stack_create: all sizes must be > 0");
     if (cfg->hidden_size != kHidden) B2_FAIL(B200ATTN_ERR_UNSUPPORTED, "stack_create: kernels are built for hidden=1024");
+    refresh_runtime_flags();
     auto* st = new (std::nothrow) b200attn_stack_s();
     if (!st) B2_FAIL(B200ATTN_ERR_NOMEM, "stack_create: host allocation failed");
     st->cfg = *cfg;
@@ -332,8 +316,8 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
         b200attn_la_state_config sc{st->n_la, cfg->max_seqs, kLaHeads, kLaKd, kLaVd, kLaConvK};
         if ((rc = b200attn_la_state_create(&sc, &st->state)) != 0) return fail(rc);
     }
-    b200attn_fa_config fc{kHidden, kFaHeads, kFaKvHeads, kHeadDim, kRotaryDim, 1e7f, B200ATTN_PROJ_BF16, cfg->max_seqs, st->max_rows};
-    b200attn_la_config lc{kHidden, kLaHeads, kLaKd, kLaVd, kLaConvK, B200ATTN_PROJ_BF16, cfg->max_seqs, st->max_rows};
+    b200attn_fa_config fc{kHidden, kFaHeads, kFaKvHeads, kHeadDim, kRotaryDim, 1e7f, B200ATTN_PROJ_FP16, cfg->max_seqs, st->max_rows};
+    b200attn_la_config lc{kHidden, kLaHeads, kLaKd, kLaVd, kLaConvK, B200ATTN_PROJ_FP16, cfg->max_seqs, st->max_rows};
     st->op_scratch.bytes = std::max(fa_scratch_bytes(fc), la_scratch_bytes(lc));
     ST_CUDA(cudaMalloc(&st->op_scratch.base, st->op_scratch.bytes));
     for (int i = 0; i < L; ++i) {
@@ -346,22 +330,6 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
             if ((rc = la_create_internal(&lc, &st->op_scratch, &l)) != 0) return fail(rc);
             st->la.push_back(l);
         }
-    }
-    {   // working buffers of the extra decode branches (decode only: one row per sequence)
-        b200attn_fa_config fd = fc; fd.max_prefill_rows = 0;
-        b200attn_la_config ld = lc; ld.max_prefill_rows = 0;
-        ST_CUDA(cudaEventCreateWithFlags(&st->ev_fork, cudaEventDisableTiming));
-        for (int b = 0; b < b200attn_stack_s::kMaxBranches - 1; ++b) {
-            ST_CUDA(cudaStreamCreateWithFlags(&st->br_stream[b], cudaStreamNonBlocking));
-            ST_CUDA(cudaEventCreateWithFlags(&st->ev_join[b], cudaEventDisableTiming));
-            st->br_fa_scratch[b].bytes = fa_scratch_bytes(fd);
-            st->br_la_scratch[b].bytes = la_scratch_bytes(ld);
-            ST_CUDA(cudaMalloc(&st->br_fa_scratch[b].base, st->br_fa_scratch[b].bytes));
-            ST_CUDA(cudaMalloc(&st->br_la_scratch[b].base, st->br_la_scratch[b].bytes));
-            ST_CUDA(cudaMalloc(&st->br_counters[b], (size_t)cfg->max_seqs * kFaKvHeads * 4));
-            ST_CUDA(cudaMemset(st->br_counters[b], 0, (size_t)cfg->max_seqs * kFaKvHeads * 4));
-        }
-        if ((rc = cublas_init_lanes(b200attn_stack_s::kMaxBranches)) != 0) return fail(rc);
     }
     const size_t R = st->max_rows;
     ST_CUDA(cudaMalloc(&st->d_h, R * kHidden * 4));
@@ -378,8 +346,7 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
     ST_CUDA(cudaMemset(st->d_packed, 0, 128 * sizeof(unsigned long long)));
     ST_CUDA(cudaMalloc(&st->d_error, sizeof(int)));
     ST_CUDA(cudaMemset(st->d_error, 0, sizeof(int)));
-    ST_CUDA(cudaMalloc(&st->d_sync, 2 * sizeof(unsigned)));
-    ST_CUDA(cudaMemset(st->d_sync, 0, 2 * sizeof(unsigned)));
+    ST_CUDA(cudaMalloc(&st->d_last_idx, (size_t)cfg->max_seqs * 4));
     iota_kernel<<<ceil_div(cfg->max_seqs, 128), 128>>>(st->d_slots, cfg->max_seqs);
     ST_CUDA(cudaDeviceSynchronize());
 #undef ST_CUDA
@@ -461,7 +428,7 @@ extern "C" int b200attn_stack_init_embedding_random(b200attn_stack st, uint64_t 
     st->d_embed = nullptr; st->d_final_norm = nullptr; st->embed_ready = false;
     const size_t n = (size_t)st->cfg.vocab_size * kHidden;
     B2_CUDA(cudaMalloc(&st->d_embed, n * 2));
-    init_normal_bf16_kernel<<<(unsigned)((n + 255) / 256), 256>>>(st->d_embed, n, seed, std_dev);
+    init_normal_fp16_kernel<<<(unsigned)((n + 255) / 256), 256>>>(st->d_embed, n, seed, std_dev);
     B2_LAUNCH_CHECK();
     B2_CUDA(cudaDeviceSynchronize());
     B2_TRY(upload_f32(h_final_norm, &st->d_final_norm, kHidden));
@@ -485,7 +452,6 @@ extern "C" int b200attn_stack_reset(b200attn_stack st, b200attn_stream stream) {
     B2_CHECK_ARG(st, "stack_reset: null stack");
     if (st->pool) B2_TRY(b200attn_kv_clear(st->pool, stream));
     if (st->state) B2_TRY(b200attn_la_state_clear(st->state, -1, stream));
-    B2_CUDA(cudaMemsetAsync(st->d_sync, 0, 2 * sizeof(unsigned), b200::as_stream(stream)));   // grid-barrier words of the decode chain
     return 0;
 }
 
@@ -499,15 +465,6 @@ static int stack_ready(b200attn_stack st) {
     return 0;
 }
 
-// Number of groups the decode step's sequences are cut into (B200ATTN_DECODE_BRANCHES, read on every call so one process
-// can compare settings); every group keeps at least 16 sequences.
-static int decode_branches(int rows) {
-    const char* e = std::getenv("B200ATTN_DECODE_BRANCHES");
-    int nb = e ? std::atoi(e) : kDefaultDecodeBranches;
-    nb = std::max(1, std::min(nb, (int)b200attn_stack_s::kMaxBranches));
-    return std::max(1, std::min(nb, rows / 16));
-}
-
 // All layers over `rows` rows already embedded in d_h.  Returns through *pending the number of split-K partial
 // matrices of the last output projection that still have to be added to d_h (decode path only).
 static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const int* h_counts, int n_seqs, const int* d_slots,
@@ -516,115 +473,6 @@ static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const i
     const bool tc = decode && rows <= 128 && gemm_tc_enabled();          // weight-streaming tcgen05 GEMMs with fused epilogues
     const size_t pstride = (size_t)128 * kHidden;
     int pending = 0;
-    if (tc && gemm_fused_enabled()) {
-        // One persistent kernel per layer boundary: out-proj(i), norm, gate/up + SwiGLU, down, norm(i+1), in-proj(i+1).
-        // The attention operators run core-only on their own projection buffers.
-        const int L = st->cfg.num_layers;
-        auto in_w = [&](int i) { return st->layer_kind[i] ? st->fa[st->layer_sub[i]]->d_wqkv_bf16 : st->la[st->layer_sub[i]]->d_win_bf16; };
-        auto in_buf = [&](int i) { return st->layer_kind[i] ? st->fa[st->layer_sub[i]]->d_qkv_raw : st->la[st->layer_sub[i]]->d_mixed; };
-        auto in_cols = [&](int i) { return st->layer_kind[i] ? kFaQkvCols : kLaProjCols; };
-        auto out_x = [&](int i) { return st->layer_kind[i] ? (const __nv_bfloat16*)st->fa[st->layer_sub[i]]->d_attn : (const __nv_bfloat16*)st->la[st->layer_sub[i]]->d_gated; };
-        auto out_w = [&](int i) { return st->layer_kind[i] ? st->fa[st->layer_sub[i]]->d_wo_bf16 : st->la[st->layer_sub[i]]->d_wout_bf16; };
-        const int attn_cols = 2048;                       // 8 x 256 = 16 x 128
-        const int s_out = gemm_tc_splits(kHidden, attn_cols, 64), s_down = std::min(kMaxSplits, gemm_tc_splits(kHidden, inter, 64));
-        launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[0], st->cfg.rms_eps, rows, st->d_xb, nullptr,
-                   st->d_partials, 0, pstride);
-        B2_LAUNCH_CHECK();
-        B2_TRY(gemm_tc_store(s, st->d_xb, in_w(0), in_buf(0), rows, in_cols(0), kHidden, in_cols(0), 1, 0, st->d_error));
-        for (int i = 0; i < L; ++i) {
-            DecodeOut core{nullptr, 0, 0, true};
-            if (st->layer_kind[i])
-                B2_TRY(fa_forward_rows(st->fa[st->layer_sub[i]], st->pool, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots, true,
-                                       nullptr, true, nullptr, 1.0f, &core, s));
-            else
-                B2_TRY(la_forward_rows(st->la[st->layer_sub[i]], st->state, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots, true,
-                                       nullptr, true, nullptr, 1.0f, &core, s));
-            ChainPhaseDesc ph[6] = {};
-            int np = 0;
-            ph[np].is_gemm = 1;
-            ph[np++].g = ChainGemmDesc{out_x(i), out_w(i), kHidden, attn_cols, s_out, 0, st->d_partials, pstride, kHidden, nullptr};
-            ph[np].is_gemm = 0;
-            ph[np++].n = ChainNormDesc{st->d_h, st->d_post_norm[i], st->d_partials, s_out, pstride, st->d_xb, st->cfg.rms_eps};
-            ph[np].is_gemm = 1;
-            ph[np++].g = ChainGemmDesc{st->d_xb, st->d_wgu[i], 2 * inter, kHidden, 1, 1, nullptr, 0, inter, st->d_act};
-            ph[np].is_gemm = 1;
-            ph[np++].g = ChainGemmDesc{st->d_act, st->d_wdown[i], kHidden, inter, s_down, 0, st->d_partials, pstride, kHidden, nullptr};
-            if (i + 1 < L) {
-                ph[np].is_gemm = 0;
-                ph[np++].n = ChainNormDesc{st->d_h, st->d_in_norm[i + 1], st->d_partials, s_down, pstride, st->d_xb, st->cfg.rms_eps};
-                ph[np].is_gemm = 1;
-                ph[np++].g = ChainGemmDesc{st->d_xb, in_w(i + 1), in_cols(i + 1), kHidden, 1, 0, in_buf(i + 1), 0, in_cols(i + 1), nullptr};
-            }
-            B2_TRY(launch_decode_chain(s, rows, ph, np, st->d_sync, st->d_error));
-        }
-        *pending_out = s_down;
-        return 0;
-    }
-    const int nb = (decode && !tc && !gemm_tc_inproj_enabled()) ? decode_branches(rows) : 1;
-    if (nb > 1) {
-        // Fork: every extra branch waits for what precedes the layers on the caller's stream (the embedding gather).
-        int r0[b200attn_stack_s::kMaxBranches + 1];
-        for (int b = 0; b <= nb; ++b) r0[b] = (int)((long long)rows * b / nb);
-        B2_CUDA(cudaEventRecord(st->ev_fork, s));
-        for (int b = 1; b < nb; ++b) B2_CUDA(cudaStreamWaitEvent(st->br_stream[b - 1], st->ev_fork, 0));
-        int rc = 0;
-        for (int i = 0; i < st->cfg.num_layers && rc == 0; ++i) {
-            for (int b = 0; b < nb && rc == 0; ++b) {
-                const int n = r0[b + 1] - r0[b];
-                cudaStream_t bs = b ? st->br_stream[b - 1] : s;
-                float* h = st->d_h + (size_t)r0[b] * kHidden;
-                __nv_bfloat16* xb = st->d_xb + (size_t)r0[b] * kHidden;
-                __nv_bfloat16* gu = st->d_gu + (size_t)r0[b] * 2 * inter;
-                __nv_bfloat16* act = st->d_act + (size_t)r0[b] * inter;
-                gemm_set_lane(b);
-                rc = [&]() -> int {
-                    launch_pdl(rmsnorm_kernel, dim3(n), dim3(256), 0, bs, h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, n, xb, nullptr,
-                               st->d_partials, 0, pstride);
-                    B2_LAUNCH_CHECK();
-                    if (st->layer_kind[i]) {
-                        b200attn_fa_s view = *st->fa[st->layer_sub[i]];      // same weights, the branch's working buffers
-                        if (b) {
-                            view.scratch = st->br_fa_scratch[b - 1];
-                            view.cfg.max_prefill_rows = 0;
-                            fa_carve_scratch(&view);
-                            view.d_counters = st->br_counters[b - 1];
-                        }
-                        B2_TRY(fa_forward_rows(&view, st->pool, st->layer_sub[i], nullptr, nullptr, n, d_slots + r0[b], true, xb, true, h,
-                                               1.0f, nullptr, bs));
-                    } else {
-                        b200attn_la_s view = *st->la[st->layer_sub[i]];
-                        if (b) {
-                            view.scratch = st->br_la_scratch[b - 1];
-                            view.cfg.max_prefill_rows = 0;
-                            la_carve_scratch(&view);
-                        }
-                        B2_TRY(la_forward_rows(&view, st->state, st->layer_sub[i], nullptr, nullptr, n, d_slots + r0[b], true, xb, true, h,
-                                               1.0f, nullptr, bs));
-                    }
-                    launch_pdl(rmsnorm_kernel, dim3(n), dim3(256), 0, bs, h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, n, xb, nullptr,
-                               st->d_partials, 0, pstride);
-                    B2_LAUNCH_CHECK();
-                    B2_TRY(gemm_xwT(bs, xb, true, st->d_wgu[i], true, gu, true, n, 2 * inter, kHidden));
-                    const size_t octs = (size_t)n * inter / 8;
-                    swiglu_kernel<<<(unsigned)((octs + 255) / 256), 256, 0, bs>>>(gu, inter, octs, act);
-                    B2_LAUNCH_CHECK();
-                    return gemm_xwT(bs, act, true, st->d_wdown[i], true, h, false, n, kHidden, inter, 1.0f);
-                }();
-            }
-        }
-        gemm_set_lane(0);
-        // Join even after a failed launch, so that a capture in progress can be ended by the caller.
-        for (int b = 1; b < nb; ++b) {
-            cudaError_t e1 = cudaEventRecord(st->ev_join[b - 1], st->br_stream[b - 1]);
-            cudaError_t e2 = cudaStreamWaitEvent(s, st->ev_join[b - 1], 0);
-            if (rc == 0 && (e1 != cudaSuccess || e2 != cudaSuccess)) {
-                set_error("decode branches: join failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
-                rc = B200ATTN_ERR_CUDA;
-            }
-        }
-        *pending_out = 0;
-        return rc;
-    }
     const bool many_rows = !decode && rows > 128;      // prefill: no pending partials, warp-per-row norm
     for (int i = 0; i < st->cfg.num_layers; ++i) {
         if (many_rows)
@@ -673,9 +521,8 @@ static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int
                                                       (size_t)128 * kHidden);
     B2_LAUNCH_CHECK();
     // LM head with the argmax in the GEMM epilogue (the logits never reach memory): 103 us per step against 112 + 31 us for
-    // the cuBLAS GEMM and the argmax kernel.  B200ATTN_LM_HEAD=cublas selects the latter.
-    const char* lm = std::getenv("B200ATTN_LM_HEAD");
-    if (n_seqs <= 128 && !(lm && lm[0] == 'c'))
+    // the cuBLAS GEMM and the argmax kernel.  B200ATTN_LM_HEAD=cublas (read at create time) selects the latter.
+    if (n_seqs <= 128 && !g_flags.lm_head_cublas)
         return gemm_tc_argmax(s, st->d_xb, st->d_embed, st->d_packed, d_next, n_seqs, st->cfg.vocab_size, kHidden, st->d_error);
     B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_embed, true, st->d_logits, false, n_seqs, st->cfg.vocab_size, kHidden));
     argmax_kernel<<<n_seqs, 1024, 0, s>>>(st->d_logits, st->cfg.vocab_size, d_next);
@@ -702,8 +549,7 @@ extern "C" int b200attn_stack_prefill(b200attn_stack st, int n_seqs, int prompt_
     cudaStream_t s = as_stream(stream);
     const int chunk = std::max(1, std::min(n_seqs, st->max_rows / prompt_len));
     std::vector<int> slots(chunk), counts(chunk, prompt_len);
-    int* d_idx = nullptr;   // row index of each sequence's last token inside the chunk: reuse the tail of d_tokens scratch
-    B2_CUDA(cudaMalloc(&d_idx, (size_t)chunk * 4));
+    int* d_idx = st->d_last_idx;   // row of each sequence's last token inside the pass
     int rc = 0;
     for (int s0 = 0; s0 < n_seqs && rc == 0; s0 += chunk) {
         const int n = std::min(chunk, n_seqs - s0);
@@ -718,16 +564,7 @@ extern "C" int b200attn_stack_prefill(b200attn_stack st, int n_seqs, int prompt_
         count_launch();
         rc = stack_head(st, n, d_idx, pending, d_next + s0, d_hidden_out ? d_hidden_out + (size_t)s0 * kHidden : nullptr, s);
     }
-    cudaError_t e = cudaStreamSynchronize(s);
-    cudaFree(d_idx);
-    if (rc != 0) return rc;
-    if (e != cudaSuccess) B2_FAIL(B200ATTN_ERR_CUDA, "stack_prefill: %s", cudaGetErrorString(e));
-    if (st->pool) {
-        int err = 0;
-        B2_CUDA(cudaMemcpy(&err, st->pool->d_error, 4, cudaMemcpyDeviceToHost));
-        if (err != 0) B2_FAIL(B200ATTN_ERR_DEVICE, "stack_prefill: device status %d", err);
-    }
-    return 0;
+    return rc;
 }
 
 extern "C" int b200attn_stack_decode(b200attn_stack st, int n_seqs, const int* d_tokens_in, int* d_tokens_out,

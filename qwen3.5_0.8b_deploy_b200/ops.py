@@ -18,7 +18,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200attn.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_NOMEM, ERR_NOT_READY, ERR_UNSUPPORTED, ERR_DEVICE = 0, -1, -2, -3, -4, -5, -6
-PROJ_FP32, PROJ_BF16 = 0, 1
+PROJ_FP32, PROJ_FP16 = 0, 1
 KV_INT8, KV_FP16 = 0, 1
 
 # Every symbol include/b200attn.h declares (tests check the library exports exactly these).
@@ -38,7 +38,6 @@ ABI_SYMBOLS = [
     "b200attn_stack_device_status",
     "b200attn_stack_prefill", "b200attn_stack_decode", "b200attn_decode_graph_capture",
     "b200attn_decode_graph_launch", "b200attn_stack_set_tokens", "b200attn_stack_get_tokens",
-    "b200attn_selftest_umma",
 ]
 
 
@@ -463,9 +462,3 @@ def profile_read(name: str) -> tuple[float, int]:
     ms, n = C.c_double(0.0), C.c_longlong(0)
     _check(_lib.b200attn_profile_read(name.encode(), C.byref(ms), C.byref(n)))
     return ms.value, n.value
-
-
-def selftest_umma(variant: int, a: torch.Tensor, b: torch.Tensor, n: int, k: int) -> torch.Tensor:
-    d = torch.empty((128, n), dtype=torch.float32, device="cuda")
-    _check(_lib.b200attn_selftest_umma(C.c_int(variant), C.c_int(n), C.c_int(k), _dev(a), _dev(b), _dev(d), _stream()))
-    return d

@@ -61,14 +61,66 @@ def test_layer_against_reference_fixture(ops, cuda, synth):
     assert ok, msg
 
 
-def test_layer_bf16_projections(ops, cuda, oracle, synth):
+@pytest.mark.parametrize("kv_dtype,kv_mode", [(0, 1), (1, 2)])
+def test_layer_prefill128_decode16_fp16_projections(ops, cuda, oracle, synth, kv_dtype, kv_mode, capsys):
+    """The same workload in the precision the benchmark runs: fp16 weights and activations in the projections, fp32
+    accumulation.  Held to the same bound as the fp32 mode; the measured error is printed."""
     w = synth.fa_weights(32)
-    x = synth.hidden_states(32, "bf16.x", 80)
-    want = oracle.OracleFullAttention(w, 80, kv_mode=1).forward_sequence(x)
-    got, _, _ = _run_layer(ops, cuda, w, x, 70, ops.KV_INT8, ops.PROJ_BF16)
-    # bf16 operands in the 1024- and 2048-long projections: looser absolute floor
-    ok, msg = allclose_report(got, want, 1e-2, 2e-2)
+    x = synth.hidden_states(32, "cfg0.fp16.x", 144)
+    want = oracle.OracleFullAttention(w, 144, kv_mode=kv_mode).forward_sequence(x)
+    got, _, _ = _run_layer(ops, cuda, w, x, 128, kv_dtype, ops.PROJ_FP16)
+    ok, msg = allclose_report(got, want, ATOL, RTOL)
+    with capsys.disabled():
+        print(f"\n[fa fp16 projections, kv_dtype {kv_dtype}] {msg}")
     assert ok, msg
+
+
+@pytest.mark.parametrize("proj", [0, 1])
+def test_int8_decode_512_steps_after_prompt_1024(ops, cuda, oracle, synth, proj, capsys):
+    """The INT8-cache decode workload at its stated length on a sub-batch the CPU checker can follow: 4 sequences,
+    prompt 1024 then 512 single-token steps (512 quantise-on-append + decode-attention launches per sequence, caches
+    growing from 1025 to 1536 tokens across page boundaries), fp32 and fp16 projections.  Outputs of the prompt pass
+    and of every step against the oracle; lengths, codes and scales at the end."""
+    import threading
+    torch = cuda
+    n, P, G = 4, 1024, 512
+    w = synth.fa_weights(34)
+    xs = [synth.hidden_states(34, f"cfg2.{i}", P + G) for i in range(n)]
+    want = [None] * n
+    refs = [oracle.OracleFullAttention(w, P + G, kv_mode=1) for _ in range(n)]
+
+    def run_ref(i):
+        want[i] = refs[i].forward_sequence(xs[i])
+    ths = [threading.Thread(target=run_ref, args=(i,)) for i in range(n)]
+    [t.start() for t in ths]
+    fa = ops.FullAttention(proj, max_batch=n, max_prefill_rows=n * P)
+    fa.set_weights(w)
+    kv = ops.KVCache(1, n, P + G, ops.KV_INT8)
+    slots = [kv.allocate_sequence(P + G) for _ in range(n)]
+    xt = [torch.from_numpy(x).cuda() for x in xs]
+    y0 = fa.forward_batch_prefill(torch.cat([x[:P] for x in xt]), kv, 0, slots, [P] * n).cpu().numpy()
+    d_slots = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    steps = []
+    for t in range(P, P + G):
+        steps.append(fa.forward(torch.stack([x[t] for x in xt]), kv, 0, d_slots))
+    got_steps = torch.stack(steps).cpu().numpy()                 # [G, n, 1024]
+    assert kv.device_status() == 0
+    [t.join() for t in ths]
+    worst = ""
+    for i in range(n):
+        got = np.concatenate([y0[i * P:(i + 1) * P], got_steps[:, i]])
+        ok, msg = allclose_report(got, want[i], ATOL, RTOL)
+        worst = msg
+        assert ok, f"sequence {i}: {msg}"
+        assert kv.length(0, slots[i]) == P + G
+        kc, vc, ks, vs = [t.cpu().numpy() for t in kv.export(0, slots[i])]
+        # the codes follow the projection's rounding (bit-exactness on identical fp32 K/V is tested in test_gpu_kv.py)
+        assert np.abs(kc.reshape(P + G, 512).astype(int) - refs[i].k_codes.astype(int)).max() <= 1
+        assert np.abs(vc.reshape(P + G, 512).astype(int) - refs[i].v_codes.astype(int)).max() <= 1
+        np.testing.assert_allclose(ks, refs[i].k_scale, rtol=2e-3 if proj else 1e-5)
+        np.testing.assert_allclose(vs, refs[i].v_scale, rtol=2e-3 if proj else 1e-5)
+    with capsys.disabled():
+        print(f"\n[fa int8 decode 1024 + 512, proj {proj}] {worst}")
 
 
 def test_prefill_ragged_batch_and_continuation(ops, cuda, oracle, synth):

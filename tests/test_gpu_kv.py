@@ -148,3 +148,55 @@ def test_append_rejects_bad_batches(ops, cuda):
     assert kv.length(0, s) == 0
     kv.clear()
     assert kv.length(0, s) == 0
+
+
+def test_bookkeeping_after_decode_on_a_side_stream(ops, cuda, synth):
+    """Decode steps advance the cache lengths on the device, on whatever stream the caller uses.  After steps on a
+    non-blocking side stream (which the legacy default stream does not wait for), the length query, a follow-up
+    prefill-append and a shrink must see the advanced lengths without any manual synchronisation in between."""
+    torch = cuda
+    w = synth.fa_weights(72)
+    fa = ops.FullAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=256)   # a continuation stages its whole context
+    fa.set_weights(w)
+    kv = ops.KVCache(1, 2, 256, ops.KV_INT8)
+    slots = [kv.allocate_sequence(200) for _ in range(2)]        # decode steps cannot grow a sequence: pages are reserved up front
+    x = torch.from_numpy(synth.hidden_states(72, "side.x", 2 * 40 + 2 * 30 + 2 * 10)).cuda()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    d_slots = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        fa.forward_batch_prefill(x[:80].contiguous(), kv, 0, slots, [40, 40])
+        for t in range(30):
+            fa.forward(x[80 + 2 * t:82 + 2 * t].contiguous(), kv, 0, d_slots)
+        assert kv.length(0, slots[0]) == 70 and kv.length(0, slots[1]) == 70        # no synchronize before the query
+        for t in range(3):
+            fa.forward(x[80 + 2 * t:82 + 2 * t].contiguous(), kv, 0, d_slots)
+        fa.forward_batch_prefill(x[140:160].contiguous(), kv, 0, slots, [10, 10])     # must append at 73, not at 70
+        assert kv.length(0, slots[0]) == 83
+        for t in range(2):
+            fa.forward(x[80 + 2 * t:82 + 2 * t].contiguous(), kv, 0, d_slots)
+        kv.shrink_sequence(slots[1], 64)                                            # 85 -> 64: one page stays
+        assert kv.length(0, slots[1]) == 64 and kv.length(0, slots[0]) == 85
+        assert kv.pages()[1] == 4 + 1                                                # slot 0 keeps its 4 reserved pages
+    assert kv.device_status() == 0
+
+
+def test_decode_after_free_gives_zero_output(ops, cuda, synth):
+    """A released slot keeps no length on the device: a decode-attention launch that still names it writes its defined
+    zero output instead of attending over pages that may belong to another sequence by then."""
+    torch = cuda
+    fa = ops.FullAttention(ops.PROJ_FP32, max_batch=2, max_prefill_rows=64)
+    kv = ops.KVCache(1, 2, 128, ops.KV_FP16)
+    a, b = kv.allocate_sequence(0), kv.allocate_sequence(0)
+    k = torch.from_numpy(synth.normal(73, "k", (100, 512), 1.0)).cuda()
+    v = torch.from_numpy(synth.normal(73, "v", (100, 512), 0.6)).cuda()
+    kv.append(0, [a, b], [60, 40], k, v)
+    q = torch.from_numpy(synth.normal(73, "q", (2, 8, 256), 1.0)).cuda()
+    d_slots = torch.tensor([a, b], dtype=torch.int32, device="cuda")
+    before = fa.decode_core(q, kv, 0, d_slots).clone()
+    kv.release_sequence(a)
+    after = fa.decode_core(q, kv, 0, d_slots)
+    assert not after[0].any(), "released slot still produced attention output"
+    assert torch.equal(after[1], before[1])
+    assert kv.device_status() == 0

@@ -35,6 +35,76 @@ def test_layer_prefill1024_outputs_and_final_state(ops, cuda, oracle, synth):
     np.testing.assert_allclose(conv.cpu().numpy(), ref.conv_state, rtol=1e-4, atol=1e-5)
 
 
+def test_layer_prefill1024_fp16_projections(ops, cuda, oracle, synth, capsys):
+    """The same workload in the precision the benchmark runs (fp16 weights and activations in the projections, fp32
+    accumulation), held to the same bounds; the measured errors are printed."""
+    torch = cuda
+    w = synth.la_weights(56)
+    x = synth.hidden_states(56, "cfg1.fp16.x", 1024)
+    ref = oracle.OracleLinearAttention(w)
+    want = ref.forward_sequence(x)
+    la = ops.LinearAttention(ops.PROJ_FP16, max_batch=2, max_prefill_rows=1024)
+    la.set_weights(w)
+    st = ops.LinearAttnState(1, 2)
+    got = la.forward_batch(torch.from_numpy(x).cuda(), st, 0, [0], [1024]).cpu().numpy()
+    ok, msg = allclose_report(got, want, ATOL, RTOL)
+    rec, conv = st.export_state(0, 0)
+    rel = _rel(rec.cpu().numpy(), ref.recurrent)
+    with capsys.disabled():
+        print(f"\n[la fp16 projections, 1024 tokens] {msg}; state rel {rel:.3e}")
+    assert ok, msg
+    assert rel <= STATE_REL
+    assert la.device_status() == 0
+
+
+@pytest.mark.parametrize("proj", [0, 1])
+def test_recurrent_decode_512_steps_three_layers(ops, cuda, oracle, synth, proj, capsys):
+    """The recurrent-decode workload at its stated length on a sub-batch the CPU checker can follow: 2 sequences x 3
+    DeltaNet layers, states ~ N(0, 0.05), conv caches warm, 512 single-token steps per layer; outputs every step and
+    the final states, fp32 and fp16 projections."""
+    import threading
+    torch = cuda
+    n, layers, steps = 2, 3, 512
+    ws = [synth.la_weights(60, f"cfg3.L{l}") for l in range(layers)]
+    las = []
+    for l in range(layers):
+        la = ops.LinearAttention(proj, max_batch=n, max_prefill_rows=64)
+        la.set_weights(ws[l])
+        las.append(la)
+    st = ops.LinearAttnState(layers, n)
+    xs = synth.normal(60, "cfg3.x", (steps, layers, n, 1024), 1.0)
+    refs, want = {}, {}
+    for l in range(layers):
+        for i in range(n):
+            r = oracle.OracleLinearAttention(ws[l])
+            r.recurrent[:] = synth.normal(60, f"state.{l}.{i}", (16, 128, 128), 0.05)
+            r.conv_state[:] = synth.normal(60, f"conv.{l}.{i}", (6144, 3), 0.5)
+            st.import_state(l, i, torch.from_numpy(r.recurrent).cuda(), torch.from_numpy(r.conv_state).cuda())
+            refs[l, i] = r
+
+    def run_ref(l, i):
+        want[l, i] = np.stack([refs[l, i].forward(xs[t, l, i]) for t in range(steps)])
+    ths = [threading.Thread(target=run_ref, args=k) for k in refs]
+    [t.start() for t in ths]
+    d_slots = torch.arange(n, dtype=torch.int32, device="cuda")
+    xd = torch.from_numpy(xs).cuda()
+    got = torch.stack([torch.stack([las[l].forward(xd[t, l].contiguous(), st, l, d_slots) for l in range(layers)]) for t in range(steps)])
+    got = got.cpu().numpy()                                      # [steps, layers, n, 1024]
+    [t.join() for t in ths]
+    worst_rel, last = 0.0, ""
+    for (l, i), r in refs.items():
+        ok, msg = allclose_report(got[:, l, i], want[l, i], ATOL, RTOL)
+        last = msg
+        assert ok, f"layer {l} sequence {i}: {msg}"
+        rec, conv = st.export_state(l, i)
+        rel = _rel(rec.cpu().numpy(), r.recurrent)
+        worst_rel = max(worst_rel, rel)
+        assert rel <= STATE_REL, f"layer {l} sequence {i}: state rel {rel:.3e}"
+        np.testing.assert_allclose(conv.cpu().numpy(), r.conv_state, rtol=1e-3 if proj else 1e-4, atol=1e-3 if proj else 1e-5)
+    with capsys.disabled():
+        print(f"\n[la decode 512 steps x 3 layers, proj {proj}] {last}; worst state rel {worst_rel:.3e}")
+
+
 def test_layer_against_reference_fixture(ops, cuda, synth):
     torch = cuda
     g = np.load(os.path.join(GOLD, "la_ref_seed202_t24.npz"))
@@ -57,14 +127,9 @@ def test_layer_against_reference_fixture(ops, cuda, synth):
     np.testing.assert_allclose(conv.cpu().numpy(), g["conv"], rtol=1e-4, atol=1e-5)
 
 
-@pytest.mark.parametrize("kernel,occ", [("classic", ""), ("classic", "512"), ("stream", ""), ("prefetch", "")])
-def test_decode_from_seeded_state(ops, cuda, oracle, synth, monkeypatch, kernel, occ):
+def test_decode_from_seeded_state(ops, cuda, oracle, synth):
     """Recurrent decode: 4 sequences, state ~ N(0, 0.05) and a warm conv cache imported in the
-    reference's layouts, 24 single-token steps; outputs every step, state at the end.  Every form of the decode
-    kernel: one CTA per unit with 256 threads or 512 threads, the persistent one with a TMA state ring, and the
-    persistent one that prefetches the next state by TMA; the library reads the variables per call."""
-    monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
-    monkeypatch.setenv("B200ATTN_LA_DECODE_OCC", occ)
+    reference's layouts, 24 single-token steps; outputs every step, state at the end."""
     torch = cuda
     w = synth.la_weights(52)
     n, steps = 4, 24
@@ -128,42 +193,41 @@ def test_decode_full_batch_against_oracle(ops, cuda, oracle, synth):
     assert la.device_status() == 0
 
 
-def test_persistent_decode_kernels_equal_classic_kernel(ops, cuda, synth, monkeypatch):
-    """72 sequences x 16 heads = 1152 units on 148 (state ring) or 444 (prefetch) persistent CTAs: every CTA walks
-    several units (stage reuse, write-back, refill).  They do the same arithmetic in the same order as the 256-thread
-    one-CTA-per-unit kernel, so outputs, recurrent states and conv states must be identical bit for bit.  One slot is
-    out of range and must be skipped."""
+def test_decode_core_back_to_back_on_one_layer(ops, cuda, oracle, synth):
+    """The core entry called eight times in a row on one layer and one stream with nothing in between (token by token,
+    two sequences = 32 CTAs, far less than one wave): launch k + 1 must see the state launch k wrote.  Outputs and the
+    final state against the CPU oracle's recurrence fed with the same projected rows."""
     torch = cuda
-    n, steps = 72, 3
+    w = synth.la_weights(59)
+    n, steps = 2, 8
     la = ops.LinearAttention(ops.PROJ_FP32, max_batch=n, max_prefill_rows=64)
-    la.set_weights(synth.la_weights(57))
-    g = torch.Generator(device="cuda").manual_seed(57)
-    results = {}
-    monkeypatch.setenv("B200ATTN_LA_DECODE_OCC", "3")     # 256 threads, 16 state rows per warp, as in the persistent kernel
-    for kernel in ("classic", "stream", "prefetch"):
-        monkeypatch.setenv("B200ATTN_LA_DECODE", kernel)
-        st = ops.LinearAttnState(1, n)
-        g.manual_seed(57)
-        for i in range(0, n, 9):
-            st.import_state(0, i, torch.randn((16, 128, 128), device="cuda", generator=g) * 0.05,
-                            torch.randn((6144, 3), device="cuda", generator=g) * 0.5)
-        slots = torch.arange(n, dtype=torch.int32, device="cuda")
-        slots[5] = -1
-        outs = []
-        for t in range(steps):
-            mixed = torch.randn((n, 8224), device="cuda", generator=g) * 0.6
-            outs.append(la.decode_core(mixed, st, 0, slots).clone())
-        states = [st.export_state(0, i) for i in (0, 5, 9, 36, 71)]
-        results[kernel] = (outs, states)
-        assert la.device_status() == 0
-    keep = torch.ones(n, dtype=torch.bool, device="cuda")
-    keep[5] = False                          # the skipped sequence's output rows are not written by any kernel
-    for other in ("stream", "prefetch"):
-        for a, b in zip(results["classic"][0], results[other][0]):
-            assert torch.equal(a[keep], b[keep]), other
-        for (ra, ca), (rb, cb) in zip(results["classic"][1], results[other][1]):
-            assert torch.equal(ra, rb) and torch.equal(ca, cb), other
-        assert not results[other][1][1][0].any()     # slot 5's state was never touched
+    la.set_weights(w)
+    st = ops.LinearAttnState(1, n)
+    refs = [oracle.OracleLinearAttention(w) for _ in range(n)]
+    for i, r in enumerate(refs):
+        r.recurrent[:] = synth.normal(59, f"state.{i}", (16, 128, 128), 0.05)
+        r.conv_state[:] = synth.normal(59, f"conv.{i}", (6144, 3), 0.5)
+        st.import_state(0, i, torch.from_numpy(r.recurrent).cuda(), torch.from_numpy(r.conv_state).cuda())
+    d_slots = torch.arange(n, dtype=torch.int32, device="cuda")
+    xs = [synth.hidden_states(59, f"b2b.{t}", n) for t in range(steps)]
+    w_in = np.concatenate([w["w_qkv"], w["w_z"], w["w_a"], w["w_b"]]).astype(np.float64)
+    mixed = [torch.from_numpy((x.astype(np.float64) @ w_in.T).astype(np.float32)).cuda() for x in xs]
+    torch.cuda.synchronize()
+    outs = [la.decode_core(m, st, 0, d_slots) for m in mixed]        # eight launches queued back to back
+    torch.cuda.synchronize()
+    for t in range(steps):
+        for i in range(n):
+            tap = {}
+            refs[i].forward(xs[t][i], tap)
+            core = tap["core"].reshape(16, 128).astype(np.float64)
+            z = (xs[t][i].astype(np.float64) @ w["w_z"].astype(np.float64).T).reshape(16, 128)
+            want = core / np.sqrt((core ** 2).mean(axis=1, keepdims=True) + 1e-6) * w["norm_w"][None, :] * (z / (1.0 + np.exp(-z)))
+            ok, msg = allclose_report(outs[t][i].cpu().numpy().reshape(16, 128), want, ATOL, RTOL)
+            assert ok, f"step {t} sequence {i}: {msg}"
+    for i in range(n):
+        rec, conv = st.export_state(0, i)
+        assert _rel(rec.cpu().numpy(), refs[i].recurrent) <= STATE_REL, f"sequence {i}"
+        np.testing.assert_allclose(conv.cpu().numpy(), refs[i].conv_state, rtol=1e-4, atol=1e-5)
 
 
 def test_ragged_batch_and_continuation(ops, cuda, oracle, synth):
