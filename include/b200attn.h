@@ -105,9 +105,9 @@ int b200attn_kv_seq_alloc(b200attn_kv_pool pool, int reserve_tokens, int* slot_o
 int b200attn_kv_seq_reserve(b200attn_kv_pool pool, int slot, int total_tokens);
 /* PagedKVCache::release_sequence (paged_kv.cpp:138-148). */
 int b200attn_kv_seq_free(b200attn_kv_pool pool, int slot);
-/* PagedKVCache::shrink_sequence (paged_kv.cpp:150-168): truncate a sequence to new_len tokens in every layer and
- * return the pages behind the new end to the pool (one page is always kept).  new_len >= the current length is a
- * no-op.  Synchronises with the device (lengths live there). */
+/* PagedKVCache::shrink_sequence (paged_kv.cpp:150-168): truncate a sequence to new_len tokens in every layer (layers
+ * that hold fewer keep theirs) and return the pages wholly behind new_len to the pool, reserved-ahead pages included
+ * (one page is always kept).  Synchronises with the device (lengths live there). */
 int b200attn_kv_seq_shrink(b200attn_kv_pool pool, int slot, int new_len);
 /* CudaKVCache::clear (full_attention_cuda.cu:337-356): all lengths to zero, pages kept. */
 int b200attn_kv_clear(b200attn_kv_pool pool, b200attn_stream stream);

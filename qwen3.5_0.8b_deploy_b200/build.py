@@ -67,14 +67,16 @@ def build_compat(force: bool = False) -> None:
     comp = os.path.join(HERE, "compat")
     lib = os.path.join(HERE, "libb200attn_compat.so")
     exe = os.path.join(comp, "compat_check")
-    srcs = [os.path.join(comp, f) for f in ("qwen_cuda_compat.cpp", "qwen_cuda_compat.hpp", "compat_check.cpp")]
+    srcs = [os.path.join(comp, f) for f in ("qwen_cuda_compat.cpp", "qwen_cuda_compat.hpp", "compat_check.cpp", "qwen_cuda_compat_free.cu")]
     newest = max(os.path.getmtime(f) for f in srcs + [OUT])
     if not force and os.path.exists(lib) and os.path.exists(exe) and min(os.path.getmtime(lib), os.path.getmtime(exe)) > newest:
         return
     cxx = os.environ.get("CXX", "g++")
     common = ["-std=c++17", "-O2", "-I/usr/local/cuda/include", "-L/usr/local/cuda/lib64", f"-L{HERE}"]
+    free_obj = os.path.join(OBJ, "qwen_cuda_compat_free.o")     # the free launchers carry small conversion kernels
     for cmd in (
-        [cxx, *common, "-fPIC", "-shared", "-o", lib, srcs[0], "-lb200attn", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"],
+        [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-c", srcs[3], "-o", free_obj],
+        [cxx, *common, "-fPIC", "-shared", "-o", lib, srcs[0], free_obj, "-lb200attn", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,/usr/local/cuda/lib64"],
         [cxx, *common, "-o", exe, srcs[2], "-lb200attn_compat", "-lb200attn", "-lcudart", "-Wl,-rpath,$ORIGIN/..",
          "-Wl,-rpath,/usr/local/cuda/lib64"],
     ):

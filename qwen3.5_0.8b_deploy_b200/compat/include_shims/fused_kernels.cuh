@@ -1,0 +1,3 @@
+// Same file name as the reference header (src/backend/cuda/include/fused_kernels.cuh); forwards to the b200attn-backed declarations.
+#pragma once
+#include "../qwen_cuda_compat.hpp"

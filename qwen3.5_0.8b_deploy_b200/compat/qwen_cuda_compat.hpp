@@ -4,7 +4,8 @@
 //   src/backend/cuda/include/full_attention_cuda.hpp:11-58   (CudaKVCache, CudaFullAttention)
 //   src/backend/cuda/include/linear_attention_cuda.hpp:11-51 (CudaLinearAttnState, CudaLinearAttention)
 //   src/backend/cuda/include/linear_attention_v2.cuh:10-33   (CudaLinearAttentionV2)
-//   src/backend/cuda/include/flash_attention.cuh:25-27       (flash_attention_decode)
+//   src/backend/cuda/include/flash_attention.cuh:25-27, flash_attention_int8.cuh:41-69, fused_kernels.cuh:37-82,
+//   kv_int8_cuda.hpp:11-43, paged_kv.hpp:18-58, cuda_engine.hpp:166-169   (free launchers and cache types, below)
 // so the reference's layer code (src/backend/cuda/kernels/cuda_engine.cu:109-156) and its stand-alone checks
 // (src/backend/cuda/verify_linear_attn_batch.cu, tests/integration/v2_kernel_accuracy_validate.cu) compile against
 // this header instead.  Differences a maintainer has to know are listed next to each member.
@@ -12,8 +13,11 @@
 
 #include <cuda_runtime.h>
 
+#include <cuda_fp16.h>
+
 #include <cstdint>
 #include <stdexcept>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/b200attn.h"
@@ -113,7 +117,7 @@ class CudaLinearAttention {
   protected:
     int hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_;
     b200attn_la op_ = nullptr;
-    int proj_precision_ = B200ATTN_PROJ_FP16;   // the reference rounds these weights to fp16 at load
+    int proj_precision_ = B200ATTN_PROJ_FP16;   // 16-bit weights (the reference rounds these weights to bf16 at load)
 };
 
 // Same operator with fp32 weights and an explicit stream on forward_batch (linear_attention_v2.cuh:10-33).
@@ -137,6 +141,92 @@ class CudaLinearAttentionV2 {
     int hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_;
     b200attn_la op_ = nullptr;
 };
+
+// ---- free launchers (qwen_cuda_compat_free.cu) ---------------------------------------------------------------------------
+// They stage the caller's contiguous caches into a private paged pool and run the library's attention cores; shapes
+// other than 8 query heads / 2 kv heads / head_dim 256 throw std::invalid_argument.  Where the reference's CUDA kernels
+// deviate from its CPU classes the CPU semantics are followed: prefill rows are causal (row i of a batch is the token
+// at position seq_len - batch_size + i) and INT8 scales are read per (token, kv head), [layer][max_seq][kv_heads].
+
+// flash_attention.cuh:25-27.  d_Q [8][256], caches [seq_len][2][256] fp32, d_output [8][256]; scale 0 = 1/sqrt(head_dim).
+void flash_attention_decode(const float* d_Q, const float* d_K_cache, const float* d_V_cache, float* d_output, int num_heads,
+                            int num_kv_heads, int q_head_dim, int kv_head_dim, int seq_len, float scale = 0.0f);
+// flash_attention_int8.cuh:41-69.  Caches [layer][max_seq_len][2][256] codes, scales [layer][max_seq_len][2].
+void flash_attention_decode_int8(const float* d_Q, const int8_t* d_K_cache, const int8_t* d_V_cache, const float* d_K_scale,
+                                 const float* d_V_scale, float* d_output, int num_heads, int num_kv_heads, int q_head_dim,
+                                 int kv_head_dim, int seq_len, int layer_idx, int max_seq_len, float scale = 0.0f);
+void flash_attention_decode_int8_batched(const float* d_Q, const int8_t* d_K_cache, const int8_t* d_V_cache,
+                                         const float* d_K_scale, const float* d_V_scale, float* d_output, int num_heads,
+                                         int num_kv_heads, int q_head_dim, int kv_head_dim, int seq_len, int layer_idx,
+                                         int max_seq_len, float scale = 0.0f);
+// fused_kernels.cuh:37-82.  Q / output [batch_size][8][256]; caches indexed layer * max_seq_len * 512 + t * 512 + kvh * 256 + d.
+void launch_flash_attn_v2_prefill(const float* Q, const float* K_cache, const float* V_cache, float* output, int num_heads,
+                                  int num_kv_heads, int head_dim, int seq_len, int batch_size, int layer_idx, int max_seq_len,
+                                  float scale, cudaStream_t stream = 0);
+void launch_flash_attn_v2_prefill_fp16_cache(const float* Q, const half* K_cache, const half* V_cache, float* output,
+                                             int num_heads, int num_kv_heads, int head_dim, int seq_len, int batch_size,
+                                             int layer_idx, int max_seq_len, float scale, cudaStream_t stream = 0);
+void launch_flash_attn_v2_prefill_int8_cache(const float* Q, const int8_t* K_cache, const int8_t* V_cache, const float* K_scale,
+                                             const float* V_scale, float* output, int num_heads, int num_kv_heads, int head_dim,
+                                             int seq_len, int batch_size, int layer_idx, int max_seq_len, float scale,
+                                             cudaStream_t stream = 0);
+
+// kv_int8_cuda.hpp:11-43.  Codes [layer][max_seq_len][kv_heads * head_dim]; scales [layer][max_seq_len][kv_heads] (one
+// per token and kv head; the reference's append kernel lets two blocks race for one slot per token).
+struct CudaKVCacheINT8 {
+    int8_t* d_k_cache = nullptr;
+    int8_t* d_v_cache = nullptr;
+    float* d_k_scale = nullptr;
+    float* d_v_scale = nullptr;
+    std::vector<int> layer_lengths;
+    int num_layers = 0;
+    int num_kv_heads = 0;
+    int head_dim = 0;
+    int max_seq_len = 0;
+    size_t bytes_allocated = 0;
+    void reset(int nl, int nkh, int hd, int max_len);
+    void clear();
+    int length(int layer_idx) const { return layer_lengths[layer_idx]; }
+    size_t memory_bytes() const { return bytes_allocated; }
+};
+// One scale per 256 consecutive values: scale = absmax / 127 (1 below 1e-8), code = roundf(x / scale).
+void kv_quantize_fp32_to_int8(const float* d_input, int8_t* d_output, float* d_scale, int num_elements, cudaStream_t stream = 0);
+void kv_dequantize_int8_to_fp32(const int8_t* d_input, const float* d_scale, float* d_output, int num_elements,
+                                cudaStream_t stream = 0);
+void kv_append_int8(CudaKVCacheINT8& cache, const float* d_k, const float* d_v, int layer_idx, cudaStream_t stream = 0);
+void kv_get_int8(const CudaKVCacheINT8& cache, float* d_k_out, float* d_v_out, int layer_idx, cudaStream_t stream = 0);
+
+// paged_kv.hpp:18-58: the reference's page bookkeeping interface on the library's page pool (pages of 64 tokens).
+class PagedKVCache {
+  public:
+    PagedKVCache();
+    ~PagedKVCache();
+    void initialize(int num_layers, int num_kv_heads, int head_dim, int page_size, int max_pages);
+    void clear();
+    int allocate_sequence(int initial_len = 0);   // -1 when the pool cannot serve it (paged_kv.cpp:90-112)
+    void append_tokens(int seq_id, int num_tokens);
+    void release_sequence(int seq_id);
+    void shrink_sequence(int seq_id, int new_len);
+    size_t get_kv_bytes() const;
+    size_t get_gpu_bytes() const;
+    int get_allocated_pages() const;
+    int get_used_pages() const;
+    void print_status() const;
+    b200attn_kv_pool pool() const { return pool_; }                 // library handle (not in the reference)
+    int slot_of(int seq_id) const { auto it = seq_to_slot_.find(seq_id); return it == seq_to_slot_.end() ? -1 : it->second; }
+
+  private:
+    b200attn_kv_pool pool_ = nullptr;
+    std::unordered_map<int, int> seq_to_slot_;
+    std::unordered_map<int, int> seq_lengths_;
+    int num_layers_ = 0, num_kv_heads_ = 0, head_dim_ = 0, page_size_ = 0, max_pages_ = 0, next_seq_id_ = 1;
+    size_t gpu_bytes_ = 0;
+};
+
+// cuda_engine.hpp:166-169.
+void set_fa_weights(CudaFullAttention* fa, const std::vector<float>& q_w, const std::vector<float>& k_w,
+                    const std::vector<float>& v_w, const std::vector<float>& qn_w, const std::vector<float>& kn_w,
+                    const std::vector<float>& o_w, int layer_idx);
 
 }  // namespace cuda
 }  // namespace qwen

@@ -1,0 +1,379 @@
+// The reference's free launchers and cache types on the b200attn C ABI: a caller that holds raw device pointers in
+// the reference's own layouts reaches the new kernels through the signatures it already uses.
+//
+//   flash_attention_decode                          src/backend/cuda/include/flash_attention.cuh:25-27
+//   flash_attention_decode_int8[_batched]           src/backend/cuda/include/flash_attention_int8.cuh:41-69
+//   launch_flash_attn_v2_prefill{,_fp16_cache,_int8_cache}   src/backend/cuda/include/fused_kernels.cuh:37-82
+//   CudaKVCacheINT8, kv_quantize_fp32_to_int8, kv_dequantize_int8_to_fp32, kv_append_int8, kv_get_int8
+//                                                   src/backend/cuda/include/kv_int8_cuda.hpp:11-43
+//   PagedKVCache                                    src/backend/cuda/include/paged_kv.hpp:18-58
+//   set_fa_weights                                  src/backend/cuda/include/cuda_engine.hpp:166-169
+//
+// The attention launchers stage the caller's contiguous cache (fp32, half or INT8 + scales, indexed
+// [layer][max_seq][kv_head][dim]) into a private paged pool and run the b200attn_*_core entries on it; the small
+// kernels in this file only convert layouts and number formats.  Semantics follow the reference's CPU classes where
+// its CUDA kernels deviate from them: prefill rows are causal (row i of a batch sits at position seq_len - batch + i),
+// and INT8 scales are read per (token, kv head).
+#include "qwen_cuda_compat.hpp"
+
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+namespace qwen {
+namespace cuda {
+namespace {
+
+void check(int status) {
+    if (status == 0) return;
+    const std::string msg = b200attn_last_error();
+    if (status == B200ATTN_ERR_INVALID) throw std::invalid_argument(msg);
+    throw std::runtime_error(msg);
+}
+void check_cuda(cudaError_t e) {
+    if (e != cudaSuccess) throw std::runtime_error(cudaGetErrorString(e));
+}
+
+// ---- conversion kernels -----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rows_to_f32_kernel(const T* __restrict__ in, const float* __restrict__ scale, int row_elems, int group,
+                                   float* __restrict__ out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = (float)in[i];
+    if (scale) v *= scale[(i / row_elems) * (row_elems / group) + (i % row_elems) / group];   // one scale per `group` elements
+    out[i] = v;
+}
+__global__ void scale_kernel(const float* __restrict__ in, float f, float* __restrict__ out, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = in[i] * f;
+}
+// One block per group of `group` consecutive values: scale = absmax / 127 (1 if below 1e-8), code = roundf(x / scale).
+// The arithmetic of kv_quantize_kernel (src/backend/cuda/kernels/kv_int8_cuda.cu:9-43); a partial last group uses the
+// values it has.
+__global__ void quantize_groups_kernel(const float* __restrict__ in, int8_t* __restrict__ out, float* __restrict__ scale,
+                                       int group, size_t n) {
+    __shared__ float s_max[32];
+    const size_t g0 = (size_t)blockIdx.x * group;
+    float m = 0.f;
+    for (int i = threadIdx.x; i < group && g0 + i < n; i += blockDim.x) m = fmaxf(m, fabsf(in[g0 + i]));
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = 0.f;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) m = fmaxf(m, s_max[w]);
+    float s = __fdiv_rn(m, 127.0f);
+    if (s < 1e-8f) s = 1.0f;
+    if (threadIdx.x == 0) scale[blockIdx.x] = s;
+    for (int i = threadIdx.x; i < group && g0 + i < n; i += blockDim.x) out[g0 + i] = (int8_t)roundf(__fdiv_rn(in[g0 + i], s));
+}
+__global__ void dequantize_groups_kernel(const int8_t* __restrict__ in, const float* __restrict__ scale, float* __restrict__ out,
+                                         int group, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = (float)in[i] * scale[i / group];
+}
+unsigned blocks_for(size_t n) { return (unsigned)((n + 255) / 256); }
+
+// ---- staging area (one per process, grown on demand, guarded: the reference's launchers are not re-entrant either) ----
+struct Staging {
+    std::mutex mu;
+    b200attn_fa fa = nullptr;
+    int fa_rows = 0;
+    b200attn_kv_pool pool = nullptr;
+    int pool_tokens = 0;
+    int slot = -1;
+    int* d_slot = nullptr;
+    float* d_buf[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t buf_elems[4] = {0, 0, 0, 0};
+    float* buf(int i, size_t elems) {
+        if (elems > buf_elems[i]) {
+            cudaFree(d_buf[i]);
+            d_buf[i] = nullptr;
+            check_cuda(cudaMalloc(&d_buf[i], elems * sizeof(float)));
+            buf_elems[i] = elems;
+        }
+        return d_buf[i];
+    }
+    void need_fa(int rows) {
+        if (fa && rows <= fa_rows) return;
+        if (fa) b200attn_fa_destroy(fa);
+        fa = nullptr;
+        fa_rows = std::max(rows, 1024);
+        b200attn_fa_config cfg{1024, 8, 2, 256, 64, 1e7f, B200ATTN_PROJ_FP32, 1, fa_rows};
+        check(b200attn_fa_create(&cfg, &fa));
+    }
+    void need_pool(int tokens) {
+        if (pool && tokens <= pool_tokens) { check(b200attn_kv_clear(pool, nullptr)); return; }
+        if (pool) b200attn_kv_pool_destroy(pool);
+        pool = nullptr;
+        pool_tokens = std::max(((tokens + 63) / 64) * 64, 1024);
+        const int pages = pool_tokens / 64;
+        b200attn_kv_config cfg{1, 2, 256, 64, pages, 1, pages, B200ATTN_KV_FP16};
+        check(b200attn_kv_pool_create(&cfg, &pool));
+        check(b200attn_kv_seq_alloc(pool, pool_tokens, &slot));
+        if (!d_slot) check_cuda(cudaMalloc(&d_slot, sizeof(int)));
+        check_cuda(cudaMemcpy(d_slot, &slot, sizeof(int), cudaMemcpyHostToDevice));
+    }
+};
+Staging& staging() {
+    static Staging s;
+    return s;
+}
+
+void check_shape(int num_heads, int num_kv_heads, int q_head_dim, int kv_head_dim) {
+    if (num_heads != 8 || num_kv_heads != 2 || q_head_dim != 256 || kv_head_dim != 256)
+        throw std::invalid_argument("attention launchers are built for 8 query heads, 2 kv heads, head_dim 256");
+}
+float q_factor(float scale, int head_dim) {       // the kernels apply 1 / sqrt(head_dim); another scale is folded into q
+    const float native = 1.0f / std::sqrt((float)head_dim);
+    return (scale == 0.0f) ? 1.0f : scale / native;
+}
+
+// Decode attention of one query against `seq_len` staged fp32 K / V rows ([seq_len][2][256]).
+void decode_staged(Staging& st, const float* d_q, const float* d_k_rows, const float* d_v_rows, float* d_out, int seq_len,
+                   float scale, cudaStream_t stream) {
+    if (seq_len <= 0) throw std::invalid_argument("seq_len must be > 0");
+    st.need_fa(1);
+    st.need_pool(seq_len);
+    check(b200attn_kv_append(st.pool, 0, &st.slot, &seq_len, 1, d_k_rows, d_v_rows, stream));
+    const float f = q_factor(scale, 256);
+    const float* q = d_q;
+    if (f != 1.0f) {
+        float* qs = st.buf(3, 8 * 256);
+        scale_kernel<<<blocks_for(8 * 256), 256, 0, stream>>>(d_q, f, qs, 8 * 256);
+        q = qs;
+    }
+    check(b200attn_fa_decode_core(st.fa, st.pool, 0, st.d_slot, 1, q, d_out, stream));
+}
+
+// Causal prefill of `batch` query rows that are the LAST `batch` tokens of a `seq_len`-token context given as fp32 rows.
+void prefill_staged(Staging& st, const float* d_q, const float* d_k_rows, const float* d_v_rows, float* d_out, int seq_len,
+                    int batch, float scale, cudaStream_t stream) {
+    if (batch <= 0 || seq_len < batch) throw std::invalid_argument("need 0 < batch_size <= seq_len");
+    st.need_fa(seq_len);
+    // the core entry wants one query row per key row: rows before the batch get zero queries and are dropped afterwards
+    const size_t qe = (size_t)seq_len * 8 * 256, be = (size_t)batch * 8 * 256, off = qe - be;
+    float* q_all = st.buf(2, 2 * qe);
+    float* o_all = q_all + qe;
+    check_cuda(cudaMemsetAsync(q_all, 0, off * sizeof(float), stream));
+    scale_kernel<<<blocks_for(be), 256, 0, stream>>>(d_q, q_factor(scale, 256), q_all + off, be);
+    check(b200attn_fa_prefill_core(st.fa, &seq_len, 1, q_all, d_k_rows, d_v_rows, o_all, 1, stream));
+    check_cuda(cudaMemcpyAsync(d_out, o_all + off, be * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+}
+
+}  // namespace
+
+// ---- decode launchers ------------------------------------------------------------------------------------------------
+void flash_attention_decode(const float* d_Q, const float* d_K_cache, const float* d_V_cache, float* d_output, int num_heads,
+                            int num_kv_heads, int q_head_dim, int kv_head_dim, int seq_len, float scale) {
+    check_shape(num_heads, num_kv_heads, q_head_dim, kv_head_dim);
+    Staging& st = staging();
+    std::lock_guard<std::mutex> lk(st.mu);
+    decode_staged(st, d_Q, d_K_cache, d_V_cache, d_output, seq_len, scale, nullptr);
+}
+
+void flash_attention_decode_int8(const float* d_Q, const int8_t* d_K_cache, const int8_t* d_V_cache, const float* d_K_scale,
+                                 const float* d_V_scale, float* d_output, int num_heads, int num_kv_heads, int q_head_dim,
+                                 int kv_head_dim, int seq_len, int layer_idx, int max_seq_len, float scale) {
+    check_shape(num_heads, num_kv_heads, q_head_dim, kv_head_dim);
+    if (seq_len <= 0 || seq_len > max_seq_len || layer_idx < 0) throw std::invalid_argument("bad seq_len / layer_idx");
+    Staging& st = staging();
+    std::lock_guard<std::mutex> lk(st.mu);
+    const size_t n = (size_t)seq_len * 512, base = (size_t)layer_idx * max_seq_len;
+    float* k = st.buf(0, n);
+    float* v = st.buf(1, n);
+    rows_to_f32_kernel<int8_t><<<blocks_for(n), 256>>>(d_K_cache + base * 512, d_K_scale + base * 2, 512, 256, k, n);
+    rows_to_f32_kernel<int8_t><<<blocks_for(n), 256>>>(d_V_cache + base * 512, d_V_scale + base * 2, 512, 256, v, n);
+    decode_staged(st, d_Q, k, v, d_output, seq_len, scale, nullptr);
+}
+
+void flash_attention_decode_int8_batched(const float* d_Q, const int8_t* d_K_cache, const int8_t* d_V_cache,
+                                         const float* d_K_scale, const float* d_V_scale, float* d_output, int num_heads,
+                                         int num_kv_heads, int q_head_dim, int kv_head_dim, int seq_len, int layer_idx,
+                                         int max_seq_len, float scale) {
+    flash_attention_decode_int8(d_Q, d_K_cache, d_V_cache, d_K_scale, d_V_scale, d_output, num_heads, num_kv_heads, q_head_dim,
+                                kv_head_dim, seq_len, layer_idx, max_seq_len, scale);
+}
+
+// ---- prefill launchers ------------------------------------------------------------------------------------------------
+void launch_flash_attn_v2_prefill(const float* Q, const float* K_cache, const float* V_cache, float* output, int num_heads,
+                                  int num_kv_heads, int head_dim, int seq_len, int batch_size, int layer_idx, int max_seq_len,
+                                  float scale, cudaStream_t stream) {
+    check_shape(num_heads, num_kv_heads, head_dim, head_dim);
+    if (layer_idx < 0 || seq_len > max_seq_len) throw std::invalid_argument("bad seq_len / layer_idx");
+    Staging& st = staging();
+    std::lock_guard<std::mutex> lk(st.mu);
+    const size_t base = (size_t)layer_idx * max_seq_len * 512;
+    prefill_staged(st, Q, K_cache + base, V_cache + base, output, seq_len, batch_size, scale, stream);
+}
+
+void launch_flash_attn_v2_prefill_fp16_cache(const float* Q, const half* K_cache, const half* V_cache, float* output,
+                                             int num_heads, int num_kv_heads, int head_dim, int seq_len, int batch_size,
+                                             int layer_idx, int max_seq_len, float scale, cudaStream_t stream) {
+    check_shape(num_heads, num_kv_heads, head_dim, head_dim);
+    if (layer_idx < 0 || seq_len <= 0 || seq_len > max_seq_len) throw std::invalid_argument("bad seq_len / layer_idx");
+    Staging& st = staging();
+    std::lock_guard<std::mutex> lk(st.mu);
+    const size_t n = (size_t)seq_len * 512, base = (size_t)layer_idx * max_seq_len * 512;
+    float* k = st.buf(0, n);
+    float* v = st.buf(1, n);
+    rows_to_f32_kernel<half><<<blocks_for(n), 256, 0, stream>>>(K_cache + base, nullptr, 512, 256, k, n);
+    rows_to_f32_kernel<half><<<blocks_for(n), 256, 0, stream>>>(V_cache + base, nullptr, 512, 256, v, n);
+    prefill_staged(st, Q, k, v, output, seq_len, batch_size, scale, stream);
+}
+
+void launch_flash_attn_v2_prefill_int8_cache(const float* Q, const int8_t* K_cache, const int8_t* V_cache, const float* K_scale,
+                                             const float* V_scale, float* output, int num_heads, int num_kv_heads, int head_dim,
+                                             int seq_len, int batch_size, int layer_idx, int max_seq_len, float scale,
+                                             cudaStream_t stream) {
+    check_shape(num_heads, num_kv_heads, head_dim, head_dim);
+    if (layer_idx < 0 || seq_len <= 0 || seq_len > max_seq_len) throw std::invalid_argument("bad seq_len / layer_idx");
+    Staging& st = staging();
+    std::lock_guard<std::mutex> lk(st.mu);
+    const size_t n = (size_t)seq_len * 512, base = (size_t)layer_idx * max_seq_len;
+    float* k = st.buf(0, n);
+    float* v = st.buf(1, n);
+    rows_to_f32_kernel<int8_t><<<blocks_for(n), 256, 0, stream>>>(K_cache + base * 512, K_scale + base * 2, 512, 256, k, n);
+    rows_to_f32_kernel<int8_t><<<blocks_for(n), 256, 0, stream>>>(V_cache + base * 512, V_scale + base * 2, 512, 256, v, n);
+    prefill_staged(st, Q, k, v, output, seq_len, batch_size, scale, stream);
+}
+
+// ---- CudaKVCacheINT8 and its helpers ---------------------------------------------------------------------------------
+// Layout: codes [layer][max_seq][kv_heads * head_dim], scales [layer][max_seq][kv_heads] (one scale per token and kv
+// head; the reference's append kernel lets two blocks race for one scale slot per token, kv_int8_cuda.cu:88-99).
+void CudaKVCacheINT8::reset(int nl, int nkh, int hd, int max_len) {
+    clear();
+    num_layers = nl; num_kv_heads = nkh; head_dim = hd; max_seq_len = max_len;
+    layer_lengths.assign(nl, 0);
+    const size_t codes = (size_t)nl * max_len * nkh * hd, scales = (size_t)nl * max_len * nkh;
+    check_cuda(cudaMalloc(&d_k_cache, codes));
+    check_cuda(cudaMalloc(&d_v_cache, codes));
+    check_cuda(cudaMalloc(&d_k_scale, scales * sizeof(float)));
+    check_cuda(cudaMalloc(&d_v_scale, scales * sizeof(float)));
+    check_cuda(cudaMemset(d_k_cache, 0, codes));
+    check_cuda(cudaMemset(d_v_cache, 0, codes));
+    check_cuda(cudaMemset(d_k_scale, 0, scales * sizeof(float)));
+    check_cuda(cudaMemset(d_v_scale, 0, scales * sizeof(float)));
+    bytes_allocated = 2 * codes + 2 * scales * sizeof(float);
+}
+void CudaKVCacheINT8::clear() {
+    cudaFree(d_k_cache); cudaFree(d_v_cache); cudaFree(d_k_scale); cudaFree(d_v_scale);
+    d_k_cache = d_v_cache = nullptr;
+    d_k_scale = d_v_scale = nullptr;
+    bytes_allocated = 0;
+}
+
+void kv_quantize_fp32_to_int8(const float* d_input, int8_t* d_output, float* d_scale, int num_elements, cudaStream_t stream) {
+    if (num_elements <= 0) return;
+    quantize_groups_kernel<<<(num_elements + 255) / 256, 256, 0, stream>>>(d_input, d_output, d_scale, 256, (size_t)num_elements);
+}
+void kv_dequantize_int8_to_fp32(const int8_t* d_input, const float* d_scale, float* d_output, int num_elements,
+                                cudaStream_t stream) {
+    if (num_elements <= 0) return;
+    dequantize_groups_kernel<<<blocks_for((size_t)num_elements), 256, 0, stream>>>(d_input, d_scale, d_output, 256, (size_t)num_elements);
+}
+void kv_append_int8(CudaKVCacheINT8& cache, const float* d_k, const float* d_v, int layer_idx, cudaStream_t stream) {
+    if (layer_idx < 0 || layer_idx >= cache.num_layers) throw std::invalid_argument("layer_idx out of range");
+    const int pos = cache.layer_lengths[layer_idx];
+    if (pos >= cache.max_seq_len) throw std::runtime_error("CudaKVCacheINT8 is full");
+    const int kv = cache.num_kv_heads * cache.head_dim;
+    const size_t row = (size_t)layer_idx * cache.max_seq_len + pos;
+    quantize_groups_kernel<<<cache.num_kv_heads, 256, 0, stream>>>(d_k, cache.d_k_cache + row * kv, cache.d_k_scale + row * cache.num_kv_heads,
+                                                                cache.head_dim, (size_t)kv);
+    quantize_groups_kernel<<<cache.num_kv_heads, 256, 0, stream>>>(d_v, cache.d_v_cache + row * kv, cache.d_v_scale + row * cache.num_kv_heads,
+                                                                cache.head_dim, (size_t)kv);
+    cache.layer_lengths[layer_idx]++;
+}
+void kv_get_int8(const CudaKVCacheINT8& cache, float* d_k_out, float* d_v_out, int layer_idx, cudaStream_t stream) {
+    if (layer_idx < 0 || layer_idx >= cache.num_layers) throw std::invalid_argument("layer_idx out of range");
+    const int pos = cache.layer_lengths[layer_idx] - 1;
+    if (pos < 0) return;
+    const int kv = cache.num_kv_heads * cache.head_dim;
+    const size_t row = (size_t)layer_idx * cache.max_seq_len + pos;
+    dequantize_groups_kernel<<<blocks_for((size_t)kv), 256, 0, stream>>>(cache.d_k_cache + row * kv, cache.d_k_scale + row * cache.num_kv_heads,
+                                                                        d_k_out, cache.head_dim, (size_t)kv);
+    dequantize_groups_kernel<<<blocks_for((size_t)kv), 256, 0, stream>>>(cache.d_v_cache + row * kv, cache.d_v_scale + row * cache.num_kv_heads,
+                                                                        d_v_out, cache.head_dim, (size_t)kv);
+}
+
+// ---- PagedKVCache: the reference's bookkeeping interface over the library's page pool ----------------------------------
+PagedKVCache::PagedKVCache() = default;
+PagedKVCache::~PagedKVCache() { clear(); }
+
+void PagedKVCache::initialize(int num_layers, int num_kv_heads, int head_dim, int page_size, int max_pages) {
+    clear();
+    if (page_size != 64) throw std::invalid_argument("PagedKVCache: the page pool is built for pages of 64 tokens");
+    num_layers_ = num_layers; num_kv_heads_ = num_kv_heads; head_dim_ = head_dim; page_size_ = page_size; max_pages_ = max_pages;
+    // every page can belong to another sequence, and one sequence can own them all
+    b200attn_kv_config cfg{num_layers, num_kv_heads, head_dim, page_size, max_pages, max_pages, max_pages, B200ATTN_KV_INT8};
+    check(b200attn_kv_pool_create(&cfg, &pool_));
+    gpu_bytes_ = (size_t)num_layers * max_pages * page_size * num_kv_heads * (2 * (size_t)head_dim + 2 * sizeof(float));
+}
+void PagedKVCache::clear() {
+    if (pool_) b200attn_kv_pool_destroy(pool_);
+    pool_ = nullptr;
+    seq_to_slot_.clear();
+    seq_lengths_.clear();
+    gpu_bytes_ = 0;
+}
+int PagedKVCache::allocate_sequence(int initial_len) {
+    if (!pool_) return -1;
+    int slot = -1;
+    // like the reference, a new sequence owns at least one page (paged_kv.cpp:93-95)
+    if (b200attn_kv_seq_alloc(pool_, std::max(initial_len, 1), &slot) != 0) return -1;
+    const int seq_id = next_seq_id_++;
+    seq_to_slot_[seq_id] = slot;
+    seq_lengths_[seq_id] = initial_len;
+    return seq_id;
+}
+void PagedKVCache::append_tokens(int seq_id, int num_tokens) {
+    auto it = seq_to_slot_.find(seq_id);
+    if (it == seq_to_slot_.end()) return;
+    const int new_len = seq_lengths_[seq_id] + num_tokens;
+    if (b200attn_kv_seq_reserve(pool_, it->second, new_len) != 0) {
+        std::fprintf(stderr, "[PagedKV] Failed to allocate page for seq %d\n", seq_id);
+        return;
+    }
+    seq_lengths_[seq_id] = new_len;
+}
+void PagedKVCache::release_sequence(int seq_id) {
+    auto it = seq_to_slot_.find(seq_id);
+    if (it == seq_to_slot_.end()) return;
+    b200attn_kv_seq_free(pool_, it->second);
+    seq_to_slot_.erase(it);
+    seq_lengths_.erase(seq_id);
+}
+void PagedKVCache::shrink_sequence(int seq_id, int new_len) {
+    auto it = seq_to_slot_.find(seq_id);
+    if (it == seq_to_slot_.end() || new_len >= seq_lengths_[seq_id]) return;
+    check(b200attn_kv_seq_shrink(pool_, it->second, new_len));   // pages wholly behind new_len go back, one page is kept
+    seq_lengths_[seq_id] = new_len;
+}
+size_t PagedKVCache::get_kv_bytes() const {
+    return (size_t)get_used_pages() * num_layers_ * page_size_ * num_kv_heads_ * (2 * (size_t)head_dim_ + 2 * sizeof(float));
+}
+size_t PagedKVCache::get_gpu_bytes() const { return gpu_bytes_; }
+int PagedKVCache::get_allocated_pages() const { return max_pages_; }
+int PagedKVCache::get_used_pages() const {
+    int total = 0, used = 0;
+    if (pool_) b200attn_kv_pages(pool_, &total, &used);
+    return used;
+}
+void PagedKVCache::print_status() const {
+    std::printf("[PagedKV] Status:\n  Total pages:   %d\n  Used pages:    %d\n  Active seqs:   %zu\n  KV bytes:      %zu MB\n"
+                "  GPU allocated: %zu MB\n", max_pages_, get_used_pages(), seq_to_slot_.size(), get_kv_bytes() >> 20, gpu_bytes_ >> 20);
+}
+
+void set_fa_weights(CudaFullAttention* fa, const std::vector<float>& q_w, const std::vector<float>& k_w,
+                    const std::vector<float>& v_w, const std::vector<float>& qn_w, const std::vector<float>& kn_w,
+                    const std::vector<float>& o_w, int layer_idx) {
+    (void)layer_idx;
+    fa->set_weights(q_w, k_w, v_w, qn_w, kn_w, o_w);
+}
+
+}  // namespace cuda
+}  // namespace qwen

@@ -261,6 +261,7 @@ struct b200attn_la_s {
     float* d_k = nullptr;
     __half* d_qh = nullptr;                // fp16 copies for the tensor-core recurrence
     __half* d_kh = nullptr;
+    __half* d_vh = nullptr;
     float* d_v = nullptr;
     int* d_error = nullptr;                // device status word of the tensor-core recurrence
     float* d_g = nullptr;                  // [max_rows, 16]

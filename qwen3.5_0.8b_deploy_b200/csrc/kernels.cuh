@@ -59,8 +59,8 @@ struct LaSeqMeta {  // per sequence, device array
 };
 int launch_la_conv_seq(const float* mixed, const int* d_row_seq, const LaSeqMeta* d_seqs, const float* conv_layer,
                        size_t conv_stride, const float* conv_w, const float* a_log, const float* dt_bias, int rows,
-                       float* q, float* k, __half* qh, __half* kh, float* v, float* g, float* beta, cudaStream_t s);
-int launch_la_chunk_tc(const __half* q_h, const __half* k_h, const float* v, const float* g, const float* beta,
+                       float* q, float* k, __half* qh, __half* kh, float* v, __half* vh, float* g, float* beta, cudaStream_t s);
+int launch_la_chunk_tc(const __half* q_h, const __half* k_h, const __half* v_h, const float* g, const float* beta,
                        const LaSeqMeta* d_seqs, int n_seqs, int rows, float* rec_layer, size_t rec_stride, float* out,
                        int* d_error, cudaStream_t s);
 int launch_la_conv_state_update(const float* mixed, const LaSeqMeta* d_seqs, int n_seqs, float* conv_layer,

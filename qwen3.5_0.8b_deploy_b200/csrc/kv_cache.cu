@@ -564,20 +564,18 @@ extern "C" int b200attn_kv_seq_shrink(b200attn_kv_pool p, int slot, int new_len)
     B2_CHECK_ARG(slot >= 0 && slot < p->cfg.max_seqs && p->slot_used[slot], "kv_seq_shrink: slot %d is not allocated", slot);
     B2_CHECK_ARG(new_len >= 0, "kv_seq_shrink: negative length");
     B2_TRY(p->sync_lens());
-    // every layer's length drops to new_len (layers that hold fewer tokens keep theirs); a longer new_len changes nothing
-    bool changed = false;
+    // every layer's length drops to new_len (layers that hold fewer tokens keep theirs)
     for (int l = 0; l < p->cfg.num_layers; ++l) {
         int& len = p->h_lens[(size_t)l * p->cfg.max_seqs + slot];
         if (new_len < len) {
             len = new_len;
-            changed = true;
             B2_TRY(push_ints(p->d_lens + (size_t)l * p->cfg.max_seqs + slot, &len, 1));
         }
     }
-    if (!changed) return 0;
-    // pages past the new end go back to the pool; like the reference, a sequence keeps at least one page
+    // pages wholly behind the new end go back to the pool; like the reference, a sequence keeps at least one page
     auto& pages = p->seq_pages[slot];
     const int keep = std::max(1, ceil_div(new_len, kPageTokens));
+    if ((int)pages.size() <= keep) return 0;
     while ((int)pages.size() > keep) {
         p->free_pages.push_back(pages.back());
         pages.pop_back();

@@ -22,7 +22,8 @@
 //   (o)  Ot  [vd x 64]  = S0^T (Q e^b)^T + V_new^T Mq^T       (Q is scaled in place in its TMA tile)
 //   (u)  D3  [vd x kd]  = e^{b_C} D3 + V_new^T (e^{b_C-b} K)  D3 holds S^T for the whole sequence; K is scaled in place
 // tcgen05.mma kind::f16: fp16 operands (the same 10-bit mantissa as tf32), fp32 accumulation; 128-byte swizzle.
-// T itself is built in fp32 in shared memory by a blocked inverse (16 x 16 blocks) on the CUDA cores.
+// T itself is built in fp32 in shared memory by a blocked inverse (16 x 16 blocks) on the CUDA cores, each warp
+// solving its own columns of T from top to bottom.
 //
 // Eight compute warps (two threads per TMEM lane, each owning half of the 64 token columns) and one warp that
 // issues TMA loads and MMAs.  All waits are bounded.
@@ -35,8 +36,9 @@ constexpr int kC = 64;
 // shared-memory map (bytes from a 1024-aligned base); regions are reused as their contents die during a chunk
 constexpr uint32_t kOffKQ = 0;        // [2 blocks of 64 key dims][rows 0-63 K chunk, rows 64-127 Q chunk][128 B]
 constexpr uint32_t kOffV = 32768;     // V chunk [2 blocks of 64 value dims][64 tokens][128 B]; after (uw): V_new^T [128 vd][64 tokens]
-constexpr uint32_t kOffR = 49152;     // 32 KB: fp32 A [64][64] + fp32 T [64][64]  ->  T diag(beta) hi, lo, T diag(beta e^b) hi, lo
-                                      //        (four [64][64] fp16 tiles)  ->  S0^T fp16 [2 blocks of 64 kd][128 vd rows][128 B]
+constexpr uint32_t kOffR = 49152;     // 32 KB: fp32 A and T ([64][68] each, 34 KB: the tail lies in the W tile, dead at that time)
+                                      //        ->  T diag(beta) hi, lo, T diag(beta e^b) hi, lo (four [64][64] fp16 tiles)
+                                      //        ->  S0^T fp16 [2 blocks of 64 kd][128 vd rows][128 B]
 constexpr uint32_t kOffW = 81920;     // W^T [128 kd rows][64 tokens] fp16                B of (ws), MN-major
 constexpr uint32_t kOffMQ = 98304;    // Mq [64][64] fp16                                 B of (o)
 constexpr uint32_t kOffSC = 106496;   // scalars: b[64], beta[64], eb[64], ebc[64]
@@ -54,20 +56,60 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 constexpr float kLog2e = 1.4426950408889634f;
 
-// dst(16x16 block at dr,dc) (+)= sign * A(16x16 at ar,ac) * B(16x16 at br,bc); matrices 64x64 fp32 row-major in
-// shared memory; 256 threads, one output each.
-__device__ __forceinline__ void block_product(float* dst, int dr, int dc, const float* A, int ar, int ac, const float* B,
-                                              int br, int bc, float sign, bool accumulate, int tid) {
-    const int r = tid >> 4, c = tid & 15;
-    float s0 = 0.f, s1 = 0.f;
+// Row pitch (floats) of the fp32 A and T matrices in shared memory: 68 keeps 16-byte alignment and moves consecutive
+// rows by four banks, so a warp's row-per-lane float4 accesses do not collide.
+constexpr int kLd = 68;
+
+// Columns [c0, c0 + NC) of the blocks below the diagonal block J of T = (I + A)^-1, given the inverted diagonal blocks
+// D_I (already in T):  T_IJ = -D_I sum_{K=J}^{I-1} A_IK T_KJ  for I = J+1 .. 3.  A column of T depends only on the same
+// column of the block rows above it, so one warp owns its columns from top to bottom and never meets another warp.
+// Lane (rg, c): RPL = NC / 2 rows rg*RPL .. of the 16-row block, column c0 + c.  The inner sums P are passed from the
+// accumulating lanes to the lanes that multiply by D_I through A's block (J, I), which lies above the diagonal, is
+// zero and not otherwise used.
+template <int NC>
+__device__ __forceinline__ void solve_column_group(float* AM, float* TF, int J, int c0, int lane) {
+    constexpr int RPL = NC / 2;
+    const int rg = lane / NC, c = lane % NC;
+    const int r0 = rg * RPL;
+    for (int I = J + 1; I < 4; ++I) {
+        float p[RPL];
 #pragma unroll
-    for (int k = 0; k < 16; k += 2) {
-        s0 += A[(ar + r) * 64 + ac + k] * B[(br + k) * 64 + bc + c];
-        s1 += A[(ar + r) * 64 + ac + k + 1] * B[(br + k + 1) * 64 + bc + c];
+        for (int i = 0; i < RPL; ++i) p[i] = 0.f;
+        for (int K = J; K < I; ++K) {
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+                float t[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) t[e] = TF[(16 * K + 4 * k4 + e) * kLd + c0 + c];
+#pragma unroll
+                for (int i = 0; i < RPL; ++i) {
+                    const float4 a = *reinterpret_cast<const float4*>(&AM[(16 * I + r0 + i) * kLd + 16 * K + 4 * k4]);
+                    p[i] += a.x * t[0] + a.y * t[1] + a.z * t[2] + a.w * t[3];
+                }
+            }
+        }
+        float* P = AM + (16 * J) * kLd + 16 * I + (c0 - 16 * J);      // 16 x NC scratch in the zero block (J, I)
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) P[(r0 + i) * kLd + c] = p[i];
+        __syncwarp();
+        float o[RPL];
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) o[i] = 0.f;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+            float t[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) t[e] = P[(4 * k4 + e) * kLd + c];
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                const float4 d = *reinterpret_cast<const float4*>(&TF[(16 * I + r0 + i) * kLd + 16 * I + 4 * k4]);
+                o[i] += d.x * t[0] + d.y * t[1] + d.z * t[2] + d.w * t[3];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) TF[(16 * I + r0 + i) * kLd + c0 + c] = -o[i];
+        __syncwarp();
     }
-    float* d = &dst[(dr + r) * 64 + dc + c];
-    const float v = sign * (s0 + s1);
-    *d = accumulate ? *d + v : v;
 }
 
 // grid (heads, n_seqs), block 288, two CTAs per SM
@@ -84,8 +126,8 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + G_BAR_COUNT);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     auto bar = [&](int i) { return base + kOffBarG + 8u * i; };
-    float* AM = reinterpret_cast<float*>(sm + kOffR);
-    float* TF = reinterpret_cast<float*>(sm + kOffR + 16384);
+    float* AM = reinterpret_cast<float*>(sm + kOffR);                      // fp32 A, [64][kLd]
+    float* TF = reinterpret_cast<float*>(sm + kOffR + 64 * kLd * 4);       // fp32 T, [64][kLd]; its tail reaches into the W tile, which is dead then
 
     const int h = blockIdx.x;
     const LaSeqMeta sq = seqs[blockIdx.y];
@@ -269,7 +311,7 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                             const int j = hf * 32 + j4 * 4 + e;
                             a4[e] = (j < r) ? be * ex2_approx((bi - s_b[j]) * kLog2e) * __uint_as_float(d1[j4 * 4 + e]) : 0.f;
                         }
-                        *reinterpret_cast<float4*>(AM + r * 64 + hf * 32 + j4 * 4) = make_float4(a4[0], a4[1], a4[2], a4[3]);
+                        *reinterpret_cast<float4*>(AM + r * kLd + hf * 32 + j4 * 4) = make_float4(a4[0], a4[1], a4[2], a4[3]);
                     }
                 } else {
                     const int i = r - 64;
@@ -308,9 +350,9 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
             named_sync_256();
-            // ---- T = (I + A)^-1, blocked 16 x 16: diagonal blocks by forward substitution, the rest by block products
-            //      T_ij = -T_ii sum_{k=j}^{i-1} A_ik T_kj.  The inner sums are staged in A's upper blocks, which are zero
-            //      and not otherwise used. ----
+            // ---- T = (I + A)^-1, blocked 16 x 16.  Diagonal blocks by forward substitution (one thread per column); then
+            //      every warp takes a group of columns of T and works down its block rows (solve_column_group): the four
+            //      leftmost groups of 4 columns have the longest way (nine 16 x 16 x 4 products), the others less. ----
             if (tid < 64) {
                 const int b0 = (tid >> 4) * 16, col = tid & 15;      // column `col` of diagonal block b0 / 16
                 float t[16];
@@ -321,49 +363,27 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
                     for (int j = 0; j + 1 < i; j += 2) {
-                        acc0 += AM[(b0 + i) * 64 + b0 + j] * t[j];
-                        acc1 += AM[(b0 + i) * 64 + b0 + j + 1] * t[j + 1];
+                        acc0 += AM[(b0 + i) * kLd + b0 + j] * t[j];
+                        acc1 += AM[(b0 + i) * kLd + b0 + j + 1] * t[j + 1];
                     }
-                    if (i & 1) acc0 += AM[(b0 + i) * 64 + b0 + i - 1] * t[i - 1];
+                    if (i & 1) acc0 += AM[(b0 + i) * kLd + b0 + i - 1] * t[i - 1];
                     t[i] -= acc0 + acc1;   // rows <= col keep their start value: A is strictly lower and t[j < col] = 0
                 }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) TF[(b0 + i) * 64 + b0 + col] = t[i];
-            } else {
-                for (int idx = tid - 64; idx < 6 * 256; idx += 192) {   // the other threads clear T's six upper blocks
-                    const int blk = idx >> 8, e = idx & 255;
-                    const int bi = (blk < 3) ? 0 : (blk < 5 ? 1 : 2);
-                    const int bj = (blk < 3) ? blk + 1 : (blk < 5 ? blk - 1 : 3);
-                    TF[(bi * 16 + (e >> 4)) * 64 + bj * 16 + (e & 15)] = 0.f;
-                }
+                for (int i = 0; i < 16; ++i) TF[(b0 + i) * kLd + b0 + col] = t[i];
             }
             named_sync_256();
-            for (int i = 1; i < 4; ++i)   // first sub-diagonal
-                block_product(AM, (i - 1) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 1) * 16, 1.f, false, tid);
-            named_sync_256();
-            for (int i = 1; i < 4; ++i)
-                block_product(TF, i * 16, (i - 1) * 16, TF, i * 16, i * 16, AM, (i - 1) * 16, i * 16, -1.f, false, tid);
-            named_sync_256();
-            for (int i = 2; i < 4; ++i) {   // second sub-diagonal
-                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 2) * 16, TF, (i - 2) * 16, (i - 2) * 16, 1.f, false, tid);
-                block_product(AM, (i - 2) * 16, i * 16, AM, i * 16, (i - 1) * 16, TF, (i - 1) * 16, (i - 2) * 16, 1.f, true, tid);
-            }
-            named_sync_256();
-            for (int i = 2; i < 4; ++i)
-                block_product(TF, i * 16, (i - 2) * 16, TF, i * 16, i * 16, AM, (i - 2) * 16, i * 16, -1.f, false, tid);
-            named_sync_256();
-            block_product(AM, 0, 48, AM, 48, 0, TF, 0, 0, 1.f, false, tid);      // corner block
-            block_product(AM, 0, 48, AM, 48, 16, TF, 16, 0, 1.f, true, tid);
-            block_product(AM, 0, 48, AM, 48, 32, TF, 32, 0, 1.f, true, tid);
-            named_sync_256();
-            block_product(TF, 48, 0, TF, 48, 48, AM, 0, 48, -1.f, false, tid);
+            if (warp < 4) solve_column_group<4>(AM, TF, 0, 4 * warp, lane);
+            else if (warp < 6) solve_column_group<8>(AM, TF, 1, 16 + 8 * (warp - 4), lane);
+            else solve_column_group<8>(AM, TF, 2, 32 + 8 * (warp - 6), lane);
             named_sync_256();
             {   // T diag(beta) and T diag(beta e^b) -> fp16 hi + lo tiles (row = i, K = j), written over A and T
                 const int i = tid >> 2, qd = tid & 3;
                 float tv[16];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float4 t4 = *reinterpret_cast<const float4*>(&TF[i * 64 + qd * 16 + 4 * e]);
+                    float4 t4 = *reinterpret_cast<const float4*>(&TF[i * kLd + qd * 16 + 4 * e]);
+                    if (qd > (i >> 4)) t4 = make_float4(0.f, 0.f, 0.f, 0.f);      // blocks above the diagonal are never written
                     tv[4 * e] = t4.x; tv[4 * e + 1] = t4.y; tv[4 * e + 2] = t4.z; tv[4 * e + 3] = t4.w;
                 }
                 named_sync_256();     // every thread holds its part of T: the tiles may overwrite it

@@ -33,8 +33,8 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : lo
 // SiLU, L2 norm of q and k (eps inside the sqrt), q * 1/sqrt(128); the v warps also produce beta and the log-decay g.
 // A warp requests its whole input window (the run's rows plus three rows of history, 16 bytes per lane and row) before
 // it computes anything, so every input row leaves HBM once and enough loads are in flight to cover the latency.
-// q and k are written as fp32 (q_out, k_out) and / or fp16 (qh_out, kh_out, the operand format of the tensor-core
-// recurrence); null pointers are skipped.
+// q, k and v are written as fp32 (q_out, k_out, v_out) and / or fp16 (qh_out, kh_out, vh_out, the operand format of the
+// tensor-core recurrence); null pointers are skipped.
 constexpr int kConvRun = 16;
 __global__ void __launch_bounds__(128)
 la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_seq,
@@ -42,7 +42,8 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
                    size_t conv_stride_slot, const float* __restrict__ conv_w, const float* __restrict__ a_log,
                    const float* __restrict__ dt_bias, int rows, float* __restrict__ q_out,
                    float* __restrict__ k_out, __half* __restrict__ qh_out, __half* __restrict__ kh_out,
-                   float* __restrict__ v_out, float* __restrict__ g_out, float* __restrict__ beta_out) {
+                   float* __restrict__ v_out, __half* __restrict__ vh_out, float* __restrict__ g_out,
+                   float* __restrict__ beta_out) {
     const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int n_runs = (rows + kConvRun - 1) / kConvRun;
@@ -84,7 +85,11 @@ la_conv_seq_kernel(const float* __restrict__ mixed, const int* __restrict__ row_
     auto store_row = [&](int row, const float (&res)[4], float ss_total) {
         const size_t o = ((size_t)row * kLaHeads + h) * kLaKd + 4 * lane;
         if (part == 2) {
-            *reinterpret_cast<float4*>(v_out + o) = make_float4(res[0], res[1], res[2], res[3]);
+            if (v_out) *reinterpret_cast<float4*>(v_out + o) = make_float4(res[0], res[1], res[2], res[3]);
+            if (vh_out) {
+                __half2 a = __floats2half2_rn(res[0], res[1]), b = __floats2half2_rn(res[2], res[3]);
+                *reinterpret_cast<uint2*>(vh_out + o) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+            }
             return;
         }
         const float inv = ((part == 0) ? q_scale : 1.0f) / sqrtf(ss_total + 1e-6f);     // one division per row, not per channel
@@ -408,9 +413,9 @@ __global__ void la_conv_export_kernel(const float* __restrict__ mine, float* __r
 // ---- launchers ------------------------------------------------------------------------------------------
 int launch_la_conv_seq(const float* mixed, const int* d_row_seq, const LaSeqMeta* d_seqs, const float* conv_layer,
                        size_t conv_stride, const float* conv_w, const float* a_log, const float* dt_bias, int rows,
-                       float* q, float* k, __half* qh, __half* kh, float* v, float* g, float* beta, cudaStream_t s) {
+                       float* q, float* k, __half* qh, __half* kh, float* v, __half* vh, float* g, float* beta, cudaStream_t s) {
     la_conv_seq_kernel<<<ceil_div(ceil_div(rows, kConvRun) * kLaHeads * 3, 4), 128, 0, s>>>(mixed, d_row_seq, d_seqs, conv_layer, conv_stride,
-                                                                  conv_w, a_log, dt_bias, rows, q, k, qh, kh, v, g, beta);
+                                                                  conv_w, a_log, dt_bias, rows, q, k, qh, kh, v, vh, g, beta);
     B2_LAUNCH_CHECK();
     return 0;
 }

@@ -18,7 +18,7 @@ size_t la_scratch_bytes(const b200attn_la_config& c) {
     size_t n = 0;
     n += align_up(R * kLaProjCols * 4, 256);            // mixed
     n += 3 * align_up(R * kLaHeads * kLaKd * 4, 256);   // q, k, v
-    n += 2 * align_up(R * kLaHeads * kLaKd * 2, 256);   // q, k as fp16
+    n += 3 * align_up(R * kLaHeads * kLaKd * 2, 256);   // q, k, v as fp16
     n += 2 * align_up(R * kLaHeads * 4, 256);           // g, beta
     n += align_up(R * kLaHeads * kLaVd * 4, 256);       // core
     n += align_up(R * kHidden * 2, 256);                // xb
@@ -39,6 +39,7 @@ void la_carve_scratch(b200attn_la la) {
     la->d_v = (float*)take(R * kLaHeads * kLaKd * 4);
     la->d_qh = (__half*)take(R * kLaHeads * kLaKd * 2);
     la->d_kh = (__half*)take(R * kLaHeads * kLaKd * 2);
+    la->d_vh = (__half*)take(R * kLaHeads * kLaVd * 2);
     la->d_g = (float*)take(R * kLaHeads * 4);
     la->d_beta = (float*)take(R * kLaHeads * 4);
     la->d_core = (float*)take(R * kLaHeads * kLaVd * 4);
@@ -256,14 +257,14 @@ static int la_build_meta(b200attn_la la, b200attn_la_state st, const int* h_slot
     return 0;
 }
 
-// Runs the delta-rule recurrence over the batch.  tensor_cores: q and k must already be in la->d_qh / d_kh.
+// Runs the delta-rule recurrence over the batch.  tensor_cores: q, k and v must already be in la->d_qh / d_kh / d_vh.
 static int la_recurrence(b200attn_la la, b200attn_la_state st, int layer, const float* q, const float* k, const float* v,
                          const float* g, const float* beta, const LaSeqMeta* d_seqs, int n_seqs, int rows, float* out,
                          bool tensor_cores, cudaStream_t s) {
     float* rec_layer = st->d_recurrent + (size_t)layer * st->cfg.max_seqs * st->rec_stride_slot();
     ProfScope prof(PROF_LA_PREFILL, s);
     if (tensor_cores)
-        return launch_la_chunk_tc(la->d_qh, la->d_kh, v, g, beta, d_seqs, n_seqs, rows, rec_layer, st->rec_stride_slot(), out,
+        return launch_la_chunk_tc(la->d_qh, la->d_kh, la->d_vh, g, beta, d_seqs, n_seqs, rows, rec_layer, st->rec_stride_slot(), out,
                                   la->d_error, s);
     return launch_la_recurrent_serial(q, k, v, g, beta, d_seqs, n_seqs, rec_layer, st->rec_stride_slot(), out, s);
 }
@@ -321,7 +322,7 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
     B2_TRY(project_in(rows));
     B2_TRY(launch_la_conv_seq(la->d_mixed, d_row_seq, d_seqs, conv_layer, st->conv_stride_slot(), la->d_conv_w, la->d_a_log,
                               la->d_dt_bias, rows, tc ? nullptr : la->d_q, tc ? nullptr : la->d_k, tc ? la->d_qh : nullptr,
-                              tc ? la->d_kh : nullptr, la->d_v, la->d_g, la->d_beta, s));
+                              tc ? la->d_kh : nullptr, tc ? nullptr : la->d_v, tc ? la->d_vh : nullptr, la->d_g, la->d_beta, s));
     B2_TRY(la_recurrence(la, st, layer, la->d_q, la->d_k, la->d_v, la->d_g, la->d_beta, d_seqs, n_seqs, rows, la->d_core, tc, s));
     B2_TRY(launch_la_conv_state_update(la->d_mixed, d_seqs, n_seqs, conv_layer, st->conv_stride_slot(), s));
     B2_TRY(launch_la_gated_norm(la->d_core, la->d_mixed, la->d_norm, rows, la->d_gated, fp16, s));
@@ -356,6 +357,7 @@ extern "C" int b200attn_la_prefill_core(b200attn_la la, b200attn_la_state st, in
     if (use_tensor_cores) {
         B2_TRY(f32_to_f16(s, d_q, la->d_qh, (size_t)rows * kLaHeads * kLaKd));
         B2_TRY(f32_to_f16(s, d_k, la->d_kh, (size_t)rows * kLaHeads * kLaKd));
+        B2_TRY(f32_to_f16(s, d_v, la->d_vh, (size_t)rows * kLaHeads * kLaVd));
         B2_CUDA(cudaMemsetAsync(la->d_error, 0, 4, s));
     }
     B2_TRY(la_recurrence(la, st, layer, d_q, d_k, d_v, d_g, d_beta, d_seqs, n_seqs, rows, d_out, use_tensor_cores != 0, s));

@@ -196,7 +196,9 @@ def test_real_shapes_ffn_3584_and_lm_head_248320(ops, cuda, oracle, synth, decod
         seq = cpu_stack.OracleStackSequence(qw, 4, kv_mode=2)
         hn, _ = seq.forward_token(int(first[i, 0]), want_logits=False)
         err = np.abs(hid[i].cpu().numpy() - hn)
-        assert np.all(err <= 2e-3 + 1e-2 * np.abs(hn)), f"sequence {i}: hidden max abs err {err.max():.3e}"
+        # one operator + FFN + three norms: twice as many fp16 roundings in a row as a single operator, whose own bound
+        # is 2e-3 + 1e-2 |ref| (tests/test_gpu_la.py); the final norm rescales the sum to unit RMS
+        assert np.all(err <= 4e-3 + 1e-2 * np.abs(hn)), f"sequence {i}: hidden max abs err {err.max():.3e}"
     # (b) LM head + argmax of the prefill path
     def check_pick(hidden, picked, what):
         logits = hidden.half().double() @ wq.T                       # [n, vocab] float64
