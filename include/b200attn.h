@@ -172,7 +172,8 @@ int b200attn_fa_prefill(b200attn_fa fa, b200attn_kv_pool pool, int layer, const 
                         const int* h_counts, int n_seqs, const float* d_x, float* d_y,
                         b200attn_stream stream);
 /* CudaFullAttention::forward (full_attention_cuda.cu:369-449) for n_seqs independent sequences:
- * one new token per sequence, d_x / d_y fp32 [n_seqs, hidden], d_slots device int32 [n_seqs].
+ * one new token per sequence, d_x / d_y fp32 [n_seqs, hidden], d_slots device int32 [n_seqs]; a slot of -1 marks an
+ * inactive row (nothing is read or written for it, here and in b200attn_la_decode).
  * No host synchronisation and no allocation: safe inside stream capture. */
 int b200attn_fa_decode(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int* d_slots,
                        int n_seqs, const float* d_x, float* d_y, b200attn_stream stream);
@@ -370,6 +371,33 @@ int b200attn_decode_graph_launch(b200attn_stack st, int steps, b200attn_stream s
 int b200attn_stack_set_tokens(b200attn_stack st, const int* d_tokens, int n_seqs, b200attn_stream stream);
 /* See b200attn_stack_set_tokens (performance_test.cu:313-319 reads the sampled ids back each step). */
 int b200attn_stack_get_tokens(b200attn_stack st, int* d_tokens, int n_seqs, b200attn_stream stream);
+/* ------------------------------------------------------------------------------------------------
+ * Continuous batching on the stack's pools: admission into free rows and retirement between decode steps.  The
+ * reference has only the page bookkeeping for it (PagedKVCache::allocate_sequence / append_tokens / release_sequence /
+ * shrink_sequence, src/backend/cuda/kernels/paged_kv.cpp:90-168) and no caller.
+ * Row r of a decode step is bound to a slot (KV pages + DeltaNet state); the device-resident row -> slot list keeps the
+ * active rows dense at the front and marks the others -1, which every decode kernel skips, so ONE captured step over
+ * max_seqs rows serves any number of active sequences.  All calls are host-synchronous bookkeeping except the prompt
+ * pass of an admission; make them between steps.
+ * ---------------------------------------------------------------------------------------------- */
+/* Enter the mode: caches cleared, every row inactive, every slot's pages back in the pool (PagedKVCache::clear,
+ * paged_kv.cpp:49-64).  b200attn_stack_reset leaves it. */
+int b200attn_stack_begin_batching(b200attn_stack st, b200attn_stream stream);
+/* Admit one sequence (PagedKVCache::allocate_sequence, paged_kv.cpp:90-112, plus the prompt pass the reference leaves
+ * to its caller): takes a free slot, reserves pages for reserve_tokens (prompt + tokens to generate;
+ * B200ATTN_ERR_NOMEM without side effects when rows or pages run out), clears its state, runs the prompt
+ * (d_prompt int32 [prompt_len]) and leaves the first generated token in the row's entry of the token buffer. */
+int b200attn_stack_admit(b200attn_stack st, const int* d_prompt, int prompt_len, int reserve_tokens, int* row_out,
+                         b200attn_stream stream);
+/* Retire the sequence in `row` (PagedKVCache::release_sequence, paged_kv.cpp:138-148): its pages go back to the pool
+ * and the last active row moves into its place. */
+int b200attn_stack_retire(b200attn_stack st, int row, b200attn_stream stream);
+/* Active rows and (optionally, h_row_slots int[max_seqs]) the slot of every row.  No reference counterpart. */
+int b200attn_stack_rows(b200attn_stack st, int* n_active_out, int* h_row_slots);
+/* One decode step over rows [0, n_rows) of the internal token buffer (CudaEngine::forward_batch_decode,
+ * cuda_engine.cu:327-352): the captured graph when it was captured for n_rows, eager launches otherwise. */
+int b200attn_stack_step(b200attn_stack st, int n_rows, b200attn_stream stream);
+
 /* Number of kernels this library launched on behalf of the calling thread since the last call
  * with reset != 0 (graph replays count the nodes of the captured step).  No reference counterpart. */
 long long b200attn_launch_count(int reset);
@@ -381,7 +409,8 @@ long long b200attn_launch_count(int reset);
  * device-side stamp slot (first CTA past its dependency wait .. last CTA done, on the GPU's global timer).  Stamps
  * also work for launches captured by b200attn_decode_graph_capture while profiling is on: every replay fills its
  * slots again, b200attn_profile_read sums and re-arms them.  Names: "fa_prefill", "fa_decode", "la_prefill",
- * "la_decode", "kv_append".  b200attn_profile_read synchronises the device and returns the summed device time and
+ * "la_decode", "kv_append", and for the projections of the fused decode step "gemm_in" (input projections),
+ * "gemm_ffn" (gate / up + SwiGLU), "gemm_res" (output projections with the residual add), "lm_head".  b200attn_profile_read synchronises the device and returns the summed device time and
  * launch count; b200attn_profile_reset forgets all pairs and slots (re-capture a graph that carried stamps).
  * ---------------------------------------------------------------------------------------------- */
 int b200attn_profile_enable(int on);

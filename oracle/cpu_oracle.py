@@ -28,6 +28,12 @@ def _fp(a):
     return a.ctypes.data_as(_f32p)
 
 
+def reference_root() -> str:
+    """Where the reference checkout lies: QWEN_REFERENCE_ROOT, else a directory named ``reference`` next to this
+    repository.  It is only needed at build time; the GPU box runs the prebuilt files under oracle/_ref."""
+    return os.environ.get("QWEN_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
 def build(force: bool = False) -> None:
     """Compile liboracle.so (always possible) and, when the reference checkout is present,
     oracle/_ref/libqwen_ref.so.  Building the checker is not using it."""
@@ -36,7 +42,7 @@ def build(force: bool = False) -> None:
     if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
         subprocess.check_call(["make", "-C", _HERE, "liboracle.so", "-B"], stdout=subprocess.DEVNULL)
     ref_so = os.path.join(_HERE, "_ref", "libqwen_ref.so")
-    ref_root = os.environ.get("QWEN_REFERENCE_ROOT", "/root/reference")
+    ref_root = reference_root()
     if os.path.isdir(os.path.join(ref_root, "src", "backend", "cpu", "core", "attention")):
         shim = os.path.join(_HERE, "ref_shim.cpp")
         if force or not os.path.exists(ref_so) or os.path.getmtime(ref_so) < os.path.getmtime(shim):

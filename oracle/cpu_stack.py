@@ -14,14 +14,18 @@ import numpy as np
 from . import cpu_oracle as O
 
 
-def make_stack_weights(synth, seed: int, num_layers: int, inter: int, vocab: int, int8: bool = True) -> dict:
-    """Random-init weights of the hybrid stack (matrices ~ N(0, 0.02), norm weights 0 / 1), optionally passed
-    through the per-output-channel INT8 quantiser (code * scale kept as fp32)."""
+def make_stack_weights(synth, seed: int, num_layers: int, inter: int, vocab: int, int8: bool = True, norm_std: float = 0.0) -> dict:
+    """Random-init weights of the hybrid stack (matrices ~ N(0, 0.02), norm weights 0 / 1 or, with norm_std, the
+    layers' RMSNorm weights ~ N(0, norm_std)), optionally passed through the per-output-channel INT8 quantiser
+    (code * scale kept as fp32)."""
     def q(m):
         return O.quantize_weight_rows(m)[0] if int8 else m
     layers = []
     for i in range(num_layers):
         lw = dict(input_norm=np.zeros(1024, np.float32), post_norm=np.zeros(1024, np.float32))
+        if norm_std > 0.0:
+            lw = dict(input_norm=synth.normal(seed, f"L{i}.input_norm", (1024,), norm_std),
+                      post_norm=synth.normal(seed, f"L{i}.post_norm", (1024,), norm_std))
         lw["ffn"] = dict(gate=synth.normal(seed, f"L{i}.gate", (inter, 1024), 0.02),
                          up=synth.normal(seed, f"L{i}.up", (inter, 1024), 0.02),
                          down=synth.normal(seed, f"L{i}.down", (1024, inter), 0.02))

@@ -112,8 +112,10 @@ void CudaFullAttention::forward_batch_prefill(const float* input, float* output,
 void CudaLinearAttnState::reset(int nh, int kd, int vd, int conv_k) {
     num_heads = nh; key_dim = kd; value_dim = vd; conv_kernel = conv_k;
     conv_dim = nh * (2 * kd + vd);
-    b200attn_la_state_config cfg{1, 1, nh, kd, vd, conv_k};
-    check(b200attn_la_state_create(&cfg, &state));
+    if (nh == 16 && kd == 128 && vd == 128 && conv_k == 4) {     // the sizes the library's kernels are built for
+        b200attn_la_state_config cfg{1, 1, nh, kd, vd, conv_k};
+        check(b200attn_la_state_create(&cfg, &state));
+    }
     check_cuda(cudaMalloc(&d_conv_state, (size_t)conv_dim * (conv_k - 1) * sizeof(float)));
     check_cuda(cudaMemset(d_conv_state, 0, (size_t)conv_dim * (conv_k - 1) * sizeof(float)));
     check_cuda(cudaMalloc(&d_recurrent_state, (size_t)nh * kd * vd * sizeof(float)));
@@ -121,8 +123,8 @@ void CudaLinearAttnState::reset(int nh, int kd, int vd, int conv_k) {
     if (!d_slot) d_slot = device_int(0);
 }
 void CudaLinearAttnState::clear() {
-    if (!state) return;
-    check(b200attn_la_state_clear(state, -1, nullptr));
+    if (!d_recurrent_state) return;
+    if (state) check(b200attn_la_state_clear(state, -1, nullptr));
     check_cuda(cudaMemset(d_recurrent_state, 0, (size_t)num_heads * key_dim * value_dim * sizeof(float)));
     check_cuda(cudaMemset(d_conv_state, 0, (size_t)conv_dim * (conv_kernel - 1) * sizeof(float)));
 }
@@ -133,6 +135,20 @@ namespace {
 void sync_in(CudaLinearAttnState& s) { check(b200attn_la_state_import(s.state, 0, 0, s.d_recurrent_state, s.d_conv_state, nullptr)); }
 void sync_out(CudaLinearAttnState& s) { check(b200attn_la_state_export(s.state, 0, 0, s.d_recurrent_state, s.d_conv_state, nullptr)); }
 
+bool model_sizes(int hidden, int heads, int kd, int vd, int ck) { return hidden == 1024 && heads == 16 && kd == 128 && vd == 128 && ck == 4; }
+void generic_set(detail::GenericLa* g, int hidden, int heads, int kd, int vd, int ck, const std::vector<float>& qkv, const std::vector<float>& a,
+                 const std::vector<float>& b, const std::vector<float>& z, const std::vector<float>& conv, const std::vector<float>& out,
+                 const std::vector<float>& a_log, const std::vector<float>& dt_bias, const std::vector<float>& norm) {
+    const size_t conv_dim = (size_t)heads * (2 * kd + vd);
+    check_size(qkv, conv_dim * hidden, "in_proj_qkv");
+    check_size(a, (size_t)heads * hidden, "in_proj_a");
+    check_size(b, (size_t)heads * hidden, "in_proj_b");
+    check_size(z, (size_t)heads * vd * hidden, "in_proj_z");
+    check_size(conv, conv_dim * ck, "conv1d");
+    check_size(out, (size_t)hidden * heads * vd, "out_proj");
+    detail::generic_la_set_weights(g, qkv, a, b, z, conv, out, a_log.empty() ? std::vector<float>(heads, 0.f) : a_log,
+                                   dt_bias.empty() ? std::vector<float>(heads, 0.f) : dt_bias, norm.empty() ? std::vector<float>(vd, 1.f) : norm);
+}
 b200attn_la make_la(int hidden, int heads, int kd, int vd, int ck, int precision) {
     if (hidden <= 0 || heads <= 0 || kd <= 0 || vd <= 0) throw std::invalid_argument("All dimensions must be > 0");
     b200attn_la_config cfg{hidden, heads, kd, vd, ck, precision, 1, kMaxRows};
@@ -181,34 +197,48 @@ void la_forward_batch(b200attn_la op, int hidden, const float* in, float* out, C
 // ---- CudaLinearAttention / V2 ------------------------------------------------------------------------------------------
 CudaLinearAttention::CudaLinearAttention(int hidden_size, int num_heads, int key_dim, int value_dim, int conv_kernel)
     : hidden_size_(hidden_size), num_heads_(num_heads), key_dim_(key_dim), value_dim_(value_dim), conv_kernel_(conv_kernel) {
-    op_ = make_la(hidden_size, num_heads, key_dim, value_dim, conv_kernel, proj_precision_);
+    if (model_sizes(hidden_size, num_heads, key_dim, value_dim, conv_kernel)) op_ = make_la(hidden_size, num_heads, key_dim, value_dim, conv_kernel, proj_precision_);
+    else generic_ = detail::generic_la_create(hidden_size, num_heads, key_dim, value_dim, conv_kernel);
 }
-CudaLinearAttention::~CudaLinearAttention() { b200attn_la_destroy(op_); }
+CudaLinearAttention::~CudaLinearAttention() { b200attn_la_destroy(op_); detail::generic_la_destroy(generic_); }
 void CudaLinearAttention::set_weights(const std::vector<float>& qkv, const std::vector<float>& a, const std::vector<float>& b,
                                       const std::vector<float>& z, const std::vector<float>& conv, const std::vector<float>& out,
                                       const std::vector<float>& a_log, const std::vector<float>& dt_bias,
                                       const std::vector<float>& norm) {
+    if (generic_) return generic_set(generic_, hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_, qkv, a, b, z, conv, out, a_log, dt_bias, norm);
     la_set(op_, hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_, qkv, a, b, z, conv, out, a_log, dt_bias, norm);
 }
-void CudaLinearAttention::forward(const float* in, float* out, CudaLinearAttnState& s) const { la_forward(op_, in, out, s, nullptr); }
+void CudaLinearAttention::forward(const float* in, float* out, CudaLinearAttnState& s) const {
+    if (generic_) return detail::generic_la_forward(generic_, in, out, s.d_recurrent_state, s.d_conv_state, 1, nullptr);
+    la_forward(op_, in, out, s, nullptr);
+}
 void CudaLinearAttention::forward_batch(const float* in, float* out, CudaLinearAttnState& s, int rows) const {
+    if (rows <= 0) throw std::invalid_argument("batch_size must be > 0");
+    if (generic_) return detail::generic_la_forward(generic_, in, out, s.d_recurrent_state, s.d_conv_state, rows, nullptr);
     la_forward_batch(op_, hidden_size_, in, out, s, rows, nullptr);
 }
 void CudaLinearAttention::forward_fused(const float* in, float* out, CudaLinearAttnState& s) const { forward(in, out, s); }
 
 CudaLinearAttentionV2::CudaLinearAttentionV2(int hidden_size, int num_heads, int key_dim, int value_dim, int conv_kernel)
     : hidden_size_(hidden_size), num_heads_(num_heads), key_dim_(key_dim), value_dim_(value_dim), conv_kernel_(conv_kernel) {
-    op_ = make_la(hidden_size, num_heads, key_dim, value_dim, conv_kernel, B200ATTN_PROJ_FP32);
+    if (model_sizes(hidden_size, num_heads, key_dim, value_dim, conv_kernel)) op_ = make_la(hidden_size, num_heads, key_dim, value_dim, conv_kernel, B200ATTN_PROJ_FP32);
+    else generic_ = detail::generic_la_create(hidden_size, num_heads, key_dim, value_dim, conv_kernel);
 }
-CudaLinearAttentionV2::~CudaLinearAttentionV2() { b200attn_la_destroy(op_); }
+CudaLinearAttentionV2::~CudaLinearAttentionV2() { b200attn_la_destroy(op_); detail::generic_la_destroy(generic_); }
 void CudaLinearAttentionV2::set_weights(const std::vector<float>& qkv, const std::vector<float>& a, const std::vector<float>& b,
                                         const std::vector<float>& z, const std::vector<float>& conv, const std::vector<float>& out,
                                         const std::vector<float>& a_log, const std::vector<float>& dt_bias,
                                         const std::vector<float>& norm) {
+    if (generic_) return generic_set(generic_, hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_, qkv, a, b, z, conv, out, a_log, dt_bias, norm);
     la_set(op_, hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_, qkv, a, b, z, conv, out, a_log, dt_bias, norm);
 }
-void CudaLinearAttentionV2::forward(const float* in, float* out, CudaLinearAttnState& s) const { la_forward(op_, in, out, s, nullptr); }
+void CudaLinearAttentionV2::forward(const float* in, float* out, CudaLinearAttnState& s) const {
+    if (generic_) return detail::generic_la_forward(generic_, in, out, s.d_recurrent_state, s.d_conv_state, 1, nullptr);
+    la_forward(op_, in, out, s, nullptr);
+}
 void CudaLinearAttentionV2::forward_batch(const float* in, float* out, CudaLinearAttnState& s, int rows, cudaStream_t stream) const {
+    if (rows <= 0) throw std::invalid_argument("batch_size must be > 0");
+    if (generic_) return detail::generic_la_forward(generic_, in, out, s.d_recurrent_state, s.d_conv_state, rows, stream);
     la_forward_batch(op_, hidden_size_, in, out, s, rows, stream);
 }
 

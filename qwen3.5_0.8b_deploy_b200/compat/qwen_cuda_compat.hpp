@@ -25,6 +25,17 @@
 namespace qwen {
 namespace cuda {
 
+namespace detail {
+// Plain fp32 DeltaNet path for sizes the library's kernels are not built for (qwen_cuda_compat_free.cu).
+struct GenericLa;
+GenericLa* generic_la_create(int hidden, int heads, int kd, int vd, int ck);
+void generic_la_destroy(GenericLa* g);
+void generic_la_set_weights(GenericLa* g, const std::vector<float>& qkv, const std::vector<float>& a, const std::vector<float>& b,
+                            const std::vector<float>& z, const std::vector<float>& conv, const std::vector<float>& out,
+                            const std::vector<float>& a_log, const std::vector<float>& dt_bias, const std::vector<float>& norm);
+void generic_la_forward(GenericLa* g, const float* in, float* out, float* d_recurrent, float* d_conv, int rows, cudaStream_t s);
+}  // namespace detail
+
 // One sequence, `num_layers` layers, stored in the paged pool of the library.
 struct CudaKVCache {
     // Kept for source compatibility. They point at the library's page arrays (K [page][head][64][256],
@@ -117,6 +128,7 @@ class CudaLinearAttention {
   protected:
     int hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_;
     b200attn_la op_ = nullptr;
+    detail::GenericLa* generic_ = nullptr;      // used instead of op_ at sizes other than the model's
     int proj_precision_ = B200ATTN_PROJ_FP16;   // 16-bit weights (the reference rounds these weights to bf16 at load)
 };
 
@@ -140,6 +152,7 @@ class CudaLinearAttentionV2 {
   private:
     int hidden_size_, num_heads_, key_dim_, value_dim_, conv_kernel_;
     b200attn_la op_ = nullptr;
+    detail::GenericLa* generic_ = nullptr;      // used instead of op_ at sizes other than the model's
 };
 
 // ---- free launchers (qwen_cuda_compat_free.cu) ---------------------------------------------------------------------------

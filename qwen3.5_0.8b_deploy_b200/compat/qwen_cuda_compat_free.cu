@@ -368,6 +368,131 @@ void PagedKVCache::print_status() const {
                 "  GPU allocated: %zu MB\n", max_pages_, get_used_pages(), seq_to_slot_.size(), get_kv_bytes() >> 20, gpu_bytes_ >> 20);
 }
 
+
+// ---- Gated DeltaNet at sizes the library's kernels are not built for -----------------------------------------------------
+// The library's DeltaNet kernels are compiled for the model's sizes (hidden 1024, 16 heads, key / value dim 128).  The
+// reference's own stand-alone checks also run the operator at small sizes (tests/integration/v2_kernel_accuracy_validate.cu:
+// hidden 256, 4 heads, dims 64), so the compat classes carry this plain fp32 path for every other size: one block per
+// head and token, the state read and written in the reference's own layout.  Math: language_linear_attn.cpp:125-266.
+namespace detail {
+
+struct GenericLa {
+    int hidden, heads, kd, vd, ck, conv_dim;
+    float *w_qkv = nullptr, *w_a = nullptr, *w_b = nullptr, *w_z = nullptr, *w_conv = nullptr, *w_out = nullptr;
+    float *a_log = nullptr, *dt_bias = nullptr, *norm = nullptr;
+    float *mixed = nullptr, *z = nullptr, *ab = nullptr, *core = nullptr;      // per-token scratch
+    bool ready = false;
+};
+
+// y[o] = W[o, :] . x, one warp per output row
+__global__ void generic_linear_kernel(const float* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, int out, int in) {
+    const int o = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (o >= out) return;
+    float s = 0.f;
+    for (int i = lane; i < in; i += 32) s += W[(size_t)o * in + i] * x[i];
+    for (int k = 16; k > 0; k >>= 1) s += __shfl_xor_sync(0xffffffffu, s, k);
+    if (lane == 0) y[o] = s;
+}
+
+__device__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int k = 16; k > 0; k >>= 1) v += __shfl_xor_sync(0xffffffffu, v, k);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) t += red[w];
+    return t;
+}
+
+// One token of one head: conv + SiLU + state shift, L2 norms, gates, delta rule, gated RMSNorm.  grid heads, block >= max(kd, vd).
+__global__ void generic_token_kernel(GenericLa p, float* __restrict__ recurrent, float* __restrict__ conv_state) {
+    extern __shared__ float sh[];                 // q[kd] k[kd] v[vd] red[32]
+    float* sq = sh; float* sk = sq + p.kd; float* sv = sk + p.kd; float* red = sv + p.vd;
+    const int h = blockIdx.x, t = threadIdx.x, qd = p.heads * p.kd, sl = p.ck - 1;
+    auto conv = [&](int ch) {
+        float s = p.w_conv[ch * p.ck + sl] * p.mixed[ch];
+        for (int k = 0; k < sl; ++k) s += p.w_conv[ch * p.ck + k] * conv_state[ch * sl + k];
+        for (int k = sl - 1; k > 0; --k) conv_state[ch * sl + k] = conv_state[ch * sl + k - 1];
+        conv_state[ch * sl] = p.mixed[ch];
+        return s / (1.0f + expf(-s));
+    };
+    if (t < p.kd) { sq[t] = conv(h * p.kd + t); sk[t] = conv(qd + h * p.kd + t); }
+    if (t < p.vd) sv[t] = conv(2 * qd + h * p.vd + t);
+    const float nq = sqrtf(block_sum(t < p.kd ? sq[t] * sq[t] : 0.f, red) + 1e-6f);
+    const float nk = sqrtf(block_sum(t < p.kd ? sk[t] * sk[t] : 0.f, red) + 1e-6f);
+    if (t < p.kd) { sq[t] = sq[t] / nq * (1.0f / sqrtf((float)p.kd)); sk[t] = sk[t] / nk; }
+    __syncthreads();
+    const float beta = 1.0f / (1.0f + expf(-p.ab[p.heads + h]));
+    const float xa = p.ab[h] + p.dt_bias[h];
+    const float gt = expf(-expf(p.a_log[h]) * (xa > 20.0f ? xa : logf(1.0f + expf(xa))));
+    float o = 0.f;
+    if (t < p.vd) {
+        float* S = recurrent + (size_t)h * p.kd * p.vd;
+        float kv = 0.f;
+        for (int k = 0; k < p.kd; ++k) { S[k * p.vd + t] *= gt; kv += S[k * p.vd + t] * sk[k]; }
+        const float dl = (sv[t] - kv) * beta;
+        for (int k = 0; k < p.kd; ++k) { S[k * p.vd + t] += sk[k] * dl; o += S[k * p.vd + t] * sq[k]; }
+    }
+    const float var = block_sum(t < p.vd ? o * o : 0.f, red) / (float)p.vd;
+    if (t < p.vd) {
+        const float zz = p.z[h * p.vd + t];
+        p.core[h * p.vd + t] = o * (1.0f / sqrtf(var + 1e-6f)) * p.norm[t] * (zz / (1.0f + expf(-zz)));
+    }
+}
+
+static float* upload(const std::vector<float>& v) {
+    float* d = nullptr;
+    check_cuda(cudaMalloc(&d, std::max<size_t>(v.size(), 1) * sizeof(float)));
+    check_cuda(cudaMemcpy(d, v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice));
+    return d;
+}
+
+GenericLa* generic_la_create(int hidden, int heads, int kd, int vd, int ck) {
+    if (hidden <= 0 || heads <= 0 || kd <= 0 || vd <= 0 || ck < 2) throw std::invalid_argument("All dimensions must be > 0");
+    if (std::max(kd, vd) > 1024) throw std::invalid_argument("key / value dim above 1024 is not supported");
+    auto* g = new GenericLa();
+    g->hidden = hidden; g->heads = heads; g->kd = kd; g->vd = vd; g->ck = ck; g->conv_dim = heads * (2 * kd + vd);
+    check_cuda(cudaMalloc(&g->mixed, (size_t)g->conv_dim * 4));
+    check_cuda(cudaMalloc(&g->z, (size_t)heads * vd * 4));
+    check_cuda(cudaMalloc(&g->ab, (size_t)2 * heads * 4));
+    check_cuda(cudaMalloc(&g->core, (size_t)heads * vd * 4));
+    return g;
+}
+void generic_la_destroy(GenericLa* g) {
+    if (!g) return;
+    for (float* p : {g->w_qkv, g->w_a, g->w_b, g->w_z, g->w_conv, g->w_out, g->a_log, g->dt_bias, g->norm, g->mixed, g->z, g->ab, g->core}) cudaFree(p);
+    delete g;
+}
+void generic_la_set_weights(GenericLa* g, const std::vector<float>& qkv, const std::vector<float>& a, const std::vector<float>& b,
+                            const std::vector<float>& z, const std::vector<float>& conv, const std::vector<float>& out,
+                            const std::vector<float>& a_log, const std::vector<float>& dt_bias, const std::vector<float>& norm) {
+    for (float** p : {&g->w_qkv, &g->w_a, &g->w_b, &g->w_z, &g->w_conv, &g->w_out, &g->a_log, &g->dt_bias, &g->norm}) { cudaFree(*p); *p = nullptr; }
+    g->w_qkv = upload(qkv); g->w_a = upload(a); g->w_b = upload(b); g->w_z = upload(z); g->w_conv = upload(conv); g->w_out = upload(out);
+    g->a_log = upload(a_log); g->dt_bias = upload(dt_bias); g->norm = upload(norm);
+    g->ready = true;
+}
+void generic_la_forward(GenericLa* g, const float* in, float* out, float* d_recurrent, float* d_conv, int rows, cudaStream_t s) {
+    if (!g->ready) throw std::runtime_error("LinearAttention weights not set");
+    auto lin = [&](const float* W, const float* x, float* y, int o, int i) {
+        generic_linear_kernel<<<(o * 32 + 255) / 256, 256, 0, s>>>(W, x, y, o, i);
+    };
+    const int block = ((std::max(g->kd, g->vd) + 31) / 32) * 32;
+    const size_t sh = (size_t)(2 * g->kd + g->vd + 32) * sizeof(float);
+    for (int r = 0; r < rows; ++r) {              // tokens in order: each one sees the state its predecessor left
+        const float* x = in + (size_t)r * g->hidden;
+        lin(g->w_qkv, x, g->mixed, g->conv_dim, g->hidden);
+        lin(g->w_a, x, g->ab, g->heads, g->hidden);
+        lin(g->w_b, x, g->ab + g->heads, g->heads, g->hidden);
+        lin(g->w_z, x, g->z, g->heads * g->vd, g->hidden);
+        generic_token_kernel<<<g->heads, block, sh, s>>>(*g, d_recurrent, d_conv);
+        lin(g->w_out, g->core, out + (size_t)r * g->hidden, g->hidden, g->heads * g->vd);
+    }
+    check_cuda(cudaGetLastError());
+}
+
+}  // namespace detail
+
 void set_fa_weights(CudaFullAttention* fa, const std::vector<float>& q_w, const std::vector<float>& k_w,
                     const std::vector<float>& v_w, const std::vector<float>& qn_w, const std::vector<float>& kn_w,
                     const std::vector<float>& o_w, int layer_idx) {

@@ -67,7 +67,8 @@ inline void count_launch(int n = 1) { g_launches += n; }
     } while (0)
 
 // ---- per-kernel event timing (gemm.cu) ------------------------------------------------------------------
-enum ProfKind { PROF_FA_PREFILL = 0, PROF_FA_DECODE, PROF_LA_PREFILL, PROF_LA_DECODE, PROF_KV_APPEND, PROF_COUNT };
+enum ProfKind { PROF_FA_PREFILL = 0, PROF_FA_DECODE, PROF_LA_PREFILL, PROF_LA_DECODE, PROF_KV_APPEND, PROF_GEMM_IN, PROF_GEMM_FFN, PROF_GEMM_RES,
+                PROF_LM_HEAD, PROF_COUNT };
 extern bool g_prof_on;
 void prof_begin(ProfKind k, cudaStream_t s);
 void prof_end(ProfKind k, cudaStream_t s);
@@ -86,7 +87,7 @@ struct ProfScope {   // brackets the launches issued during its lifetime when pr
 // before it builds its operators, and no launch path touches the environment.
 struct RuntimeFlags {
     bool pdl = true;                 // B200ATTN_PDL=0: ordinary stream order instead of programmatic dependent launch
-    bool decode_gemm_tc = false;     // B200ATTN_DECODE_GEMM=tc: tcgen05 skinny GEMMs with fused epilogues in the decode step (default: library GEMMs)
+    bool decode_gemm_tc = false;     // B200ATTN_DECODE_GEMM=tc: the fused decode step on the tcgen05 skinny GEMMs (default: library GEMMs + norm / SwiGLU kernels)
     bool lm_head_cublas = false;     // B200ATTN_LM_HEAD=cublas: library GEMM + argmax kernel instead of the fused epilogue
     bool la_prefill_serial = false;  // B200ATTN_LA_PREFILL=serial: token-serial fp32 recurrence instead of the chunked tensor-core kernels
     unsigned la_stagger_ns = 2750;   // B200ATTN_LA_DECODE_STAGGER_NS

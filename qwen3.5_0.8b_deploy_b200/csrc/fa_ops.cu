@@ -162,8 +162,12 @@ static int fa_check(b200attn_fa fa, b200attn_kv_pool pool, int layer) {
     return 0;
 }
 
-static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_fp16, int rows, bool decode, bool kv_int8, int* d_error, cudaStream_t s) {
+static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_fp16, int rows, bool kv_int8, DecodeOut* fused, int* d_error,
+                         cudaStream_t s) {
     if (fa->cfg.proj_precision == B200ATTN_PROJ_FP16) {
+        if (fused)   // decode step of a stack: d_x is the un-normalised residual stream, its RMSNorm scale is applied in the epilogue
+            return gemm_tc_store(s, (const __half*)d_x, fa->d_wqkv_fp16, fa->d_qkv_raw, rows, kFaQkvCols, kHidden, kFaQkvCols, fused->rowsq,
+                                 fused->eps, d_error);
         const void* xb = d_x;
         const bool compensate = kv_int8 && !x_is_fp16;      // fp32 activations at hand and a quantising cache behind K / V
         if (!x_is_fp16) {
@@ -171,8 +175,6 @@ static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_fp16, int ro
             else B2_TRY(f32_to_f16(s, (const float*)d_x, fa->d_xb, (size_t)rows * kHidden));
             xb = fa->d_xb;
         }
-        if (decode && rows <= 128 && gemm_tc_enabled() && !compensate)   // weight-streaming tcgen05 GEMM
-            return gemm_tc_store(s, (const __half*)xb, fa->d_wqkv_fp16, fa->d_qkv_raw, rows, kFaQkvCols, kHidden, kFaQkvCols, 1, 0, d_error);
         B2_TRY(gemm_xwT(s, xb, true, fa->d_wqkv_fp16, true, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden));
         if (compensate) {
             // K | V columns += (x_lo W_hi^T + x_hi W_lo^T) / kLoScale
@@ -187,16 +189,9 @@ static int fa_project_in(b200attn_fa fa, const void* d_x, bool x_is_fp16, int ro
     return gemm_xwT(s, d_x, false, fa->d_wqkv_f32, false, fa->d_qkv_raw, false, rows, kFaQkvCols, kHidden);
 }
 
-static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, bool decode, DecodeOut* dout, int* d_error, cudaStream_t s) {
-    if (fa->cfg.proj_precision == B200ATTN_PROJ_FP16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || beta == 0.f)) {
-        const int K = kFaHeads * kHeadDim;
-        if (dout) {
-            dout->n_splits = gemm_tc_splits(kHidden, K, 64);
-            return gemm_tc_store(s, (const __half*)fa->d_attn, fa->d_wo_fp16, dout->partials, rows, kHidden, K, kHidden,
-                                 dout->n_splits, dout->stride, d_error);
-        }
-        return gemm_tc_store(s, (const __half*)fa->d_attn, fa->d_wo_fp16, d_y, rows, kHidden, K, kHidden, 1, 0, d_error);
-    }
+static int fa_project_out(b200attn_fa fa, float* d_y, float beta, int rows, DecodeOut* fused, int* d_error, cudaStream_t s) {
+    if (fused)   // residual stream += attn W_o^T, with the fp16 copy and the sums of squares for the next projection
+        return gemm_tc_residual(s, (const __half*)fa->d_attn, fa->d_wo_fp16, d_y, fused->xh, fused->rowsq, rows, kHidden, kFaHeads * kHeadDim, d_error);
     if (fa->cfg.proj_precision == B200ATTN_PROJ_FP16)
         return gemm_xwT(s, fa->d_attn, true, fa->d_wo_fp16, true, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
     return gemm_xwT(s, fa->d_attn, false, fa->d_wo_f32, false, d_y, false, rows, kHidden, kFaHeads * kHeadDim, beta);
@@ -217,14 +212,14 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
     if (decode) {
         B2_CHECK_ARG(d_slots_in, "fa_decode: null slots");
         B2_CHECK_ARG(n_seqs > 0 && n_seqs <= fa->cfg.max_batch, "fa_decode: n_seqs %d outside (0, max_batch %d]", n_seqs, fa->cfg.max_batch);
-        B2_TRY(fa_project_in(fa, d_x, x_is_fp16, n_seqs, true, !kv.is_fp16, pool->d_error, s));
+        B2_TRY(fa_project_in(fa, d_x, x_is_fp16, n_seqs, !kv.is_fp16, dout, pool->d_error, s));
         // q / gate epilogue, append of the new token's K and V, and the length increment in one launch; the attention
         // kernel then sees the new length already
         B2_TRY(launch_fa_decode_pre(kv, layer, d_slots_in, n_seqs, fa->d_qkv_raw, fa->d_qnorm, fa->d_knorm, fa->d_inv_freq, fa->d_q,
                                     fa->d_gate, s));
         B2_TRY(launch_fa_decode(kv, layer, d_slots_in, n_seqs, fa->d_q, fa->d_gate, kMaxSplitsCap, fa->d_part_o,
                                 fa->d_part_ml, fa->d_counters, fa->d_attn, fp16, s));
-        B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, true, dout, pool->d_error, s));
+        B2_TRY(fa_project_out(fa, d_y, y_beta, n_seqs, dout, pool->d_error, s));
         pool->lens_dirty = true;
         return 0;
     }
@@ -261,7 +256,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
     B2_CUDA(cudaMemcpyAsync(d_atiles, atiles.data(), atiles.size() * sizeof(AppendTile), cudaMemcpyHostToDevice, s));
     B2_CUDA(cudaMemcpyAsync(d_ptiles, ptiles.data(), ptiles.size() * sizeof(PrefillTile), cudaMemcpyHostToDevice, s));
 
-    B2_TRY(fa_project_in(fa, d_x, x_is_fp16, rows, false, !kv.is_fp16, pool->d_error, s));
+    B2_TRY(fa_project_in(fa, d_x, x_is_fp16, rows, !kv.is_fp16, nullptr, pool->d_error, s));
     B2_TRY(launch_fa_q_epilogue(fa->d_qkv_raw, rows, fa->d_qnorm, fa->d_inv_freq, d_row_pos, fa->d_q, fa->d_gate, s));
     for (int i = 0; i < n_seqs; ++i)
         B2_TRY(launch_kv_stage_gather(kv, layer, h_slots[i], base[i], ctx0[i], fa->d_kstage, fa->d_vstage, s));
@@ -276,7 +271,7 @@ int fa_forward_rows(b200attn_fa fa, b200attn_kv_pool pool, int layer, const int*
                                     fa->d_gate, fa->d_attn, fp16, pool->d_error, s));
     }
     B2_TRY(launch_kv_advance(kv, layer, d_slots, d_counts, n_seqs, s));
-    B2_TRY(fa_project_out(fa, d_y, y_beta, rows, false, nullptr, pool->d_error, s));
+    B2_TRY(fa_project_out(fa, d_y, y_beta, rows, nullptr, pool->d_error, s));
     for (int i = 0; i < n_seqs; ++i) pool->h_lens[(size_t)layer * pool->cfg.max_seqs + h_slots[i]] += h_counts[i];
     return 0;
 }

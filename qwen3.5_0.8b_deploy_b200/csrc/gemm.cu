@@ -71,7 +71,7 @@ constexpr int kMaxStampSlots = 4096;
 unsigned long long* g_stamps = nullptr;     // [kMaxStampSlots][2] on the device
 int g_stamp_next = 0;
 ProfRec g_prof[PROF_COUNT];
-const char* kProfNames[PROF_COUNT] = {"fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append"};
+const char* kProfNames[PROF_COUNT] = {"fa_prefill", "fa_decode", "la_prefill", "la_decode", "kv_append", "gemm_in", "gemm_ffn", "gemm_res", "lm_head"};
 }  // namespace
 unsigned long long* prof_stamp_slot(ProfKind k) {
     if (!g_prof_on || !g_stamps || g_stamp_next >= kMaxStampSlots) return nullptr;

@@ -77,22 +77,25 @@ int launch_la_conv_import(const float* ref_conv, float* mine, cudaStream_t s);
 int launch_la_conv_export(const float* mine, float* ref_conv, cudaStream_t s);
 
 // ---- tcgen05 skinny GEMMs for the decode step (gemm_tc.cu) ---------------------------------------------------------
-int gemm_tc_splits(int N, int K, int bn);
+constexpr int kRowsqParts = 16;   // partial sums of squares per row of the residual stream, one per 64-column tile of its producer
 bool gemm_tc_enabled();
-int gemm_tc_store(cudaStream_t s, const __half* X, const __half* W, float* Y, int M, int N, int K, int ld_out,
-                  int splits, size_t split_stride, int* d_error);
-int gemm_tc_swiglu(cudaStream_t s, const __half* X, const __half* W, __half* act, int M, int N, int K,
+int gemm_tc_store(cudaStream_t s, const __half* X, const __half* W, float* Y, int M, int N, int K, int ld_out, const float* rowsq,
+                  float rs_eps, int* d_error);
+int gemm_tc_swiglu(cudaStream_t s, const __half* X, const __half* W, __half* act, int M, int N, int K, const float* rowsq, float rs_eps,
                    int* d_error);
+int gemm_tc_residual(cudaStream_t s, const __half* X, const __half* W, float* h, __half* xh, float* rowsq, int M, int N, int K,
+                     int* d_error);
 int gemm_tc_argmax(cudaStream_t s, const __half* X, const __half* W, unsigned long long* d_packed, int* tokens,
                    int M, int N, int K, int* d_error);
 void gemm_tc_forget(const void* ptr);
-
-// Where a decode-step output projection leaves its result when the caller sums split-K partials itself (the stack's
-// next RMSNorm does): `n_splits` matrices [rows, hidden], `stride` floats apart.  n_splits is set by the operator.
+int gemm_tc_map(const void* ptr, int rows, int cols, int box_rows, void* tensor_map_out);   // cached CUtensorMap of a fp16 matrix
+// The fused form of a decode step (tcgen05 projections): the operator's input is the UN-normalised residual stream as
+// fp16 (`d_x`), whose RMSNorm scale the input projection applies in its epilogue from `rowsq`; the output projection
+// adds into the residual stream `d_y` and refreshes `xh` and `rowsq` for the next projection.
 struct DecodeOut {
-    float* partials;
-    size_t stride;
-    int n_splits;
+    __half* xh;        // [rows, hidden] fp16 copy of the residual stream (read as d_x, rewritten by the output projection)
+    float* rowsq;      // [128][kRowsqParts] partial sums of squares of the residual rows
+    float eps;         // RMSNorm epsilon
 };
 
 // ---- operator internals shared with the stack ------------------------------------------------------------------------

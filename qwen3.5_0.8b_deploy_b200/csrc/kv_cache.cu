@@ -216,6 +216,7 @@ fa_decode_pre_kernel(KvView kv, int layer, const int* __restrict__ slots, const 
     pdl_enter();
     const int seq = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slot = slots[seq];
+    if (slot == -1) return;                 // inactive row of a decode batch: nothing is read or written for it
     if (slot < 0 || slot >= kv.max_seqs) {
         if (threadIdx.x == 0) atomicExch(kv.error, 1);
         return;

@@ -184,6 +184,14 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     umma_f16(tm_x, umma_smem_desc(kq + off, 16, 1024), umma_smem_desc(kq + off, 16, 1024), id64, ks > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(G_A_DONE));
+                if (c + 1 < n_chunks) {            // the next chunk's tiles can only land after this chunk's last product: ask L2 for them now
+                    const int row = sq.row0 + (c + 1) * kC;
+                    for (int blk = 0; blk < 2; ++blk) {
+                        tma_prefetch_l2_3d(&map_k, blk * 64, h, row);
+                        tma_prefetch_l2_3d(&map_q, blk * 64, h, row);
+                        tma_prefetch_l2_3d(&map_v, blk * 64, h, row);
+                    }
+                }
                 if (!mbar_wait(bar(G_B1), par, abort_flag)) break;
                 tc_fence_after();
 #pragma unroll
@@ -262,34 +270,32 @@ la_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint32_t par = c & 1;
             const int tok0 = c * kC;
             const int n_valid = min(kC, sq.count - tok0);
-            // this chunk's decay and beta values are requested before the wait on the previous chunk's tensor-core work
-            float gv = 0.f, bv = 0.f;
-            if (tid < 64 && tid < n_valid) {
-                const size_t gi = (size_t)(sq.row0 + tok0 + tid) * kLaHeads + h;
-                gv = g[gi];
-                bv = beta[gi];
+            // this chunk's decay and beta values are requested before the wait on the previous chunk's tensor-core work:
+            // warp 0, two consecutive tokens per lane
+            float g0 = 0.f, g1 = 0.f, bt0 = 0.f, bt1 = 0.f;
+            if (warp == 0) {
+                const size_t gi = (size_t)(sq.row0 + tok0 + 2 * lane) * kLaHeads + h;
+                if (2 * lane < n_valid) { g0 = g[gi]; bt0 = beta[gi]; }
+                if (2 * lane + 1 < n_valid) { g1 = g[gi + kLaHeads]; bt1 = beta[gi + kLaHeads]; }
             }
             if (c > 0) {
                 if (!mbar_wait_warp(bar(G_C3), (c - 1) & 1, abort_flag)) ok = false;
                 tc_fence_after();
                 store_out(c - 1, ok);
             }
-            // ---- per-chunk scalars: b = cumsum(g), beta; padded tokens get g = 0, beta = 0 ----
-            if (tid < 64) {
+            // ---- per-chunk scalars: b = cumsum(g), beta, e^b, e^{b_C - b}; padded tokens get g = 0, beta = 0 ----
+            if (warp == 0) {
+                float run = g0 + g1;
 #pragma unroll
                 for (int o = 1; o < 32; o <<= 1) {
-                    const float t2 = __shfl_up_sync(0xffffffffu, gv, o);
-                    if (lane >= o) gv += t2;
+                    const float t2 = __shfl_up_sync(0xffffffffu, run, o);
+                    if (lane >= o) run += t2;
                 }
-                s_b[tid] = gv;
-                s_beta[tid] = bv;
-            }
-            named_sync_256();
-            if (warp == 1) s_b[tid] += s_b[31];
-            named_sync_256();
-            if (tid < 64) {
-                s_eb[tid] = ex2_approx(s_b[tid] * kLog2e);
-                s_ebc[tid] = ex2_approx((s_b[63] - s_b[tid]) * kLog2e);
+                const float b1 = run, b0 = run - g1, b_last = __shfl_sync(0xffffffffu, run, 31);
+                s_b[2 * lane] = b0; s_b[2 * lane + 1] = b1;
+                s_beta[2 * lane] = bt0; s_beta[2 * lane + 1] = bt1;
+                s_eb[2 * lane] = ex2_approx(b0 * kLog2e); s_eb[2 * lane + 1] = ex2_approx(b1 * kLog2e);
+                s_ebc[2 * lane] = ex2_approx((b_last - b0) * kLog2e); s_ebc[2 * lane + 1] = ex2_approx((b_last - b1) * kLog2e);
             }
             named_sync_256();
             const float e_bc = ex2_approx(s_b[63] * kLog2e);

@@ -281,24 +281,19 @@ int la_forward_rows(b200attn_la la, b200attn_la_state st, int layer, const int* 
     float* conv_layer = st->d_conv + (size_t)layer * st->cfg.max_seqs * st->conv_stride_slot();
     auto project_in = [&](int rows) -> int {
         if (fp16) {
+            if (decode && dout)   // decode step of a stack: d_x is the un-normalised residual stream, its RMSNorm scale is applied in the epilogue
+                return gemm_tc_store(s, (const __half*)d_x, la->d_win_fp16, la->d_mixed, rows, kLaProjCols, kHidden, kLaProjCols, dout->rowsq,
+                                     dout->eps, la->d_error);
             const void* xb = d_x;
             if (!x_is_fp16) { B2_TRY(f32_to_f16(s, (const float*)d_x, la->d_xb, (size_t)rows * kHidden)); xb = la->d_xb; }
-            if (decode && rows <= 128 && gemm_tc_enabled())   // weight-streaming tcgen05 GEMM
-                return gemm_tc_store(s, (const __half*)xb, la->d_win_fp16, la->d_mixed, rows, kLaProjCols, kHidden, kLaProjCols, 1, 0, la->d_error);
             return gemm_xwT(s, xb, true, la->d_win_fp16, true, la->d_mixed, false, rows, kLaProjCols, kHidden);
         }
         return gemm_xwT(s, d_x, false, la->d_win_f32, false, la->d_mixed, false, rows, kLaProjCols, kHidden);
     };
     auto project_out = [&](int rows) -> int {
-        if (fp16 && decode && rows <= 128 && gemm_tc_enabled() && (dout || y_beta == 0.f)) {
-            const int K = kLaHeads * kLaVd;
-            if (dout) {
-                dout->n_splits = gemm_tc_splits(kHidden, K, 64);
-                return gemm_tc_store(s, (const __half*)la->d_gated, la->d_wout_fp16, dout->partials, rows, kHidden, K, kHidden,
-                                     dout->n_splits, dout->stride, la->d_error);
-            }
-            return gemm_tc_store(s, (const __half*)la->d_gated, la->d_wout_fp16, d_y, rows, kHidden, K, kHidden, 1, 0, la->d_error);
-        }
+        if (decode && dout)   // residual stream += gated W_out^T, with the fp16 copy and the sums of squares for the next projection
+            return gemm_tc_residual(s, (const __half*)la->d_gated, la->d_wout_fp16, d_y, dout->xh, dout->rowsq, rows, kHidden, kLaHeads * kLaVd,
+                                    la->d_error);
         if (fp16) return gemm_xwT(s, la->d_gated, true, la->d_wout_fp16, true, d_y, false, rows, kHidden, kLaHeads * kLaVd, y_beta);
         return gemm_xwT(s, la->d_gated, false, la->d_wout_f32, false, d_y, false, rows, kHidden, kLaHeads * kLaVd, y_beta);
     };

@@ -39,10 +39,17 @@ struct b200attn_stack_s {
     float* d_logits = nullptr;         // [max_seqs, vocab]
     int* d_tokens = nullptr;           // [max_seqs] decode token buffer (in place)
     int* d_slots = nullptr;            // [max_seqs] identity slots
-    float* d_partials = nullptr;       // [kMaxSplits][128][hidden] split-K partials of the decode-step output projections
+    __half* d_xh = nullptr;            // [128, hidden] fp16 copy of the residual stream in the fused decode step
+    float* d_rowsq = nullptr;          // [128][kRowsqParts] partial sums of squares of the residual rows
     unsigned long long* d_packed = nullptr;   // [128] running argmax words of the LM head
     int* d_error = nullptr;            // device status word of the stack's own tcgen05 GEMMs
     int* d_last_idx = nullptr;         // [max_seqs] row of every sequence's last prompt token inside a prefill pass
+    // Continuous batching: row r of a decode step is bound to slot row_slot[r] (its KV pages and DeltaNet state), -1 =
+    // inactive.  Empty in the plain mode, where row r is slot r.
+    bool batching = false;
+    std::vector<int> row_slot;
+    std::vector<int> free_slots;
+    int n_active = 0;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
     int graph_nseqs = 0;
@@ -70,33 +77,44 @@ __global__ void embed_gather_kernel(const int* __restrict__ tokens, const __half
     *reinterpret_cast<float4*>(h + (size_t)row * kHidden + 4 * threadIdx.x) = make_float4(a.x, a.y, b.x, b.y);
 }
 
-// RMSNorm with (1 + w), fp32 in, fp16 out (and optional fp32 copy).  One 256-thread block per row, one float4 per
-// thread; optional row gather.  n_splits > 0: first x[row] += sum of the split-K partial rows (written back), i.e.
-// the residual add of the preceding output projection happens here; the partial loads are issued four at a time.
+// The same gather for the fused decode step: besides h it leaves the fp16 copy of the row and the row's sum of squares
+// (part 0 of kRowsqParts, the others zero), which the first input projection turns into the RMSNorm scale.
 __global__ void __launch_bounds__(256)
-rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w, float eps,
-               int rows, __half* __restrict__ out_fp16, float* __restrict__ out_f32,
-               const float* __restrict__ partials, int n_splits, size_t split_stride) {
+embed_gather_fused_kernel(const int* __restrict__ tokens, const __half* __restrict__ embed, int vocab, float* __restrict__ h,
+                          __half* __restrict__ xh, float* __restrict__ rowsq) {
+    __shared__ float s_part[8];
+    pdl_enter();
+    const int row = blockIdx.x, t = threadIdx.x;
+    int tok = tokens[row];
+    tok = min(max(tok, 0), vocab - 1);
+    const uint2 raw = *reinterpret_cast<const uint2*>(embed + (size_t)tok * kHidden + 4 * t);
+    const __half2* p = reinterpret_cast<const __half2*>(&raw);
+    const float2 a = __half22float2(p[0]), b = __half22float2(p[1]);
+    *reinterpret_cast<float4*>(h + (size_t)row * kHidden + 4 * t) = make_float4(a.x, a.y, b.x, b.y);
+    *reinterpret_cast<uint2*>(xh + (size_t)row * kHidden + 4 * t) = raw;
+    float ss = wsum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y);
+    if ((t & 31) == 0) s_part[t >> 5] = ss;
+    __syncthreads();
+    if (t < kRowsqParts) {
+        float tot = 0.f;
+        if (t == 0)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tot += s_part[i];
+        rowsq[(size_t)row * kRowsqParts + t] = tot;
+    }
+}
+
+// RMSNorm with (1 + w), fp32 in, fp16 out (and optional fp32 copy).  One 256-thread block per row, one float4 per
+// thread; optional row gather.
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ w, float eps,
+               int rows, __half* __restrict__ out_fp16, float* __restrict__ out_f32) {
     __shared__ float s_part[8];
     const int row = blockIdx.x, t = threadIdx.x;
     const float4 ww = *reinterpret_cast<const float4*>(w + 4 * t);
     pdl_enter();
     const size_t srow = (size_t)(row_index ? row_index[row] : row);
-    float4* src = reinterpret_cast<float4*>(x + srow * kHidden) + t;
-    float4 v = *src;
-    if (n_splits > 0) {
-        const float4* p = reinterpret_cast<const float4*>(partials + srow * kHidden) + t;
-        const size_t step = split_stride / 4;
-        for (int sp = 0; sp < n_splits; sp += 4) {
-            float4 q[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                q[e] = (sp + e < n_splits) ? __ldcg(p + (size_t)(sp + e) * step) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { v.x += q[e].x; v.y += q[e].y; v.z += q[e].z; v.w += q[e].w; }
-        }
-        *src = v;
-    }
+    const float4 v = *(reinterpret_cast<const float4*>(x + srow * kHidden) + t);
     float ss = wsum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
     if ((t & 31) == 0) s_part[t >> 5] = ss;
     __syncthreads();
@@ -116,7 +134,7 @@ rmsnorm_kernel(float* __restrict__ x, const int* __restrict__ row_index, const f
     if (out_f32) *reinterpret_cast<float4*>(out_f32 + (size_t)row * kHidden + 4 * t) = make_float4(r0, r1, r2, r3);
 }
 
-// The same RMSNorm for many rows without pending partials (prefill): one warp per row, 32 values per lane, four rows per
+// The same RMSNorm for many rows (prefill): one warp per row, 32 values per lane, four rows per
 // block, so that a pass over 131072 rows is 32768 blocks of useful size instead of 131072 blocks of one float4 per thread.
 __global__ void __launch_bounds__(128)
 rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int rows, __half* __restrict__ out_fp16) {
@@ -233,7 +251,6 @@ __global__ void quantize_rows_kernel(float* __restrict__ w, int rows, int cols) 
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-constexpr int kMaxSplits = 16;
 
 // Uploads a host fp32 matrix as fp16, optionally through the INT8 fake quantiser.
 static int upload_matrix(const float* h, int rows, int cols, bool int8, __half** out) {
@@ -273,7 +290,7 @@ extern "C" int b200attn_stack_destroy(b200attn_stack st) {
     cudaFree(st->op_scratch.base);
     cudaFree(st->d_h); cudaFree(st->d_xb); cudaFree(st->d_gu); cudaFree(st->d_act); cudaFree(st->d_last);
     cudaFree(st->d_logits); cudaFree(st->d_tokens); cudaFree(st->d_slots);
-    cudaFree(st->d_partials); cudaFree(st->d_packed); cudaFree(st->d_error); cudaFree(st->d_last_idx);
+    cudaFree(st->d_xh); cudaFree(st->d_rowsq); cudaFree(st->d_packed); cudaFree(st->d_error); cudaFree(st->d_last_idx);
     delete st;
     return 0;
 }
@@ -341,7 +358,9 @@ extern "C" int b200attn_stack_create(const b200attn_stack_config* cfg, b200attn_
     ST_CUDA(cudaMalloc(&st->d_tokens, (size_t)cfg->max_seqs * 4));
     ST_CUDA(cudaMalloc(&st->d_slots, (size_t)cfg->max_seqs * 4));
     ST_CUDA(cudaMemset(st->d_tokens, 0, (size_t)cfg->max_seqs * 4));
-    ST_CUDA(cudaMalloc(&st->d_partials, (size_t)kMaxSplits * 128 * kHidden * 4));
+    ST_CUDA(cudaMalloc(&st->d_xh, (size_t)128 * kHidden * 2));
+    ST_CUDA(cudaMalloc(&st->d_rowsq, (size_t)128 * kRowsqParts * 4));
+    ST_CUDA(cudaMemset(st->d_rowsq, 0, (size_t)128 * kRowsqParts * 4));
     ST_CUDA(cudaMalloc(&st->d_packed, 128 * sizeof(unsigned long long)));
     ST_CUDA(cudaMemset(st->d_packed, 0, 128 * sizeof(unsigned long long)));
     ST_CUDA(cudaMalloc(&st->d_error, sizeof(int)));
@@ -363,18 +382,14 @@ extern "C" int b200attn_stack_set_layer_weights(b200attn_stack st, int layer, co
     st->layer_ready[layer] = 0;
     cudaFree(st->d_in_norm[layer]); cudaFree(st->d_post_norm[layer]); cudaFree(st->d_wgu[layer]); cudaFree(st->d_wdown[layer]);
     st->d_in_norm[layer] = st->d_post_norm[layer] = nullptr; st->d_wgu[layer] = st->d_wdown[layer] = nullptr;
-    B2_TRY(upload_f32(w->input_norm, &st->d_in_norm[layer], kHidden));
-    B2_TRY(upload_f32(w->post_norm, &st->d_post_norm[layer], kHidden));
-    // rows in tiles of 64: 32 gate rows then the 32 matching up rows (see swiglu_kernel)
-    std::vector<float> gu((size_t)2 * inter * kHidden);
-    for (int c = 0; c < inter; ++c) {
-        const size_t tile = c / 32, j = c % 32;
-        std::memcpy(gu.data() + (tile * 64 + j) * kHidden, w->ffn_gate + (size_t)c * kHidden, (size_t)kHidden * 4);
-        std::memcpy(gu.data() + (tile * 64 + 32 + j) * kHidden, w->ffn_up + (size_t)c * kHidden, (size_t)kHidden * 4);
-    }
-    B2_TRY(upload_matrix(gu.data(), 2 * inter, kHidden, q8, &st->d_wgu[layer]));
-    B2_TRY(upload_matrix(w->ffn_down, kHidden, inter, q8, &st->d_wdown[layer]));
-    // Attention matrices go through the same per-output-channel quantiser when int8_weights is set.
+    // The (1 + w) factors of the two RMSNorms are folded into the columns of the matrices that consume the normalised
+    // rows (after quantisation, so the INT8 codes are those of the original matrix): x / rms * (1 + w) W^T = x / rms W'^T.
+    // The norm kernels of the unfused paths therefore run with zero weights, and the fused decode step needs no norm
+    // launch at all: its projections scale their output rows by 1 / rms.
+    const std::vector<float> zeros(kHidden, 0.f);
+    B2_TRY(upload_f32(zeros.data(), &st->d_in_norm[layer], kHidden));
+    B2_TRY(upload_f32(zeros.data(), &st->d_post_norm[layer], kHidden));
+    // Per-output-channel INT8 fake quantisation on the host (the arithmetic of quantize_rows_kernel).
     auto q8_copy = [&](const float* src, int rows, int cols, std::vector<float>& dst) {
         dst.assign(src, src + (size_t)rows * cols);
         if (!q8) return;
@@ -387,6 +402,25 @@ extern "C" int b200attn_stack_set_layer_weights(b200attn_stack st, int layer, co
             for (int c = 0; c < cols; ++c) row[c] = std::max(-127.f, std::min(127.f, roundf(row[c] / s))) * s;
         }
     };
+    auto fold = [&](std::vector<float>& m, int rows, const float* norm_w) {     // column k of an [rows, hidden] matrix *= 1 + w[k]
+        for (int r = 0; r < rows; ++r) {
+            float* row = m.data() + (size_t)r * kHidden;
+            for (int c = 0; c < kHidden; ++c) row[c] *= 1.0f + norm_w[c];
+        }
+    };
+    {
+        // rows in tiles of 64: 32 gate rows then the 32 matching up rows (see swiglu_kernel)
+        std::vector<float> gu_src((size_t)2 * inter * kHidden), gu;
+        for (int c = 0; c < inter; ++c) {
+            const size_t tile = c / 32, j = c % 32;
+            std::memcpy(gu_src.data() + (tile * 64 + j) * kHidden, w->ffn_gate + (size_t)c * kHidden, (size_t)kHidden * 4);
+            std::memcpy(gu_src.data() + (tile * 64 + 32 + j) * kHidden, w->ffn_up + (size_t)c * kHidden, (size_t)kHidden * 4);
+        }
+        q8_copy(gu_src.data(), 2 * inter, kHidden, gu);
+        fold(gu, 2 * inter, w->post_norm);
+        B2_TRY(upload_matrix(gu.data(), 2 * inter, kHidden, false, &st->d_wgu[layer]));
+    }
+    B2_TRY(upload_matrix(w->ffn_down, kHidden, inter, q8, &st->d_wdown[layer]));
     if (st->layer_kind[layer]) {
         B2_CHECK_ARG(w->fa, "stack_set_layer_weights: layer %d is full attention, fa weights missing", layer);
         std::vector<float> q, k, v, o;
@@ -394,6 +428,9 @@ extern "C" int b200attn_stack_set_layer_weights(b200attn_stack st, int layer, co
         q8_copy(w->fa->k_proj, kFaKvHeads * kHeadDim, kHidden, k);
         q8_copy(w->fa->v_proj, kFaKvHeads * kHeadDim, kHidden, v);
         q8_copy(w->fa->o_proj, kHidden, kFaHeads * kHeadDim, o);
+        fold(q, kFaHeads * kHeadDim * 2, w->input_norm);
+        fold(k, kFaKvHeads * kHeadDim, w->input_norm);
+        fold(v, kFaKvHeads * kHeadDim, w->input_norm);
         b200attn_fa_weights fw{q.data(), k.data(), v.data(), w->fa->q_norm, w->fa->k_norm, o.data()};
         B2_TRY(b200attn_fa_set_weights(st->fa[st->layer_sub[layer]], &fw));
     } else {
@@ -404,6 +441,10 @@ extern "C" int b200attn_stack_set_layer_weights(b200attn_stack st, int layer, co
         q8_copy(w->la->in_proj_b, kLaHeads, kHidden, b);
         q8_copy(w->la->in_proj_z, kLaHeads * kLaVd, kHidden, z);
         q8_copy(w->la->out_proj, kHidden, kLaHeads * kLaVd, o);
+        fold(qkv, kLaConvDim, w->input_norm);
+        fold(a, kLaHeads, w->input_norm);
+        fold(b, kLaHeads, w->input_norm);
+        fold(z, kLaHeads * kLaVd, w->input_norm);
         b200attn_la_weights lw{qkv.data(), a.data(), b.data(), z.data(), w->la->conv1d, w->la->a_log, w->la->dt_bias,
                                w->la->norm, o.data()};
         B2_TRY(b200attn_la_set_weights(st->la[st->layer_sub[layer]], &lw));
@@ -452,6 +493,14 @@ extern "C" int b200attn_stack_reset(b200attn_stack st, b200attn_stream stream) {
     B2_CHECK_ARG(st, "stack_reset: null stack");
     if (st->pool) B2_TRY(b200attn_kv_clear(st->pool, stream));
     if (st->state) B2_TRY(b200attn_la_state_clear(st->state, -1, stream));
+    if (st->batching) {     // back to the plain mode: row r is slot r, every slot holds pages for max_seq_len tokens
+        st->batching = false;
+        st->n_active = 0;
+        if (st->pool)
+            for (int i = 0; i < st->cfg.max_seqs; ++i) B2_TRY(b200attn_kv_seq_reserve(st->pool, i, st->cfg.max_seq_len));
+        iota_kernel<<<ceil_div(st->cfg.max_seqs, 128), 128, 0, b200::as_stream(stream)>>>(st->d_slots, st->cfg.max_seqs);
+        B2_LAUNCH_CHECK();
+    }
     return 0;
 }
 
@@ -465,60 +514,58 @@ static int stack_ready(b200attn_stack st) {
     return 0;
 }
 
-// All layers over `rows` rows already embedded in d_h.  Returns through *pending the number of split-K partial
-// matrices of the last output projection that still have to be added to d_h (decode path only).
+// All layers over `rows` rows already embedded in d_h (and, for the fused decode step, in d_xh / d_rowsq).
 static int stack_layers(b200attn_stack st, int rows, const int* h_slots, const int* h_counts, int n_seqs, const int* d_slots,
-                        bool decode, int* pending_out, cudaStream_t s) {
+                        bool decode, cudaStream_t s) {
     const int inter = st->cfg.intermediate_size;
-    const bool tc = decode && rows <= 128 && gemm_tc_enabled();          // weight-streaming tcgen05 GEMMs with fused epilogues
-    const size_t pstride = (size_t)128 * kHidden;
-    int pending = 0;
-    const bool many_rows = !decode && rows > 128;      // prefill: no pending partials, warp-per-row norm
+    if (decode && rows <= 128 && gemm_tc_enabled()) {
+        // Fused decode step, five launches per DeltaNet layer: input projection (RMSNorm scale in its epilogue, the norm's
+        // (1 + w) folded into the weights at load), attention, output projection + residual, gate/up + SwiGLU, down +
+        // residual.  The residual projections also leave the fp16 copy and the sums of squares the next projection needs.
+        DecodeOut f{st->d_xh, st->d_rowsq, st->cfg.rms_eps};
+        for (int i = 0; i < st->cfg.num_layers; ++i) {
+            if (st->layer_kind[i])
+                B2_TRY(fa_forward_rows(st->fa[st->layer_sub[i]], st->pool, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots, true,
+                                       st->d_xh, true, st->d_h, 1.0f, &f, s));
+            else
+                B2_TRY(la_forward_rows(st->la[st->layer_sub[i]], st->state, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots, true,
+                                       st->d_xh, true, st->d_h, 1.0f, &f, s));
+            B2_TRY(gemm_tc_swiglu(s, st->d_xh, st->d_wgu[i], st->d_act, rows, 2 * inter, kHidden, st->d_rowsq, st->cfg.rms_eps, st->d_error));
+            B2_TRY(gemm_tc_residual(s, st->d_act, st->d_wdown[i], st->d_h, st->d_xh, st->d_rowsq, rows, kHidden, inter, st->d_error));
+        }
+        return 0;
+    }
+    const bool many_rows = !decode && rows > 128;      // prefill: warp-per-row norm
     for (int i = 0; i < st->cfg.num_layers; ++i) {
         if (many_rows)
             rmsnorm_rows_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb);
         else
-            launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
-                       st->d_partials, pending, pstride);
+            launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_in_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr);
         B2_LAUNCH_CHECK();
-        DecodeOut dout{st->d_partials, pstride, 0};
         if (st->layer_kind[i])
             B2_TRY(fa_forward_rows(st->fa[st->layer_sub[i]], st->pool, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots,
-                                   decode, st->d_xb, true, st->d_h, 1.0f, tc ? &dout : nullptr, s));
+                                   decode, st->d_xb, true, st->d_h, 1.0f, nullptr, s));
         else
             B2_TRY(la_forward_rows(st->la[st->layer_sub[i]], st->state, st->layer_sub[i], h_slots, h_counts, n_seqs, d_slots,
-                                   decode, st->d_xb, true, st->d_h, 1.0f, tc ? &dout : nullptr, s));
+                                   decode, st->d_xb, true, st->d_h, 1.0f, nullptr, s));
         if (many_rows)
             rmsnorm_rows_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(st->d_h, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb);
         else
-            launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr,
-                       st->d_partials, dout.n_splits, pstride);
+            launch_pdl(rmsnorm_kernel, dim3(rows), dim3(256), 0, s, st->d_h, nullptr, st->d_post_norm[i], st->cfg.rms_eps, rows, st->d_xb, nullptr);
         B2_LAUNCH_CHECK();
-        if (tc) {
-            B2_TRY(gemm_tc_swiglu(s, st->d_xb, st->d_wgu[i], st->d_act, rows, 2 * inter, kHidden, st->d_error));
-            pending = std::min(kMaxSplits, gemm_tc_splits(kHidden, inter, 64));
-            B2_TRY(gemm_tc_store(s, st->d_act, st->d_wdown[i], st->d_partials, rows, kHidden, inter, kHidden, pending, pstride, st->d_error));
-        } else {
-            // (the tcgen05 gate/up GEMM with the SwiGLU in its epilogue was measured here as well: 2.39 ms per decode step
-            // against 2.31 ms for cuBLAS followed by the SwiGLU kernel)
-            B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_wgu[i], true, st->d_gu, true, rows, 2 * inter, kHidden));
-            const size_t octs = (size_t)rows * inter / 8;
-            swiglu_kernel<<<(unsigned)((octs + 255) / 256), 256, 0, s>>>(st->d_gu, inter, octs, st->d_act);
-            B2_LAUNCH_CHECK();
-            B2_TRY(gemm_xwT(s, st->d_act, true, st->d_wdown[i], true, st->d_h, false, rows, kHidden, inter, 1.0f));
-            pending = 0;
-        }
+        B2_TRY(gemm_xwT(s, st->d_xb, true, st->d_wgu[i], true, st->d_gu, true, rows, 2 * inter, kHidden));
+        const size_t octs = (size_t)rows * inter / 8;
+        swiglu_kernel<<<(unsigned)((octs + 255) / 256), 256, 0, s>>>(st->d_gu, inter, octs, st->d_act);
+        B2_LAUNCH_CHECK();
+        B2_TRY(gemm_xwT(s, st->d_act, true, st->d_wdown[i], true, st->d_h, false, rows, kHidden, inter, 1.0f));
     }
-    *pending_out = pending;
     return 0;
 }
 
-// Final norm of the selected rows (after adding `pending` partial matrices), tied LM head, greedy argmax.
-static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int pending, int* d_next, float* d_hidden_out,
-                      cudaStream_t s) {
+// Final norm of the selected rows, tied LM head, greedy argmax.
+static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int* d_next, float* d_hidden_out, cudaStream_t s) {
     launch_pdl(rmsnorm_kernel, dim3(n_seqs), dim3(256), 0, s, st->d_h, d_row_index, st->d_final_norm, st->cfg.rms_eps, n_seqs, st->d_xb,
-                                                      d_hidden_out ? d_hidden_out : nullptr, st->d_partials, pending,
-                                                      (size_t)128 * kHidden);
+               d_hidden_out);
     B2_LAUNCH_CHECK();
     // LM head with the argmax in the GEMM epilogue (the logits never reach memory): 103 us per step against 112 + 31 us for
     // the cuBLAS GEMM and the argmax kernel.  B200ATTN_LM_HEAD=cublas (read at create time) selects the latter.
@@ -531,13 +578,40 @@ static int stack_head(b200attn_stack st, int n_seqs, const int* d_row_index, int
 }
 
 static int stack_decode_step(b200attn_stack st, int n_seqs, const int* d_tokens_in, int* d_tokens_out, cudaStream_t s) {
-    launch_pdl(embed_gather_kernel, dim3(n_seqs), dim3(256), 0, s, d_tokens_in, st->d_embed, st->cfg.vocab_size, st->d_h);
+    if (n_seqs <= 128 && gemm_tc_enabled())
+        launch_pdl(embed_gather_fused_kernel, dim3(n_seqs), dim3(256), 0, s, d_tokens_in, st->d_embed, st->cfg.vocab_size, st->d_h, st->d_xh,
+                   st->d_rowsq);
+    else
+        launch_pdl(embed_gather_kernel, dim3(n_seqs), dim3(256), 0, s, d_tokens_in, st->d_embed, st->cfg.vocab_size, st->d_h);
     B2_LAUNCH_CHECK();
-    int pending = 0;
-    B2_TRY(stack_layers(st, n_seqs, nullptr, nullptr, n_seqs, st->d_slots, true, &pending, s));
-    return stack_head(st, n_seqs, nullptr, pending, d_tokens_out, nullptr, s);
+    B2_TRY(stack_layers(st, n_seqs, nullptr, nullptr, n_seqs, st->d_slots, true, s));
+    return stack_head(st, n_seqs, nullptr, d_tokens_out, nullptr, s);
 }
 
+}  // namespace b200
+
+namespace b200 {
+// Prefill of n_seqs prompts of prompt_len tokens into the given slots (host array); the greedy next token of sequence
+// i goes to d_next[i].
+static int stack_prefill_slots(b200attn_stack st, const int* h_slots, int n_seqs, int prompt_len, const int* d_tokens, int* d_next,
+                               float* d_hidden_out, cudaStream_t s) {
+    const int chunk = std::max(1, std::min(n_seqs, st->max_rows / prompt_len));
+    std::vector<int> counts(chunk, prompt_len);
+    int* d_idx = st->d_last_idx;   // row of each sequence's last token inside the pass
+    int rc = 0;
+    for (int s0 = 0; s0 < n_seqs && rc == 0; s0 += chunk) {
+        const int n = std::min(chunk, n_seqs - s0);
+        const int rows = n * prompt_len;
+        launch_pdl(embed_gather_kernel, dim3(rows), dim3(256), 0, s, d_tokens + (size_t)s0 * prompt_len, st->d_embed, st->cfg.vocab_size, st->d_h);
+        count_launch();
+        rc = stack_layers(st, rows, h_slots + s0, counts.data(), n, nullptr, false, s);
+        if (rc != 0) break;
+        last_row_index_kernel<<<ceil_div(n, 128), 128, 0, s>>>(d_idx, n, prompt_len);
+        count_launch();
+        rc = stack_head(st, n, d_idx, d_next + s0, d_hidden_out ? d_hidden_out + (size_t)s0 * kHidden : nullptr, s);
+    }
+    return rc;
+}
 }  // namespace b200
 
 extern "C" int b200attn_stack_prefill(b200attn_stack st, int n_seqs, int prompt_len, const int* d_tokens, int* d_next,
@@ -546,25 +620,90 @@ extern "C" int b200attn_stack_prefill(b200attn_stack st, int n_seqs, int prompt_
     B2_CHECK_ARG(d_tokens && d_next, "stack_prefill: null argument");
     B2_CHECK_ARG(n_seqs > 0 && n_seqs <= st->cfg.max_seqs, "stack_prefill: n_seqs %d outside (0, %d]", n_seqs, st->cfg.max_seqs);
     B2_CHECK_ARG(prompt_len > 0 && prompt_len <= st->cfg.max_seq_len, "stack_prefill: prompt_len %d outside (0, %d]", prompt_len, st->cfg.max_seq_len);
+    if (st->batching) B2_FAIL(B200ATTN_ERR_INVALID, "stack_prefill: the stack is in continuous-batching mode (use b200attn_stack_admit, or b200attn_stack_reset first)");
+    std::vector<int> slots(n_seqs);
+    for (int i = 0; i < n_seqs; ++i) slots[i] = i;
+    return stack_prefill_slots(st, slots.data(), n_seqs, prompt_len, d_tokens, d_next, d_hidden_out, as_stream(stream));
+}
+
+// ---- continuous batching ---------------------------------------------------------------------------------------------
+namespace b200 {
+static int push_row_slots(b200attn_stack st, cudaStream_t s) {
+    B2_CUDA(cudaMemcpyAsync(st->d_slots, st->row_slot.data(), st->row_slot.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+    B2_CUDA(cudaStreamSynchronize(s));      // the host vector may change right after
+    return 0;
+}
+}  // namespace b200
+
+extern "C" int b200attn_stack_begin_batching(b200attn_stack st, b200attn_stream stream) {
+    B2_TRY(stack_ready(st));
     cudaStream_t s = as_stream(stream);
-    const int chunk = std::max(1, std::min(n_seqs, st->max_rows / prompt_len));
-    std::vector<int> slots(chunk), counts(chunk, prompt_len);
-    int* d_idx = st->d_last_idx;   // row of each sequence's last token inside the pass
-    int rc = 0;
-    for (int s0 = 0; s0 < n_seqs && rc == 0; s0 += chunk) {
-        const int n = std::min(chunk, n_seqs - s0);
-        const int rows = n * prompt_len;
-        for (int i = 0; i < n; ++i) slots[i] = s0 + i;
-        launch_pdl(embed_gather_kernel, dim3(rows), dim3(256), 0, s, d_tokens + (size_t)s0 * prompt_len, st->d_embed, st->cfg.vocab_size, st->d_h);
-        count_launch();
-        int pending = 0;
-        rc = stack_layers(st, rows, slots.data(), counts.data(), n, nullptr, false, &pending, s);
-        if (rc != 0) break;
-        last_row_index_kernel<<<ceil_div(n, 128), 128, 0, s>>>(d_idx, n, prompt_len);
-        count_launch();
-        rc = stack_head(st, n, d_idx, pending, d_next + s0, d_hidden_out ? d_hidden_out + (size_t)s0 * kHidden : nullptr, s);
+    B2_CUDA(cudaStreamSynchronize(s));
+    B2_TRY(b200attn_stack_reset(st, stream));
+    const int n = st->cfg.max_seqs;
+    st->batching = true;
+    st->row_slot.assign(n, -1);
+    st->free_slots.clear();
+    for (int i = n - 1; i >= 0; --i) st->free_slots.push_back(i);          // slot 0 is handed out first
+    st->n_active = 0;
+    if (st->pool)
+        for (int i = 0; i < n; ++i) B2_TRY(b200attn_kv_seq_shrink(st->pool, i, 0));   // pages go back to the pool (one stays with the slot)
+    return push_row_slots(st, s);
+}
+
+extern "C" int b200attn_stack_admit(b200attn_stack st, const int* d_prompt, int prompt_len, int reserve_tokens, int* row_out,
+                                    b200attn_stream stream) {
+    B2_TRY(stack_ready(st));
+    B2_CHECK_ARG(d_prompt && row_out, "stack_admit: null argument");
+    if (!st->batching) B2_FAIL(B200ATTN_ERR_INVALID, "stack_admit: call b200attn_stack_begin_batching first");
+    B2_CHECK_ARG(prompt_len > 0 && prompt_len <= reserve_tokens && reserve_tokens <= st->cfg.max_seq_len,
+                 "stack_admit: need 0 < prompt_len (%d) <= reserve_tokens (%d) <= max_seq_len (%d)", prompt_len, reserve_tokens, st->cfg.max_seq_len);
+    B2_CHECK_ARG(prompt_len <= st->max_rows, "stack_admit: prompt of %d tokens exceeds the prefill scratch (%d rows)", prompt_len, st->max_rows);
+    if (st->free_slots.empty()) B2_FAIL(B200ATTN_ERR_NOMEM, "stack_admit: all %d rows are in use", st->cfg.max_seqs);
+    cudaStream_t s = as_stream(stream);
+    const int slot = st->free_slots.back();
+    if (st->pool) B2_TRY(b200attn_kv_seq_reserve(st->pool, slot, reserve_tokens));      // NOMEM when the page pool cannot hold it: nothing changed
+    st->free_slots.pop_back();
+    if (st->state) B2_TRY(b200attn_la_state_clear(st->state, slot, stream));
+    const int row = st->n_active;
+    B2_TRY(stack_prefill_slots(st, &slot, 1, prompt_len, d_prompt, st->d_tokens + row, nullptr, s));
+    st->row_slot[row] = slot;
+    st->n_active = row + 1;
+    B2_TRY(push_row_slots(st, s));
+    *row_out = row;
+    return 0;
+}
+
+extern "C" int b200attn_stack_retire(b200attn_stack st, int row, b200attn_stream stream) {
+    B2_CHECK_ARG(st, "stack_retire: null stack");
+    if (!st->batching) B2_FAIL(B200ATTN_ERR_INVALID, "stack_retire: the stack is not in continuous-batching mode");
+    B2_CHECK_ARG(row >= 0 && row < st->n_active, "stack_retire: row %d is not active (%d active rows)", row, st->n_active);
+    cudaStream_t s = as_stream(stream);
+    B2_CUDA(cudaStreamSynchronize(s));            // no step may be in flight while rows move
+    const int slot = st->row_slot[row], last = st->n_active - 1;
+    if (st->pool) B2_TRY(b200attn_kv_seq_shrink(st->pool, slot, 0));
+    st->free_slots.push_back(slot);
+    if (row != last) {                            // keep the rows dense: the last active row takes the freed place
+        st->row_slot[row] = st->row_slot[last];
+        B2_CUDA(cudaMemcpyAsync(st->d_tokens + row, st->d_tokens + last, sizeof(int), cudaMemcpyDeviceToDevice, s));
     }
-    return rc;
+    st->row_slot[last] = -1;
+    st->n_active = last;
+    return push_row_slots(st, s);
+}
+
+extern "C" int b200attn_stack_rows(b200attn_stack st, int* n_active_out, int* h_row_slots) {
+    B2_CHECK_ARG(st && n_active_out, "stack_rows: null argument");
+    *n_active_out = st->batching ? st->n_active : 0;
+    if (h_row_slots && st->batching) std::memcpy(h_row_slots, st->row_slot.data(), st->row_slot.size() * sizeof(int));
+    return 0;
+}
+
+extern "C" int b200attn_stack_step(b200attn_stack st, int n_rows, b200attn_stream stream) {
+    B2_TRY(stack_ready(st));
+    B2_CHECK_ARG(n_rows > 0 && n_rows <= st->cfg.max_seqs, "stack_step: n_rows %d outside (0, %d]", n_rows, st->cfg.max_seqs);
+    if (st->graph_exec && st->graph_nseqs == n_rows) return b200attn_decode_graph_launch(st, 1, stream);
+    return stack_decode_step(st, n_rows, st->d_tokens, st->d_tokens, as_stream(stream));
 }
 
 extern "C" int b200attn_stack_decode(b200attn_stack st, int n_seqs, const int* d_tokens_in, int* d_tokens_out,

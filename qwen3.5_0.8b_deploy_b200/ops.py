@@ -38,6 +38,7 @@ ABI_SYMBOLS = [
     "b200attn_stack_device_status",
     "b200attn_stack_prefill", "b200attn_stack_decode", "b200attn_decode_graph_capture",
     "b200attn_decode_graph_launch", "b200attn_stack_set_tokens", "b200attn_stack_get_tokens",
+    "b200attn_stack_begin_batching", "b200attn_stack_admit", "b200attn_stack_retire", "b200attn_stack_rows", "b200attn_stack_step",
 ]
 
 
@@ -434,6 +435,28 @@ class HybridStack:
         out = torch.empty(n_seqs, dtype=torch.int32, device="cuda")
         _check(_lib.b200attn_stack_get_tokens(self.h, _dev(out), C.c_int(n_seqs), _stream()))
         return out
+
+    # ---- continuous batching ----
+    def begin_batching(self) -> None:
+        _check(_lib.b200attn_stack_begin_batching(self.h, _stream()))
+
+    def admit(self, prompt: torch.Tensor, reserve_tokens: int) -> int:
+        """Admit one sequence (prompt: int32 device tensor); returns its row."""
+        row = C.c_int(-1)
+        _check(_lib.b200attn_stack_admit(self.h, _dev(prompt), C.c_int(prompt.numel()), C.c_int(reserve_tokens), C.byref(row), _stream()))
+        return row.value
+
+    def retire(self, row: int) -> None:
+        _check(_lib.b200attn_stack_retire(self.h, C.c_int(row), _stream()))
+
+    def rows(self) -> tuple[int, list[int]]:
+        n = C.c_int(0)
+        slots = (C.c_int * self.cfg.max_seqs)()
+        _check(_lib.b200attn_stack_rows(self.h, C.byref(n), slots))
+        return n.value, list(slots)
+
+    def step(self, n_rows: int) -> None:
+        _check(_lib.b200attn_stack_step(self.h, C.c_int(n_rows), _stream()))
 
     def __del__(self):
         try:

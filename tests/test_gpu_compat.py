@@ -24,3 +24,14 @@ def test_reference_verify_linear_attn_batch_unmodified(cuda):
         pytest.skip("oracle/_ref/verify_linear_attn_batch not built (needs the reference checkout at build time)")
     p = subprocess.run([exe], capture_output=True, text=True, timeout=300)
     assert p.returncode == 0 and "PASS" in p.stdout, p.stdout + p.stderr
+
+
+def test_reference_v2_kernel_accuracy_validate_unmodified(cuda):
+    """tests/integration/v2_kernel_accuracy_validate.cu of the reference, built as it is against the compat headers: it
+    runs CudaLinearAttentionV2 at hidden 256 / 4 heads / dims 64 (the plain path for sizes other than the model's) and
+    checks determinism of forward and forward_batch and that the state moves."""
+    exe = os.path.join(entry.ROOT, "oracle", "_ref", "v2_kernel_accuracy_validate")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/v2_kernel_accuracy_validate not built (needs the reference checkout at build time)")
+    p = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and "FAILED" not in p.stdout, p.stdout + p.stderr

@@ -20,8 +20,9 @@ def _build(ops, synth, weights, max_seqs=4, max_seq_len=128, kv_dtype=1):
 
 @pytest.fixture(params=["cublas", "tc"])
 def decode_gemm(request, monkeypatch):
-    """Both implementations of the decode-step projections: cuBLAS + separate SwiGLU / argmax kernels, and the tcgen05
-    skinny GEMM with fused epilogues.  The library reads the variable when a stack is created."""
+    """Both implementations of the decode-step projections: cuBLAS + separate norm / SwiGLU kernels, and the fused step
+    on the tcgen05 skinny GEMMs (norm scale and SwiGLU in the epilogues, residual add through a cluster reduction).
+    The library reads the variable when a stack is created."""
     monkeypatch.setenv("B200ATTN_DECODE_GEMM", request.param)
     return request.param
 
@@ -29,7 +30,8 @@ def decode_gemm(request, monkeypatch):
 def test_prefill_and_decode_against_cpu_composition(ops, cuda, oracle, synth, decode_gemm):
     torch = cuda
     from oracle import cpu_stack
-    weights = cpu_stack.make_stack_weights(synth, 61, L, INTER, VOCAB, int8=True)
+    # RMSNorm weights away from zero: the stack folds (1 + w) into the matrices behind each norm
+    weights = cpu_stack.make_stack_weights(synth, 61, L, INTER, VOCAB, int8=True, norm_std=0.1)
     qw = cpu_stack.quantized_view(weights)
     n, T, D = 3, 48, 4            # 144 prefill rows: the many-row form of the norm kernel is on the path
     tokens = synth.rng(61, "tokens").integers(0, VOCAB, (n, T)).astype(np.int32)
