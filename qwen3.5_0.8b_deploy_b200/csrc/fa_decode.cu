@@ -235,6 +235,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
 #pragma unroll
         for (int j = 0; j < 16; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        float c0 = 0.f, c1 = 0.f;       // INT8 cache: sums of the fp16 weights that multiplied V codes carrying the +1152 bias
 
         for (int i = 0; i < n_my; ++i, ++round) {
             if (!mbar_wait_warp(my_full_k, round & 1, abort_flag)) { alive = false; break; }
@@ -303,6 +304,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
             const float a0 = exp2f(m0 - mn0), a1 = exp2f(m1 - mn1);
             m0 = mn0; m1 = mn1;
             l0 *= a0; l1 *= a1;
+            if constexpr (!kFp16) { c0 *= a0; c1 *= a1; }
 #pragma unroll
             for (int j = 0; j < 16; ++j) { o[j][0] *= a0; o[j][2] *= a0; o[j][1] *= a1; o[j][3] *= a1; }
             float p[4][4];
@@ -322,8 +324,14 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                     const int tok_lo = 16 * (g >> 1) + 4 * w + (g & 1);
                     vl = sVs[tok_lo] * Cfg::kVBoost; vh = sVs[tok_lo + 2] * Cfg::kVBoost;
                 }
-                pb[w][0] = movmatrix_trans(pack_half2(p[w][0] * vl, p[w][1] * vl));
-                pb[w][1] = movmatrix_trans(pack_half2(p[w][2] * vh, p[w][3] * vh));
+                const uint32_t plo = pack_half2(p[w][0] * vl, p[w][1] * vl), phi = pack_half2(p[w][2] * vh, p[w][3] * vh);
+                if constexpr (!kFp16) {         // the rounded weights, exactly as the tensor core sees them
+                    const float2 fl = __half22float2(*reinterpret_cast<const __half2*>(&plo));
+                    const float2 fh = __half22float2(*reinterpret_cast<const __half2*>(&phi));
+                    c0 += fl.x + fh.x; c1 += fl.y + fh.y;
+                }
+                pb[w][0] = movmatrix_trans(plo);
+                pb[w][1] = movmatrix_trans(phi);
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -347,8 +355,8 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
 #pragma unroll
                     for (int w = 0; w < 4; ++w) {
                         uint32_t r0, r2, r1, r3;
-                        cvt_s8x4_half2x2(wl[w], r0, r2);
-                        cvt_s8x4_half2x2(wh[w], r1, r3);
+                        cvt_s8x4_half2x2_biased(wl[w], r0, r2);
+                        cvt_s8x4_half2x2_biased(wh[w], r1, r3);
                         mma_16816(o[j], r0, r1, r2, r3, pb[w][0], pb[w][1]);
                     }
                 }
@@ -362,6 +370,15 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
         for (int off = 4; off < 32; off <<= 1) {
             l0 += __shfl_xor_sync(0xffffffffu, l0, off);
             l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+            if constexpr (!kFp16) {
+                c0 += __shfl_xor_sync(0xffffffffu, c0, off);
+                c1 += __shfl_xor_sync(0xffffffffu, c1, off);
+            }
+        }
+        if constexpr (!kFp16) {                  // take the bias of the V codes back out: 1152 * sum of weights, per head
+            const float b0 = 1152.0f * c0, b1 = 1152.0f * c1;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { o[j][0] -= b0; o[j][2] -= b0; o[j][1] -= b1; o[j][3] -= b1; }
         }
         constexpr float inv_boost = 1.0f / Cfg::kVBoost;
         const int pair = seq * kFaKvHeads + kvh;

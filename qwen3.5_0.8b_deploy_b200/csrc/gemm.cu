@@ -13,6 +13,7 @@ namespace b200 {
 thread_local char g_error[512] = "";
 thread_local long long g_launches = 0;
 RuntimeFlags g_flags;
+
 static std::mutex g_dev_mu;
 static int g_sm_count[kMaxDevices] = {};
 

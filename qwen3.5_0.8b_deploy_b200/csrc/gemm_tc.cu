@@ -313,6 +313,18 @@ gemm_residual_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         if (ok) umma_commit(acc_done);
     }
     float* part = reinterpret_cast<float*>(sm);     // [128][kResLd] over the operand ring once every product has completed
+    // Reduction roles of the epilogue threads: 128 / S rows per CTA, S threads per row, 64 / S columns per thread.  The
+    // residual values they will add to are requested right after the dependency wait, long before they are needed.
+    constexpr int kCols = kResBN / S, kV4 = kCols / 4;
+    const int rt = (int)threadIdx.x - 64;
+    const int rrow = (int)rank * (128 / S) + (rt >= 0 ? rt / S : 0), rseg = rt >= 0 ? rt % S : 0;
+    const bool ract = warp >= 2 && rrow < M && !dead;
+    float* hrow = h + (size_t)rrow * N + n0 + rseg * kCols;
+    float4 acc[kV4];
+    if (ract) {
+#pragma unroll
+        for (int c4 = 0; c4 < kV4; ++c4) acc[c4] = __ldcg(reinterpret_cast<const float4*>(hrow) + c4);
+    }
     if (warp >= 2) {
         const int q = warp & 3, m = 32 * q + lane;
         if (mbar_wait_warp(acc_done, 0, abort_flag)) {
@@ -331,27 +343,32 @@ gemm_residual_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     }
     tc_fence_before();
     cluster_sync_all();                              // every partial tile of the cluster is in place (or its CTA has flagged a failure)
-    if (warp >= 2 && !*abort_flag) {
-        // 128 / S rows per CTA, S threads per row, 64 / S columns per thread: sixteen 16-byte remote loads per thread, all
-        // requested before the first one is used
-        constexpr int kCols = kResBN / S, kV4 = kCols / 4;
-        const int t = threadIdx.x - 64;
-        const int row = (int)rank * (128 / S) + t / S, seg = t % S;
-        const bool act = row < M;
-        float4 pv[S][kV4];
-        float4 acc[kV4];
-        float* hrow = h + (size_t)row * N + n0 + seg * kCols;
-        const uint32_t local = smem_u32(part + row * kResLd + seg * kCols);
+    const bool reduce = warp >= 2 && !*abort_flag;
+    float4 pv[S][kV4];
+    if (reduce) {
+        // sixteen 16-byte remote loads per thread, all requested before the first one is used
+        const uint32_t local = smem_u32(part + rrow * kResLd + rseg * kCols);
 #pragma unroll
         for (int sp = 0; sp < S; ++sp) {
             const uint32_t remote = dsmem_addr(local, (uint32_t)sp);
 #pragma unroll
             for (int c4 = 0; c4 < kV4; ++c4) pv[sp][c4] = dsmem_ld_f4(remote + 16 * c4);
         }
-        float ss = 0.f;
-        if (act) {
+        // touch every loaded value so that all remote reads of this thread have completed before it reports to the peers
+        float touch = 0.f;
 #pragma unroll
-            for (int c4 = 0; c4 < kV4; ++c4) acc[c4] = __ldcg(reinterpret_cast<const float4*>(hrow) + c4);
+        for (int sp = 0; sp < S; ++sp)
+#pragma unroll
+            for (int c4 = 0; c4 < kV4; ++c4) touch += pv[sp][c4].x;
+        asm volatile("" ::"f"(touch));
+    }
+    // This CTA has finished reading its peers' shared memory: tell them now, wait for them only before leaving, so the
+    // write-back below runs under the barrier's latency.
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    if (reduce) {
+        float ss = 0.f;
+        if (ract) {
 #pragma unroll
             for (int sp = 0; sp < S; ++sp)             // fixed order: the sum does not depend on which CTA finished first
 #pragma unroll
@@ -366,15 +383,16 @@ gemm_residual_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 pk[2 * c4 + 1] = pack_half2(acc[c4].z, acc[c4].w);
                 ss += acc[c4].x * acc[c4].x + acc[c4].y * acc[c4].y + acc[c4].z * acc[c4].z + acc[c4].w * acc[c4].w;
             }
-            uint4* xrow = reinterpret_cast<uint4*>(xh + (size_t)row * N + n0 + seg * kCols);
+            uint4* xrow = reinterpret_cast<uint4*>(xh + (size_t)rrow * N + n0 + rseg * kCols);
 #pragma unroll
             for (int c8 = 0; c8 < kV4 / 2; ++c8) xrow[c8] = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
         }
 #pragma unroll
         for (int o = 1; o < S; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (act && seg == 0) rowsq[(size_t)row * kRowsqParts + blockIdx.x] = ss;
+        if (ract && rseg == 0) rowsq[(size_t)rrow * kRowsqParts + blockIdx.x] = ss;
     }
-    cluster_sync_all();                              // nobody reads this CTA's shared memory any more
+    __syncwarp();
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // nobody reads this CTA's shared memory any more
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -444,9 +462,10 @@ void gemm_tc_forget(const void* ptr) {     // drop cached maps of a buffer that 
 
 // B200ATTN_DECODE_GEMM=tc selects the kernels of this file for the projections of the decode step (five launches per
 // DeltaNet layer instead of eight).  The default is library GEMMs with separate norm / SwiGLU kernels, which is still
-// the faster step as a whole: measured at 128 rows inside the captured step, an input projection here takes 10 - 12 us
-// and a residual projection 16 us (each CTA has about 96 KB of weights in flight, half of what it takes to keep HBM
-// busy from 65 SMs; the cluster reduction adds two barriers and a remote read), 2.9 ms per step against 2.2 ms.
+// the faster step as a whole: measured at 128 rows inside the captured step, an input or gate / up projection here
+// takes 8.5 us and a residual projection 11 us (2.5 us from the dependency wait to the accumulators, then the cluster
+// barrier, the remote reads and the write-back), 2.27 ms per step against 2.13 ms at a cache length of 256.  Asking
+// L2 for the coming weights from inside the attention kernels made it worse (2.60 ms): the state stream evicts them.
 bool gemm_tc_enabled() { return g_flags.decode_gemm_tc; }
 
 // Y[M, N] = rs[m] * X W^T (fp32 store).  rowsq == nullptr: no row scale.
@@ -455,12 +474,9 @@ int gemm_tc_store(cudaStream_t s, const __half* X, const __half* W, float* Y, in
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N > 0, "gemm_tc: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
     B2_TRY(fp16_map(X, M, K, 128, &mx));
-    // Every CTA reads all of X from L2, so wide N (the input projections) takes 128-column tiles: half as many CTAs
-    // pull the activations, and 40-65 SMs still stream the weights faster than HBM delivers them.
-    if (N >= 2048) {
-        B2_TRY(fp16_map(W, N, K, 128, &mw));
-        return launch_one<128, kEpiStore>(mx, mw, M, N, K, 1, Y, ld_out, 0, nullptr, nullptr, rowsq, rs_eps, d_error, s);
-    }
+    // 64-column tiles: 129 CTAs for the 8224-wide input projection.  Every CTA reads all of X from L2, so 128-column
+    // tiles would halve that traffic, but with half as many CTAs there are too few weight bytes in flight to keep HBM
+    // busy: measured 12.5 us per launch against 8.5 us inside the captured step.
     B2_TRY(fp16_map(W, N, K, 64, &mw));
     return launch_one<64, kEpiStore>(mx, mw, M, N, K, 1, Y, ld_out, 0, nullptr, nullptr, rowsq, rs_eps, d_error, s);
 }
@@ -472,10 +488,8 @@ int gemm_tc_swiglu(cudaStream_t s, const __half* X, const __half* W, __half* act
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N % 64 == 0, "gemm_tc_swiglu: unsupported shape %d x %d x %d", M, N, K);
     CUtensorMap mx, mw;
     B2_TRY(fp16_map(X, M, K, 128, &mx));
-    // 128-column tiles (two gate/up groups): half as many CTAs re-read the activations, and 56 SMs still stream the
-    // 14.7 MB of gate/up weights of the model's FFN faster than HBM delivers them
-    B2_TRY(fp16_map(W, N, K, 128, &mw));
-    return launch_one<128, kEpiSwiglu>(mx, mw, M, N, K, 1, nullptr, N / 2, 0, act, nullptr, rowsq, rs_eps, d_error, s);
+    B2_TRY(fp16_map(W, N, K, 64, &mw));      // one gate / up group of 32 + 32 columns per CTA, 112 CTAs for the model's FFN
+    return launch_one<64, kEpiSwiglu>(mx, mw, M, N, K, 1, nullptr, N / 2, 0, act, nullptr, rowsq, rs_eps, d_error, s);
 }
 
 // h[M, N] += X[M, K] W[N, K]^T; also xh = fp16(h) and the per-row sums of squares (see gemm_residual_kernel).  N must be
@@ -485,7 +499,9 @@ int gemm_tc_residual(cudaStream_t s, const __half* X, const __half* W, float* h,
     B2_CHECK_ARG(M > 0 && M <= 128 && K % 64 == 0 && N == kHidden, "gemm_tc_residual: unsupported shape %d x %d x %d", M, N, K);
     const int k_steps = K / 64;
     int S = 0;
-    for (int cand : {8, 4}) if (k_steps % cand == 0 && k_steps / cand <= kResStages) { S = cand; break; }
+    // the smaller cluster where the slice still fits the ring: clusters of four start sooner than clusters of eight
+    // (measured 10.9 against 13.7 us per launch for the 2048-deep attention output projection)
+    for (int cand : {4, 8}) if (k_steps % cand == 0 && k_steps / cand <= kResStages) { S = cand; break; }
     B2_CHECK_ARG(S != 0, "gemm_tc_residual: K = %d does not split into 4 or 8 slices of at most %d k-steps", K, kResStages);
     CUtensorMap mx, mw;
     B2_TRY(fp16_map(X, M, K, 128, &mx));

@@ -142,20 +142,9 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
-// Four signed bytes -> two half2 (b0,b1) and (b2,b3), exact.
-__device__ __forceinline__ void cvt_s8x4_half2x2(uint32_t x, uint32_t& lo, uint32_t& hi) {
-    x ^= 0x80808080u;                                          // signed -> biased unsigned
-    uint32_t l = __byte_perm(x, 0x64646464u, 0x4140);          // halves 1024 + u0, 1024 + u1
-    uint32_t h = __byte_perm(x, 0x64646464u, 0x4342);
-    const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);  // 1024 + 128
-    __half2 lh = __hsub2(*reinterpret_cast<__half2*>(&l), bias);
-    __half2 hh = __hsub2(*reinterpret_cast<__half2*>(&h), bias);
-    lo = *reinterpret_cast<uint32_t*>(&lh);
-    hi = *reinterpret_cast<uint32_t*>(&hh);
-}
-
-// Four signed bytes -> two half2 holding b + 1152 (exact integers 1024..1279): the same byte placement without the
-// subtraction.  For a dot product with a vector q the caller subtracts 1152 * sum(q) once instead.
+// Four signed bytes -> two half2 (b0,b1) and (b2,b3) holding b + 1152 (exact integers 1024..1279): the sign bit is
+// flipped and each byte dropped into the mantissa of 1024.0.  For a dot product with a vector q the caller subtracts
+// 1152 * sum(q) once instead of subtracting the bias from every element.
 __device__ __forceinline__ void cvt_s8x4_half2x2_biased(uint32_t x, uint32_t& lo, uint32_t& hi) {
     x ^= 0x80808080u;
     lo = __byte_perm(x, 0x64646464u, 0x4140);
