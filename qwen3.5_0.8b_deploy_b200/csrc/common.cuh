@@ -142,7 +142,7 @@ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // Y = alpha * X W^T + beta * Y; ld_out > 0 gives the row pitch of Y (elements) when it is a column block of a wider matrix.
 int gemm_xwT(cudaStream_t stream, const void* X, bool x_fp16, const void* W, bool w_fp16, void* Y,
              bool y_fp16, int rows, int out, int in, float beta = 0.f, float alpha = 1.f, int ld_out = 0);
-int cublas_init();   // creates the per-process handle and its capture-safe workspace
+int cublas_init();   // creates the current device's handle and its capture-safe workspace (call outside stream capture)
 
 // ---- small elementwise helpers (elementwise.cu) ----------------------------------------------------
 int f32_to_f16(cudaStream_t s, const float* in, __half* out, size_t n);

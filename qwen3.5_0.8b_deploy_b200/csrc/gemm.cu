@@ -101,32 +101,47 @@ void prof_end(ProfKind k, cudaStream_t s) {
     g_prof[k].open = nullptr;
 }
 
-// One handle per process with a fixed workspace, which keeps cuBLAS from allocating inside stream capture.
-static cublasHandle_t g_handle = nullptr;
-static void* g_workspace = nullptr;
+// One handle per device with a fixed workspace, which keeps cuBLAS from allocating inside stream capture.
+static cublasHandle_t g_handle[kMaxDevices] = {};
+static void* g_workspace[kMaxDevices] = {};
 static constexpr size_t kWorkspaceBytes = 64ull << 20;
 static std::mutex g_mu;
 
-int cublas_init() {
+static int cublas_for_current_device(cublasHandle_t* out) {
+    int dev = 0;
+    B2_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) B2_FAIL(B200ATTN_ERR_UNSUPPORTED, "device index %d not supported", dev);
     std::lock_guard<std::mutex> lk(g_mu);
-    if (g_handle) return 0;
-    cublasStatus_t st = cublasCreate(&g_handle);
-    if (st != CUBLAS_STATUS_SUCCESS) {
-        g_handle = nullptr;
-        B2_FAIL(B200ATTN_ERR_CUDA, "cublasCreate failed with status %d", (int)st);
+    if (!g_handle[dev]) {
+        cublasHandle_t h = nullptr;
+        cublasStatus_t st = cublasCreate(&h);
+        if (st != CUBLAS_STATUS_SUCCESS) B2_FAIL(B200ATTN_ERR_CUDA, "cublasCreate failed with status %d", (int)st);
+        void* ws = nullptr;
+        if (cudaMalloc(&ws, kWorkspaceBytes) != cudaSuccess) {
+            cublasDestroy(h);
+            B2_FAIL(B200ATTN_ERR_NOMEM, "cudaMalloc of the cuBLAS workspace failed");
+        }
+        st = cublasSetWorkspace(h, ws, kWorkspaceBytes);
+        if (st != CUBLAS_STATUS_SUCCESS) {
+            cublasDestroy(h);
+            cudaFree(ws);
+            B2_FAIL(B200ATTN_ERR_CUDA, "cublasSetWorkspace failed with status %d", (int)st);
+        }
+        cublasSetMathMode(h, CUBLAS_DEFAULT_MATH);
+        g_handle[dev] = h;
+        g_workspace[dev] = ws;
     }
-    B2_CUDA(cudaMalloc(&g_workspace, kWorkspaceBytes));
-    st = cublasSetWorkspace(g_handle, g_workspace, kWorkspaceBytes);
-    if (st != CUBLAS_STATUS_SUCCESS) B2_FAIL(B200ATTN_ERR_CUDA, "cublasSetWorkspace failed with status %d", (int)st);
-    cublasSetMathMode(g_handle, CUBLAS_DEFAULT_MATH);
+    if (out) *out = g_handle[dev];
     return 0;
 }
+
+int cublas_init() { return cublas_for_current_device(nullptr); }
 
 int gemm_xwT(cudaStream_t stream, const void* X, bool x_fp16, const void* W, bool w_fp16, void* Y, bool y_fp16, int rows,
              int out, int in, float beta, float alpha, int ld_out) {
     if (rows <= 0) return 0;
-    B2_TRY(cublas_init());
-    cublasHandle_t handle = g_handle;
+    cublasHandle_t handle = nullptr;
+    B2_TRY(cublas_for_current_device(&handle));
     if (x_fp16 != w_fp16) B2_FAIL(B200ATTN_ERR_INVALID, "gemm: activation and weight types must match");
     cublasStatus_t st = cublasSetStream(handle, stream);
     if (st != CUBLAS_STATUS_SUCCESS) B2_FAIL(B200ATTN_ERR_CUDA, "cublasSetStream failed with status %d", (int)st);
