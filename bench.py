@@ -376,13 +376,14 @@ def main():
                         ms, cnt = ops.profile_read(name)
                         acc[name][0] += ms; acc[name][1] += cnt
                 return {k2: tuple(v) for k2, v in acc.items()}
-            early = read_steps(4)
+            early = read_steps(max(1, min(4, G // 4)))
             timing = "in-kernel time stamps (first CTA past its dependency wait .. last CTA done) inside the captured decode step, programmatic dependent launch on"
             if early["la_decode"][1] == 0 or early["fa_decode"][1] == 0:
                 raise RuntimeError("the stamped decode step returned no times")
             prof.update(early)
-            st.launch_decode(G // 2 - 6)
-            fa_mid = read_steps(4)["fa_decode"]
+            if G // 2 - 6 > 0:
+                st.launch_decode(G // 2 - 6)
+                fa_mid = read_steps(4)["fa_decode"]
             st.capture_decode(B)                       # back to the plain graph before the events go away
             ops.profile_reset()
             # where the job time goes: prefill pass vs captured decode steps
@@ -456,9 +457,9 @@ def main():
             la_prefill=dict(bound="tensor", achieved=algo_la_prefill_flops(seqs_per_chunk, P) / (per["la_prefill"] * 1e-3) / 1e12, peak=peaks["tflops_sustained"], unit="TFLOP/s"),
         )
         # units of one bench launch / units of the launch captured under ncu (kernel_bench.py commands in profiles/):
-        # la_decode 128 sequences; fa_decode 128 sequences x 1280 cached tokens; fa_prefill 16 and la_prefill 10 sequences x 1024
+        # la_decode 128 sequences; fa_decode 128 sequences x 1280 cached tokens; fa_prefill 16 and la_prefill 18 sequences x 1024
         traffic_scale = dict(la_decode=B / 128.0, fa_decode=(B / 128.0) * (ctx_avg / 1280.0), fa_prefill=seqs_per_chunk * P / (16.0 * 1024),
-                             la_prefill=seqs_per_chunk * P / (10.0 * 1024))
+                             la_prefill=seqs_per_chunk * P / (18.0 * 1024))
         for k, r in roof.items():
             r.update(kernel=k, frac=r["achieved"] / r["peak"], ms_per_launch=per[k], timing=(timing if k.endswith("decode") else "eager launches"), job_ms=job_ms[k],
                      ctx_len=(ctx_avg if k == "fa_decode" else None),
