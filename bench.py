@@ -483,7 +483,9 @@ def main():
                                            note="back-to-back launches through the core entry" + ("; includes its query-conversion launch" if k == "fa_decode" else ""))
             extra.append(dict(kernel="fa_decode_int8", bound="hbm", achieved=i8["achieved"], peak=peaks["hbm_gbs"], unit="GB/s", frac=i8["achieved"] / peaks["hbm_gbs"],
                               ms_per_launch=i8["ms"], ctx_len=P + G // 2, timing="back-to-back launches through the core entry on an INT8 cache "
-                              "(includes its query-conversion launch); the job itself runs the FP16 cache", traffic=None, peak_source=peaks["source"]))
+                              "(includes its query-conversion launch); the job itself runs the FP16 cache",
+                              traffic=ncu_traffic("fa_decode_int8", (B / 128.0) * ((P + G // 2) / 1280.0)),
+                              traffic_source="ncu capture of the small case in profiles/, scaled by the units one bench launch processes", peak_source=peaks["source"]))
         except Exception as e:          # the job's own numbers stand without it
             roof["la_decode"]["isolated"] = dict(error=str(e)[:200])
         dominant = max(job_ms, key=job_ms.get)
