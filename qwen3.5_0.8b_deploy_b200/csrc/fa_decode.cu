@@ -127,52 +127,51 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
     auto owner_of = [&](int x) { return (int)((((long long)(x + 1)) * W_eff - 1) / P); };   // worker whose range holds page x
 
     if (warp == Cfg::kWarps) {
-        // ---------------- producer: one lane keeps every warp's K and V buffer refilled ----------------
-        if (lane == 0) {
-            int xk[Cfg::kWarps], xv[Cfg::kWarps], xe[Cfg::kWarps], sk[Cfg::kWarps], sv[Cfg::kWarps];
-            int rk[Cfg::kWarps], rv[Cfg::kWarps];      // rounds issued per warp
-            int remaining = 0;
-#pragma unroll
-            for (int w = 0; w < Cfg::kWarps; ++w) {
-                const int wid = blockIdx.x + gridDim.x * w;
-                rk[w] = 0; rv[w] = 0;
-                xk[w] = xv[w] = xe[w] = 0; sk[w] = sv[w] = 0;
-                if (wid < W_eff) {
-                    xk[w] = xv[w] = range_start(wid);
-                    xe[w] = range_start(wid + 1);
-                    if (xe[w] > xk[w]) sk[w] = sv[w] = find_seq(s_pref, n_seqs, xk[w]);
-                    remaining += 2 * (xe[w] - xk[w]);
-                }
+        // ---------------- producer warp: lane w keeps the K and the V buffer of consumer warp w refilled ----------------
+        // One lane per consumer: the look-ups in front of a copy (sequence, block table) are a chain of dependent loads,
+        // and a single lane serving every buffer could not start copies faster than the memory system delivers them.
+        // The page number of a buffer's next fill is fetched right after the current one is issued.
+        if (lane < Cfg::kWarps) {
+            const int w = lane;
+            const int wid = blockIdx.x + gridDim.x * w;
+            int x[2] = {0, 0}, seq[2] = {0, 0}, rounds[2] = {0, 0}, next_page[2] = {0, 0}, next_kvh[2] = {0, 0};
+            int xe = 0;
+            if (wid < W_eff) {
+                x[0] = x[1] = range_start(wid);
+                xe = range_start(wid + 1);
+            }
+            auto look_up = [&](int is_v) {     // sequence, kv head and physical page of linear page x[is_v]
+                int kvh, pg;
+                locate_page(s_pref, n_seqs, x[is_v], seq[is_v], kvh, pg);
+                next_kvh[is_v] = kvh;
+                next_page[is_v] = kv.block_table[(size_t)slots[seq[is_v]] * kv.max_pages_per_seq + pg];
+            };
+            if (x[0] < xe) {
+                seq[0] = seq[1] = find_seq(s_pref, n_seqs, x[0]);
+                look_up(0);
+                next_page[1] = next_page[0]; next_kvh[1] = next_kvh[0];
             }
             const uint64_t t0 = global_timer_ns();
             uint32_t idle = 0;
-            while (remaining > 0) {
+            while (x[0] < xe || x[1] < xe) {
                 bool progressed = false;
 #pragma unroll
-                for (int w = 0; w < Cfg::kWarps; ++w) {
-#pragma unroll
-                    for (int is_v = 0; is_v < 2; ++is_v) {
-                        const int x = is_v ? xv[w] : xk[w];
-                        if (x >= xe[w]) continue;
-                        const int r = is_v ? rv[w] : rk[w];
-                        const uint32_t eb = (is_v ? empty_v0 : empty_k0) + 8 * w;
-                        if (r > 0 && !mbar_test_wait(eb, (r - 1) & 1)) continue;
-                        int seq = is_v ? sv[w] : sk[w], kvh, pg;
-                        locate_page(s_pref, n_seqs, x, seq, kvh, pg);
-                        if (is_v) sv[w] = seq; else sk[w] = seq;
-                        const int page = kv.block_table[(size_t)slots[seq] * kv.max_pages_per_seq + pg];
-                        const size_t head_base = (size_t)(layer * kv.num_pages + page) * kFaKvHeads + kvh;
-                        const unsigned char* src = reinterpret_cast<const unsigned char*>(is_v ? kv.v : kv.k) + head_base * Cfg::kBlockBytes;
-                        const uint32_t dst = smem_u32(stage_base + w * Cfg::kStageBytes + is_v * Cfg::kHalfBytes);
-                        const uint32_t fb = (is_v ? full_v0 : full_k0) + 8 * w;
-                        mbar_arrive_expect_tx(fb, Cfg::kHalfBytes);
-                        bulk_g2s(dst, src, Cfg::kBlockBytes, fb);
-                        if constexpr (!kFp16)
-                            bulk_g2s(dst + Cfg::kBlockBytes, (is_v ? kv.vs : kv.ks) + head_base * kPageTokens, Cfg::kScaleBytes, fb);
-                        if (is_v) { ++rv[w]; ++xv[w]; } else { ++rk[w]; ++xk[w]; }
-                        --remaining;
-                        progressed = true;
-                    }
+                for (int is_v = 0; is_v < 2; ++is_v) {
+                    if (x[is_v] >= xe) continue;
+                    const int r = rounds[is_v];
+                    const uint32_t eb = (is_v ? empty_v0 : empty_k0) + 8 * w;
+                    if (r > 0 && !mbar_test_wait(eb, (r - 1) & 1)) continue;
+                    const size_t head_base = (size_t)(layer * kv.num_pages + next_page[is_v]) * kFaKvHeads + next_kvh[is_v];
+                    const unsigned char* src = reinterpret_cast<const unsigned char*>(is_v ? kv.v : kv.k) + head_base * Cfg::kBlockBytes;
+                    const uint32_t dst = smem_u32(stage_base + w * Cfg::kStageBytes + is_v * Cfg::kHalfBytes);
+                    const uint32_t fb = (is_v ? full_v0 : full_k0) + 8 * w;
+                    mbar_arrive_expect_tx(fb, Cfg::kHalfBytes);
+                    bulk_g2s(dst, src, Cfg::kBlockBytes, fb);
+                    if constexpr (!kFp16)
+                        bulk_g2s(dst + Cfg::kBlockBytes, (is_v ? kv.vs : kv.ks) + head_base * kPageTokens, Cfg::kScaleBytes, fb);
+                    ++rounds[is_v];
+                    if (++x[is_v] < xe) look_up(is_v);
+                    progressed = true;
                 }
                 if (!progressed && ((++idle & 255u) == 0u)) {
                     if (*abort_flag) break;
@@ -426,37 +425,57 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
             last = __shfl_sync(0xffffffffu, last, 0);
             if (last) {                                // the last partial of the pair to arrive: combine them all
                 __threadfence();
-                // eight lanes per head, 32 consecutive output dims per lane: every part costs one round of independent
-                // 16-byte loads, so the whole combine is a few L2 latencies long
+                // Eight lanes per head, 32 consecutive output dims per lane.  The warp that combines is often among the last
+                // of the launch to finish, so the loads are issued in groups (all maxima; two parts at a time; the gate up
+                // front): about three L2 round trips for the usual three or four parts instead of two per part.
                 const int hd = lane >> 3, sub = lane & 7;
+                const size_t oo = obase + (size_t)hd * kHeadDim + sub * 32;
+                uint2 g2[8];
+                if (gate) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) g2[k] = *reinterpret_cast<const uint2*>(gate + oo + 4 * k);
+                }
                 float mmax = -INFINITY;
-                for (int sp = 0; sp < n_parts; ++sp) mmax = fmaxf(mmax, __ldcg(&part_ml[(pbase + sp * 4 + hd) * 2]));
+                for (int sp0 = 0; sp0 < n_parts; sp0 += 4) {
+                    float mv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        mv[u] = (sp0 + u < n_parts) ? __ldcg(&part_ml[(pbase + (sp0 + u) * 4 + hd) * 2]) : -INFINITY;
+                    mmax = fmaxf(fmaxf(mmax, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
+                }
                 float4 acc[8];
 #pragma unroll
                 for (int k = 0; k < 8; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
                 float lsum = 0.f;
-                for (int sp = 0; sp < n_parts; ++sp) {
-                    const float2 ml = __ldcg(reinterpret_cast<const float2*>(&part_ml[(pbase + sp * 4 + hd) * 2]));
-                    const float wgt = exp2f(ml.x - mmax);
-                    lsum += ml.y * wgt;
-                    const float4* po = reinterpret_cast<const float4*>(part_o + (pbase + sp * 4 + hd) * kHeadDim + sub * 32);
-                    float4 pv[8];
+                for (int sp0 = 0; sp0 < n_parts; sp0 += 2) {
+                    float2 ml[2];
+                    float4 pv[2][8];
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) pv[k] = __ldcg(po + k);
+                    for (int u = 0; u < 2; ++u) {
+                        const int sp = min(sp0 + u, n_parts - 1);      // the odd one out is loaded twice and weighted zero
+                        ml[u] = __ldcg(reinterpret_cast<const float2*>(&part_ml[(pbase + sp * 4 + hd) * 2]));
+                        const float4* po = reinterpret_cast<const float4*>(part_o + (pbase + sp * 4 + hd) * kHeadDim + sub * 32);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        acc[k].x += pv[k].x * wgt; acc[k].y += pv[k].y * wgt; acc[k].z += pv[k].z * wgt; acc[k].w += pv[k].w * wgt;
+                        for (int k = 0; k < 8; ++k) pv[u][k] = __ldcg(po + k);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const float wgt = (sp0 + u < n_parts) ? exp2f(ml[u].x - mmax) : 0.f;
+                        lsum += ml[u].y * wgt;
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            acc[k].x += pv[u][k].x * wgt; acc[k].y += pv[u][k].y * wgt;
+                            acc[k].z += pv[u][k].z * wgt; acc[k].w += pv[u][k].w * wgt;
+                        }
                     }
                 }
                 const float inv = inv_boost / lsum;
-                const size_t oo = obase + (size_t)hd * kHeadDim + sub * 32;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     float r0 = acc[k].x * inv, r1 = acc[k].y * inv, r2 = acc[k].z * inv, r3 = acc[k].w * inv;
                     if (gate) {
-                        const uint2 g2 = *reinterpret_cast<const uint2*>(gate + oo + 4 * k);
-                        const float2 ga = __half22float2(*reinterpret_cast<const __half2*>(&g2.x));
-                        const float2 gb = __half22float2(*reinterpret_cast<const __half2*>(&g2.y));
+                        const float2 ga = __half22float2(*reinterpret_cast<const __half2*>(&g2[k].x));
+                        const float2 gb = __half22float2(*reinterpret_cast<const __half2*>(&g2[k].y));
                         r0 *= ga.x; r1 *= ga.y; r2 *= gb.x; r3 *= gb.y;
                     }
                     if constexpr (sizeof(OutT) == 4) {
