@@ -149,6 +149,7 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
             if (x[0] < xe) {
                 seq[0] = seq[1] = find_seq(s_pref, n_seqs, x[0]);
                 look_up(0);
+                seq[1] = seq[0];
                 next_page[1] = next_page[0]; next_kvh[1] = next_kvh[0];
             }
             const uint64_t t0 = global_timer_ns();
@@ -399,92 +400,88 @@ fa_decode_split_kernel(KvView kv, int layer, const int* __restrict__ slots, int 
                 }
             }
         } else {
+            // A partial is stored in the order the accumulators lie in the registers (lane (g, t < 2): its 64 values as
+            // sixteen 16-byte pieces), so writing it takes 16 stores per lane and reading it back 16-byte loads as well.
             const size_t pbase = ((size_t)pair * max_parts) * 4;
             const int part = wid - w_first;
             if (t < 2) {
-                float* po0 = part_o + (pbase + part * 4 + 2 * t) * kHeadDim;
-                float* po1 = po0 + kHeadDim;
+                float4* po = reinterpret_cast<float4*>(part_o + (pbase + part * 4) * kHeadDim) + (g * 2 + t) * 16;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    po0[16 * j + g] = o[j][0]; po1[16 * j + g] = o[j][1];
-                    po0[16 * j + 8 + g] = o[j][2]; po1[16 * j + 8 + g] = o[j][3];
-                }
-                if (g == 0) {
-                    float* ml = part_ml + (pbase + part * 4 + 2 * t) * 2;
-                    ml[0] = m0; ml[1] = l0; ml[2] = m1; ml[3] = l1;
+                for (int j = 0; j < 16; ++j) po[j] = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
+                if (g == 0)
+                    *reinterpret_cast<float4*>(part_ml + (pbase + part * 4 + 2 * t) * 2) = make_float4(m0, l0, m1, l1);
+            }
+            // One release / acquire atomic per warp instead of a fence on either side of a relaxed one: the warp barrier
+            // orders the lanes' stores before lane 0's release, the shuffle orders its acquire before the lanes' loads
+            // (which go to L2).  The gate values do not depend on the partials and are requested before the atomic.
+            const int tt = t & 1, half = t >> 1;
+            __half gv[32];
+            if (gate) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const size_t a0 = obase + (size_t)(2 * tt) * kHeadDim + 16 * (8 * half + k) + g, a1 = a0 + kHeadDim;
+                    gv[4 * k] = gate[a0]; gv[4 * k + 1] = gate[a1]; gv[4 * k + 2] = gate[a0 + 8]; gv[4 * k + 3] = gate[a1 + 8];
                 }
             }
-            __threadfence();
             __syncwarp();
             int last = 0;
             if (lane == 0) {
-                const int old = atomicAdd(&counters[pair], 1);
+                int old;
+                asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(counters + pair) : "memory");
                 last = (old == n_parts - 1);
                 if (last) counters[pair] = 0;          // ready for the next launch
             }
             last = __shfl_sync(0xffffffffu, last, 0);
             if (last) {                                // the last partial of the pair to arrive: combine them all
-                __threadfence();
-                // Eight lanes per head, 32 consecutive output dims per lane.  The warp that combines is often among the last
-                // of the launch to finish, so the loads are issued in groups (all maxima; two parts at a time; the gate up
-                // front): about three L2 round trips for the usual three or four parts instead of two per part.
-                const int hd = lane >> 3, sub = lane & 7;
-                const size_t oo = obase + (size_t)hd * kHeadDim + sub * 32;
-                uint2 g2[8];
-                if (gate) {
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) g2[k] = *reinterpret_cast<const uint2*>(gate + oo + 4 * k);
-                }
-                float mmax = -INFINITY;
-                for (int sp0 = 0; sp0 < n_parts; sp0 += 4) {
-                    float mv[4];
-#pragma unroll
-                    for (int u = 0; u < 4; ++u)
-                        mv[u] = (sp0 + u < n_parts) ? __ldcg(&part_ml[(pbase + (sp0 + u) * 4 + hd) * 2]) : -INFINITY;
-                    mmax = fmaxf(fmaxf(mmax, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
-                }
+                // The warp that combines is usually among the last of the launch to finish, so this is on the kernel's
+                // critical path: every lane takes half of a (g, t) fragment (heads 2tt, 2tt + 1; eight of the sixteen
+                // 16-dim tiles), and the loads of up to four parts, their (m, l) included, are issued together - one L2
+                // round trip for the usual case.  More parts are folded in with the running-maximum rule.
                 float4 acc[8];
 #pragma unroll
                 for (int k = 0; k < 8; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-                float lsum = 0.f;
-                for (int sp0 = 0; sp0 < n_parts; sp0 += 2) {
-                    float2 ml[2];
-                    float4 pv[2][8];
+                float rm0 = -INFINITY, rm1 = -INFINITY, ls0 = 0.f, ls1 = 0.f;
+                for (int sp0 = 0; sp0 < n_parts; sp0 += 4) {
+                    float4 ml[4], pv[4][8];
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const int sp = min(sp0 + u, n_parts - 1);      // the odd one out is loaded twice and weighted zero
-                        ml[u] = __ldcg(reinterpret_cast<const float2*>(&part_ml[(pbase + sp * 4 + hd) * 2]));
-                        const float4* po = reinterpret_cast<const float4*>(part_o + (pbase + sp * 4 + hd) * kHeadDim + sub * 32);
+                    for (int u = 0; u < 4; ++u) {
+                        const int sp = min(sp0 + u, n_parts - 1);      // parts past the end are loaded again and weighted zero
+                        ml[u] = __ldcg(reinterpret_cast<const float4*>(part_ml + (pbase + sp * 4 + 2 * tt) * 2));
+                        const float4* po = reinterpret_cast<const float4*>(part_o + (pbase + sp * 4) * kHeadDim) + (g * 2 + tt) * 16 + 8 * half;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) pv[u][k] = __ldcg(po + k);
                     }
+                    float nm0 = rm0, nm1 = rm1;
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        const float wgt = (sp0 + u < n_parts) ? exp2f(ml[u].x - mmax) : 0.f;
-                        lsum += ml[u].y * wgt;
+                    for (int u = 0; u < 4; ++u)
+                        if (sp0 + u < n_parts) { nm0 = fmaxf(nm0, ml[u].x); nm1 = fmaxf(nm1, ml[u].z); }
+                    const float s0 = exp2f(rm0 - nm0), s1 = exp2f(rm1 - nm1);     // 0 for the first group
+                    rm0 = nm0; rm1 = nm1;
+                    ls0 *= s0; ls1 *= s1;
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) { acc[k].x *= s0; acc[k].z *= s0; acc[k].y *= s1; acc[k].w *= s1; }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const bool valid = sp0 + u < n_parts;
+                        const float w0 = valid ? exp2f(ml[u].x - nm0) : 0.f, w1 = valid ? exp2f(ml[u].z - nm1) : 0.f;
+                        ls0 += ml[u].y * w0; ls1 += ml[u].w * w1;
 #pragma unroll
                         for (int k = 0; k < 8; ++k) {
-                            acc[k].x += pv[u][k].x * wgt; acc[k].y += pv[u][k].y * wgt;
-                            acc[k].z += pv[u][k].z * wgt; acc[k].w += pv[u][k].w * wgt;
+                            acc[k].x += pv[u][k].x * w0; acc[k].z += pv[u][k].z * w0;
+                            acc[k].y += pv[u][k].y * w1; acc[k].w += pv[u][k].w * w1;
                         }
                     }
                 }
-                const float inv = inv_boost / lsum;
+                const float i0 = inv_boost / ls0, i1 = inv_boost / ls1;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    float r0 = acc[k].x * inv, r1 = acc[k].y * inv, r2 = acc[k].z * inv, r3 = acc[k].w * inv;
+                    const size_t a0 = obase + (size_t)(2 * tt) * kHeadDim + 16 * (8 * half + k) + g, a1 = a0 + kHeadDim;
+                    float r0 = acc[k].x * i0, r1 = acc[k].y * i1, r2 = acc[k].z * i0, r3 = acc[k].w * i1;
                     if (gate) {
-                        const float2 ga = __half22float2(*reinterpret_cast<const __half2*>(&g2[k].x));
-                        const float2 gb = __half22float2(*reinterpret_cast<const __half2*>(&g2[k].y));
-                        r0 *= ga.x; r1 *= ga.y; r2 *= gb.x; r3 *= gb.y;
+                        r0 *= __half2float(gv[4 * k]); r1 *= __half2float(gv[4 * k + 1]);
+                        r2 *= __half2float(gv[4 * k + 2]); r3 *= __half2float(gv[4 * k + 3]);
                     }
-                    if constexpr (sizeof(OutT) == 4) {
-                        *reinterpret_cast<float4*>(out + oo + 4 * k) = make_float4(r0, r1, r2, r3);
-                    } else {
-                        __half2 h0 = __floats2half2_rn(r0, r1), h1 = __floats2half2_rn(r2, r3);
-                        *reinterpret_cast<uint2*>(out + oo + 4 * k) =
-                            make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
-                    }
+                    out[a0] = (OutT)r0; out[a1] = (OutT)r1; out[a0 + 8] = (OutT)r2; out[a1 + 8] = (OutT)r3;
                 }
             }
         }
