@@ -302,94 +302,127 @@ fa_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
             const bool valid = r < tile.n_rows;
             const size_t orow = ((size_t)(tile.q_row0 + r) * kFaHeads + head) * kHeadDim;
-            // Output columns of this thread: round k (0, 1) covers columns [128k, 128k + 128); in it the thread owns the two
-            // 32-column chunks k*4 + hf*2 + {0, 1}.  Gate values are requested before the wait on the last PV product.
-            uint4 gpre[4][4];
-            if (gate && valid) {
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4)
-                        gpre[cc][q4] = *reinterpret_cast<const uint4*>(gate + orow + ((cc >> 1) * 4 + hf * 2 + (cc & 1)) * 32 + q4 * 8);
-            }
-            if (!mbar_wait_warp(bar(BAR_OF), it & 1, abort_flag)) ok = false;
-            tc_fence_after();
-            const float inv_l = 1.0f / l;
-            // fp16 output of a full tile leaves through shared memory and two tiled TMA stores per round (the P buffers are
-            // idle between the last PV product and the next item's first P tile); anything else is stored from registers
+            // fp16 output of a full tile leaves through shared memory and tiled TMA stores (the P buffers are idle between
+            // the last PV product and the next item's first P tile); anything else is stored from registers.
             const bool via_tma = (sizeof(OutT) == 2) && (tile.n_rows == kBM);
+            if (!via_tma) {
+                // columns [32 ch, 32 ch + 32) of this thread's row, ch = 2 cc + hf
+                if (!mbar_wait_warp(bar(BAR_OF), it & 1, abort_flag)) ok = false;
+                tc_fence_after();
+                const float inv_l = 1.0f / l;
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                const int ch = (cc >> 1) * 4 + hf * 2 + (cc & 1);
-                uint32_t orr[32];
-                tmem_ld32(tmem_o + lane_base + ch * 32, orr);
-                tmem_wait_ld();
-                float vals[32];
+                for (int cc = 0; cc < 4; ++cc) {
+                    const int ch = 2 * cc + hf;
+                    uint32_t orr[32];
+                    tmem_ld32(tmem_o + lane_base + ch * 32, orr);
+                    tmem_wait_ld();
+                    float vals[32];
 #pragma unroll
-                for (int c = 0; c < 32; ++c) vals[c] = __uint_as_float(orr[c]) * inv_l;
-                if (gate && valid) {
+                    for (int c = 0; c < 32; ++c) vals[c] = __uint_as_float(orr[c]) * inv_l;
+                    if (gate && valid) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
-                        const uint4 gv = gpre[cc][q4];
-                        const __half2* gh = reinterpret_cast<const __half2*>(&gv);
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            const uint4 gv = *reinterpret_cast<const uint4*>(gate + orow + ch * 32 + q4 * 8);
+                            const __half2* gh = reinterpret_cast<const __half2*>(&gv);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 gf = __half22float2(gh[e]);
-                            vals[q4 * 8 + 2 * e] *= gf.x;
-                            vals[q4 * 8 + 2 * e + 1] *= gf.y;
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 gf = __half22float2(gh[e]);
+                                vals[q4 * 8 + 2 * e] *= gf.x;
+                                vals[q4 * 8 + 2 * e + 1] *= gf.y;
+                            }
                         }
                     }
-                }
-                if constexpr (sizeof(OutT) == 2) {
-                    if (via_tma) {
-                        // staging tile of round cc>>1: two boxes [128 rows][64 columns] fp16, 128-byte swizzle
-                        const int col = (hf * 2 + (cc & 1)) * 32;              // column inside the round's 128
-                        unsigned char* srow = sm + kOffP + (col >> 6) * kPBytes + r * 128;
-#pragma unroll
-                        for (int q8 = 0; q8 < 4; ++q8) {
-                            __half2 h[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
-                            const int chunk16 = ((col & 63) >> 3) + q8;
-                            *reinterpret_cast<uint4*>(srow + ((chunk16 ^ (r & 7)) << 4)) = *reinterpret_cast<uint4*>(h);
-                        }
-                    } else if (valid && ok) {
-                        OutT* dst = out + orow + ch * 32;
-#pragma unroll
-                        for (int q8 = 0; q8 < 4; ++q8) {
-                            __half2 h[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
-                            *reinterpret_cast<uint4*>(dst + 8 * q8) = *reinterpret_cast<uint4*>(h);
-                        }
-                    }
-                } else {
                     if (valid && ok) {
                         OutT* dst = out + orow + ch * 32;          // 32 consecutive outputs of this row: 16-byte stores
+                        if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
-                        for (int q4 = 0; q4 < 8; ++q4)
-                            *reinterpret_cast<float4*>(dst + 4 * q4) =
-                                make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
-                    }
-                }
-                if constexpr (sizeof(OutT) == 2) {
-                    if (via_tma && (cc & 1)) {
-                        // the round's 128 columns are staged: one thread sends them, everybody waits until the staging tile
-                        // has been read before it is written again (next round, or the next item's P tiles)
-                        fence_proxy_async_smem();
-                        asm volatile("bar.sync 5, 256;" ::: "memory");
-                        if (threadIdx.x == 0) {
-                            if (ok) {
-                                const int c0 = (cc >> 1) * 128;
-                                tma_store_3d(&map_o, base + kOffP, c0, head, tile.q_row0);
-                                tma_store_3d(&map_o, base + kOffP + kPBytes, c0 + 64, head, tile.q_row0);
-                                bulk_commit_group();
+                            for (int q8 = 0; q8 < 4; ++q8) {
+                                __half2 h[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(vals[8 * q8 + 2 * e], vals[8 * q8 + 2 * e + 1]);
+                                *reinterpret_cast<uint4*>(dst + 8 * q8) = *reinterpret_cast<uint4*>(h);
                             }
-                            bulk_wait_group_read0();
+                        } else {
+#pragma unroll
+                            for (int q4 = 0; q4 < 8; ++q4)
+                                *reinterpret_cast<float4*>(dst + 4 * q4) =
+                                    make_float4(vals[4 * q4], vals[4 * q4 + 1], vals[4 * q4 + 2], vals[4 * q4 + 3]);
                         }
-                        asm volatile("bar.sync 5, 256;" ::: "memory");
                     }
                 }
+            } else {
+                // Four rounds of 64 columns, alternating between the two P buffers: while the TMA store of one round
+                // reads its buffer, the next round is read out of TMEM, converted and staged into the other one.  In a
+                // round the thread owns columns [64 k + 32 hf, +32) of its row.
+                // The gate: a thread's own row of it lies a 4 KB stride away from its neighbour's, so fetched per row
+                // every 16-byte load of a warp touches 32 lines.  It is applied to the staged tile instead, where
+                // consecutive threads take consecutive 16-byte pieces of a row (four pieces per thread and round) and
+                // the loads coalesce; each round's pieces are requested one round ahead.
+                uint4 gst[4];
+                const size_t gate_tile = ((size_t)tile.q_row0 * kFaHeads + head) * kHeadDim;
+                auto load_gate_round = [&](int k) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int idx = (int)threadIdx.x + 256 * i, grow = idx >> 3, c16 = idx & 7;
+                        gst[i] = *reinterpret_cast<const uint4*>(gate + gate_tile + (size_t)grow * kFaHeads * kHeadDim + k * 64 + c16 * 8);
+                    }
+                };
+                if (gate) load_gate_round(0);
+                if (!mbar_wait_warp(bar(BAR_OF), it & 1, abort_flag)) ok = false;
+                tc_fence_after();
+                const float inv_l = 1.0f / l;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    uint32_t orr[32];
+                    tmem_ld32(tmem_o + lane_base + (2 * k + hf) * 32, orr);
+                    tmem_wait_ld();
+                    if (k == 3) {          // this thread has read its part of O: the next item's first PV may overwrite it
+                        tc_fence_before();
+                        mbar_arrive(bar(BAR_OD));
+                    }
+                    uint32_t hv[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)
+                        hv[c] = pack_half2(__uint_as_float(orr[2 * c]) * inv_l, __uint_as_float(orr[2 * c + 1]) * inv_l);
+                    unsigned char* buf = sm + kOffP + (k & 1) * kPBytes;
+                    if (k >= 2) {          // the store of round k - 2 must have read this buffer
+                        if (threadIdx.x == 0) bulk_wait_group_read1();
+                        asm volatile("bar.sync 5, 256;" ::: "memory");
+                    }
+                    unsigned char* srow = buf + r * 128;
+#pragma unroll
+                    for (int q8 = 0; q8 < 4; ++q8)
+                        *reinterpret_cast<uint4*>(srow + (((hf * 4 + q8) ^ (r & 7)) << 4)) =
+                            make_uint4(hv[4 * q8], hv[4 * q8 + 1], hv[4 * q8 + 2], hv[4 * q8 + 3]);
+                    if (gate) {
+                        asm volatile("bar.sync 5, 256;" ::: "memory");       // the round's tile is complete
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int idx = (int)threadIdx.x + 256 * i, grow = idx >> 3, c16 = idx & 7;
+                            uint4* p4 = reinterpret_cast<uint4*>(buf + grow * 128 + ((c16 ^ (grow & 7)) << 4));
+                            uint4 ov = *p4;
+                            __half2* oh = reinterpret_cast<__half2*>(&ov);
+                            const __half2* gh = reinterpret_cast<const __half2*>(&gst[i]);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 of = __half22float2(oh[e]), gf = __half22float2(gh[e]);
+                                oh[e] = __floats2half2_rn(of.x * gf.x, of.y * gf.y);
+                            }
+                            *p4 = ov;
+                        }
+                        if (k < 3) load_gate_round(k + 1);
+                    }
+                    fence_proxy_async_smem();
+                    asm volatile("bar.sync 5, 256;" ::: "memory");
+                    if (threadIdx.x == 0 && ok) {
+                        tma_store_3d(&map_o, base + kOffP + (k & 1) * kPBytes, k * 64, head, tile.q_row0);
+                        bulk_commit_group();
+                    }
+                }
+                // the P buffers go back to the softmax of the next item: both stores must have read them
+                if (threadIdx.x == 0) bulk_wait_group_read0();
+                asm volatile("bar.sync 5, 256;" ::: "memory");
+                continue;
             }
             tc_fence_before();
             mbar_arrive(bar(BAR_OD));      // this thread has read its part of O: the next item's first PV may overwrite it
